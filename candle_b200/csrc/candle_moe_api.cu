@@ -1,0 +1,289 @@
+// extern "C" entry points of libcandle_moe_sm100.so (declared in include/candle_moe.h): argument
+// validation on the host, workspace carving, and the launch sequence of the whole block.
+#include <cstring>
+
+#include "common.cuh"
+
+using namespace cmoe;
+
+namespace {
+
+struct Workspace {
+    // routing
+    uint32_t* topk_ids;
+    float* topk_w;
+    uint32_t* counts;
+    uint32_t* offsets;
+    uint32_t* perm_token;
+    uint32_t* pair_pos;
+    // quantized input rows (one per token; experts gather through perm_token)
+    int8_t* xq;
+    float* xs;
+    int16_t* xb;
+    // routed experts
+    float* hidden;  // [T*k, ff]
+    int8_t* hq;
+    float* hs;
+    int16_t* hb;
+    float* eo;  // [T*k, d]
+    // shared expert
+    uint32_t* sh_offsets;  // [2] = {0, T}
+    int8_t* sxq;
+    float* sxs;
+    int16_t* sxb;
+    float* shidden;  // [T, ff_s]
+    int8_t* shq;
+    float* shs;
+    int16_t* shb;
+    float* so;  // [T, d]
+    size_t total;
+};
+
+template <class T>
+T* carve(uint8_t* base, size_t& off, size_t count) {
+    off = align_up(off, 256);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+}
+
+Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
+    uint8_t* base = static_cast<uint8_t*>(base_);
+    Workspace ws{};
+    size_t off = 0;
+    const size_t Tk = (size_t)T * w->top_k, d = w->d_model, ff = w->d_ff, E = w->n_experts;
+    ws.topk_ids = carve<uint32_t>(base, off, Tk);
+    ws.topk_w = carve<float>(base, off, Tk);
+    ws.counts = carve<uint32_t>(base, off, E);
+    ws.offsets = carve<uint32_t>(base, off, E + 1);
+    ws.perm_token = carve<uint32_t>(base, off, Tk);
+    ws.pair_pos = carve<uint32_t>(base, off, Tk);
+    ws.xq = carve<int8_t>(base, off, (size_t)T * d);
+    ws.xs = carve<float>(base, off, (size_t)T * d / act_block(w->dtype_w13));
+    ws.xb = carve<int16_t>(base, off, (size_t)T * d / 16);
+    ws.hidden = carve<float>(base, off, Tk * ff);
+    ws.hq = carve<int8_t>(base, off, Tk * ff);
+    ws.hs = carve<float>(base, off, Tk * ff / act_block(w->dtype_w2));
+    ws.hb = carve<int16_t>(base, off, Tk * ff / 16);
+    ws.eo = carve<float>(base, off, Tk * d);
+    if (w->d_ff_shared > 0) {
+        const size_t fs = w->d_ff_shared;
+        ws.sh_offsets = carve<uint32_t>(base, off, 2);
+        if (act_block(w->dtype_shared13) != act_block(w->dtype_w13)) {
+            ws.sxq = carve<int8_t>(base, off, (size_t)T * d);
+            ws.sxs = carve<float>(base, off, (size_t)T * d / act_block(w->dtype_shared13));
+            ws.sxb = carve<int16_t>(base, off, (size_t)T * d / 16);
+        } else {
+            ws.sxq = ws.xq;
+            ws.sxs = ws.xs;
+            ws.sxb = ws.xb;
+        }
+        ws.shidden = carve<float>(base, off, (size_t)T * fs);
+        ws.shq = carve<int8_t>(base, off, (size_t)T * fs);
+        ws.shs = carve<float>(base, off, (size_t)T * fs / act_block(w->dtype_shared2));
+        ws.shb = carve<int16_t>(base, off, (size_t)T * fs / 16);
+        ws.so = carve<float>(base, off, (size_t)T * d);
+    }
+    ws.total = align_up(off, 256);
+    return ws;
+}
+
+int check_weights(const candle_moe_weights_t* w) {
+    if (!w) return CANDLE_MOE_E_NULL;
+    if (w->d_model <= 0 || w->d_ff <= 0 || w->n_experts <= 0 || w->top_k <= 0) return CANDLE_MOE_E_SHAPE;
+    if (w->n_experts > CANDLE_MOE_MAX_EXPERTS || w->top_k > CANDLE_MOE_MAX_TOPK || w->top_k > w->n_experts)
+        return CANDLE_MOE_E_SHAPE;
+    if (!dtype_supported(w->dtype_w13) || !dtype_supported(w->dtype_w2)) return CANDLE_MOE_E_DTYPE;
+    if (w->d_model % block_elems(w->dtype_w13) || w->d_ff % block_elems(w->dtype_w2)) return CANDLE_MOE_E_SHAPE;
+    if (w->d_model % 32 || w->d_ff % 32) return CANDLE_MOE_E_SHAPE;
+    if (w->d_ff_shared < 0) return CANDLE_MOE_E_SHAPE;
+    if (w->d_ff_shared > 0) {
+        if (!dtype_supported(w->dtype_shared13) || !dtype_supported(w->dtype_shared2)) return CANDLE_MOE_E_DTYPE;
+        if (w->d_model % block_elems(w->dtype_shared13) || w->d_ff_shared % block_elems(w->dtype_shared2) ||
+            w->d_ff_shared % 32)
+            return CANDLE_MOE_E_SHAPE;
+    }
+    return CANDLE_MOE_OK;
+}
+
+int fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
+    if (!host) return CANDLE_MOE_E_NULL;
+    std::memset(&out, 0, sizeof(out));
+    for (int e = 0; e < E; ++e) {
+        if (!host[e]) return CANDLE_MOE_E_NULL;
+        if (reinterpret_cast<uintptr_t>(host[e]) & 15) return CANDLE_MOE_E_ALIGN;
+        out.p[e] = static_cast<const uint8_t*>(host[e]);
+    }
+    return CANDLE_MOE_OK;
+}
+
+inline int rc(cudaError_t e) { return e == cudaSuccess ? CANDLE_MOE_OK : (int)e; }
+
+#define CM_TRY(expr)                    \
+    do {                                \
+        const int _r = (expr);          \
+        if (_r != CANDLE_MOE_OK) return _r; \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+const char* candle_moe_version(void) { return "candle_moe_sm100 0.1"; }
+
+int candle_moe_workspace_bytes(const candle_moe_weights_t* w, int64_t max_tokens, size_t* out_bytes) {
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    CM_TRY(check_weights(w));
+    if (max_tokens < 0 || max_tokens > (int64_t)1 << 24) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = layout(w, max_tokens, nullptr).total;
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_router_topk(void* stream, const float* x, const float* router, const float* bias, int64_t T,
+                           int32_t d, int32_t E, int32_t k, int32_t renorm, uint32_t* topk_ids, float* topk_w) {
+    if (!x || !router || !topk_ids || !topk_w) return CANDLE_MOE_E_NULL;
+    if (T < 0 || d <= 0 || d % 4 || E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || k <= 0 || k > CANDLE_MOE_MAX_TOPK || k > E)
+        return CANDLE_MOE_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(router)) & 15) return CANDLE_MOE_E_ALIGN;
+    return rc(launch_router_topk((cudaStream_t)stream, x, router, bias, T, d, E, k, renorm, topk_ids, topk_w));
+}
+
+int candle_moe_permute(void* stream, const uint32_t* topk_ids, int64_t T, int32_t k, int32_t E,
+                       uint32_t* expert_counts, uint32_t* expert_offsets, uint32_t* perm_token, uint32_t* pair_pos) {
+    if (!topk_ids || !expert_counts || !expert_offsets || !perm_token || !pair_pos) return CANDLE_MOE_E_NULL;
+    if (T < 0 || k <= 0 || k > CANDLE_MOE_MAX_TOPK || E <= 0 || E > CANDLE_MOE_MAX_EXPERTS) return CANDLE_MOE_E_SHAPE;
+    return rc(launch_permute((cudaStream_t)stream, topk_ids, T, k, E, expert_counts, expert_offsets, perm_token,
+                             pair_pos));
+}
+
+int candle_moe_quantize_act(void* stream, const float* x, int64_t rows, int32_t kdim, int32_t for_weight_dtype,
+                            int8_t* qs, float* scales, int16_t* bsums) {
+    if (!x || !qs || !scales) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(for_weight_dtype)) return CANDLE_MOE_E_DTYPE;
+    if (for_weight_dtype != CANDLE_GGML_Q8_0 && !bsums) return CANDLE_MOE_E_NULL;
+    if (rows < 0 || kdim <= 0 || kdim % act_block(for_weight_dtype)) return CANDLE_MOE_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(qs) & 7)) return CANDLE_MOE_E_ALIGN;
+    return rc(launch_quantize_act((cudaStream_t)stream, x, rows, kdim, for_weight_dtype, qs, scales, bsums));
+}
+
+int candle_moe_combine(void* stream, const float* expert_out, const uint32_t* topk_ids, const float* topk_w,
+                       const uint32_t* pair_pos, int64_t T, int32_t k, int32_t d, const float* shared_out,
+                       const float* x, const float* shared_gate, float* y) {
+    if (!expert_out || !topk_ids || !topk_w || !pair_pos || !y) return CANDLE_MOE_E_NULL;
+    if (shared_out && (!x || !shared_gate)) return CANDLE_MOE_E_NULL;
+    if (T < 0 || k <= 0 || k > CANDLE_MOE_MAX_TOPK || d <= 0 || d % 4) return CANDLE_MOE_E_SHAPE;
+    return rc(launch_combine((cudaStream_t)stream, expert_out, topk_ids, topk_w, pair_pos, T, k, d, shared_out, x,
+                             shared_gate, y));
+}
+
+int candle_moe_grouped_gate_up(void* stream, const void* const* w1, const void* const* w3, int32_t dtype,
+                               int32_t E, int32_t d, int32_t ff, const uint32_t* expert_offsets,
+                               const uint32_t* row_of, int64_t max_rows, const int8_t* xq, const float* xscales,
+                               const int16_t* xbsums, float* hidden) {
+    if (!expert_offsets || !xq || !xscales || !hidden) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (dtype != CANDLE_GGML_Q8_0 && !xbsums) return CANDLE_MOE_E_NULL;
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || d % block_elems(dtype) || max_rows < 0)
+        return CANDLE_MOE_E_SHAPE;
+    ExpertPtrs p1, p3;
+    CM_TRY(fill_ptrs(w1, E, p1));
+    CM_TRY(fill_ptrs(w3, E, p3));
+    return rc(launch_grouped_gate_up((cudaStream_t)stream, p1, p3, dtype, E, d, ff, expert_offsets, row_of, max_rows,
+                                     xq, xscales, xbsums, hidden));
+}
+
+int candle_moe_grouped_down(void* stream, const void* const* w2, int32_t dtype, int32_t E, int32_t d, int32_t ff,
+                            const uint32_t* expert_offsets, int64_t max_rows, const int8_t* hq, const float* hscales,
+                            const int16_t* hbsums, float* out) {
+    if (!expert_offsets || !hq || !hscales || !out) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (dtype != CANDLE_GGML_Q8_0 && !hbsums) return CANDLE_MOE_E_NULL;
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || ff % block_elems(dtype) || max_rows < 0)
+        return CANDLE_MOE_E_SHAPE;
+    ExpertPtrs p2;
+    CM_TRY(fill_ptrs(w2, E, p2));
+    return rc(launch_grouped_down((cudaStream_t)stream, p2, dtype, E, d, ff, expert_offsets, max_rows, hq, hscales,
+                                  hbsums, out));
+}
+
+int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
+                       void* workspace, size_t workspace_bytes) {
+    CM_TRY(check_weights(w));
+    if (!x || !y || !w->router) return CANDLE_MOE_E_NULL;
+    if (T < 0 || T > (int64_t)1 << 24) return CANDLE_MOE_E_SHAPE;
+    if (T == 0) return CANDLE_MOE_OK;
+    if (!workspace) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(w->router) & 15))
+        return CANDLE_MOE_E_ALIGN;
+    const Workspace ws = layout(w, T, workspace);
+    if (workspace_bytes < ws.total) return CANDLE_MOE_E_WORKSPACE;
+    const int E = w->n_experts, k = w->top_k, d = w->d_model, ff = w->d_ff;
+    ExpertPtrs p1, p3, p2;
+    CM_TRY(fill_ptrs(w->w1, E, p1));
+    CM_TRY(fill_ptrs(w->w3, E, p3));
+    CM_TRY(fill_ptrs(w->w2, E, p2));
+    if (w->d_ff_shared > 0) {
+        if (!w->shared_w1 || !w->shared_w3 || !w->shared_w2 || !w->shared_gate) return CANDLE_MOE_E_NULL;
+        if (reinterpret_cast<uintptr_t>(w->shared_gate) & 15) return CANDLE_MOE_E_ALIGN;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t Tk = T * k;
+
+    CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w)));
+    CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
+    CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
+    CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, Tk, ws.xq, ws.xs,
+                                     ws.xb, ws.hidden)));
+    CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
+    CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, Tk, ws.hq, ws.hs, ws.hb, ws.eo)));
+
+    const float* shared_out = nullptr;
+    if (w->d_ff_shared > 0) {
+        const int fs = w->d_ff_shared;
+        CM_TRY(rc(launch_single_group(st, ws.sh_offsets, (uint32_t)T)));
+        ExpertPtrs s1{}, s3{}, s2{};
+        s1.p[0] = static_cast<const uint8_t*>(w->shared_w1);
+        s3.p[0] = static_cast<const uint8_t*>(w->shared_w3);
+        s2.p[0] = static_cast<const uint8_t*>(w->shared_w2);
+        if (ws.sxq != ws.xq)
+            CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_shared13, ws.sxq, ws.sxs, ws.sxb)));
+        CM_TRY(rc(launch_grouped_gate_up(st, s1, s3, w->dtype_shared13, 1, d, fs, ws.sh_offsets, nullptr, T, ws.sxq,
+                                         ws.sxs, ws.sxb, ws.shidden)));
+        CM_TRY(rc(launch_quantize_act(st, ws.shidden, T, fs, w->dtype_shared2, ws.shq, ws.shs, ws.shb)));
+        CM_TRY(rc(launch_grouped_down(st, s2, w->dtype_shared2, 1, d, fs, ws.sh_offsets, T, ws.shq, ws.shs, ws.shb,
+                                      ws.so)));
+        shared_out = ws.so;
+    }
+    CM_TRY(rc(launch_combine(st, ws.eo, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out, x, w->shared_gate, y)));
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,
+                               float** topk_w, uint32_t** expert_counts, uint32_t** perm_token) {
+    CM_TRY(check_weights(w));
+    if (!workspace) return CANDLE_MOE_E_NULL;
+    const Workspace ws = layout(w, T, workspace);
+    if (topk_ids) *topk_ids = ws.topk_ids;
+    if (topk_w) *topk_w = ws.topk_w;
+    if (expert_counts) *expert_counts = ws.counts;
+    if (perm_token) *perm_token = ws.perm_token;
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_quantize_weights(void* stream, int32_t dtype, const float* src, int64_t n_elems, void* dst) {
+    if (!src || !dst) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (n_elems < 0 || n_elems % block_elems(dtype)) return CANDLE_MOE_E_SHAPE;
+    if (reinterpret_cast<uintptr_t>(src) & 15) return CANDLE_MOE_E_ALIGN;
+    return rc(launch_quantize_weights((cudaStream_t)stream, dtype, src, n_elems, dst));
+}
+
+int candle_moe_dequantize(void* stream, int32_t dtype, const void* blocks, int64_t n_elems, float* dst) {
+    if (!blocks || !dst) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (n_elems < 0 || n_elems % block_elems(dtype)) return CANDLE_MOE_E_SHAPE;
+    return rc(launch_dequantize((cudaStream_t)stream, dtype, blocks, n_elems, dst));
+}
+
+}  // extern "C"

@@ -1,0 +1,88 @@
+// Shared definitions for the sm_100a kernels of the quantized MoE feed-forward block.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/candle_moe.h"
+
+namespace cmoe {
+
+// GGUF block layouts (candle-core/src/quantized/k_quants.rs:81-87, 119-127, 141-149); raw bytes.
+constexpr int QK_K = 256;
+constexpr int QK8_0 = 32;
+constexpr int Q4K_BYTES = 144;  // f16 d, f16 dmin, u8 scales[12], u8 qs[128]
+constexpr int Q6K_BYTES = 210;  // u8 ql[128], u8 qh[64], i8 scales[16], f16 d
+constexpr int Q8_0_BYTES = 34;  // f16 d, i8 qs[32]
+
+__host__ __device__ inline int block_elems(int dtype) {
+    return dtype == CANDLE_GGML_Q8_0 ? 32 : 256;
+}
+__host__ __device__ inline int block_bytes(int dtype) {
+    return dtype == CANDLE_GGML_Q8_0 ? Q8_0_BYTES : (dtype == CANDLE_GGML_Q4K ? Q4K_BYTES : Q6K_BYTES);
+}
+inline bool dtype_supported(int dtype) {
+    return dtype == CANDLE_GGML_Q8_0 || dtype == CANDLE_GGML_Q4K || dtype == CANDLE_GGML_Q6K;
+}
+// Activation block length used against a weight dtype (GgmlType::VecDotType): Q8K (256) for the
+// k-quants, Q8_0 (32) for Q8_0.
+__host__ __device__ inline int act_block(int dtype) { return dtype == CANDLE_GGML_Q8_0 ? 32 : 256; }
+
+// Per-expert weight base pointers travel as a kernel parameter (no device-side table to allocate).
+struct ExpertPtrs {
+    const uint8_t* p[CANDLE_MOE_MAX_EXPERTS];
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// 6-bit scale / min of sub-block j of a Q4_K block (candle-core/src/quantized/utils.rs:50-60)
+__device__ __forceinline__ void q4k_scale_min(int j, const uint8_t* q, int& sc, int& m) {
+    if (j < 4) {
+        sc = q[j] & 63;
+        m = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+// candle-core/src/op.rs:645-648 and candle-nn/src/ops.rs:59-61; IEEE division, libm-grade expf.
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (expf(-v) + 1.0f); }
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- launchers implemented in the other translation units (all enqueue on `st`) ----
+cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
+                               int d, int E, int k, int renorm, uint32_t* ids, float* w);
+cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
+                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos);
+// offsets[0..2) = {0, rows}: one group holding every row (used for the always-on shared expert)
+cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows);
+cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, int kdim, int for_dtype, int8_t* qs,
+                                float* scales, int16_t* bsums);
+cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
+                                   int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
+                                   const int8_t* xq, const float* xs, const int16_t* xb, float* hidden);
+cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype, int E, int d, int ff,
+                                const uint32_t* offsets, int64_t max_rows, const int8_t* hq, const float* hs,
+                                const int16_t* hb, float* out);
+cudaError_t launch_combine(cudaStream_t st, const float* expert_out, const uint32_t* ids, const float* w,
+                           const uint32_t* pair_pos, int64_t T, int k, int d, const float* shared_out,
+                           const float* x, const float* shared_gate, float* y);
+cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);
+cudaError_t launch_dequantize(cudaStream_t st, int dtype, const void* blocks, int64_t n, float* dst);
+
+}  // namespace cmoe

@@ -1,0 +1,294 @@
+// Router (f32 GEMV + softmax + stable top-k), dispatch (group pairs by expert) and the weighted
+// combine of the quantized MoE block.  All three are small, latency- or HBM-bound kernels.
+#include "common.cuh"
+
+namespace cmoe {
+
+// ------------------------------------------------------------------------------------------------
+// Router.  One CTA of 128 threads per token: the four warps split d with 128-bit loads, 8 experts
+// at a time; partial sums meet through warp shuffles and a 4-entry shared array.  Warp 0 then does
+// the softmax over all E experts and k rounds of arg-max with "lower expert id wins a tie", which
+// is what a stable descending sort followed by take(k) yields
+// (candle-transformers/src/models/quantized_llama.rs:162-179).
+// Arithmetic is plain f32 FMA (no TF32): the reference's router product is full f32.
+// ------------------------------------------------------------------------------------------------
+constexpr int ROUTER_THREADS = 128;
+
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, const float* __restrict__ bias,
+                   int d, int E, int k, int renorm, uint32_t* __restrict__ ids, float* __restrict__ wout) {
+    __shared__ float s_logits[CANDLE_MOE_MAX_EXPERTS];
+    __shared__ float s_part[ROUTER_THREADS / 32][8];
+    const int64_t t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float4* xr = reinterpret_cast<const float4*>(x + t * (int64_t)d);
+    const int d4 = d >> 2;
+
+    for (int e0 = 0; e0 < E; e0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int i = tid; i < d4; i += ROUTER_THREADS) {
+            const float4 xv = xr[i];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (e0 + j < E) {
+                    const float4 wv = reinterpret_cast<const float4*>(wg + (int64_t)(e0 + j) * d)[i];
+                    acc[j] = fmaf(xv.x, wv.x, acc[j]);
+                    acc[j] = fmaf(xv.y, wv.y, acc[j]);
+                    acc[j] = fmaf(xv.z, wv.z, acc[j]);
+                    acc[j] = fmaf(xv.w, wv.w, acc[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float v = warp_sum(acc[j]);
+            if (lane == 0) s_part[warp][j] = v;
+        }
+        __syncthreads();
+        if (tid < 8 && e0 + tid < E) {
+            float v = (s_part[0][tid] + s_part[1][tid]) + (s_part[2][tid] + s_part[3][tid]);
+            if (bias) v += bias[e0 + tid];
+            s_logits[e0 + tid] = v;
+        }
+        __syncthreads();
+    }
+    if (warp != 0) return;
+
+    // softmax over E (candle-nn/src/ops.rs:326-339): exp(v - max) / sum, true division
+    constexpr int PER = CANDLE_MOE_MAX_EXPERTS / 32;
+    float p[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = lane + 32 * j;
+        p[j] = e < E ? s_logits[e] : -INFINITY;
+        mx = fmaxf(mx, p[j]);
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = lane + 32 * j;
+        p[j] = e < E ? expf(p[j] - mx) : 0.f;
+        s += p[j];
+    }
+    s = warp_sum(s);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) p[j] = (lane + 32 * j) < E ? p[j] / s : -1.f;  // -1 = not a candidate
+
+    float sel_p[CANDLE_MOE_MAX_TOPK];
+    int sel_e[CANDLE_MOE_MAX_TOPK];
+    float sum = 0.f;
+#pragma unroll
+    for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+        if (r < k) {
+            float bv = -1.f;
+            int be = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) {  // ascending expert id inside a lane: strict > keeps the lower id
+                if (p[j] > bv) {
+                    bv = p[j];
+                    be = lane + 32 * j;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) {
+                    bv = ov;
+                    be = oe;
+                }
+            }
+            sel_p[r] = bv;
+            sel_e[r] = be;
+            sum += bv;  // rank order, like `sum_routing_weights += routing_weight`
+#pragma unroll
+            for (int j = 0; j < PER; ++j)
+                if (lane + 32 * j == be) p[j] = -1.f;
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+            if (r < k) {
+                ids[t * k + r] = (uint32_t)sel_e[r];
+                wout[t * k + r] = renorm ? sel_p[r] / sum : sel_p[r];
+            }
+        }
+    }
+}
+
+cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
+                               int d, int E, int k, int renorm, uint32_t* ids, float* w) {
+    if (T == 0) return cudaSuccess;
+    router_topk_kernel<<<(unsigned)T, ROUTER_THREADS, 0, st>>>(x, router, bias, d, E, k, renorm, ids, w);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Dispatch.  A counting sort of the T*k (token, rank) pairs by expert that keeps pair order inside
+// an expert, so every expert's token list is ascending like the reference's `top_x[e]`.  One CTA:
+// each warp owns experts warp, warp+32, ... and walks the pair list 32 at a time with a ballot, first
+// to count, then (after an exclusive scan over experts) to place.
+// ------------------------------------------------------------------------------------------------
+constexpr int PERMUTE_THREADS = 1024;
+
+__global__ void __launch_bounds__(PERMUTE_THREADS)
+permute_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int k, int E, uint32_t* __restrict__ counts,
+               uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm_token, uint32_t* __restrict__ pair_pos) {
+    __shared__ uint32_t s_count[CANDLE_MOE_MAX_EXPERTS];
+    __shared__ uint32_t s_off[CANDLE_MOE_MAX_EXPERTS + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = PERMUTE_THREADS / 32;
+    for (int e = warp; e < E; e += n_warps) {
+        uint32_t c = 0;
+        for (int64_t i0 = 0; i0 < n_pairs; i0 += 32) {
+            const int64_t i = i0 + lane;
+            const bool hit = i < n_pairs && ids[i] == (uint32_t)e;
+            c += __popc(__ballot_sync(0xffffffffu, hit));
+        }
+        if (lane == 0) s_count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (int e = 0; e < E; ++e) {
+            s_off[e] = run;
+            run += s_count[e];
+        }
+        s_off[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += PERMUTE_THREADS) counts[e] = s_count[e];
+    for (int e = threadIdx.x; e <= E; e += PERMUTE_THREADS) offsets[e] = s_off[e];
+    for (int e = warp; e < E; e += n_warps) {
+        uint32_t base = s_off[e];
+        for (int64_t i0 = 0; i0 < n_pairs; i0 += 32) {
+            const int64_t i = i0 + lane;
+            const bool hit = i < n_pairs && ids[i] == (uint32_t)e;
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const uint32_t pos = base + __popc(m & ((1u << lane) - 1u));
+                perm_token[pos] = (uint32_t)(i / k);
+                pair_pos[i] = pos;
+            }
+            base += __popc(m);
+        }
+    }
+}
+
+cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
+                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos) {
+    permute_kernel<<<1, PERMUTE_THREADS, 0, st>>>(ids, T * k, k, E, counts, offsets, perm_token, pair_pos);
+    return cudaGetLastError();
+}
+
+__global__ void single_group_kernel(uint32_t* offsets, uint32_t rows) {
+    offsets[0] = 0u;
+    offsets[1] = rows;
+}
+cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows) {
+    single_group_kernel<<<1, 1, 0, st>>>(offsets, rows);
+    return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Combine.  One CTA per token, threads over d with 128-bit accesses.  The k contributions are added
+// in ascending expert id, each product rounded first (no FMA), starting from +0.0: the order of the
+// reference's expert loop with broadcast_mul followed by index_add (quantized_llama.rs:185-203).
+// Optional shared expert: y += shared_out * sigmoid(x . g) (qwen2_moe.rs:315-319).
+// ------------------------------------------------------------------------------------------------
+constexpr int COMBINE_THREADS = 256;
+
+__global__ void __launch_bounds__(COMBINE_THREADS)
+combine_kernel(const float* __restrict__ eo, const uint32_t* __restrict__ ids, const float* __restrict__ w,
+               const uint32_t* __restrict__ pair_pos, int k, int d, const float* __restrict__ shared_out,
+               const float* __restrict__ x, const float* __restrict__ gate, float* __restrict__ y) {
+    __shared__ float s_red[COMBINE_THREADS / 32];
+    __shared__ float s_gate;
+    const int64_t t = blockIdx.x;
+    // every thread sorts the token's k selections by expert id (k <= 8)
+    uint32_t se[CANDLE_MOE_MAX_TOPK], sp[CANDLE_MOE_MAX_TOPK];
+    float sw[CANDLE_MOE_MAX_TOPK];
+#pragma unroll
+    for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+        if (r < k) {
+            se[r] = ids[t * k + r];
+            sp[r] = pair_pos[t * k + r];
+            sw[r] = w[t * k + r];
+        } else {
+            se[r] = 0xffffffffu;
+            sp[r] = 0;
+            sw[r] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < CANDLE_MOE_MAX_TOPK - 1; ++a)
+#pragma unroll
+        for (int b = 0; b < CANDLE_MOE_MAX_TOPK - 1 - a; ++b)
+            if (se[b] > se[b + 1]) {
+                uint32_t te = se[b]; se[b] = se[b + 1]; se[b + 1] = te;
+                uint32_t tp = sp[b]; sp[b] = sp[b + 1]; sp[b + 1] = tp;
+                float tw = sw[b]; sw[b] = sw[b + 1]; sw[b + 1] = tw;
+            }
+
+    float g = 0.f;
+    if (shared_out) {
+        float part = 0.f;
+        const float4* xr = reinterpret_cast<const float4*>(x + t * (int64_t)d);
+        const float4* gr = reinterpret_cast<const float4*>(gate);
+        for (int i = threadIdx.x; i < (d >> 2); i += COMBINE_THREADS) {
+            const float4 a = xr[i], b = gr[i];
+            part = fmaf(a.x, b.x, part);
+            part = fmaf(a.y, b.y, part);
+            part = fmaf(a.z, b.z, part);
+            part = fmaf(a.w, b.w, part);
+        }
+        part = warp_sum(part);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float v = 0.f;
+            for (int i = 0; i < COMBINE_THREADS / 32; ++i) v += s_red[i];
+            s_gate = sigmoid_f(v);
+        }
+        __syncthreads();
+        g = s_gate;
+    }
+
+    float4* yr = reinterpret_cast<float4*>(y + t * (int64_t)d);
+    for (int i = threadIdx.x; i < (d >> 2); i += COMBINE_THREADS) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+            if (r < k) {
+                const float4 v = reinterpret_cast<const float4*>(eo + (int64_t)sp[r] * d)[i];
+                acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, sw[r]));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, sw[r]));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, sw[r]));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, sw[r]));
+            }
+        }
+        if (shared_out) {
+            const float4 s = reinterpret_cast<const float4*>(shared_out + t * (int64_t)d)[i];
+            acc.x = __fadd_rn(acc.x, __fmul_rn(s.x, g));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(s.y, g));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(s.z, g));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(s.w, g));
+        }
+        yr[i] = acc;
+    }
+}
+
+cudaError_t launch_combine(cudaStream_t st, const float* expert_out, const uint32_t* ids, const float* w,
+                           const uint32_t* pair_pos, int64_t T, int k, int d, const float* shared_out,
+                           const float* x, const float* shared_gate, float* y) {
+    if (T == 0) return cudaSuccess;
+    combine_kernel<<<(unsigned)T, COMBINE_THREADS, 0, st>>>(expert_out, ids, w, pair_pos, k, d, shared_out, x,
+                                                            shared_gate, y);
+    return cudaGetLastError();
+}
+
+}  // namespace cmoe

@@ -1,0 +1,146 @@
+"""Host-side mirror of candle's quantized tensor types for the MoE feed-forward path.
+
+Names and meaning follow candle-core/src/quantized/mod.rs: `GgmlDType` (:134-253), `QTensor`
+(:35-38, :286-398) and `QMatMul` (:400-556).  A `QTensor` here owns a CUDA buffer holding the raw
+GGUF blocks, row-major `[n][k / block]`, exactly the bytes `QCudaStorage` keeps
+(candle-core/src/quantized/cuda.rs:597-616).  Device memory and streams come from torch.
+"""
+from __future__ import annotations
+
+import enum
+from typing import Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class GgmlDType(enum.IntEnum):
+    """GGML ids as returned by `GgmlDType::to_u32` (candle-core/src/quantized/mod.rs:176-195)."""
+    F32 = 0
+    Q8_0 = 8
+    Q4K = 12
+    Q6K = 14
+
+    def block_size(self) -> int:
+        """`GgmlDType::block_size` (mod.rs:232-252)."""
+        return {GgmlDType.F32: 1, GgmlDType.Q8_0: 32, GgmlDType.Q4K: 256, GgmlDType.Q6K: 256}[self]
+
+    def type_size(self) -> int:
+        """`GgmlDType::type_size` (mod.rs:208-229): bytes per block."""
+        return {GgmlDType.F32: 4, GgmlDType.Q8_0: 34, GgmlDType.Q4K: 144, GgmlDType.Q6K: 210}[self]
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class QTensor:
+    """A quantized `[n, k]` matrix on a CUDA device (`QTensor`, mod.rs:35-38)."""
+
+    def __init__(self, data: torch.Tensor, dtype: GgmlDType, shape: Tuple[int, int]):
+        if not data.is_cuda or data.dtype != torch.uint8:
+            raise ValueError("QTensor storage must be a CUDA uint8 tensor")
+        n, k = shape
+        if k % dtype.block_size():
+            raise ValueError(f"last dim {k} is not a multiple of the {dtype.name} block size")
+        if data.numel() != n * (k // dtype.block_size()) * dtype.type_size():
+            raise ValueError("storage size does not match shape and dtype")
+        self.data, self._dtype, self._shape = data, GgmlDType(dtype), (int(n), int(k))
+
+    # -- constructors -----------------------------------------------------------------------------
+    @classmethod
+    def from_blocks(cls, blocks, dtype: GgmlDType, shape: Tuple[int, int], device="cuda") -> "QTensor":
+        """Upload raw GGUF block bytes (what `qtensor_from_ggml` + `load_quantized` do,
+        candle-core/src/quantized/ggml_file.rs:138-189, cuda.rs:597-616)."""
+        if isinstance(blocks, np.ndarray):
+            blocks = torch.from_numpy(np.ascontiguousarray(blocks).view(np.uint8))
+        return cls(blocks.to(device=device, dtype=torch.uint8).contiguous(), dtype, shape)
+
+    @classmethod
+    def quantize(cls, src: torch.Tensor, dtype: GgmlDType) -> "QTensor":
+        """`QTensor::quantize` (mod.rs:288-318), on the device and bit-exact with the CPU quantizer."""
+        if src.dim() != 2 or not src.is_cuda:
+            raise ValueError("quantize expects a 2-D CUDA tensor")
+        src = src.to(torch.float32).contiguous()
+        n, k = src.shape
+        dtype = GgmlDType(dtype)
+        if k % dtype.block_size():
+            raise ValueError(f"last dim {k} is not a multiple of the {dtype.name} block size")
+        out = torch.empty(n * (k // dtype.block_size()) * dtype.type_size(), dtype=torch.uint8, device=src.device)
+        with torch.cuda.device(src.device):
+            st = _lib.load().candle_moe_quantize_weights(_stream_ptr(src.device), int(dtype), src.data_ptr(),
+                                                          src.numel(), out.data_ptr())
+        _lib.check("candle_moe_quantize_weights", st)
+        return cls(out, dtype, (n, k))
+
+    # -- accessors ---------------------------------------------------------------------------------
+    def dtype(self) -> GgmlDType:
+        return self._dtype
+
+    def shape(self) -> Tuple[int, int]:
+        return self._shape
+
+    def device(self) -> torch.device:
+        return self.data.device
+
+    def storage_size_in_bytes(self) -> int:
+        return self.data.numel()
+
+    def device_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    def dequantize(self) -> torch.Tensor:
+        """`QTensor::dequantize` (mod.rs:349-353)."""
+        n, k = self._shape
+        out = torch.empty((n, k), dtype=torch.float32, device=self.data.device)
+        with torch.cuda.device(self.data.device):
+            st = _lib.load().candle_moe_dequantize(_stream_ptr(self.data.device), int(self._dtype),
+                                                   self.data.data_ptr(), n * k, out.data_ptr())
+        _lib.check("candle_moe_dequantize", st)
+        return out
+
+
+class QMatMul:
+    """`QMatMul::QTensor` (mod.rs:400-404): `forward(xs)` computes `xs . W^T` with the k-quant
+    arithmetic of `k_quants::matmul` (activations quantized per row, integer block dots)."""
+
+    def __init__(self, qtensor: QTensor):
+        self.inner = qtensor
+
+    @classmethod
+    def from_qtensor(cls, qtensor: QTensor) -> "QMatMul":
+        return cls(qtensor)
+
+    def forward(self, xs: torch.Tensor) -> torch.Tensor:
+        lib = _lib.load()
+        n, k = self.inner.shape()
+        if xs.shape[-1] != k:
+            raise ValueError(f"shape mismatch in qmatmul: {tuple(xs.shape)} x ({n}, {k})^T")
+        if not xs.is_cuda or xs.dtype != torch.float32:
+            raise ValueError("QMatMul.forward expects a CUDA f32 tensor")
+        lead = xs.shape[:-1]
+        x2 = xs.reshape(-1, k).contiguous()
+        rows = x2.shape[0]
+        dev, dt = x2.device, int(self.inner.dtype())
+        ab = 32 if dt == GgmlDType.Q8_0 else 256
+        qs = torch.empty((rows, k), dtype=torch.int8, device=dev)
+        sc = torch.empty((rows, k // ab), dtype=torch.float32, device=dev)
+        bs = torch.empty((rows, k // 16), dtype=torch.int16, device=dev)
+        offs = torch.tensor([0, rows], dtype=torch.int32, device=dev)
+        out = torch.empty((rows, n), dtype=torch.float32, device=dev)
+        import ctypes as C
+        ptrs = (C.c_void_p * 1)(self.inner.device_ptr())
+        with torch.cuda.device(dev):
+            st = _stream_ptr(dev)
+            _lib.check("candle_moe_quantize_act",
+                       lib.candle_moe_quantize_act(st, x2.data_ptr(), rows, k, dt, qs.data_ptr(), sc.data_ptr(),
+                                                   bs.data_ptr()))
+            # W is [n, k]: the "down" form computes out[p, :] = W . act[p]
+            _lib.check("candle_moe_grouped_down",
+                       lib.candle_moe_grouped_down(st, ptrs, dt, 1, n, k, offs.data_ptr(), rows, qs.data_ptr(),
+                                                   sc.data_ptr(), bs.data_ptr(), out.data_ptr()))
+        return out.reshape(*lead, n)
+
+    __call__ = forward

@@ -1,0 +1,166 @@
+/* C ABI of libcandle_moe_sm100.so: the quantized mixture-of-experts feed-forward block of
+ * candle-transformers' quantized_llama (MlpOrMoe::MoE) as CUDA launchers for sm_100a.
+ *
+ * Conventions (all entry points):
+ *   - return 0 on success, a negative CANDLE_MOE_E_* code for an argument error found on the host
+ *     before anything is enqueued, or a positive cudaError_t value; nothing aborts or throws;
+ *   - every pointer named "device" is a CUDA device pointer borrowed until the enqueued work has
+ *     run; the caller owns every buffer; nothing is allocated or freed inside the library unless
+ *     the entry point says so;
+ *   - work is enqueued on the caller's stream (a cudaStream_t passed as void*) and is
+ *     asynchronous; no entry point synchronises the stream;
+ *   - weights are raw GGUF blocks exactly as candle's QCudaStorage holds them (row-major
+ *     [n][k / block] blocks, candle-core/src/quantized/cuda.rs:597-616); dtypes are GGML ids
+ *     (GgmlDType::to_u32, candle-core/src/quantized/mod.rs:176-195);
+ *   - activations are contiguous row-major f32, ids are u32, like the tensors the reference block
+ *     passes between its steps.
+ * Each declaration cites the reference code it replaces (paths inside the candle workspace).
+ */
+#ifndef CANDLE_MOE_H_
+#define CANDLE_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CANDLE_MOE_API __attribute__((visibility("default")))
+#else
+#define CANDLE_MOE_API
+#endif
+
+#define CANDLE_MOE_MAX_EXPERTS 128
+#define CANDLE_MOE_MAX_TOPK 8
+
+/* GGML dtype ids of the supported weight formats */
+#define CANDLE_GGML_Q8_0 8
+#define CANDLE_GGML_Q4K 12
+#define CANDLE_GGML_Q6K 14
+
+/* error codes */
+#define CANDLE_MOE_OK 0
+#define CANDLE_MOE_E_NULL (-1)        /* a required pointer is NULL */
+#define CANDLE_MOE_E_SHAPE (-2)       /* a dimension is zero, too large or not a block multiple */
+#define CANDLE_MOE_E_DTYPE (-3)       /* weight dtype not one of Q8_0 / Q4K / Q6K */
+#define CANDLE_MOE_E_WORKSPACE (-4)   /* workspace smaller than candle_moe_workspace_bytes says */
+#define CANDLE_MOE_E_ALIGN (-5)       /* a pointer does not meet the documented alignment */
+#define CANDLE_MOE_E_NO_DEVICE (-6)   /* no CUDA device / not an sm_100 device */
+
+/* Weights of one block, as MlpOrMoe::MoE holds them
+ * (candle-transformers/src/models/quantized_llama.rs:134-141; Mlp :117-122).  The pointer arrays
+ * are HOST arrays of n_experts DEVICE pointers, one per `experts[i].feed_forward_w{1,2,3}`. */
+typedef struct candle_moe_weights {
+    int32_t d_model;          /* hidden size d; multiple of the w1/w3 block size */
+    int32_t d_ff;             /* expert inner size; multiple of the w2 block size */
+    int32_t n_experts;        /* <= CANDLE_MOE_MAX_EXPERTS */
+    int32_t top_k;            /* n_expert_used, <= CANDLE_MOE_MAX_TOPK */
+    int32_t renorm;           /* 1: divide the selected weights by their sum (quantized_llama.rs:170-178);
+                                 0: keep the softmax values (qwen2_moe.rs:281-282, norm_topk_prob = false) */
+    int32_t dtype_w13;        /* GGML id of w1 and w3, each [d_ff, d_model] */
+    int32_t dtype_w2;         /* GGML id of w2, [d_model, d_ff] */
+    int32_t d_ff_shared;      /* 0 = no shared expert (qwen2_moe.rs:315-319 when > 0) */
+    int32_t dtype_shared13;
+    int32_t dtype_shared2;
+    const float* router;          /* device f32 [n_experts, d_model] (feed_forward_gate_inp) */
+    const float* router_bias;     /* device f32 [n_experts] added to the logits, or NULL */
+    const void* const* w1;        /* host array of device pointers */
+    const void* const* w3;
+    const void* const* w2;
+    const void* shared_w1;        /* device, [d_ff_shared, d_model] */
+    const void* shared_w3;
+    const void* shared_w2;        /* device, [d_model, d_ff_shared] */
+    const float* shared_gate;     /* device f32 [d_model] (shared_expert_gate) */
+} candle_moe_weights_t;
+
+/* Library identification: returns a static string "candle_moe_sm100 <version>". */
+CANDLE_MOE_API const char* candle_moe_version(void);
+
+/* Bytes of scratch that candle_moe_forward needs for up to max_tokens rows.  Replaces the
+ * per-call allocations of the reference block (dev.alloc in candle-core/src/quantized/cuda.rs:253,
+ * 321 and the zeros_like/index_add copies of quantized_llama.rs:184,202). */
+CANDLE_MOE_API int candle_moe_workspace_bytes(const candle_moe_weights_t* w, int64_t max_tokens, size_t* out_bytes);
+
+/* Router: logits = x . Wg^T (+ bias), softmax over all experts, stable descending top-k (ties keep
+ * the lower expert id), optional renormalisation.  Replaces quantized_llama.rs:153-179
+ * (QMatMul::forward on the f32 gate, candle_nn::ops::softmax_last_dim, the host-side sort).
+ *   x [T, d] f32, router [E, d] f32, bias [E] f32 or NULL
+ *   topk_ids [T, k] u32 in rank order, topk_w [T, k] f32 */
+CANDLE_MOE_API int candle_moe_router_topk(void* stream, const float* x, const float* router, const float* bias, int64_t T,
+                           int32_t d, int32_t E, int32_t k, int32_t renorm, uint32_t* topk_ids, float* topk_w);
+
+/* Dispatch: groups the T*k (token, expert) pairs by expert, tokens ascending inside an expert,
+ * which is the order of the reference's `top_x[e]` lists (quantized_llama.rs:162-173) that feed
+ * index_select (:197).
+ *   expert_counts [E], expert_offsets [E + 1] (exclusive prefix sum of counts),
+ *   perm_token [T*k]: token id of the row at each grouped position,
+ *   pair_pos   [T*k]: grouped position of pair (t, rank) at index t*k + rank. */
+CANDLE_MOE_API int candle_moe_permute(void* stream, const uint32_t* topk_ids, int64_t T, int32_t k, int32_t E,
+                       uint32_t* expert_counts, uint32_t* expert_offsets, uint32_t* perm_token,
+                       uint32_t* pair_pos);
+
+/* Activation quantization, the `T::VecDotType::from_float` step of k_quants::matmul
+ * (candle-core/src/quantized/k_quants.rs:1898-1902): per row, per block.
+ *   for_weight_dtype Q4K / Q6K -> BlockQ8K arithmetic (k_quants.rs:1819-1856): per 256 a signed-max
+ *       scale, int8 values, 16 int16 block sums
+ *   for_weight_dtype Q8_0      -> BlockQ8_0 arithmetic (k_quants.rs:605-634): per 32 an f16 scale
+ * Outputs are planar: qs int8 [rows, kdim]; scales f32 [rows, kdim / block] (for Q8_0 the f16-rounded
+ * scale widened to f32); bsums int16 [rows, kdim / 16] (Q8K only, may be NULL for Q8_0). */
+CANDLE_MOE_API int candle_moe_quantize_act(void* stream, const float* x, int64_t rows, int32_t kdim, int32_t for_weight_dtype,
+                            int8_t* qs, float* scales, int16_t* bsums);
+
+/* Weighted combine: y[t] = sum over the token's selected experts, in ascending expert id, of
+ * topk_w * expert_out[pair_pos], each product rounded before it is added, starting from zero --
+ * the order of broadcast_mul + index_add over the expert loop (quantized_llama.rs:185-203).
+ * With a shared expert (shared_out != NULL): y[t] += shared_out[t] * sigmoid(x[t] . shared_gate)
+ * afterwards (qwen2_moe.rs:315-319). */
+CANDLE_MOE_API int candle_moe_combine(void* stream, const float* expert_out, const uint32_t* topk_ids, const float* topk_w,
+                       const uint32_t* pair_pos, int64_t T, int32_t k, int32_t d, const float* shared_out,
+                       const float* x, const float* shared_gate, float* y);
+
+/* Grouped expert products over rows already grouped by expert (Mlp::forward,
+ * quantized_llama.rs:124-131, applied to every expert's row list; QMatMul::forward ->
+ * k_quants::matmul semantics, candle-core/src/quantized/mod.rs:533-556, k_quants.rs:1873-1920).
+ *   gate_up: hidden[p, :] = silu(W1_e . xq[row(p)]) * (W3_e . xq[row(p)])   for p in expert e's range
+ *   down   : out[p, :]    = W2_e . hq[p]
+ * `row_of` maps a grouped position to the row of the quantized activations (NULL = identity).
+ * Activations are the planar outputs of candle_moe_quantize_act.
+ * `weights` are host arrays of E device pointers; `expert_offsets` is a device array [E + 1]. */
+CANDLE_MOE_API int candle_moe_grouped_gate_up(void* stream, const void* const* w1, const void* const* w3, int32_t dtype,
+                               int32_t E, int32_t d, int32_t ff, const uint32_t* expert_offsets,
+                               const uint32_t* row_of, int64_t max_rows, const int8_t* xq, const float* xscales,
+                               const int16_t* xbsums, float* hidden);
+CANDLE_MOE_API int candle_moe_grouped_down(void* stream, const void* const* w2, int32_t dtype, int32_t E, int32_t d, int32_t ff,
+                            const uint32_t* expert_offsets, int64_t max_rows, const int8_t* hq,
+                            const float* hscales, const int16_t* hbsums, float* out);
+
+/* The whole block on one GPU: MlpOrMoe::MoE::forward (quantized_llama.rs:143-210), plus the shared
+ * expert of qwen2_moe.rs:261-323 when w->d_ff_shared > 0.
+ *   x [T, d_model] f32 device, y [T, d_model] f32 device (overwritten), workspace device memory of at
+ *   least candle_moe_workspace_bytes(w, T) bytes, 256-byte aligned.
+ * No host synchronisation, no allocation: the reference's to_vec2 round trip (:158) and per-expert
+ * uploads (:190-193) do not exist on this path. */
+CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
+                       void* workspace, size_t workspace_bytes);
+
+/* Views into the workspace of the last candle_moe_forward call with the same (w, T), for tests and
+ * for expert-parallel callers: device pointers to topk_ids [T,k], topk_w [T,k], expert_counts [E],
+ * perm_token [T*k].  Any output pointer may be NULL. */
+CANDLE_MOE_API int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,
+                               float** topk_w, uint32_t** expert_counts, uint32_t** perm_token);
+
+/* Weight quantization on the device, bit-exact with QTensor::quantize -> GgmlType::from_float for
+ * Q8_0 / Q4K / Q6K (k_quants.rs:605-634, 1287-1345, 1675-1744); replaces the CPU round trip of
+ * QCudaStorage::quantize (candle-core/src/quantized/cuda.rs:457-478).
+ *   src f32 [n_elems] device, dst raw blocks device; n_elems a multiple of the block size. */
+CANDLE_MOE_API int candle_moe_quantize_weights(void* stream, int32_t dtype, const float* src, int64_t n_elems, void* dst);
+
+/* Dequantize raw blocks to f32 (GgmlType::to_float; k_quants.rs:587-603, 1347-1374, 1747-1778). */
+CANDLE_MOE_API int candle_moe_dequantize(void* stream, int32_t dtype, const void* blocks, int64_t n_elems, float* dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CANDLE_MOE_H_ */
