@@ -230,6 +230,39 @@ def test_qmatmul_forward_matches_oracle(orc, torch_cuda, name, m, k, n):
     assert np.array_equal(got2[:m], got) and np.array_equal(got2[m:2 * m], got) and np.array_equal(got2[2 * m], got[0])
 
 
+@pytest.mark.parametrize("name13,name2,rows,d,ff", [("Q4K", "Q6K", 5, 512, 1024), ("Q4K", "Q4K", 13, 1024, 3584),
+                                                    ("Q8_0", "Q8_0", 9, 2048, 1408)])
+def test_expert_hidden_before_requantization(orc, torch_cuda, name13, name2, rows, d, ff):
+    """silu(W1 x) * (W3 x) in f32, before it is re-quantized for W2: same integers as the oracle, so
+    only f32 summation order and the last bit of expf differ (Mlp::forward, quantized_llama.rs:125-128)."""
+    torch = torch_cuda
+    from candle_b200 import _lib
+    dt13, dt2 = getattr(orc, name13), getattr(orc, name2)
+    rng = np.random.default_rng(rows + d)
+    x = rng.standard_normal((rows, d), dtype=np.float32)
+    w1 = orc.quantize(dt13, rng.standard_normal((ff, d), dtype=np.float32) * np.float32(0.02))
+    w3 = orc.quantize(dt13, rng.standard_normal((ff, d), dtype=np.float32) * np.float32(0.02))
+    w2 = orc.quantize(dt2, rng.standard_normal((d, ff), dtype=np.float32) * np.float32(0.02))
+    _, hid_ref = orc.mlp_forward(dt13, dt2, x, w1, w3, w2, ff)
+    L = _lib.load()
+    ab = 32 if dt13 == orc.Q8_0 else 256
+    xd = torch.from_numpy(x).cuda()
+    w1d, w3d = torch.from_numpy(w1).cuda(), torch.from_numpy(w3).cuda()
+    qs = torch.empty((rows, d), dtype=torch.int8, device="cuda")
+    sc = torch.empty((rows, d // ab), dtype=torch.float32, device="cuda")
+    bs = torch.empty((rows, d // 16), dtype=torch.int16, device="cuda")
+    offs = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    hid = torch.empty((rows, ff), dtype=torch.float32, device="cuda")
+    st = _st(torch)
+    assert L.candle_moe_quantize_act(st, xd.data_ptr(), rows, d, dt13, qs.data_ptr(), sc.data_ptr(), bs.data_ptr()) == 0
+    p1, p3 = (C.c_void_p * 1)(w1d.data_ptr()), (C.c_void_p * 1)(w3d.data_ptr())
+    assert L.candle_moe_grouped_gate_up(st, p1, p3, dt13, 1, d, ff, offs.data_ptr(), None, rows, qs.data_ptr(),
+                                        sc.data_ptr(), bs.data_ptr(), hid.data_ptr()) == 0
+    torch.cuda.synchronize()
+    got = hid.cpu().numpy()
+    assert H.rel_l2(got, hid_ref) < 2e-6 and H.max_rel(got, hid_ref) < 1e-5
+
+
 # ------------------------------------------------------------------------------------------------
 # the whole block
 # ------------------------------------------------------------------------------------------------
@@ -252,9 +285,10 @@ def _check_block(orc, torch, mw, x, label=""):
         assert np.array_equal(perm, ref.expert_rows), label
         mr, l2 = H.max_rel(y, ref.y), H.rel_l2(y, ref.y)
         assert mr <= H.MAX_REL_TOL and l2 <= H.REL_L2_TOL, f"{label}: max-rel {mr:.3e} rel-L2 {l2:.3e}"
-        # with identical integer activations the only differences are f32 summation order and the
-        # last bit of expf: far below the acceptance bound
-        assert l2 < 2e-5, f"{label}: rel-L2 {l2:.3e}"
+        # Last-bit differences in the f32 hidden values (summation order, expf) flip a few of its
+        # int8 re-quantized values by one step before W2; that is the whole error budget here and
+        # stays several times below the acceptance bound.
+        assert l2 < 5e-4, f"{label}: rel-L2 {l2:.3e}"
     else:
         same = (ref.topk_ids == ids).all(axis=1)
         assert H.rel_l2(y[same], ref.y[same]) <= H.REL_L2_TOL
