@@ -21,6 +21,7 @@ ERROR_NAMES = {
     -4: "CANDLE_MOE_E_WORKSPACE (workspace too small)",
     -5: "CANDLE_MOE_E_ALIGN (pointer alignment)",
     -6: "CANDLE_MOE_E_NO_DEVICE",
+    -7: "CANDLE_MOE_E_STATIC_SCRATCH (needs more than the built-in 16 MiB scratch)",
 }
 
 
@@ -59,6 +60,7 @@ SYMBOLS = {
     "candle_moe_grouped_gate_up": (C.c_int, [_P, _PP, _PP, _I32, _I32, _I32, _I32, _P, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_grouped_down": (C.c_int, [_P, _PP, _I32, _I32, _I32, _I32, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_forward": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ]),
+    "candle_moe_forward_static": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P]),
     "candle_moe_workspace_views": (C.c_int, [C.POINTER(MoeWeightsC), _I64, _P, _PP, _PP, _PP, _PP]),
     "candle_moe_quantize_weights": (C.c_int, [_P, _I32, _P, _I64, _P]),
     "candle_moe_dequantize": (C.c_int, [_P, _I32, _P, _I64, _P]),

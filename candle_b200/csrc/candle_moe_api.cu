@@ -1,6 +1,7 @@
 // extern "C" entry points of libcandle_moe_sm100.so (declared in include/candle_moe.h): argument
 // validation on the host, workspace carving, and the launch sequence of the whole block.
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -257,6 +258,45 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     }
     CM_TRY(rc(launch_combine(st, ws.eo, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out, x, w->shared_gate, y)));
     return CANDLE_MOE_OK;
+}
+
+// ---- allocation-free variant -------------------------------------------------------------------
+// Scratch for candle_moe_forward_static.  In host code `g_static_scratch` is only a handle for the
+// symbol, not an address a kernel could use: the device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the launches get.
+static __device__ __align__(256) unsigned char g_static_scratch[CANDLE_MOE_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the built-in scratch on the current device; 0 on success.
+int static_scratch_ptr(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return CANDLE_MOE_E_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p || (reinterpret_cast<uintptr_t>(p) & 255)) return CANDLE_MOE_E_ALIGN;
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return CANDLE_MOE_OK;
+}
+}  // namespace
+
+int candle_moe_forward_static(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y) {
+    size_t need = 0;
+    CM_TRY(candle_moe_workspace_bytes(w, T, &need));
+    if (need > (size_t)CANDLE_MOE_STATIC_SCRATCH_BYTES) return CANDLE_MOE_E_STATIC_SCRATCH;
+    void* scratch = nullptr;
+    CM_TRY(static_scratch_ptr(&scratch));
+    return candle_moe_forward(stream, w, x, T, y, scratch, (size_t)CANDLE_MOE_STATIC_SCRATCH_BYTES);
 }
 
 int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,

@@ -48,6 +48,10 @@ extern "C" {
 #define CANDLE_MOE_E_WORKSPACE (-4)   /* workspace smaller than candle_moe_workspace_bytes says */
 #define CANDLE_MOE_E_ALIGN (-5)       /* a pointer does not meet the documented alignment */
 #define CANDLE_MOE_E_NO_DEVICE (-6)   /* no CUDA device / not an sm_100 device */
+#define CANDLE_MOE_E_STATIC_SCRATCH (-7) /* the call needs more scratch than CANDLE_MOE_STATIC_SCRATCH_BYTES */
+
+/* size of the built-in scratch area used by candle_moe_forward_static (per GPU, held until exit) */
+#define CANDLE_MOE_STATIC_SCRATCH_BYTES (16u << 20)
 
 /* Weights of one block, as MlpOrMoe::MoE holds them
  * (candle-transformers/src/models/quantized_llama.rs:134-141; Mlp :117-122).  The pointer arrays
@@ -144,6 +148,31 @@ CANDLE_MOE_API int candle_moe_grouped_down(void* stream, const void* const* w2, 
  * uploads (:190-193) do not exist on this path. */
 CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
                        void* workspace, size_t workspace_bytes);
+
+/* The same block as candle_moe_forward for callers that may not allocate device memory at all.
+ * (No counterpart in the reference: candle allocates its temporaries per call.)
+ *
+ * Who needs it: a host whose device memory is entirely owned by its own pool or arena and who
+ * therefore has no buffer to hand over as `workspace` and no permission to call cudaMalloc next
+ * to that pool; a decode loop with a latency budget, where an allocation could stall the device;
+ * a plugin living inside a process that forbids foreign allocations.  Such a caller passes only
+ * inputs and outputs; the scratch lives in a fixed array of CANDLE_MOE_STATIC_SCRATCH_BYTES that is
+ * part of the library image, so every GPU that loads the library keeps that much memory until
+ * the process exits.
+ *
+ * Rules:
+ *   - a call whose scratch need (candle_moe_workspace_bytes(w, T)) exceeds
+ *     CANDLE_MOE_STATIC_SCRATCH_BYTES is refused with CANDLE_MOE_E_STATIC_SCRATCH before anything is
+ *     enqueued (the Mixtral-8x7B-shaped layer fits up to T = 80 rows);
+ *   - the first call on each device looks the array's device address up (a host-side query, no
+ *     allocation); make that first call with the device current and before starting any stream
+ *     capture;
+ *   - all calls on one GPU share the one array: two calls that can overlap on the GPU (different
+ *     streams) race on it -- serialise them; the array keeps whatever the previous call left, and
+ *     nothing in it needs clearing because every region is written before it is read in a call;
+ *   - nothing is allocated or freed: no cudaMalloc, cudaFree or allocating library routine. */
+CANDLE_MOE_API int candle_moe_forward_static(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T,
+                                             float* y);
 
 /* Views into the workspace of the last candle_moe_forward call with the same (w, T), for tests and
  * for expert-parallel callers: device pointers to topk_ids [T,k], topk_w [T,k], expert_counts [E],
