@@ -62,6 +62,7 @@ SYMBOLS = {
     "candle_moe_forward": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ]),
     "candle_moe_forward_static": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P]),
     "candle_moe_workspace_views": (C.c_int, [C.POINTER(MoeWeightsC), _I64, _P, _PP, _PP, _PP, _PP]),
+    "candle_moe_device_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "candle_moe_quantize_weights": (C.c_int, [_P, _I32, _P, _I64, _P]),
     "candle_moe_dequantize": (C.c_int, [_P, _I32, _P, _I64, _P]),
 }

@@ -20,6 +20,7 @@ SOURCES = {
     "quantize_act.cu": ["-fmad=false"],
     "weight_quantize.cu": ["-fmad=false"],
     "expert_rows.cu": [],
+    "expert_stream.cu": [],
 }
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
           "-Xcompiler", "-fvisibility=hidden"]

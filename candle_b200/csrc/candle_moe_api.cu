@@ -9,6 +9,8 @@ using namespace cmoe;
 
 namespace {
 
+constexpr int MAX_K_SPLITS = 4;  // partial outputs the down product may leave for the combine kernel
+
 struct Workspace {
     // routing
     uint32_t* topk_ids;
@@ -66,7 +68,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     ws.hq = carve<int8_t>(base, off, Tk * ff);
     ws.hs = carve<float>(base, off, Tk * ff / act_block(w->dtype_w2));
     ws.hb = carve<int16_t>(base, off, Tk * ff / 16);
-    ws.eo = carve<float>(base, off, Tk * d);
+    ws.eo = carve<float>(base, off, Tk * d * MAX_K_SPLITS);
     if (w->d_ff_shared > 0) {
         const size_t fs = w->d_ff_shared;
         ws.sh_offsets = carve<uint32_t>(base, off, 2);
@@ -83,7 +85,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
         ws.shq = carve<int8_t>(base, off, (size_t)T * fs);
         ws.shs = carve<float>(base, off, (size_t)T * fs / act_block(w->dtype_shared2));
         ws.shb = carve<int16_t>(base, off, (size_t)T * fs / 16);
-        ws.so = carve<float>(base, off, (size_t)T * d);
+        ws.so = carve<float>(base, off, (size_t)T * d * MAX_K_SPLITS);
     }
     ws.total = align_up(off, 256);
     return ws;
@@ -173,8 +175,8 @@ int candle_moe_combine(void* stream, const float* expert_out, const uint32_t* to
     if (!expert_out || !topk_ids || !topk_w || !pair_pos || !y) return CANDLE_MOE_E_NULL;
     if (shared_out && (!x || !shared_gate)) return CANDLE_MOE_E_NULL;
     if (T < 0 || k <= 0 || k > CANDLE_MOE_MAX_TOPK || d <= 0 || d % 4) return CANDLE_MOE_E_SHAPE;
-    return rc(launch_combine((cudaStream_t)stream, expert_out, topk_ids, topk_w, pair_pos, T, k, d, shared_out, x,
-                             shared_gate, y));
+    return rc(launch_combine((cudaStream_t)stream, expert_out, 1, 0, topk_ids, topk_w, pair_pos, T, k, d, shared_out, 1,
+                             0, x, shared_gate, y));
 }
 
 int candle_moe_grouped_gate_up(void* stream, const void* const* w1, const void* const* w3, int32_t dtype,
@@ -204,7 +206,7 @@ int candle_moe_grouped_down(void* stream, const void* const* w2, int32_t dtype, 
     ExpertPtrs p2;
     CM_TRY(fill_ptrs(w2, E, p2));
     return rc(launch_grouped_down((cudaStream_t)stream, p2, dtype, E, d, ff, expert_offsets, max_rows, hq, hscales,
-                                  hbsums, out));
+                                  hbsums, out, 0, 1, nullptr));
 }
 
 int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
@@ -234,10 +236,13 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w)));
     CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
     CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
-    CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, Tk, ws.xq, ws.xs,
+    // a token selects an expert at most once: no expert sees more than T rows
+    CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
                                      ws.xb, ws.hidden)));
     CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
-    CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, Tk, ws.hq, ws.hs, ws.hb, ws.eo)));
+    int eo_splits = 1, so_splits = 1;
+    CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
+                                  MAX_K_SPLITS, &eo_splits)));
 
     const float* shared_out = nullptr;
     if (w->d_ff_shared > 0) {
@@ -253,10 +258,11 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
                                          ws.sxs, ws.sxb, ws.shidden)));
         CM_TRY(rc(launch_quantize_act(st, ws.shidden, T, fs, w->dtype_shared2, ws.shq, ws.shs, ws.shb)));
         CM_TRY(rc(launch_grouped_down(st, s2, w->dtype_shared2, 1, d, fs, ws.sh_offsets, T, ws.shq, ws.shs, ws.shb,
-                                      ws.so)));
+                                      ws.so, T * (int64_t)d, MAX_K_SPLITS, &so_splits)));
         shared_out = ws.so;
     }
-    CM_TRY(rc(launch_combine(st, ws.eo, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out, x, w->shared_gate, y)));
+    CM_TRY(rc(launch_combine(st, ws.eo, eo_splits, Tk * d, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out,
+                             so_splits, T * (int64_t)d, x, w->shared_gate, y)));
     return CANDLE_MOE_OK;
 }
 
@@ -309,6 +315,14 @@ int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* w
     if (expert_counts) *expert_counts = ws.counts;
     if (perm_token) *perm_token = ws.perm_token;
     return CANDLE_MOE_OK;
+}
+
+int candle_moe_device_status(int32_t* flags) {
+    if (!flags) return CANDLE_MOE_E_NULL;
+    int v = 0;
+    const cudaError_t e = read_stream_status(&v);
+    *flags = v;
+    return rc(e);
 }
 
 int candle_moe_quantize_weights(void* stream, int32_t dtype, const float* src, int64_t n_elems, void* dst) {

@@ -76,12 +76,24 @@ cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, i
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
                                    int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden);
+// `max_rows` bounds the rows of any single expert.  `out` may receive up to `max_splits` partial
+// results (K-splits) spaced `split_stride` floats apart; *n_splits says how many were written and
+// the caller (the combine kernel) adds them in split order.
 cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype, int E, int d, int ff,
                                 const uint32_t* offsets, int64_t max_rows, const int8_t* hq, const float* hs,
-                                const int16_t* hb, float* out);
-cudaError_t launch_combine(cudaStream_t st, const float* expert_out, const uint32_t* ids, const float* w,
-                           const uint32_t* pair_pos, int64_t T, int k, int d, const float* shared_out,
-                           const float* x, const float* shared_gate, float* y);
+                                const int16_t* hb, float* out, int64_t split_stride, int max_splits, int* n_splits);
+cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_splits, int64_t split_stride,
+                           const uint32_t* ids, const float* w, const uint32_t* pair_pos, int64_t T, int k, int d,
+                           const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
+                           const float* shared_gate, float* y);
+// streaming (TMA ring + tensor-core) form; cudaErrorNotSupported when the shape is not taken
+cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
+                                 int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
+                                 int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
+                                 const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
+                                 int max_splits);
+// flags raised by kernels whose bounded waits expired (0 = none); synchronises the device
+cudaError_t read_stream_status(int* out);
 cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);
 cudaError_t launch_dequantize(cudaStream_t st, int dtype, const void* blocks, int64_t n, float* dst);
 

@@ -11,9 +11,20 @@
 // count, unaligned Q6_K / Q8_0 rows) and is the path used for shapes the tiled kernels do not
 // take.  One warp owns one weight row (for gate_up: the same row of W1 and of W3) and walks the
 // expert's activation rows TOK at a time, so a weight row is fetched from HBM once per expert.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace cmoe {
+
+// Rows per expert up to which the streaming form is used; beyond it its per-expert token groups
+// would re-stream the weights too often.
+constexpr int64_t STREAM_MAX_ROWS = 64;
+
+static bool force_rows() {
+    const char* v = std::getenv("CANDLE_MOE_FORCE_ROWS");
+    return v && v[0] == '1';
+}
 
 constexpr int ROWS_WARPS = 8;  // weight rows per CTA
 constexpr int TOK = 4;         // activation rows per pass
@@ -205,15 +216,27 @@ static cudaError_t launch_rows(cudaStream_t st, const ExpertPtrs& wa, const Expe
 }
 
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
-                                   int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t /*max_rows*/,
+                                   int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden) {
+    if (!force_rows() && max_rows <= STREAM_MAX_ROWS) {
+        const cudaError_t e = launch_expert_stream(st, true, w1, w3, dtype, E, d, ff, offsets, row_of, max_rows, xq, xs,
+                                                   xb, hidden, nullptr, 0, 1);
+        if (e != cudaErrorNotSupported) return e;
+    }
     ActView a{xq, xs, xb};
     return launch_rows<true>(st, w1, w3, dtype, E, d, ff, offsets, row_of, a, hidden);
 }
 
 cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype, int E, int d, int ff,
-                                const uint32_t* offsets, int64_t /*max_rows*/, const int8_t* hq, const float* hs,
-                                const int16_t* hb, float* out) {
+                                const uint32_t* offsets, int64_t max_rows, const int8_t* hq, const float* hs,
+                                const int16_t* hb, float* out, int64_t split_stride, int max_splits, int* n_splits) {
+    if (n_splits) *n_splits = 1;
+    if (!force_rows() && max_rows <= STREAM_MAX_ROWS) {
+        const cudaError_t e = launch_expert_stream(st, false, w2, w2, dtype, E, ff, d, offsets, nullptr, max_rows, hq, hs,
+                                                   hb, out, n_splits, split_stride, max_splits);
+        if (e != cudaErrorNotSupported) return e;
+        if (n_splits) *n_splits = 1;
+    }
     ActView a{hq, hs, hb};
     return launch_rows<false>(st, w2, w2, dtype, E, ff, d, offsets, nullptr, a, out);
 }

@@ -1,0 +1,678 @@
+// Grouped expert products, streaming form for decode-sized batches (a few rows per expert).
+//
+// The work is HBM-bound: every active expert's weight blocks are read once and the arithmetic per
+// byte is tiny.  Design:
+//   * persistent CTAs (one per SM), each owning a CONTIGUOUS, cost-balanced range of work items;
+//     an item is a tile of 16 weight rows of one expert over one K-range ("split");
+//   * warp 0 is the producer: one `cp.async.bulk` (TMA, no tensor map needed: a row chunk is
+//     contiguous) per weight row per stage into a padded, bank-conflict-free shared-memory ring,
+//     completion counted on an mbarrier; several stages (>= 75 KB) are always in flight per SM;
+//   * warps 1..8 are consumers: each takes one 256-element block column of the stage, unpacks the
+//     quants in registers straight from `ldmatrix` fragments and multiplies them with the int8
+//     activations (resident in shared memory for the expert's rows) on the tensor cores with
+//     `mma.sync m16n8k32 / m16n8k16` (s8 x s8 -> s32).  Sub-block scales are applied to the exact
+//     integer partial sums, the per-block f16 scales in f32 -- the same integers as the reference's
+//     vec_dot (candle-core/src/quantized/k_quants.rs:1205-1285, 1616-1673), different f32 order;
+//   * the 8 K-slices of a tile meet in shared memory in a fixed order; gate_up applies
+//     silu(w1 x) * (w3 x) there and stores f32, down stores one partial per K-split which the
+//     combine kernel adds in split order (deterministic, no atomics).
+// Every wait on an mbarrier is bounded; on expiry the CTA raises a flag in `status`, stops waiting
+// and runs its loops to the end so that no thread is left behind at a barrier.
+#include "common.cuh"
+#include "stream_common.cuh"
+
+namespace cmoe {
+
+namespace {
+
+constexpr int TILE_ROWS = 16;
+constexpr int KC = 8;                 // 256-element blocks per stage chunk (one per consumer warp)
+constexpr int N_CONSUMER_WARPS = 8;
+constexpr int STREAM_THREADS = 32 * (1 + N_CONSUMER_WARPS);
+constexpr int RED_PAD = 17;           // floats per (warp, matrix, token) in the reduction buffer
+
+// ---------------------------------------------------------------------------------------------
+// Q4_K (144 B per 256): f16 d, f16 dmin, 12 B of 6-bit scales/mins, 128 B of nibbles.
+// ---------------------------------------------------------------------------------------------
+struct FmtQ4K {
+    static constexpr int BLOCK_BYTES = Q4K_BYTES;
+    static constexpr int CHUNK_BYTES = KC * Q4K_BYTES;        // 1152
+    static constexpr int ROW_STRIDE = CHUNK_BYTES + 16;       // 1168 = 73 * 16: ldmatrix rows hit 8 distinct 16-B lanes
+    static constexpr bool NEEDS_BSUMS = false;
+
+    // One block column (block index `wblk` of the chunk) of a 16-row tile against NT token tiles.
+    template <int NT>
+    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
+                                                 int kblk_local, const float* act_scale, int scale_stride,
+                                                 const uint8_t*, const uint8_t*, int, int lane, float (&f)[NT][4]) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint8_t* rowA = tile + g * ROW_STRIDE + wblk * BLOCK_BYTES;
+        const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
+        const uint32_t hA = *reinterpret_cast<const uint32_t*>(rowA), hB = *reinterpret_cast<const uint32_t*>(rowB);
+        const float dA = half_bits_to_float((uint16_t)(hA & 0xffff)), mnA = half_bits_to_float((uint16_t)(hA >> 16));
+        const float dB = half_bits_to_float((uint16_t)(hB & 0xffff)), mnB = half_bits_to_float((uint16_t)(hB >> 16));
+        uint32_t scA[2], mA[2], scB[2], mB[2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
+        {
+            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(rowA + 4), s1 = *reinterpret_cast<const uint32_t*>(rowA + 8),
+                           s2 = *reinterpret_cast<const uint32_t*>(rowA + 12);
+            scA[0] = s0 & 0x3f3f3f3fu;
+            mA[0] = s1 & 0x3f3f3f3fu;
+            scA[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
+            mA[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+        }
+        {
+            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(rowB + 4), s1 = *reinterpret_cast<const uint32_t*>(rowB + 8),
+                           s2 = *reinterpret_cast<const uint32_t*>(rowB + 12);
+            scB[0] = s0 & 0x3f3f3f3fu;
+            mB[0] = s1 & 0x3f3f3f3fu;
+            scB[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
+            mB[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+        }
+        int c[NT][4], cm[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[nt][i] = cm[nt][i] = 0;
+
+        // ldmatrix lane addressing: A matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of the group
+        const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + wblk * BLOCK_BYTES + 16 +
+                                16 * (lane >> 4);
+        const uint8_t* b_addr = act + (lane & 7) * act_stride + kblk_local * 256 + 16 * (lane >> 3);
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+            uint32_t a[4];
+            ldmatrix_x4(a, a_addr + 32 * grp);
+            uint32_t alo[4], ahi[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                alo[i] = a[i] & 0x0f0f0f0fu;
+                ahi[i] = (a[i] >> 4) & 0x0f0f0f0fu;
+            }
+            const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
+            const int sAl = (scA[jl >> 2] >> (8 * (jl & 3))) & 0xff, sAh = (scA[jh >> 2] >> (8 * (jh & 3))) & 0xff;
+            const int sBl = (scB[jl >> 2] >> (8 * (jl & 3))) & 0xff, sBh = (scB[jh >> 2] >> (8 * (jh & 3))) & 0xff;
+            const uint32_t mAl = ((mA[jl >> 2] >> (8 * (jl & 3))) & 0xff) * 0x01010101u;
+            const uint32_t mAh = ((mA[jh >> 2] >> (8 * (jh & 3))) & 0xff) * 0x01010101u;
+            const uint32_t mBl = ((mB[jl >> 2] >> (8 * (jl & 3))) & 0xff) * 0x01010101u;
+            const uint32_t mBh = ((mB[jh >> 2] >> (8 * (jh & 3))) & 0xff) * 0x01010101u;
+            const uint32_t aml[4] = {mAl, mBl, mAl, mBl}, amh[4] = {mAh, mBh, mAh, mBh};
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                uint32_t b[4];
+                ldmatrix_x4(b, b_addr + nt * 8 * act_stride + 64 * grp);
+                int p[4] = {0, 0, 0, 0};
+                mma_s8_k32(p, alo, b[0], b[1]);
+                c[nt][0] += sAl * p[0];
+                c[nt][1] += sAl * p[1];
+                c[nt][2] += sBl * p[2];
+                c[nt][3] += sBl * p[3];
+                int q[4] = {0, 0, 0, 0};
+                mma_s8_k32(q, ahi, b[2], b[3]);
+                c[nt][0] += sAh * q[0];
+                c[nt][1] += sAh * q[1];
+                c[nt][2] += sBh * q[2];
+                c[nt][3] += sBh * q[3];
+                mma_s8_k32(cm[nt], aml, b[0], b[1]);  // sum_i min_j * q8_i, the reference's bsums term
+                mma_s8_k32(cm[nt], amh, b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const float d8a = act_scale[(nt * 8 + 2 * t) * scale_stride + kblk_local];
+            const float d8b = act_scale[(nt * 8 + 2 * t + 1) * scale_stride + kblk_local];
+            f[nt][0] = fmaf(d8a * dA, (float)c[nt][0], f[nt][0]);
+            f[nt][0] = fmaf(-(d8a * mnA), (float)cm[nt][0], f[nt][0]);
+            f[nt][1] = fmaf(d8b * dA, (float)c[nt][1], f[nt][1]);
+            f[nt][1] = fmaf(-(d8b * mnA), (float)cm[nt][1], f[nt][1]);
+            f[nt][2] = fmaf(d8a * dB, (float)c[nt][2], f[nt][2]);
+            f[nt][2] = fmaf(-(d8a * mnB), (float)cm[nt][2], f[nt][2]);
+            f[nt][3] = fmaf(d8b * dB, (float)c[nt][3], f[nt][3]);
+            f[nt][3] = fmaf(-(d8b * mnB), (float)cm[nt][3], f[nt][3]);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Q6_K (210 B per 256): 128 B low nibbles, 64 B high 2-bit pairs, 16 int8 scales, f16 d.
+// A block is only 2-byte aligned inside the row, so its words are read as one 32-bit or two
+// 16-bit shared loads depending on the (warp-uniform) parity of the block index.
+// The quants are used unsigned (0..63); the reference's "- 32" becomes
+//   - 32 * sum_j scale_j * bsum_j(token),
+// itself a 16x16 by 16x8 integer product done with two more MMAs on the activation block sums
+// split into a signed high byte and an unsigned low byte.
+// ---------------------------------------------------------------------------------------------
+struct FmtQ6K {
+    static constexpr int BLOCK_BYTES = Q6K_BYTES;
+    static constexpr int CHUNK_BYTES = KC * Q6K_BYTES;        // 1680 (8 blocks keep 16-byte alignment)
+    static constexpr int ROW_STRIDE = CHUNK_BYTES;            // 420 words, 420 % 32 = 4: rows g, words t never share a bank
+    static constexpr bool NEEDS_BSUMS = true;
+
+    template <bool ODD>
+    __device__ static __forceinline__ uint32_t ld32(const uint8_t* p) {
+        if (ODD) {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
+            return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
+        }
+        return *reinterpret_cast<const uint32_t*>(p);
+    }
+
+    template <int NT, bool ODD>
+    __device__ static __forceinline__ void block_impl(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
+                                                      int kblk_local, const float* act_scale, int scale_stride,
+                                                      const uint8_t* bs_hi, const uint8_t* bs_lo, int bs_stride, int lane,
+                                                      float (&f)[NT][4]) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint8_t* rowA = tile + g * ROW_STRIDE + wblk * BLOCK_BYTES;
+        const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
+        const float dA = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowA + 208));
+        const float dB = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowB + 208));
+        uint32_t scA[4], scB[4];  // 16 int8 scales per row
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            scA[i] = ld32<ODD>(rowA + 192 + 4 * i);
+            scB[i] = ld32<ODD>(rowB + 192 + 4 * i);
+        }
+        int c[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+        const uint8_t* b_addr = act + (lane & 7) * act_stride + kblk_local * 256 + 16 * (lane >> 3);
+
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            // hq[lr][x]: for l-range lr (l = 16*lr + 4t .. +3), the 2-bit highs of quarter x moved to bits 4..5
+            uint32_t hqA[2][4], hqB[2][4];
+#pragma unroll
+            for (int lr = 0; lr < 2; ++lr) {
+                const uint32_t qa = ld32<ODD>(rowA + 128 + 32 * h + 16 * lr + 4 * t);
+                const uint32_t qb = ld32<ODD>(rowB + 128 + 32 * h + 16 * lr + 4 * t);
+                hqA[lr][0] = (qa << 4) & 0x30303030u;
+                hqA[lr][1] = (qa << 2) & 0x30303030u;
+                hqA[lr][2] = qa & 0x30303030u;
+                hqA[lr][3] = (qa >> 2) & 0x30303030u;
+                hqB[lr][0] = (qb << 4) & 0x30303030u;
+                hqB[lr][1] = (qb << 2) & 0x30303030u;
+                hqB[lr][2] = qb & 0x30303030u;
+                hqB[lr][3] = (qb >> 2) & 0x30303030u;
+            }
+            // low nibbles: ql[64h + 32*(x&1) + 16*lr + 4t ..], nibble (x >> 1)
+            uint32_t qlA[2][2], qlB[2][2];  // [x & 1][lr]
+#pragma unroll
+            for (int xo = 0; xo < 2; ++xo)
+#pragma unroll
+                for (int lr = 0; lr < 2; ++lr) {
+                    qlA[xo][lr] = ld32<ODD>(rowA + 64 * h + 32 * xo + 16 * lr + 4 * t);
+                    qlB[xo][lr] = ld32<ODD>(rowB + 64 * h + 32 * xo + 16 * lr + 4 * t);
+                }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {  // quarter: elements 128h + 32x .. +31 = sub-blocks 8h + 2x, 8h + 2x + 1
+                uint32_t aA[2], aB[2];
+#pragma unroll
+                for (int lr = 0; lr < 2; ++lr) {
+                    const uint32_t la = (x >> 1) ? (qlA[x & 1][lr] >> 4) : qlA[x & 1][lr];
+                    const uint32_t lb = (x >> 1) ? (qlB[x & 1][lr] >> 4) : qlB[x & 1][lr];
+                    aA[lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
+                    aB[lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
+                }
+                const int j0 = 8 * h + 2 * x;  // sub-block of lr = 0; lr = 1 is j0 + 1
+                const int sA0 = (int)(int8_t)(scA[j0 >> 2] >> (8 * (j0 & 3))), sA1 = (int)(int8_t)(scA[(j0 + 1) >> 2] >> (8 * ((j0 + 1) & 3)));
+                const int sB0 = (int)(int8_t)(scB[j0 >> 2] >> (8 * (j0 & 3))), sB1 = (int)(int8_t)(scB[(j0 + 1) >> 2] >> (8 * ((j0 + 1) & 3)));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    // the four 16-element sub-blocks of 64 elements come from one ldmatrix.x4; quarters x = 2y, 2y+1 share it
+                    uint32_t b[4];
+                    ldmatrix_x4(b, b_addr + nt * 8 * act_stride + 128 * h + 64 * (x >> 1));
+                    const uint32_t b0 = b[2 * (x & 1)], b1 = b[2 * (x & 1) + 1];
+                    int p[4] = {0, 0, 0, 0};
+                    mma_s8_k16(p, aA[0], aB[0], b0);
+                    c[nt][0] += sA0 * p[0];
+                    c[nt][1] += sA0 * p[1];
+                    c[nt][2] += sB0 * p[2];
+                    c[nt][3] += sB0 * p[3];
+                    int q[4] = {0, 0, 0, 0};
+                    mma_s8_k16(q, aA[1], aB[1], b1);
+                    c[nt][0] += sA1 * q[0];
+                    c[nt][1] += sA1 * q[1];
+                    c[nt][2] += sB1 * q[2];
+                    c[nt][3] += sB1 * q[3];
+                }
+            }
+        }
+        // offset term: corr[row][tok] = sum_j scale[row][j] * bsum[tok][j], bsum = 256 * hi + lo
+        const uint32_t sa = ld32<ODD>(rowA + 192 + 4 * t), sb = ld32<ODD>(rowB + 192 + 4 * t);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int tok = nt * 8 + g;
+            const uint32_t bh = *reinterpret_cast<const uint32_t*>(bs_hi + tok * bs_stride + kblk_local * 16 + 4 * t);
+            const uint32_t bl = *reinterpret_cast<const uint32_t*>(bs_lo + tok * bs_stride + kblk_local * 16 + 4 * t);
+            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+            mma_s8_k16(ch, sa, sb, bh);
+            mma_s8u8_k16(cl, sa, sb, bl);
+            const float d8a = act_scale[(nt * 8 + 2 * t) * scale_stride + kblk_local];
+            const float d8b = act_scale[(nt * 8 + 2 * t + 1) * scale_stride + kblk_local];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
+                const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
+                f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+            }
+        }
+    }
+
+    template <int NT>
+    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
+                                                 int kblk_local, const float* act_scale, int scale_stride,
+                                                 const uint8_t* bs_hi, const uint8_t* bs_lo, int bs_stride, int lane,
+                                                 float (&f)[NT][4]) {
+        if (wblk & 1)
+            block_impl<NT, true>(tile, wblk, act, act_stride, kblk_local, act_scale, scale_stride, bs_hi, bs_lo, bs_stride,
+                                 lane, f);
+        else
+            block_impl<NT, false>(tile, wblk, act, act_stride, kblk_local, act_scale, scale_stride, bs_hi, bs_lo,
+                                  bs_stride, lane, f);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Work decomposition shared by producer and consumers (pure function of the kernel arguments and
+// the expert offsets, so every warp walks the same sequence).
+// ---------------------------------------------------------------------------------------------
+struct StreamParams {
+    ExpertPtrs wa, wb;
+    const uint32_t* offsets;
+    const uint32_t* row_of;
+    const int8_t* aq;
+    const float* ascale;
+    const int16_t* absum;
+    float* out;
+    int* status;
+    int64_t out_split_stride;  // elements between the partial outputs of consecutive K-splits
+    int E, K, N, kb, n_chunks, splits, MT, stages;
+    int chunk_start[5];        // split s covers chunks [chunk_start[s], chunk_start[s+1])
+    int act_stride;            // bytes per token row of the resident activations
+    int scale_stride;          // floats per token row of the resident activation scales
+    int bs_stride;             // bytes per token row of each block-sum plane
+    uint32_t off_act, off_scale, off_bs_hi, off_bs_lo, off_red, off_stage, stage_bytes;
+};
+
+struct WorkItem {
+    int e, grp, split, tile;
+};
+
+struct Walker {
+    const StreamParams& P;
+    const uint32_t* offs;  // expert offsets (shared memory copy)
+    int tiles;
+    long long pos, hi;     // cost position of the next item, end of this CTA's range
+    int gidx, e, grp, ng_e, split, tile;
+
+    __device__ Walker(const StreamParams& p, const uint32_t* offsets_sm, int cta, int n_cta) : P(p), offs(offsets_sm) {
+        tiles = P.N / TILE_ROWS;
+        int gtot = 0;
+        for (int i = 0; i < P.E; ++i) gtot += (int)((offs[i + 1] - offs[i] + P.MT - 1) / P.MT);
+        const long long gcost = (long long)tiles * P.n_chunks;
+        const long long ctot = gcost * gtot;
+        const long long lo = ctot * cta / n_cta;
+        hi = ctot * (cta + 1) / n_cta;
+        e = grp = ng_e = 0;
+        // first item whose start cost is >= lo
+        gidx = (int)(lo / gcost);
+        long long rem = lo % gcost;
+        split = 0;
+        tile = 0;
+        for (int s = 0; s < P.splits; ++s) {
+            const long long s_lo = (long long)tiles * P.chunk_start[s], s_hi = (long long)tiles * P.chunk_start[s + 1];
+            if (rem < s_hi) {
+                const int cps = P.chunk_start[s + 1] - P.chunk_start[s];
+                split = s;
+                tile = rem <= s_lo ? 0 : (int)((rem - s_lo + cps - 1) / cps);
+                break;
+            }
+        }
+        normalize();
+        pos = item_cost_pos();
+        // locate (expert, token group) of gidx
+        grp = 0;
+        ng_e = 0;
+        int acc = 0;
+        for (e = 0; e < P.E; ++e) {
+            ng_e = (int)((offs[e + 1] - offs[e] + P.MT - 1) / P.MT);
+            if (gidx < acc + ng_e) {
+                grp = gidx - acc;
+                break;
+            }
+            acc += ng_e;
+        }
+    }
+    __device__ void normalize() {
+        if (tile >= tiles) {
+            tile = 0;
+            ++split;
+        }
+        if (split >= P.splits) {
+            split = 0;
+            ++gidx;
+            ++grp;
+        }
+    }
+    __device__ long long item_cost_pos() const {
+        return (long long)gidx * tiles * P.n_chunks + (long long)tiles * P.chunk_start[split] +
+               (long long)tile * (P.chunk_start[split + 1] - P.chunk_start[split]);
+    }
+    __device__ bool valid() const { return pos < hi && e < P.E; }
+    __device__ WorkItem item() const { return WorkItem{e, grp, split, tile}; }
+    __device__ void next() {
+        ++tile;
+        const int g0 = gidx;
+        normalize();
+        if (gidx != g0) {
+            while (e < P.E && grp >= ng_e) {  // move to the next expert that has rows
+                grp = 0;
+                ++e;
+                ng_e = e < P.E ? (int)((offs[e + 1] - offs[e] + P.MT - 1) / P.MT) : 0;
+            }
+        }
+        pos = item_cost_pos();
+    }
+};
+
+template <class F, bool GATE_UP, int NT>
+__global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const __grid_constant__ StreamParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t full_bar[8], empty_bar[8];
+    __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
+    __shared__ int s_abort;
+    constexpr int NM = GATE_UP ? 2 : 1;
+    constexpr int MT = 8 * NT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    for (int i = threadIdx.x; i <= P.E; i += blockDim.x) s_offs[i] = P.offsets[i];
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < P.stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], N_CONSUMER_WARPS);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+    volatile int* abort_flag = &s_abort;
+
+    Walker wk(P, s_offs, blockIdx.x, gridDim.x);
+    const size_t row_bytes = (size_t)P.kb * F::BLOCK_BYTES;
+    uint8_t* stage0 = smem + P.off_stage;
+
+    if (warp == 0) {
+        // ================= producer =================
+        uint32_t it = 0;
+        for (; wk.valid(); wk.next()) {
+            const WorkItem w = wk.item();
+            const int m = lane >> 4, r = lane & 15;
+            const bool active = m < NM;
+            const uint8_t* src_row = (m == 0 ? P.wa.p[w.e] : P.wb.p[w.e]);
+            if (active) src_row += (size_t)(w.tile * TILE_ROWS + r) * row_bytes;
+            for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
+                const int s = it % P.stages;
+                const uint32_t ph = (it / P.stages) & 1;
+                if (it >= (uint32_t)P.stages) mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+                const int blocks = min(KC, P.kb - ch * KC);
+                const uint32_t bytes = (uint32_t)blocks * F::BLOCK_BYTES;
+                if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * TILE_ROWS * NM);
+                __syncwarp();
+                if (active && !*abort_flag)
+                    bulk_g2s(stage0 + (size_t)s * P.stage_bytes + (m * TILE_ROWS + r) * F::ROW_STRIDE,
+                             src_row + (size_t)ch * F::CHUNK_BYTES, bytes, &full_bar[s]);
+            }
+        }
+        // do not leave while copies into this CTA's shared memory may still be in flight
+        if (lane == 0) {
+            const uint32_t n = it < (uint32_t)P.stages ? it : (uint32_t)P.stages;
+            for (uint32_t j = 0; j < n; ++j) {
+                const uint32_t last = it - 1 - j;
+                mbar_wait(&full_bar[last % P.stages], (last / P.stages) & 1, abort_flag);
+            }
+        }
+    } else {
+        // ================= consumers =================
+        const int cw = warp - 1;                         // K-slice of this warp inside a chunk
+        const int ctid = threadIdx.x - 32;               // 0..255
+        uint8_t* act = smem + P.off_act;
+        float* act_scale = reinterpret_cast<float*>(smem + P.off_scale);
+        uint8_t* bs_hi = smem + P.off_bs_hi;
+        uint8_t* bs_lo = smem + P.off_bs_lo;
+        float* red = reinterpret_cast<float*>(smem + P.off_red);
+        uint32_t it = 0;
+        int cur_e = -1, cur_grp = -1, cur_split = -1;
+        for (; wk.valid(); wk.next()) {
+            const WorkItem w = wk.item();
+            const uint32_t p_base = s_offs[w.e] + (uint32_t)w.grp * MT;
+            const uint32_t p_end = min(s_offs[w.e + 1], p_base + MT);
+            const int blk0 = P.chunk_start[w.split] * KC;                      // first block of this split
+            const int nblk = min(P.kb, P.chunk_start[w.split + 1] * KC) - blk0;  // blocks in this split
+            if (w.e != cur_e || w.grp != cur_grp || w.split != cur_split) {
+                // ---- make the int8 rows (and scales / block sums) of this token group resident ----
+                cur_e = w.e;
+                cur_grp = w.grp;
+                cur_split = w.split;
+                consumer_sync();
+                const int vec_per_row = nblk * 16;  // 16-byte vectors per token row
+                for (int idx = ctid; idx < MT * vec_per_row; idx += 32 * N_CONSUMER_WARPS) {
+                    const int j = idx / vec_per_row, v = idx - j * vec_per_row;
+                    int4 val = make_int4(0, 0, 0, 0);
+                    if (p_base + j < p_end) {
+                        const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
+                        val = *reinterpret_cast<const int4*>(P.aq + row * P.K + (int64_t)blk0 * 256 + 16 * v);
+                    }
+                    *reinterpret_cast<int4*>(act + j * P.act_stride + 16 * v) = val;
+                }
+                for (int idx = ctid; idx < MT * nblk; idx += 32 * N_CONSUMER_WARPS) {
+                    const int j = idx / nblk, b = idx - j * nblk;
+                    float sv = 0.f;
+                    if (p_base + j < p_end) {
+                        const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
+                        sv = P.ascale[row * P.kb + blk0 + b];
+                    }
+                    act_scale[j * P.scale_stride + b] = sv;
+                }
+                if (F::NEEDS_BSUMS) {
+                    for (int idx = ctid; idx < MT * nblk * 16; idx += 32 * N_CONSUMER_WARPS) {
+                        const int j = idx / (nblk * 16), b = idx - j * nblk * 16;
+                        int v = 0;
+                        if (p_base + j < p_end) {
+                            const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
+                            v = P.absum[row * (P.K / 16) + blk0 * 16 + b];
+                        }
+                        bs_lo[j * P.bs_stride + b] = (uint8_t)(v & 0xff);
+                        bs_hi[j * P.bs_stride + b] = (uint8_t)((v >> 8) & 0xff);  // arithmetic shift: signed high byte
+                    }
+                }
+                consumer_sync();
+            }
+
+            float f[NM][NT][4];
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) f[m][nt][i] = 0.f;
+
+            for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
+                const int s = it % P.stages;
+                const bool ok = mbar_wait(&full_bar[s], (it / P.stages) & 1, abort_flag);
+                const int blk = ch * KC + cw;
+                if (ok && blk < P.kb) {
+                    const uint8_t* st = stage0 + (size_t)s * P.stage_bytes;
+#pragma unroll
+                    for (int m = 0; m < NM; ++m)
+                        F::template block<NT>(st + m * TILE_ROWS * F::ROW_STRIDE, cw, act, P.act_stride, blk - blk0,
+                                              act_scale, P.scale_stride, bs_hi, bs_lo, P.bs_stride, lane, f[m]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);
+            }
+
+            // ---- the 8 K-slices of the tile meet in shared memory, fixed order ----
+            {
+                const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+                for (int m = 0; m < NM; ++m)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int tok = nt * 8 + 2 * t + (i & 1), row = g + 8 * (i >> 1);
+                            red[((cw * NM + m) * MT + tok) * RED_PAD + row] = f[m][nt][i];
+                        }
+            }
+            consumer_sync();
+            for (int idx = ctid; idx < MT * TILE_ROWS; idx += 32 * N_CONSUMER_WARPS) {
+                const int tok = idx / TILE_ROWS, row = idx - tok * TILE_ROWS;
+                if (p_base + tok < p_end) {
+                    float va = 0.f, vb = 0.f;
+#pragma unroll
+                    for (int sw = 0; sw < N_CONSUMER_WARPS; ++sw) {
+                        va += red[((sw * NM + 0) * MT + tok) * RED_PAD + row];
+                        if (GATE_UP) vb += red[((sw * NM + 1) * MT + tok) * RED_PAD + row];
+                    }
+                    const int64_t o = (int64_t)(p_base + tok) * P.N + w.tile * TILE_ROWS + row;
+                    if (GATE_UP)
+                        P.out[o] = silu_f(va) * vb;
+                    else
+                        P.out[(int64_t)w.split * P.out_split_stride + o] = va;
+                }
+            }
+            consumer_sync();
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && s_abort) atomicOr(P.status, 1);
+}
+
+int g_max_smem = -1;
+int g_num_sms = -1;
+
+cudaError_t device_limits() {
+    if (g_max_smem >= 0) return cudaSuccess;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    int v = 0, n = 0;
+    e = cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e != cudaSuccess) return e;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    g_max_smem = v;
+    g_num_sms = n;
+    return cudaSuccess;
+}
+
+template <class F, bool GATE_UP, int NT>
+cudaError_t launch_one(cudaStream_t st, const StreamParams& P, size_t smem_bytes) {
+    auto kfn = expert_stream_kernel<F, GATE_UP, NT>;
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    if (e != cudaSuccess) return e;
+    kfn<<<g_num_sms, STREAM_THREADS, smem_bytes, st>>>(P);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+__device__ int g_stream_status = 0;
+
+// Plans and launches the streaming kernel; returns cudaErrorNotSupported when the shape is outside
+// what the streaming form takes (the caller then uses the row-per-warp form).
+cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
+                                 int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
+                                 int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
+                                 const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
+                                 int max_splits) {
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return cudaErrorNotSupported;
+    if (N % TILE_ROWS != 0 || K % 256 != 0) return cudaErrorNotSupported;
+    const int kb = K / 256;
+    if (dtype == CANDLE_GGML_Q6K && kb % KC != 0) return cudaErrorNotSupported;  // rows must stay 16-byte aligned
+    cudaError_t e = device_limits();
+    if (e != cudaSuccess) return e;
+    const int NT = max_rows_per_expert <= 8 ? 1 : 2;
+    const int MT = 8 * NT, NM = gate_up ? 2 : 1;
+    const int n_chunks = (kb + KC - 1) / KC;
+    const int row_stride = dtype == CANDLE_GGML_Q4K ? FmtQ4K::ROW_STRIDE : FmtQ6K::ROW_STRIDE;
+    const uint32_t stage_bytes = (uint32_t)(NM * TILE_ROWS * row_stride);
+    const bool bsums = dtype == CANDLE_GGML_Q6K;
+
+    StreamParams P{};
+    P.wa = wa;
+    P.wb = wb;
+    int status_ok = 0;
+    (void)status_ok;
+    for (int splits = 1; splits <= max_splits; ++splits) {
+        if (splits > n_chunks) break;
+        if (gate_up && splits > 1) break;  // the gate needs the full sum before silu
+        const int cps = (n_chunks + splits - 1) / splits;  // chunks of the largest split
+        const int ks_blocks = min(cps * KC, kb);
+        uint32_t off = 0;
+        auto take = [&](uint32_t bytes) {
+            off = (off + 127u) & ~127u;
+            const uint32_t o = off;
+            off += bytes;
+            return o;
+        };
+        P.act_stride = ks_blocks * 256 + 16;
+        P.scale_stride = ks_blocks;
+        P.bs_stride = ks_blocks * 16 + 16;
+        P.off_act = take((uint32_t)MT * P.act_stride);
+        P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
+        P.off_bs_hi = bsums ? take((uint32_t)MT * P.bs_stride) : 0;
+        P.off_bs_lo = bsums ? take((uint32_t)MT * P.bs_stride) : 0;
+        P.off_red = take((uint32_t)(N_CONSUMER_WARPS * NM * MT * RED_PAD * 4));
+        off = (off + 1023u) & ~1023u;
+        P.off_stage = off;
+        const int avail = g_max_smem - (int)off - 2048;  // static shared memory of the kernel
+        int stages = avail / (int)stage_bytes;
+        if (stages > 8) stages = 8;
+        if (stages < 3) continue;  // try a finer K-split
+        P.stages = stages;
+        P.splits = splits;
+        int cs = 0;
+        for (int s = 0; s < splits; ++s) {
+            P.chunk_start[s] = cs;
+            const int rem_chunks = n_chunks - cs, rem_splits = splits - s;
+            cs += (rem_chunks + rem_splits - 1) / rem_splits;
+        }
+        P.chunk_start[splits] = n_chunks;
+        P.offsets = offsets;
+        P.row_of = row_of;
+        P.aq = aq;
+        P.ascale = ascale;
+        P.absum = absum;
+        P.out = out;
+        P.out_split_stride = split_stride;
+        P.E = E;
+        P.K = K;
+        P.N = N;
+        P.kb = kb;
+        P.n_chunks = n_chunks;
+        P.MT = MT;
+        P.stage_bytes = stage_bytes;
+        void* sp = nullptr;
+        e = cudaGetSymbolAddress(&sp, g_stream_status);
+        if (e != cudaSuccess) return e;
+        P.status = static_cast<int*>(sp);
+        const size_t smem_bytes = (size_t)off + (size_t)stages * stage_bytes;
+        if (n_splits_out) *n_splits_out = splits;
+        if (dtype == CANDLE_GGML_Q4K) {
+            if (gate_up) return NT == 1 ? launch_one<FmtQ4K, true, 1>(st, P, smem_bytes) : launch_one<FmtQ4K, true, 2>(st, P, smem_bytes);
+            return NT == 1 ? launch_one<FmtQ4K, false, 1>(st, P, smem_bytes) : launch_one<FmtQ4K, false, 2>(st, P, smem_bytes);
+        }
+        if (gate_up) return NT == 1 ? launch_one<FmtQ6K, true, 1>(st, P, smem_bytes) : launch_one<FmtQ6K, true, 2>(st, P, smem_bytes);
+        return NT == 1 ? launch_one<FmtQ6K, false, 1>(st, P, smem_bytes) : launch_one<FmtQ6K, false, 2>(st, P, smem_bytes);
+    }
+    return cudaErrorNotSupported;
+}
+
+cudaError_t read_stream_status(int* out) {
+    return cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int));
+}
+
+}  // namespace cmoe

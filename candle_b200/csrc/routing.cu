@@ -203,8 +203,9 @@ cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t row
 constexpr int COMBINE_THREADS = 256;
 
 __global__ void __launch_bounds__(COMBINE_THREADS)
-combine_kernel(const float* __restrict__ eo, const uint32_t* __restrict__ ids, const float* __restrict__ w,
-               const uint32_t* __restrict__ pair_pos, int k, int d, const float* __restrict__ shared_out,
+combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride, const uint32_t* __restrict__ ids,
+               const float* __restrict__ w, const uint32_t* __restrict__ pair_pos, int k, int d,
+               const float* __restrict__ shared_out, int shared_splits, int64_t shared_split_stride,
                const float* __restrict__ x, const float* __restrict__ gate, float* __restrict__ y) {
     __shared__ float s_red[COMBINE_THREADS / 32];
     __shared__ float s_gate;
@@ -264,7 +265,15 @@ combine_kernel(const float* __restrict__ eo, const uint32_t* __restrict__ ids, c
 #pragma unroll
         for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
             if (r < k) {
-                const float4 v = reinterpret_cast<const float4*>(eo + (int64_t)sp[r] * d)[i];
+                // an expert output may arrive as K-split partials: add them in split order first
+                float4 v = reinterpret_cast<const float4*>(eo + (int64_t)sp[r] * d)[i];
+                for (int s = 1; s < n_splits; ++s) {
+                    const float4 u = reinterpret_cast<const float4*>(eo + s * split_stride + (int64_t)sp[r] * d)[i];
+                    v.x += u.x;
+                    v.y += u.y;
+                    v.z += u.z;
+                    v.w += u.w;
+                }
                 acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, sw[r]));
                 acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, sw[r]));
                 acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, sw[r]));
@@ -272,7 +281,14 @@ combine_kernel(const float* __restrict__ eo, const uint32_t* __restrict__ ids, c
             }
         }
         if (shared_out) {
-            const float4 s = reinterpret_cast<const float4*>(shared_out + t * (int64_t)d)[i];
+            float4 s = reinterpret_cast<const float4*>(shared_out + t * (int64_t)d)[i];
+            for (int q = 1; q < shared_splits; ++q) {
+                const float4 u = reinterpret_cast<const float4*>(shared_out + q * shared_split_stride + t * (int64_t)d)[i];
+                s.x += u.x;
+                s.y += u.y;
+                s.z += u.z;
+                s.w += u.w;
+            }
             acc.x = __fadd_rn(acc.x, __fmul_rn(s.x, g));
             acc.y = __fadd_rn(acc.y, __fmul_rn(s.y, g));
             acc.z = __fadd_rn(acc.z, __fmul_rn(s.z, g));
@@ -282,11 +298,13 @@ combine_kernel(const float* __restrict__ eo, const uint32_t* __restrict__ ids, c
     }
 }
 
-cudaError_t launch_combine(cudaStream_t st, const float* expert_out, const uint32_t* ids, const float* w,
-                           const uint32_t* pair_pos, int64_t T, int k, int d, const float* shared_out,
-                           const float* x, const float* shared_gate, float* y) {
+cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_splits, int64_t split_stride,
+                           const uint32_t* ids, const float* w, const uint32_t* pair_pos, int64_t T, int k, int d,
+                           const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
+                           const float* shared_gate, float* y) {
     if (T == 0) return cudaSuccess;
-    combine_kernel<<<(unsigned)T, COMBINE_THREADS, 0, st>>>(expert_out, ids, w, pair_pos, k, d, shared_out, x,
+    combine_kernel<<<(unsigned)T, COMBINE_THREADS, 0, st>>>(expert_out, n_splits, split_stride, ids, w, pair_pos, k, d,
+                                                            shared_out, shared_splits, shared_split_stride, x,
                                                             shared_gate, y);
     return cudaGetLastError();
 }

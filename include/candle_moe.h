@@ -180,6 +180,12 @@ CANDLE_MOE_API int candle_moe_forward_static(void* stream, const candle_moe_weig
 CANDLE_MOE_API int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,
                                float** topk_w, uint32_t** expert_counts, uint32_t** perm_token);
 
+/* Health word of the device-side kernels.  Every wait inside a kernel (on a copy in flight) has an
+ * iteration limit; a kernel whose wait expired raises bit 0 here and finishes without hanging.
+ * Synchronises the device and returns the accumulated flags in *flags (0 = healthy).
+ * No counterpart in the reference (its kernels do not wait on asynchronous copies). */
+CANDLE_MOE_API int candle_moe_device_status(int32_t* flags);
+
 /* Weight quantization on the device, bit-exact with QTensor::quantize -> GgmlType::from_float for
  * Q8_0 / Q4K / Q6K (k_quants.rs:605-634, 1287-1345, 1675-1744); replaces the CPU round trip of
  * QCudaStorage::quantize (candle-core/src/quantized/cuda.rs:457-478).

@@ -263,6 +263,67 @@ def test_expert_hidden_before_requantization(orc, torch_cuda, name13, name2, row
     assert H.rel_l2(got, hid_ref) < 2e-6 and H.max_rel(got, hid_ref) < 1e-5
 
 
+@pytest.mark.parametrize("name,rows_per_expert,k,n,gate_up", [
+    ("Q4K", [3, 0, 8, 1], 4096, 64, True), ("Q4K", [16, 5], 1024, 48, True), ("Q4K", [37, 2, 9], 2048, 32, True),
+    ("Q4K", [7, 1, 0, 12], 3584, 64, False), ("Q6K", [5, 8, 0, 1], 14336, 64, False), ("Q6K", [16, 23], 2048, 32, False),
+    ("Q6K", [3, 4], 4096, 32, True), ("Q4K", [1], 6144, 128, True), ("Q6K", [9], 16384, 32, False)])
+def test_streaming_form_equals_row_form(orc, torch_cuda, name, rows_per_expert, k, n, gate_up, monkeypatch):
+    """The TMA-ring / tensor-core form and the row-per-warp form compute the same integers; their f32
+    sums differ only in order.  Both are also checked against the oracle matmul."""
+    torch = torch_cuda
+    from candle_b200 import _lib
+    L = _lib.load()
+    dt = getattr(orc, name)
+    E = len(rows_per_expert)
+    rng = np.random.default_rng(k + n + E)
+    P = int(sum(rows_per_expert))
+    x = rng.standard_normal((P, k), dtype=np.float32)
+    wa = [orc.quantize(dt, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)) for _ in range(E)]
+    wb = [orc.quantize(dt, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)) for _ in range(E)]
+    offs_h = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
+    perm_h = rng.permutation(P).astype(np.int32)  # rows gathered through row_of in the gate_up form
+    xd = torch.from_numpy(x).cuda()
+    wad = [torch.from_numpy(w).cuda() for w in wa]
+    wbd = [torch.from_numpy(w).cuda() for w in wb]
+    qs = torch.empty((P, k), dtype=torch.int8, device="cuda")
+    sc = torch.empty((P, k // 256), dtype=torch.float32, device="cuda")
+    bs = torch.empty((P, k // 16), dtype=torch.int16, device="cuda")
+    offs = torch.from_numpy(offs_h).cuda()
+    perm = torch.from_numpy(perm_h).cuda()
+    st = _st(torch)
+    assert L.candle_moe_quantize_act(st, xd.data_ptr(), P, k, dt, qs.data_ptr(), sc.data_ptr(), bs.data_ptr()) == 0
+    pa = (C.c_void_p * E)(*[w.data_ptr() for w in wad])
+    pb = (C.c_void_p * E)(*[w.data_ptr() for w in wbd])
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("CANDLE_MOE_FORCE_ROWS", mode)
+        out = torch.full((P, n), float("nan"), dtype=torch.float32, device="cuda")
+        if gate_up:
+            rc = L.candle_moe_grouped_gate_up(st, pa, pb, dt, E, k, n, offs.data_ptr(), perm.data_ptr(), max(rows_per_expert),
+                                              qs.data_ptr(), sc.data_ptr(), bs.data_ptr(), out.data_ptr())
+        else:
+            rc = L.candle_moe_grouped_down(st, pa, dt, E, n, k, offs.data_ptr(), max(rows_per_expert), qs.data_ptr(),
+                                           sc.data_ptr(), bs.data_ptr(), out.data_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        outs[mode] = out.cpu().numpy()
+    flags = C.c_int32(-1)
+    assert L.candle_moe_device_status(C.byref(flags)) == 0 and flags.value == 0
+    # oracle
+    want = np.empty((P, n), np.float32)
+    for e in range(E):
+        for p in range(offs_h[e], offs_h[e + 1]):
+            row = x[perm_h[p]] if gate_up else x[p]
+            a = orc.matmul(dt, row[None, :], wa[e], n)[0]
+            if gate_up:
+                b = orc.matmul(dt, row[None, :], wb[e], n)[0]
+                a = orc.silu(a) * b
+            want[p] = a
+    for mode in ("0", "1"):
+        assert np.isfinite(outs[mode]).all(), f"mode {mode}: rows not written"
+        assert H.rel_l2(outs[mode], want) < 2e-6 and H.max_rel(outs[mode], want) < 1e-5, f"mode {mode}"
+
+
 # ------------------------------------------------------------------------------------------------
 # the whole block
 # ------------------------------------------------------------------------------------------------
