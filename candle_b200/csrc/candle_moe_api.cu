@@ -10,6 +10,8 @@ using namespace cmoe;
 namespace {
 
 constexpr int MAX_K_SPLITS = 4;  // partial outputs the down product may leave for the combine kernel
+// Only the decode-sized streaming form splits K; larger batches get a single output slot.
+inline int k_split_slots(int64_t T) { return T <= 64 ? MAX_K_SPLITS : 1; }
 
 struct Workspace {
     // routing
@@ -68,7 +70,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     ws.hq = carve<int8_t>(base, off, Tk * ff);
     ws.hs = carve<float>(base, off, Tk * ff / act_block(w->dtype_w2));
     ws.hb = carve<int16_t>(base, off, Tk * ff / 16);
-    ws.eo = carve<float>(base, off, Tk * d * MAX_K_SPLITS);
+    ws.eo = carve<float>(base, off, Tk * d * k_split_slots(T));
     if (w->d_ff_shared > 0) {
         const size_t fs = w->d_ff_shared;
         ws.sh_offsets = carve<uint32_t>(base, off, 2);
@@ -85,7 +87,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
         ws.shq = carve<int8_t>(base, off, (size_t)T * fs);
         ws.shs = carve<float>(base, off, (size_t)T * fs / act_block(w->dtype_shared2));
         ws.shb = carve<int16_t>(base, off, (size_t)T * fs / 16);
-        ws.so = carve<float>(base, off, (size_t)T * d * MAX_K_SPLITS);
+        ws.so = carve<float>(base, off, (size_t)T * d * k_split_slots(T));
     }
     ws.total = align_up(off, 256);
     return ws;
@@ -242,7 +244,7 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
     int eo_splits = 1, so_splits = 1;
     CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
-                                  MAX_K_SPLITS, &eo_splits)));
+                                  k_split_slots(T), &eo_splits)));
 
     const float* shared_out = nullptr;
     if (w->d_ff_shared > 0) {
@@ -258,7 +260,7 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
                                          ws.sxs, ws.sxb, ws.shidden)));
         CM_TRY(rc(launch_quantize_act(st, ws.shidden, T, fs, w->dtype_shared2, ws.shq, ws.shs, ws.shb)));
         CM_TRY(rc(launch_grouped_down(st, s2, w->dtype_shared2, 1, d, fs, ws.sh_offsets, T, ws.shq, ws.shs, ws.shb,
-                                      ws.so, T * (int64_t)d, MAX_K_SPLITS, &so_splits)));
+                                      ws.so, T * (int64_t)d, k_split_slots(T), &so_splits)));
         shared_out = ws.so;
     }
     CM_TRY(rc(launch_combine(st, ws.eo, eo_splits, Tk * d, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out,

@@ -163,7 +163,7 @@ CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* 
  * Rules:
  *   - a call whose scratch need (candle_moe_workspace_bytes(w, T)) exceeds
  *     CANDLE_MOE_STATIC_SCRATCH_BYTES is refused with CANDLE_MOE_E_STATIC_SCRATCH before anything is
- *     enqueued (the Mixtral-8x7B-shaped layer fits up to T = 80 rows);
+ *     enqueued (the Mixtral-8x7B-shaped layer fits up to T = 56 rows);
  *   - the first call on each device looks the array's device address up (a host-side query, no
  *     allocation); make that first call with the device current and before starting any stream
  *     capture;

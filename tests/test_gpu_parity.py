@@ -423,8 +423,8 @@ def test_block_mixtral_layer_decode_sizes(orc, torch_cuda):
 def test_block_prefill_properties_at_full_size(orc, torch_cuda):
     """Config-2 shapes at T = 2048 (too slow for the CPU oracle inside a test): size-independent
     properties instead.  (a) routing is a partition: counts sum to T*k and every token appears k
-    times; (b) row independence: rows copied from a small batch give bit-identical outputs inside
-    the large batch; (c) the small batch itself is checked against the oracle above."""
+    times; (b) row independence: rows copied into a small batch give the same outputs as inside
+    the large batch (to f32 summation order), and a rerun is bit-identical; (c) the small batch itself is checked against the oracle above."""
     torch = torch_cuda
     from candle_b200 import GgmlDType, Mlp, MlpOrMoe, QMatMul, QTensor
     d, ff, E, k, T = 4096, 14336, 8, 2, 2048
@@ -441,5 +441,10 @@ def test_block_prefill_properties_at_full_size(orc, torch_cuda):
     assert int(counts.sum()) == T * k
     assert np.array_equal(np.sort(perm.numpy()), np.repeat(np.arange(T), k))
     assert torch.isfinite(y).all()
+    # the 8-row batch takes the streaming kernels, the 2048-row batch the large-batch form: same
+    # integers, different f32 summation order (the reference's own CUDA path documents such a
+    # difference between its <= 8-row and > 8-row kernels, candle-core/tests/quantized_tests.rs:243-249)
     small = blk.forward(x[100:108].clone())
-    assert torch.equal(small, y[100:108])
+    assert H.rel_l2(small.cpu().numpy(), y[100:108].cpu().numpy()) < 5e-4
+    again = blk.forward(x)
+    assert torch.equal(again, y)  # determinism at full size
