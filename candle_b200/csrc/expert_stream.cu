@@ -31,103 +31,133 @@ constexpr int N_CONSUMER_WARPS = 8;
 constexpr int STREAM_THREADS = 32 * (1 + N_CONSUMER_WARPS);
 constexpr int RED_PAD = 17;           // floats per (warp, matrix, token) in the reduction buffer
 
+// Everything a consumer warp needs besides the weight tile itself.
+struct BlockArgs {
+    const uint8_t* act;      // int8 rows of the token group, [MT][act_stride]
+    const float* act_scale;  // per (token, block) scale d8, [MT][scale_stride]
+    const uint8_t* bs_hi;    // activation block sums split into two byte planes, [MT][bs_stride]
+    const uint8_t* bs_lo;
+    int act_stride, scale_stride, bs_stride;
+    int kblk_local;          // block index inside the resident K-range
+    int ntiles;              // token tiles (of 8) that hold rows; the others are skipped
+};
+
 // ---------------------------------------------------------------------------------------------
 // Q4_K (144 B per 256): f16 d, f16 dmin, 12 B of 6-bit scales/mins, 128 B of nibbles.
+//   value = d * sc_j * q - dmin * m_j  =>  dot = d*d8 * sum_j sc_j (q . a)_j  -  dmin*d8 * sum_j m_j * bsum_j
+// The first sum: one m16n8k32 MMA per 32-element sub-block, scaled by sc_j in int32.
+// The second sum is a [16 x 8] by [8 x 8] integer product per block: the 8 mins of a row are
+// already packed as bytes, the block sums of the activations (|.| <= 4096) are split base 128 into
+// two int8 planes, so it costs two m16n8k16 MMAs per block and token tile.
 // ---------------------------------------------------------------------------------------------
 struct FmtQ4K {
     static constexpr int BLOCK_BYTES = Q4K_BYTES;
     static constexpr int CHUNK_BYTES = KC * Q4K_BYTES;        // 1152
     static constexpr int ROW_STRIDE = CHUNK_BYTES + 16;       // 1168 = 73 * 16: ldmatrix rows hit 8 distinct 16-B lanes
-    static constexpr bool NEEDS_BSUMS = false;
+    static constexpr int BS_PER_BLOCK = 8;                    // one block sum per 32-element sub-block
+    __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[2 * i] + (int)bs16[2 * i + 1]; }
+    __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
+        lo = (uint8_t)(v & 127);
+        hi = (uint8_t)((v >> 7) & 0xff);
+    }
 
-    // One block column (block index `wblk` of the chunk) of a 16-row tile against NT token tiles.
-    template <int NT>
-    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
-                                                 int kblk_local, const float* act_scale, int scale_stride,
-                                                 const uint8_t*, const uint8_t*, int, int lane, float (&f)[NT][4]) {
+    template <int NT, int NM>
+    __device__ static __forceinline__ void block(const uint8_t* const (&tiles)[NM], int wblk, const BlockArgs& A,
+                                                 int lane, float (&f)[NM][NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint8_t* rowA = tile + g * ROW_STRIDE + wblk * BLOCK_BYTES;
-        const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
-        const uint32_t hA = *reinterpret_cast<const uint32_t*>(rowA), hB = *reinterpret_cast<const uint32_t*>(rowB);
-        const float dA = half_bits_to_float((uint16_t)(hA & 0xffff)), mnA = half_bits_to_float((uint16_t)(hA >> 16));
-        const float dB = half_bits_to_float((uint16_t)(hB & 0xffff)), mnB = half_bits_to_float((uint16_t)(hB >> 16));
-        uint32_t scA[2], mA[2], scB[2], mB[2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
-        {
-            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(rowA + 4), s1 = *reinterpret_cast<const uint32_t*>(rowA + 8),
-                           s2 = *reinterpret_cast<const uint32_t*>(rowA + 12);
-            scA[0] = s0 & 0x3f3f3f3fu;
-            mA[0] = s1 & 0x3f3f3f3fu;
-            scA[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
-            mA[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
-        }
-        {
-            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(rowB + 4), s1 = *reinterpret_cast<const uint32_t*>(rowB + 8),
-                           s2 = *reinterpret_cast<const uint32_t*>(rowB + 12);
-            scB[0] = s0 & 0x3f3f3f3fu;
-            mB[0] = s1 & 0x3f3f3f3fu;
-            scB[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
-            mB[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
-        }
-        int c[NT][4], cm[NT][4];
+        float dA[NM], mnA[NM], dB[NM], mnB[NM];
+        uint32_t scA[NM][2], mA[NM][2], scB[NM][2], mB[NM][2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
+        const uint8_t* a_addr[NM];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int m = 0; m < NM; ++m) {
+            const uint8_t* rowA = tiles[m] + g * ROW_STRIDE + wblk * BLOCK_BYTES;
+            const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
+            const uint4 ha = *reinterpret_cast<const uint4*>(rowA), hb = *reinterpret_cast<const uint4*>(rowB);
+            dA[m] = half_bits_to_float((uint16_t)(ha.x & 0xffff));
+            mnA[m] = half_bits_to_float((uint16_t)(ha.x >> 16));
+            dB[m] = half_bits_to_float((uint16_t)(hb.x & 0xffff));
+            mnB[m] = half_bits_to_float((uint16_t)(hb.x >> 16));
+            scA[m][0] = ha.y & 0x3f3f3f3fu;
+            mA[m][0] = ha.z & 0x3f3f3f3fu;
+            scA[m][1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
+            mA[m][1] = ((ha.w >> 4) & 0x0f0f0f0fu) | (((ha.z >> 6) & 0x03030303u) << 4);
+            scB[m][0] = hb.y & 0x3f3f3f3fu;
+            mB[m][0] = hb.z & 0x3f3f3f3fu;
+            scB[m][1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
+            mB[m][1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
+            // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
+            a_addr[m] = tiles[m] + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
+        }
+        int c[NM][NT][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[nt][i] = cm[nt][i] = 0;
-
-        // ldmatrix lane addressing: A matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of the group
-        const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + wblk * BLOCK_BYTES + 16 +
-                                16 * (lane >> 4);
-        const uint8_t* b_addr = act + (lane & 7) * act_stride + kblk_local * 256 + 16 * (lane >> 3);
+        for (int m = 0; m < NM; ++m)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) c[m][nt][i] = 0;
+        const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
-            uint32_t a[4];
-            ldmatrix_x4(a, a_addr + 32 * grp);
-            uint32_t alo[4], ahi[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                alo[i] = a[i] & 0x0f0f0f0fu;
-                ahi[i] = (a[i] >> 4) & 0x0f0f0f0fu;
-            }
             const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
-            const int sAl = (scA[jl >> 2] >> (8 * (jl & 3))) & 0xff, sAh = (scA[jh >> 2] >> (8 * (jh & 3))) & 0xff;
-            const int sBl = (scB[jl >> 2] >> (8 * (jl & 3))) & 0xff, sBh = (scB[jh >> 2] >> (8 * (jh & 3))) & 0xff;
-            const uint32_t mAl = ((mA[jl >> 2] >> (8 * (jl & 3))) & 0xff) * 0x01010101u;
-            const uint32_t mAh = ((mA[jh >> 2] >> (8 * (jh & 3))) & 0xff) * 0x01010101u;
-            const uint32_t mBl = ((mB[jl >> 2] >> (8 * (jl & 3))) & 0xff) * 0x01010101u;
-            const uint32_t mBh = ((mB[jh >> 2] >> (8 * (jh & 3))) & 0xff) * 0x01010101u;
-            const uint32_t aml[4] = {mAl, mBl, mAl, mBl}, amh[4] = {mAh, mBh, mAh, mBh};
+            uint32_t alo[NM][4], ahi[NM][4];
+            int sAl[NM], sAh[NM], sBl[NM], sBh[NM];
+#pragma unroll
+            for (int m = 0; m < NM; ++m) {
+                uint32_t a[4];
+                ldmatrix_x4(a, a_addr[m] + 32 * grp);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    alo[m][i] = a[i] & 0x0f0f0f0fu;
+                    ahi[m][i] = (a[i] >> 4) & 0x0f0f0f0fu;
+                }
+                sAl[m] = byte_u(scA[m][jl >> 2], jl & 3);
+                sAh[m] = byte_u(scA[m][jh >> 2], jh & 3);
+                sBl[m] = byte_u(scB[m][jl >> 2], jl & 3);
+                sBh[m] = byte_u(scB[m][jh >> 2], jh & 3);
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                uint32_t b[4];
-                ldmatrix_x4(b, b_addr + nt * 8 * act_stride + 64 * grp);
-                int p[4] = {0, 0, 0, 0};
-                mma_s8_k32(p, alo, b[0], b[1]);
-                c[nt][0] += sAl * p[0];
-                c[nt][1] += sAl * p[1];
-                c[nt][2] += sBl * p[2];
-                c[nt][3] += sBl * p[3];
-                int q[4] = {0, 0, 0, 0};
-                mma_s8_k32(q, ahi, b[2], b[3]);
-                c[nt][0] += sAh * q[0];
-                c[nt][1] += sAh * q[1];
-                c[nt][2] += sBh * q[2];
-                c[nt][3] += sBh * q[3];
-                mma_s8_k32(cm[nt], aml, b[0], b[1]);  // sum_i min_j * q8_i, the reference's bsums term
-                mma_s8_k32(cm[nt], amh, b[2], b[3]);
+                if (nt < A.ntiles) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
+#pragma unroll
+                    for (int m = 0; m < NM; ++m) {
+                        int p[4], q[4];
+                        mma_s8_k32_z(p, alo[m], b[0], b[1]);
+                        mma_s8_k32_z(q, ahi[m], b[2], b[3]);
+                        c[m][nt][0] += sAl[m] * p[0] + sAh[m] * q[0];
+                        c[m][nt][1] += sAl[m] * p[1] + sAh[m] * q[1];
+                        c[m][nt][2] += sBl[m] * p[2] + sBh[m] * q[2];
+                        c[m][nt][3] += sBl[m] * p[3] + sBh[m] * q[3];
+                    }
+                }
             }
         }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const float d8a = act_scale[(nt * 8 + 2 * t) * scale_stride + kblk_local];
-            const float d8b = act_scale[(nt * 8 + 2 * t + 1) * scale_stride + kblk_local];
-            f[nt][0] = fmaf(d8a * dA, (float)c[nt][0], f[nt][0]);
-            f[nt][0] = fmaf(-(d8a * mnA), (float)cm[nt][0], f[nt][0]);
-            f[nt][1] = fmaf(d8b * dA, (float)c[nt][1], f[nt][1]);
-            f[nt][1] = fmaf(-(d8b * mnA), (float)cm[nt][1], f[nt][1]);
-            f[nt][2] = fmaf(d8a * dB, (float)c[nt][2], f[nt][2]);
-            f[nt][2] = fmaf(-(d8a * mnB), (float)cm[nt][2], f[nt][2]);
-            f[nt][3] = fmaf(d8b * dB, (float)c[nt][3], f[nt][3]);
-            f[nt][3] = fmaf(-(d8b * mnB), (float)cm[nt][3], f[nt][3]);
+            if (nt < A.ntiles) {
+                const int boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 8 + 4 * (t & 1);
+                const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
+                const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
+                const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
+                const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
+#pragma unroll
+                for (int m = 0; m < NM; ++m) {
+                    // A operand of the min product: k = sub-block id, lanes t = 0,1 carry the 8 packed mins
+                    const uint32_t a0 = t == 0 ? mA[m][0] : (t == 1 ? mA[m][1] : 0u);
+                    const uint32_t a1 = t == 0 ? mB[m][0] : (t == 1 ? mB[m][1] : 0u);
+                    int ch[4], cl[4];
+                    mma_s8_k16_z(ch, a0, a1, bh);
+                    mma_s8_k16_z(cl, a0, a1, bl);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float d8 = (i & 1) ? d8b : d8a;
+                        const float dw = (i >> 1) ? dB[m] : dA[m], mw = (i >> 1) ? mnB[m] : mnA[m];
+                        f[m][nt][i] = fmaf(d8 * dw, (float)c[m][nt][i], f[m][nt][i]);
+                        f[m][nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[m][nt][i]);
+                    }
+                }
+            }
         }
     }
 };
@@ -138,14 +168,19 @@ struct FmtQ4K {
 // 16-bit shared loads depending on the (warp-uniform) parity of the block index.
 // The quants are used unsigned (0..63); the reference's "- 32" becomes
 //   - 32 * sum_j scale_j * bsum_j(token),
-// itself a 16x16 by 16x8 integer product done with two more MMAs on the activation block sums
-// split into a signed high byte and an unsigned low byte.
+// itself a [16 x 16] by [16 x 8] integer product done with two more MMAs on the activation block
+// sums split into a signed high byte and an unsigned low byte.
 // ---------------------------------------------------------------------------------------------
 struct FmtQ6K {
     static constexpr int BLOCK_BYTES = Q6K_BYTES;
     static constexpr int CHUNK_BYTES = KC * Q6K_BYTES;        // 1680 (8 blocks keep 16-byte alignment)
     static constexpr int ROW_STRIDE = CHUNK_BYTES;            // 420 words, 420 % 32 = 4: rows g, words t never share a bank
-    static constexpr bool NEEDS_BSUMS = true;
+    static constexpr int BS_PER_BLOCK = 16;                   // one block sum per 16-element sub-block
+    __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[i]; }
+    __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
+        lo = (uint8_t)(v & 0xff);
+        hi = (uint8_t)((v >> 8) & 0xff);  // arithmetic shift: signed high byte
+    }
 
     template <bool ODD>
     __device__ static __forceinline__ uint32_t ld32(const uint8_t* p) {
@@ -157,9 +192,7 @@ struct FmtQ6K {
     }
 
     template <int NT, bool ODD>
-    __device__ static __forceinline__ void block_impl(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
-                                                      int kblk_local, const float* act_scale, int scale_stride,
-                                                      const uint8_t* bs_hi, const uint8_t* bs_lo, int bs_stride, int lane,
+    __device__ static __forceinline__ void block_impl(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
                                                       float (&f)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
         const uint8_t* rowA = tile + g * ROW_STRIDE + wblk * BLOCK_BYTES;
@@ -177,7 +210,7 @@ struct FmtQ6K {
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
-        const uint8_t* b_addr = act + (lane & 7) * act_stride + kblk_local * 256 + 16 * (lane >> 3);
+        const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -206,36 +239,38 @@ struct FmtQ6K {
                     qlB[xo][lr] = ld32<ODD>(rowB + 64 * h + 32 * xo + 16 * lr + 4 * t);
                 }
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {  // quarter: elements 128h + 32x .. +31 = sub-blocks 8h + 2x, 8h + 2x + 1
-                uint32_t aA[2], aB[2];
+            for (int y = 0; y < 2; ++y) {  // 64 elements = quarters 2y, 2y+1 = four 16-element sub-blocks
+                uint32_t aA[4], aB[4];  // [2*(x&1) + lr]
+                int sA[4], sB[4];
 #pragma unroll
-                for (int lr = 0; lr < 2; ++lr) {
-                    const uint32_t la = (x >> 1) ? (qlA[x & 1][lr] >> 4) : qlA[x & 1][lr];
-                    const uint32_t lb = (x >> 1) ? (qlB[x & 1][lr] >> 4) : qlB[x & 1][lr];
-                    aA[lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
-                    aB[lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
+                for (int xo = 0; xo < 2; ++xo) {
+                    const int x = 2 * y + xo;  // quarter: elements 128h + 32x .. +31; low nibbles for x < 2
+#pragma unroll
+                    for (int lr = 0; lr < 2; ++lr) {
+                        const uint32_t la = (x >> 1) ? (qlA[x & 1][lr] >> 4) : qlA[x & 1][lr];
+                        const uint32_t lb = (x >> 1) ? (qlB[x & 1][lr] >> 4) : qlB[x & 1][lr];
+                        aA[2 * xo + lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
+                        aB[2 * xo + lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
+                        const int j = 8 * h + 2 * x + lr;  // sub-block id
+                        sA[2 * xo + lr] = byte_s(scA[j >> 2], j & 3);
+                        sB[2 * xo + lr] = byte_s(scB[j >> 2], j & 3);
+                    }
                 }
-                const int j0 = 8 * h + 2 * x;  // sub-block of lr = 0; lr = 1 is j0 + 1
-                const int sA0 = (int)(int8_t)(scA[j0 >> 2] >> (8 * (j0 & 3))), sA1 = (int)(int8_t)(scA[(j0 + 1) >> 2] >> (8 * ((j0 + 1) & 3)));
-                const int sB0 = (int)(int8_t)(scB[j0 >> 2] >> (8 * (j0 & 3))), sB1 = (int)(int8_t)(scB[(j0 + 1) >> 2] >> (8 * ((j0 + 1) & 3)));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    // the four 16-element sub-blocks of 64 elements come from one ldmatrix.x4; quarters x = 2y, 2y+1 share it
-                    uint32_t b[4];
-                    ldmatrix_x4(b, b_addr + nt * 8 * act_stride + 128 * h + 64 * (x >> 1));
-                    const uint32_t b0 = b[2 * (x & 1)], b1 = b[2 * (x & 1) + 1];
-                    int p[4] = {0, 0, 0, 0};
-                    mma_s8_k16(p, aA[0], aB[0], b0);
-                    c[nt][0] += sA0 * p[0];
-                    c[nt][1] += sA0 * p[1];
-                    c[nt][2] += sB0 * p[2];
-                    c[nt][3] += sB0 * p[3];
-                    int q[4] = {0, 0, 0, 0};
-                    mma_s8_k16(q, aA[1], aB[1], b1);
-                    c[nt][0] += sA1 * q[0];
-                    c[nt][1] += sA1 * q[1];
-                    c[nt][2] += sB1 * q[2];
-                    c[nt][3] += sB1 * q[3];
+                    if (nt < A.ntiles) {
+                        uint32_t b[4];  // int8 activations of the four sub-blocks
+                        ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
+#pragma unroll
+                        for (int s4 = 0; s4 < 4; ++s4) {
+                            int p[4];
+                            mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
+                            c[nt][0] += sA[s4] * p[0];
+                            c[nt][1] += sA[s4] * p[1];
+                            c[nt][2] += sB[s4] * p[2];
+                            c[nt][3] += sB[s4] * p[3];
+                        }
+                    }
                 }
             }
         }
@@ -243,34 +278,35 @@ struct FmtQ6K {
         const uint32_t sa = ld32<ODD>(rowA + 192 + 4 * t), sb = ld32<ODD>(rowB + 192 + 4 * t);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const int tok = nt * 8 + g;
-            const uint32_t bh = *reinterpret_cast<const uint32_t*>(bs_hi + tok * bs_stride + kblk_local * 16 + 4 * t);
-            const uint32_t bl = *reinterpret_cast<const uint32_t*>(bs_lo + tok * bs_stride + kblk_local * 16 + 4 * t);
-            int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
-            mma_s8_k16(ch, sa, sb, bh);
-            mma_s8u8_k16(cl, sa, sb, bl);
-            const float d8a = act_scale[(nt * 8 + 2 * t) * scale_stride + kblk_local];
-            const float d8b = act_scale[(nt * 8 + 2 * t + 1) * scale_stride + kblk_local];
+            if (nt < A.ntiles) {
+                const int boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 16 + 4 * t;
+                const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
+                const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
+                int ch[4], cl[4];
+                mma_s8_k16_z(ch, sa, sb, bh);
+                mma_s8u8_k16_z(cl, sa, sb, bl);
+                const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
+                const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
-                const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
-                f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+                for (int i = 0; i < 4; ++i) {
+                    const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
+                    const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
+                    f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+                }
             }
         }
     }
 
-    template <int NT>
-    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const uint8_t* act, int act_stride,
-                                                 int kblk_local, const float* act_scale, int scale_stride,
-                                                 const uint8_t* bs_hi, const uint8_t* bs_lo, int bs_stride, int lane,
-                                                 float (&f)[NT][4]) {
-        if (wblk & 1)
-            block_impl<NT, true>(tile, wblk, act, act_stride, kblk_local, act_scale, scale_stride, bs_hi, bs_lo, bs_stride,
-                                 lane, f);
-        else
-            block_impl<NT, false>(tile, wblk, act, act_stride, kblk_local, act_scale, scale_stride, bs_hi, bs_lo,
-                                  bs_stride, lane, f);
+    template <int NT, int NM>
+    __device__ static __forceinline__ void block(const uint8_t* const (&tiles)[NM], int wblk, const BlockArgs& A,
+                                                 int lane, float (&f)[NM][NT][4]) {
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            if (wblk & 1)
+                block_impl<NT, true>(tiles[m], wblk, A, lane, f[m]);
+            else
+                block_impl<NT, false>(tiles[m], wblk, A, lane, f[m]);
+        }
     }
 };
 
@@ -475,21 +511,33 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
                     }
                     act_scale[j * P.scale_stride + b] = sv;
                 }
-                if (F::NEEDS_BSUMS) {
-                    for (int idx = ctid; idx < MT * nblk * 16; idx += 32 * N_CONSUMER_WARPS) {
-                        const int j = idx / (nblk * 16), b = idx - j * nblk * 16;
+                {
+                    const int per_row = nblk * F::BS_PER_BLOCK;
+                    for (int idx = ctid; idx < MT * per_row; idx += 32 * N_CONSUMER_WARPS) {
+                        const int j = idx / per_row, b = idx - j * per_row;
                         int v = 0;
                         if (p_base + j < p_end) {
                             const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
-                            v = P.absum[row * (P.K / 16) + blk0 * 16 + b];
+                            v = F::bs_value(P.absum + row * (P.K / 16) + blk0 * 16, b);
                         }
-                        bs_lo[j * P.bs_stride + b] = (uint8_t)(v & 0xff);
-                        bs_hi[j * P.bs_stride + b] = (uint8_t)((v >> 8) & 0xff);  // arithmetic shift: signed high byte
+                        uint8_t hi, lo;
+                        F::bs_split(v, hi, lo);
+                        bs_lo[j * P.bs_stride + b] = lo;
+                        bs_hi[j * P.bs_stride + b] = hi;
                     }
                 }
                 consumer_sync();
             }
 
+            BlockArgs bargs;
+            bargs.act = act;
+            bargs.act_scale = act_scale;
+            bargs.bs_hi = bs_hi;
+            bargs.bs_lo = bs_lo;
+            bargs.act_stride = P.act_stride;
+            bargs.scale_stride = P.scale_stride;
+            bargs.bs_stride = P.bs_stride;
+            bargs.ntiles = (int)(p_end - p_base + 7) / 8;
             float f[NM][NT][4];
 #pragma unroll
             for (int m = 0; m < NM; ++m)
@@ -504,10 +552,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
                 const int blk = ch * KC + cw;
                 if (ok && blk < P.kb) {
                     const uint8_t* st = stage0 + (size_t)s * P.stage_bytes;
+                    const uint8_t* tiles[NM];
 #pragma unroll
-                    for (int m = 0; m < NM; ++m)
-                        F::template block<NT>(st + m * TILE_ROWS * F::ROW_STRIDE, cw, act, P.act_stride, blk - blk0,
-                                              act_scale, P.scale_stride, bs_hi, bs_lo, P.bs_stride, lane, f[m]);
+                    for (int m = 0; m < NM; ++m) tiles[m] = st + m * TILE_ROWS * F::ROW_STRIDE;
+                    bargs.kblk_local = blk - blk0;
+                    F::template block<NT, NM>(tiles, cw, bargs, lane, f);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -599,13 +648,11 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
     const int n_chunks = (kb + KC - 1) / KC;
     const int row_stride = dtype == CANDLE_GGML_Q4K ? FmtQ4K::ROW_STRIDE : FmtQ6K::ROW_STRIDE;
     const uint32_t stage_bytes = (uint32_t)(NM * TILE_ROWS * row_stride);
-    const bool bsums = dtype == CANDLE_GGML_Q6K;
+    const int bs_per_block = dtype == CANDLE_GGML_Q4K ? FmtQ4K::BS_PER_BLOCK : FmtQ6K::BS_PER_BLOCK;
 
     StreamParams P{};
     P.wa = wa;
     P.wb = wb;
-    int status_ok = 0;
-    (void)status_ok;
     for (int splits = 1; splits <= max_splits; ++splits) {
         if (splits > n_chunks) break;
         if (gate_up && splits > 1) break;  // the gate needs the full sum before silu
@@ -620,11 +667,12 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
         };
         P.act_stride = ks_blocks * 256 + 16;
         P.scale_stride = ks_blocks;
-        P.bs_stride = ks_blocks * 16 + 16;
+        P.bs_stride = ks_blocks * bs_per_block + 16;
+        while ((P.bs_stride / 4) % 8 != 4) P.bs_stride += 4;  // token rows g = 0..7 land in distinct banks
         P.off_act = take((uint32_t)MT * P.act_stride);
         P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
-        P.off_bs_hi = bsums ? take((uint32_t)MT * P.bs_stride) : 0;
-        P.off_bs_lo = bsums ? take((uint32_t)MT * P.bs_stride) : 0;
+        P.off_bs_hi = take((uint32_t)MT * P.bs_stride);
+        P.off_bs_lo = take((uint32_t)MT * P.bs_stride);
         P.off_red = take((uint32_t)(N_CONSUMER_WARPS * NM * MT * RED_PAD * 4));
         off = (off + 1023u) & ~1023u;
         P.off_stage = off;
