@@ -3,19 +3,23 @@
 // The work is HBM-bound: every active expert's weight blocks are read once and the arithmetic per
 // byte is tiny.  Design:
 //   * persistent CTAs (one per SM), each owning a CONTIGUOUS, cost-balanced range of work items;
-//     an item is a tile of 16 weight rows of one expert over one K-range ("split");
+//     an item is a tile of 16 weight rows of one expert over one K-range ("split"); for gate_up the
+//     16 rows are 8 rows of W1 and the same 8 rows of W3, so one MMA tile yields both factors of
+//     silu(w1 x) * (w3 x);
 //   * warp 0 is the producer: one `cp.async.bulk` (TMA, no tensor map needed: a row chunk is
 //     contiguous) per weight row per stage into a padded, bank-conflict-free shared-memory ring,
-//     completion counted on an mbarrier; several stages (>= 75 KB) are always in flight per SM;
-//   * warps 1..8 are consumers: each takes one 256-element block column of the stage, unpacks the
-//     quants in registers straight from `ldmatrix` fragments and multiplies them with the int8
-//     activations (resident in shared memory for the expert's rows) on the tensor cores with
-//     `mma.sync m16n8k32 / m16n8k16` (s8 x s8 -> s32).  Sub-block scales are applied to the exact
-//     integer partial sums, the per-block f16 scales in f32 -- the same integers as the reference's
-//     vec_dot (candle-core/src/quantized/k_quants.rs:1205-1285, 1616-1673), different f32 order;
-//   * the 8 K-slices of a tile meet in shared memory in a fixed order; gate_up applies
-//     silu(w1 x) * (w3 x) there and stores f32, down stores one partial per K-split which the
-//     combine kernel adds in split order (deterministic, no atomics).
+//     completion counted on an mbarrier.  Copies are >= 1.7 KB (measured: below ~2 KB the per-copy
+//     cost, not HBM, limits a bulk-copy ring) and >= 70 KB are always in flight per SM;
+//   * the other CW warps are consumers: each takes one 256-element block column of the stage,
+//     unpacks the quants in registers straight from `ldmatrix` fragments and multiplies them with
+//     the int8 activations (resident in shared memory for the expert's rows) on the tensor cores
+//     with `mma.sync m16n8k32 / m16n8k16` (s8 x s8 -> s32).  Sub-block scales are applied to the
+//     exact integer partial sums, the per-block f16 scales in f32 -- the same integers as the
+//     reference's vec_dot (candle-core/src/quantized/k_quants.rs:1205-1285, 1616-1673), different
+//     f32 order;
+//   * the CW K-slices of a tile meet in shared memory in a fixed order; gate_up applies the SiLU
+//     gate there and stores f32, down stores one partial per K-split which the combine kernel adds
+//     in split order (deterministic, no atomics).
 // Every wait on an mbarrier is bounded; on expiry the CTA raises a flag in `status`, stops waiting
 // and runs its loops to the end so that no thread is left behind at a barrier.
 #include "common.cuh"
@@ -25,11 +29,8 @@ namespace cmoe {
 
 namespace {
 
-constexpr int TILE_ROWS = 16;
-constexpr int KC = 8;                 // 256-element blocks per stage chunk (one per consumer warp)
-constexpr int N_CONSUMER_WARPS = 8;
-constexpr int STREAM_THREADS = 32 * (1 + N_CONSUMER_WARPS);
-constexpr int RED_PAD = 17;           // floats per (warp, matrix, token) in the reduction buffer
+constexpr int TILE_ROWS = 16;         // weight rows per stage (gate_up: 8 rows of W1 followed by the same 8 rows of W3)
+constexpr int RED_PAD = 17;           // floats per (warp, token) in the reduction buffer
 
 // Everything a consumer warp needs besides the weight tile itself.
 struct BlockArgs {
@@ -52,87 +53,72 @@ struct BlockArgs {
 // ---------------------------------------------------------------------------------------------
 struct FmtQ4K {
     static constexpr int BLOCK_BYTES = Q4K_BYTES;
-    static constexpr int CHUNK_BYTES = KC * Q4K_BYTES;        // 1152
-    static constexpr int ROW_STRIDE = CHUNK_BYTES + 16;       // 1168 = 73 * 16: ldmatrix rows hit 8 distinct 16-B lanes
-    static constexpr int BS_PER_BLOCK = 8;                    // one block sum per 32-element sub-block
+    static constexpr int BS_PER_BLOCK = 8;  // one block sum per 32-element sub-block
+    // shared-memory row stride for CW blocks per row: an odd multiple of 16 bytes, so the 8 rows of
+    // an ldmatrix land in 8 distinct 16-byte bank groups
+    __host__ __device__ static constexpr int row_stride(int cw) { return cw * Q4K_BYTES + 16; }
     __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[2 * i] + (int)bs16[2 * i + 1]; }
     __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
         lo = (uint8_t)(v & 127);
         hi = (uint8_t)((v >> 7) & 0xff);
     }
 
-    template <int NT, int NM>
-    __device__ static __forceinline__ void block(const uint8_t* const (&tiles)[NM], int wblk, const BlockArgs& A,
-                                                 int lane, float (&f)[NM][NT][4]) {
+    template <int NT, int RS>
+    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
+                                                 float (&f)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        float dA[NM], mnA[NM], dB[NM], mnB[NM];
-        uint32_t scA[NM][2], mA[NM][2], scB[NM][2], mB[NM][2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
-        const uint8_t* a_addr[NM];
+        const uint8_t* rowA = tile + g * RS + wblk * BLOCK_BYTES;
+        const uint8_t* rowB = rowA + 8 * RS;
+        const uint4 ha = *reinterpret_cast<const uint4*>(rowA), hb = *reinterpret_cast<const uint4*>(rowB);
+        const float dA = half_bits_to_float((uint16_t)(ha.x & 0xffff)), mnA = half_bits_to_float((uint16_t)(ha.x >> 16));
+        const float dB = half_bits_to_float((uint16_t)(hb.x & 0xffff)), mnB = half_bits_to_float((uint16_t)(hb.x >> 16));
+        uint32_t scA[2], mA[2], scB[2], mB[2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
+        scA[0] = ha.y & 0x3f3f3f3fu;
+        mA[0] = ha.z & 0x3f3f3f3fu;
+        scA[1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
+        mA[1] = ((ha.w >> 4) & 0x0f0f0f0fu) | (((ha.z >> 6) & 0x03030303u) << 4);
+        scB[0] = hb.y & 0x3f3f3f3fu;
+        mB[0] = hb.z & 0x3f3f3f3fu;
+        scB[1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
+        mB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
+        int c[NT][4];
 #pragma unroll
-        for (int m = 0; m < NM; ++m) {
-            const uint8_t* rowA = tiles[m] + g * ROW_STRIDE + wblk * BLOCK_BYTES;
-            const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
-            const uint4 ha = *reinterpret_cast<const uint4*>(rowA), hb = *reinterpret_cast<const uint4*>(rowB);
-            dA[m] = half_bits_to_float((uint16_t)(ha.x & 0xffff));
-            mnA[m] = half_bits_to_float((uint16_t)(ha.x >> 16));
-            dB[m] = half_bits_to_float((uint16_t)(hb.x & 0xffff));
-            mnB[m] = half_bits_to_float((uint16_t)(hb.x >> 16));
-            scA[m][0] = ha.y & 0x3f3f3f3fu;
-            mA[m][0] = ha.z & 0x3f3f3f3fu;
-            scA[m][1] = (ha.w & 0x0f0f0f0fu) | (((ha.y >> 6) & 0x03030303u) << 4);
-            mA[m][1] = ((ha.w >> 4) & 0x0f0f0f0fu) | (((ha.z >> 6) & 0x03030303u) << 4);
-            scB[m][0] = hb.y & 0x3f3f3f3fu;
-            mB[m][0] = hb.z & 0x3f3f3f3fu;
-            scB[m][1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
-            mB[m][1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
-            // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
-            a_addr[m] = tiles[m] + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROW_STRIDE + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
-        }
-        int c[NM][NT][4];
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int m = 0; m < NM; ++m)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) c[m][nt][i] = 0;
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+        // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
+        const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
         const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
             const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
-            uint32_t alo[NM][4], ahi[NM][4];
-            int sAl[NM], sAh[NM], sBl[NM], sBh[NM];
+            uint32_t a[4], alo[4], ahi[4];
+            ldmatrix_x4(a, a_addr + 32 * grp);
 #pragma unroll
-            for (int m = 0; m < NM; ++m) {
-                uint32_t a[4];
-                ldmatrix_x4(a, a_addr[m] + 32 * grp);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    alo[m][i] = a[i] & 0x0f0f0f0fu;
-                    ahi[m][i] = (a[i] >> 4) & 0x0f0f0f0fu;
-                }
-                sAl[m] = byte_u(scA[m][jl >> 2], jl & 3);
-                sAh[m] = byte_u(scA[m][jh >> 2], jh & 3);
-                sBl[m] = byte_u(scB[m][jl >> 2], jl & 3);
-                sBh[m] = byte_u(scB[m][jh >> 2], jh & 3);
+            for (int i = 0; i < 4; ++i) {
+                alo[i] = a[i] & 0x0f0f0f0fu;
+                ahi[i] = (a[i] >> 4) & 0x0f0f0f0fu;
             }
+            const int sAl = byte_u(scA[jl >> 2], jl & 3), sAh = byte_u(scA[jh >> 2], jh & 3);
+            const int sBl = byte_u(scB[jl >> 2], jl & 3), sBh = byte_u(scB[jh >> 2], jh & 3);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 if (nt < A.ntiles) {
                     uint32_t b[4];
                     ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
-#pragma unroll
-                    for (int m = 0; m < NM; ++m) {
-                        int p[4], q[4];
-                        mma_s8_k32_z(p, alo[m], b[0], b[1]);
-                        mma_s8_k32_z(q, ahi[m], b[2], b[3]);
-                        c[m][nt][0] += sAl[m] * p[0] + sAh[m] * q[0];
-                        c[m][nt][1] += sAl[m] * p[1] + sAh[m] * q[1];
-                        c[m][nt][2] += sBl[m] * p[2] + sBh[m] * q[2];
-                        c[m][nt][3] += sBl[m] * p[3] + sBh[m] * q[3];
-                    }
+                    int p[4], q[4];
+                    mma_s8_k32_z(p, alo, b[0], b[1]);
+                    mma_s8_k32_z(q, ahi, b[2], b[3]);
+                    c[nt][0] += sAl * p[0] + sAh * q[0];
+                    c[nt][1] += sAl * p[1] + sAh * q[1];
+                    c[nt][2] += sBl * p[2] + sBh * q[2];
+                    c[nt][3] += sBl * p[3] + sBh * q[3];
                 }
             }
         }
+        // A operand of the min product: k = sub-block id, lanes t = 0, 1 carry the 8 packed mins
+        const uint32_t am0 = t == 0 ? mA[0] : (t == 1 ? mA[1] : 0u);
+        const uint32_t am1 = t == 0 ? mB[0] : (t == 1 ? mB[1] : 0u);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             if (nt < A.ntiles) {
@@ -141,21 +127,15 @@ struct FmtQ4K {
                 const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
                 const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
                 const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
+                int ch[4], cl[4];
+                mma_s8_k16_z(ch, am0, am1, bh);
+                mma_s8_k16_z(cl, am0, am1, bl);
 #pragma unroll
-                for (int m = 0; m < NM; ++m) {
-                    // A operand of the min product: k = sub-block id, lanes t = 0,1 carry the 8 packed mins
-                    const uint32_t a0 = t == 0 ? mA[m][0] : (t == 1 ? mA[m][1] : 0u);
-                    const uint32_t a1 = t == 0 ? mB[m][0] : (t == 1 ? mB[m][1] : 0u);
-                    int ch[4], cl[4];
-                    mma_s8_k16_z(ch, a0, a1, bh);
-                    mma_s8_k16_z(cl, a0, a1, bl);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float d8 = (i & 1) ? d8b : d8a;
-                        const float dw = (i >> 1) ? dB[m] : dA[m], mw = (i >> 1) ? mnB[m] : mnA[m];
-                        f[m][nt][i] = fmaf(d8 * dw, (float)c[m][nt][i], f[m][nt][i]);
-                        f[m][nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[m][nt][i]);
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const float d8 = (i & 1) ? d8b : d8a;
+                    const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
+                    f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
+                    f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
                 }
             }
         }
@@ -173,9 +153,11 @@ struct FmtQ4K {
 // ---------------------------------------------------------------------------------------------
 struct FmtQ6K {
     static constexpr int BLOCK_BYTES = Q6K_BYTES;
-    static constexpr int CHUNK_BYTES = KC * Q6K_BYTES;        // 1680 (8 blocks keep 16-byte alignment)
-    static constexpr int ROW_STRIDE = CHUNK_BYTES;            // 420 words, 420 % 32 = 4: rows g, words t never share a bank
-    static constexpr int BS_PER_BLOCK = 16;                   // one block sum per 16-element sub-block
+    static constexpr int BS_PER_BLOCK = 16;  // one block sum per 16-element sub-block
+    // stride in words must be 4 mod 8 so that rows g = 0..7 at word t = 0..3 never share a bank
+    __host__ __device__ static constexpr int row_stride(int cw) {
+        return ((cw * Q6K_BYTES / 4) % 8 == 4) ? cw * Q6K_BYTES : cw * Q6K_BYTES + 16;
+    }
     __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[i]; }
     __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
         lo = (uint8_t)(v & 0xff);
@@ -191,12 +173,12 @@ struct FmtQ6K {
         return *reinterpret_cast<const uint32_t*>(p);
     }
 
-    template <int NT, bool ODD>
+    template <int NT, int RS, bool ODD>
     __device__ static __forceinline__ void block_impl(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
                                                       float (&f)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint8_t* rowA = tile + g * ROW_STRIDE + wblk * BLOCK_BYTES;
-        const uint8_t* rowB = rowA + 8 * ROW_STRIDE;
+        const uint8_t* rowA = tile + g * RS + wblk * BLOCK_BYTES;
+        const uint8_t* rowB = rowA + 8 * RS;
         const float dA = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowA + 208));
         const float dB = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowB + 208));
         uint32_t scA[4], scB[4];  // 16 int8 scales per row
@@ -297,16 +279,13 @@ struct FmtQ6K {
         }
     }
 
-    template <int NT, int NM>
-    __device__ static __forceinline__ void block(const uint8_t* const (&tiles)[NM], int wblk, const BlockArgs& A,
-                                                 int lane, float (&f)[NM][NT][4]) {
-#pragma unroll
-        for (int m = 0; m < NM; ++m) {
-            if (wblk & 1)
-                block_impl<NT, true>(tiles[m], wblk, A, lane, f[m]);
-            else
-                block_impl<NT, false>(tiles[m], wblk, A, lane, f[m]);
-        }
+    template <int NT, int RS>
+    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
+                                                 float (&f)[NT][4]) {
+        if ((wblk & 1) || (RS & 3))
+            block_impl<NT, RS, true>(tile, wblk, A, lane, f);
+        else
+            block_impl<NT, RS, false>(tile, wblk, A, lane, f);
     }
 };
 
@@ -325,6 +304,7 @@ struct StreamParams {
     int* status;
     int64_t out_split_stride;  // elements between the partial outputs of consecutive K-splits
     int E, K, N, kb, n_chunks, splits, MT, stages;
+    int tile_n;                // output rows per item: 16, or 8 for gate_up
     int chunk_start[5];        // split s covers chunks [chunk_start[s], chunk_start[s+1])
     int act_stride;            // bytes per token row of the resident activations
     int scale_stride;          // floats per token row of the resident activation scales
@@ -344,7 +324,7 @@ struct Walker {
     int gidx, e, grp, ng_e, split, tile;
 
     __device__ Walker(const StreamParams& p, const uint32_t* offsets_sm, int cta, int n_cta) : P(p), offs(offsets_sm) {
-        tiles = P.N / TILE_ROWS;
+        tiles = P.N / P.tile_n;
         int gtot = 0;
         for (int i = 0; i < P.E; ++i) gtot += (int)((offs[i + 1] - offs[i] + P.MT - 1) / P.MT);
         const long long gcost = (long long)tiles * P.n_chunks;
@@ -413,14 +393,18 @@ struct Walker {
     }
 };
 
-template <class F, bool GATE_UP, int NT>
-__global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const __grid_constant__ StreamParams P) {
+// CW = consumer warps = 256-element blocks per stage chunk.
+template <class F, bool GATE_UP, int NT, int CW>
+__global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const __grid_constant__ StreamParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t full_bar[8], empty_bar[8];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ int s_abort;
-    constexpr int NM = GATE_UP ? 2 : 1;
     constexpr int MT = 8 * NT;
+    constexpr int RS = F::row_stride(CW);
+    constexpr int CHUNK_BYTES = CW * F::BLOCK_BYTES;
+    constexpr int N_CONS = 32 * CW;
+    constexpr int TILE_N = GATE_UP ? 8 : 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     for (int i = threadIdx.x; i <= P.E; i += blockDim.x) s_offs[i] = P.offsets[i];
@@ -428,7 +412,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
         s_abort = 0;
         for (int s = 0; s < P.stages; ++s) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], N_CONSUMER_WARPS);
+            mbar_init(&empty_bar[s], CW);
         }
         fence_barrier_init();
     }
@@ -440,25 +424,29 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
     uint8_t* stage0 = smem + P.off_stage;
 
     if (warp == 0) {
-        // ================= producer =================
+        // ================= producer: lane r < 16 copies weight row r of the tile =================
         uint32_t it = 0;
         for (; wk.valid(); wk.next()) {
             const WorkItem w = wk.item();
-            const int m = lane >> 4, r = lane & 15;
-            const bool active = m < NM;
-            const uint8_t* src_row = (m == 0 ? P.wa.p[w.e] : P.wb.p[w.e]);
-            if (active) src_row += (size_t)(w.tile * TILE_ROWS + r) * row_bytes;
+            const bool active = lane < TILE_ROWS;
+            const uint8_t* src_row = nullptr;
+            if (active) {
+                if (GATE_UP)
+                    src_row = (lane < 8 ? P.wa.p[w.e] : P.wb.p[w.e]) + (size_t)(w.tile * TILE_N + (lane & 7)) * row_bytes;
+                else
+                    src_row = P.wa.p[w.e] + (size_t)(w.tile * TILE_N + lane) * row_bytes;
+            }
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
                 const uint32_t ph = (it / P.stages) & 1;
                 if (it >= (uint32_t)P.stages) mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
-                const int blocks = min(KC, P.kb - ch * KC);
+                const int blocks = min(CW, P.kb - ch * CW);
                 const uint32_t bytes = (uint32_t)blocks * F::BLOCK_BYTES;
-                if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * TILE_ROWS * NM);
+                if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * TILE_ROWS);
                 __syncwarp();
                 if (active && !*abort_flag)
-                    bulk_g2s(stage0 + (size_t)s * P.stage_bytes + (m * TILE_ROWS + r) * F::ROW_STRIDE,
-                             src_row + (size_t)ch * F::CHUNK_BYTES, bytes, &full_bar[s]);
+                    bulk_g2s(stage0 + (size_t)s * P.stage_bytes + lane * RS, src_row + (size_t)ch * CHUNK_BYTES, bytes,
+                             &full_bar[s]);
             }
         }
         // do not leave while copies into this CTA's shared memory may still be in flight
@@ -471,29 +459,30 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
         }
     } else {
         // ================= consumers =================
-        const int cw = warp - 1;                         // K-slice of this warp inside a chunk
-        const int ctid = threadIdx.x - 32;               // 0..255
+        const int cw = warp - 1;            // K-slice of this warp inside a chunk
+        const int ctid = threadIdx.x - 32;  // 0 .. N_CONS-1
         uint8_t* act = smem + P.off_act;
         float* act_scale = reinterpret_cast<float*>(smem + P.off_scale);
         uint8_t* bs_hi = smem + P.off_bs_hi;
         uint8_t* bs_lo = smem + P.off_bs_lo;
-        float* red = reinterpret_cast<float*>(smem + P.off_red);
-        uint32_t it = 0;
+        float* red0 = reinterpret_cast<float*>(smem + P.off_red);
+        constexpr int RED_FLOATS = CW * MT * RED_PAD;
+        uint32_t it = 0, n_item = 0;
         int cur_e = -1, cur_grp = -1, cur_split = -1;
-        for (; wk.valid(); wk.next()) {
+        for (; wk.valid(); wk.next(), ++n_item) {
             const WorkItem w = wk.item();
             const uint32_t p_base = s_offs[w.e] + (uint32_t)w.grp * MT;
             const uint32_t p_end = min(s_offs[w.e + 1], p_base + MT);
-            const int blk0 = P.chunk_start[w.split] * KC;                      // first block of this split
-            const int nblk = min(P.kb, P.chunk_start[w.split + 1] * KC) - blk0;  // blocks in this split
+            const int blk0 = P.chunk_start[w.split] * CW;                      // first block of this split
+            const int nblk = min(P.kb, P.chunk_start[w.split + 1] * CW) - blk0;  // blocks in this split
             if (w.e != cur_e || w.grp != cur_grp || w.split != cur_split) {
-                // ---- make the int8 rows (and scales / block sums) of this token group resident ----
+                // ---- make the int8 rows, scales and block sums of this token group resident ----
                 cur_e = w.e;
                 cur_grp = w.grp;
                 cur_split = w.split;
-                consumer_sync();
+                consumer_sync(N_CONS);
                 const int vec_per_row = nblk * 16;  // 16-byte vectors per token row
-                for (int idx = ctid; idx < MT * vec_per_row; idx += 32 * N_CONSUMER_WARPS) {
+                for (int idx = ctid; idx < MT * vec_per_row; idx += N_CONS) {
                     const int j = idx / vec_per_row, v = idx - j * vec_per_row;
                     int4 val = make_int4(0, 0, 0, 0);
                     if (p_base + j < p_end) {
@@ -502,7 +491,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
                     }
                     *reinterpret_cast<int4*>(act + j * P.act_stride + 16 * v) = val;
                 }
-                for (int idx = ctid; idx < MT * nblk; idx += 32 * N_CONSUMER_WARPS) {
+                for (int idx = ctid; idx < MT * nblk; idx += N_CONS) {
                     const int j = idx / nblk, b = idx - j * nblk;
                     float sv = 0.f;
                     if (p_base + j < p_end) {
@@ -513,7 +502,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
                 }
                 {
                     const int per_row = nblk * F::BS_PER_BLOCK;
-                    for (int idx = ctid; idx < MT * per_row; idx += 32 * N_CONSUMER_WARPS) {
+                    for (int idx = ctid; idx < MT * per_row; idx += N_CONS) {
                         const int j = idx / per_row, b = idx - j * per_row;
                         int v = 0;
                         if (p_base + j < p_end) {
@@ -526,7 +515,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
                         bs_hi[j * P.bs_stride + b] = hi;
                     }
                 }
-                consumer_sync();
+                consumer_sync(N_CONS);
             }
 
             BlockArgs bargs;
@@ -538,61 +527,54 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) expert_stream_kernel(const 
             bargs.scale_stride = P.scale_stride;
             bargs.bs_stride = P.bs_stride;
             bargs.ntiles = (int)(p_end - p_base + 7) / 8;
-            float f[NM][NT][4];
+            float f[NT][4];
 #pragma unroll
-            for (int m = 0; m < NM; ++m)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) f[m][nt][i] = 0.f;
+                for (int i = 0; i < 4; ++i) f[nt][i] = 0.f;
 
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
                 const bool ok = mbar_wait(&full_bar[s], (it / P.stages) & 1, abort_flag);
-                const int blk = ch * KC + cw;
+                const int blk = ch * CW + cw;
                 if (ok && blk < P.kb) {
-                    const uint8_t* st = stage0 + (size_t)s * P.stage_bytes;
-                    const uint8_t* tiles[NM];
-#pragma unroll
-                    for (int m = 0; m < NM; ++m) tiles[m] = st + m * TILE_ROWS * F::ROW_STRIDE;
                     bargs.kblk_local = blk - blk0;
-                    F::template block<NT, NM>(tiles, cw, bargs, lane, f);
+                    F::template block<NT, RS>(stage0 + (size_t)s * P.stage_bytes, cw, bargs, lane, f);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
             }
 
-            // ---- the 8 K-slices of the tile meet in shared memory, fixed order ----
+            // ---- the CW K-slices of the tile meet in shared memory (two buffers, one barrier per
+            // item: a buffer is rewritten only after every warp has passed the next item's barrier) ----
+            float* red = red0 + (n_item & 1) * RED_FLOATS;
             {
                 const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-                for (int m = 0; m < NM; ++m)
+                for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int tok = nt * 8 + 2 * t + (i & 1), row = g + 8 * (i >> 1);
-                            red[((cw * NM + m) * MT + tok) * RED_PAD + row] = f[m][nt][i];
-                        }
+                    for (int i = 0; i < 4; ++i) {
+                        const int tok = nt * 8 + 2 * t + (i & 1), row = g + 8 * (i >> 1);
+                        red[(cw * MT + tok) * RED_PAD + row] = f[nt][i];
+                    }
             }
-            consumer_sync();
-            for (int idx = ctid; idx < MT * TILE_ROWS; idx += 32 * N_CONSUMER_WARPS) {
-                const int tok = idx / TILE_ROWS, row = idx - tok * TILE_ROWS;
+            consumer_sync(N_CONS);
+            for (int idx = ctid; idx < MT * TILE_N; idx += N_CONS) {
+                const int tok = idx / TILE_N, row = idx - tok * TILE_N;
                 if (p_base + tok < p_end) {
                     float va = 0.f, vb = 0.f;
 #pragma unroll
-                    for (int sw = 0; sw < N_CONSUMER_WARPS; ++sw) {
-                        va += red[((sw * NM + 0) * MT + tok) * RED_PAD + row];
-                        if (GATE_UP) vb += red[((sw * NM + 1) * MT + tok) * RED_PAD + row];
+                    for (int sw = 0; sw < CW; ++sw) {
+                        va += red[(sw * MT + tok) * RED_PAD + row];
+                        if (GATE_UP) vb += red[(sw * MT + tok) * RED_PAD + row + 8];
                     }
-                    const int64_t o = (int64_t)(p_base + tok) * P.N + w.tile * TILE_ROWS + row;
+                    const int64_t o = (int64_t)(p_base + tok) * P.N + w.tile * TILE_N + row;
                     if (GATE_UP)
                         P.out[o] = silu_f(va) * vb;
                     else
                         P.out[(int64_t)w.split * P.out_split_stride + o] = va;
                 }
             }
-            consumer_sync();
         }
     }
     __syncthreads();
@@ -617,13 +599,19 @@ cudaError_t device_limits() {
     return cudaSuccess;
 }
 
-template <class F, bool GATE_UP, int NT>
+template <class F, bool GATE_UP, int NT, int CW>
 cudaError_t launch_one(cudaStream_t st, const StreamParams& P, size_t smem_bytes) {
-    auto kfn = expert_stream_kernel<F, GATE_UP, NT>;
+    auto kfn = expert_stream_kernel<F, GATE_UP, NT, CW>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (e != cudaSuccess) return e;
-    kfn<<<g_num_sms, STREAM_THREADS, smem_bytes, st>>>(P);
+    kfn<<<g_num_sms, 32 * (1 + CW), smem_bytes, st>>>(P);
     return cudaGetLastError();
+}
+
+template <class F, int CW>
+cudaError_t launch_nt(cudaStream_t st, bool gate_up, int NT, const StreamParams& P, size_t smem_bytes) {
+    if (gate_up) return NT == 1 ? launch_one<F, true, 1, CW>(st, P, smem_bytes) : launch_one<F, true, 2, CW>(st, P, smem_bytes);
+    return NT == 1 ? launch_one<F, false, 1, CW>(st, P, smem_bytes) : launch_one<F, false, 2, CW>(st, P, smem_bytes);
 }
 
 }  // namespace
@@ -638,16 +626,19 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
                                  int max_splits) {
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return cudaErrorNotSupported;
-    if (N % TILE_ROWS != 0 || K % 256 != 0) return cudaErrorNotSupported;
+    const int tile_n = gate_up ? 8 : 16;
+    if (N % tile_n != 0 || K % 256 != 0) return cudaErrorNotSupported;
     const int kb = K / 256;
-    if (dtype == CANDLE_GGML_Q6K && kb % KC != 0) return cudaErrorNotSupported;  // rows must stay 16-byte aligned
+    if (dtype == CANDLE_GGML_Q6K && kb % 8 != 0) return cudaErrorNotSupported;  // rows must stay 16-byte aligned
     cudaError_t e = device_limits();
     if (e != cudaSuccess) return e;
     const int NT = max_rows_per_expert <= 8 ? 1 : 2;
-    const int MT = 8 * NT, NM = gate_up ? 2 : 1;
-    const int n_chunks = (kb + KC - 1) / KC;
-    const int row_stride = dtype == CANDLE_GGML_Q4K ? FmtQ4K::ROW_STRIDE : FmtQ6K::ROW_STRIDE;
-    const uint32_t stage_bytes = (uint32_t)(NM * TILE_ROWS * row_stride);
+    const int MT = 8 * NT;
+    // blocks per stage chunk = consumer warps: full 4096-element rows for Q4_K (2.3 KB copies)
+    const int CW = (dtype == CANDLE_GGML_Q4K && kb >= 16) ? 16 : 8;
+    const int n_chunks = (kb + CW - 1) / CW;
+    const int row_stride = dtype == CANDLE_GGML_Q4K ? FmtQ4K::row_stride(CW) : FmtQ6K::row_stride(CW);
+    const uint32_t stage_bytes = (uint32_t)(TILE_ROWS * row_stride);
     const int bs_per_block = dtype == CANDLE_GGML_Q4K ? FmtQ4K::BS_PER_BLOCK : FmtQ6K::BS_PER_BLOCK;
 
     StreamParams P{};
@@ -657,7 +648,7 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
         if (splits > n_chunks) break;
         if (gate_up && splits > 1) break;  // the gate needs the full sum before silu
         const int cps = (n_chunks + splits - 1) / splits;  // chunks of the largest split
-        const int ks_blocks = min(cps * KC, kb);
+        const int ks_blocks = min(cps * CW, kb);
         uint32_t off = 0;
         auto take = [&](uint32_t bytes) {
             off = (off + 127u) & ~127u;
@@ -673,10 +664,10 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
         P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
         P.off_bs_hi = take((uint32_t)MT * P.bs_stride);
         P.off_bs_lo = take((uint32_t)MT * P.bs_stride);
-        P.off_red = take((uint32_t)(N_CONSUMER_WARPS * NM * MT * RED_PAD * 4));
+        P.off_red = take((uint32_t)(2 * CW * MT * RED_PAD * 4));
         off = (off + 1023u) & ~1023u;
         P.off_stage = off;
-        const int avail = g_max_smem - (int)off - 2048;  // static shared memory of the kernel
+        const int avail = g_max_smem - (int)off - 2048;  // minus the static shared memory of the kernel
         int stages = avail / (int)stage_bytes;
         if (stages > 8) stages = 8;
         if (stages < 3) continue;  // try a finer K-split
@@ -702,6 +693,7 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
         P.kb = kb;
         P.n_chunks = n_chunks;
         P.MT = MT;
+        P.tile_n = tile_n;
         P.stage_bytes = stage_bytes;
         void* sp = nullptr;
         e = cudaGetSymbolAddress(&sp, g_stream_status);
@@ -709,12 +701,9 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
         P.status = static_cast<int*>(sp);
         const size_t smem_bytes = (size_t)off + (size_t)stages * stage_bytes;
         if (n_splits_out) *n_splits_out = splits;
-        if (dtype == CANDLE_GGML_Q4K) {
-            if (gate_up) return NT == 1 ? launch_one<FmtQ4K, true, 1>(st, P, smem_bytes) : launch_one<FmtQ4K, true, 2>(st, P, smem_bytes);
-            return NT == 1 ? launch_one<FmtQ4K, false, 1>(st, P, smem_bytes) : launch_one<FmtQ4K, false, 2>(st, P, smem_bytes);
-        }
-        if (gate_up) return NT == 1 ? launch_one<FmtQ6K, true, 1>(st, P, smem_bytes) : launch_one<FmtQ6K, true, 2>(st, P, smem_bytes);
-        return NT == 1 ? launch_one<FmtQ6K, false, 1>(st, P, smem_bytes) : launch_one<FmtQ6K, false, 2>(st, P, smem_bytes);
+        if (dtype == CANDLE_GGML_Q4K)
+            return CW == 16 ? launch_nt<FmtQ4K, 16>(st, gate_up, NT, P, smem_bytes) : launch_nt<FmtQ4K, 8>(st, gate_up, NT, P, smem_bytes);
+        return launch_nt<FmtQ6K, 8>(st, gate_up, NT, P, smem_bytes);
     }
     return cudaErrorNotSupported;
 }
