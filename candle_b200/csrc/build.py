@@ -22,6 +22,8 @@ SOURCES = {
     "expert_rows.cu": [],
     "expert_stream.cu": [],
 }
+# extra nvcc flags for local experiments, e.g. CANDLE_MOE_NVCC_FLAGS="-DCMOE_STREAM_TIMING"
+EXTRA = os.environ.get("CANDLE_MOE_NVCC_FLAGS", "").split()
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
           "-Xcompiler", "-fvisibility=hidden"]
 
@@ -48,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src, extra in SOURCES.items():
         obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc(), *COMMON, *extra, "-c", os.path.join(HERE, src), "-o", obj]
+        cmd = [nvcc(), *COMMON, *EXTRA, *extra, "-c", os.path.join(HERE, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -27,6 +27,10 @@
 
 namespace cmoe {
 
+#ifdef CMOE_STREAM_TIMING
+__device__ long long g_stream_timing[32];  // cycle counters of one probed CTA (local experiments only)
+#endif
+
 namespace {
 
 constexpr int TILE_ROWS = 16;         // weight rows per stage (gate_up: 8 rows of W1 followed by the same 8 rows of W3)
@@ -81,38 +85,48 @@ struct FmtQ4K {
         mB[0] = hb.z & 0x3f3f3f3fu;
         scB[1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
         mB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
-        int c[NT][4];
+        // per-row, per-sub-block float scales d * sc_j (exact: 11-bit f16 mantissa times 6 bits); the
+        // high-nibble operand is used as 16 * q, so its scale carries the 1/16
+        float SA[8], SB[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float k16 = (j & 1) ? 0.0625f : 1.0f;
+            SA[j] = byte_to_float(scA[j >> 2], j & 3) * (dA * k16);
+            SB[j] = byte_to_float(scB[j >> 2], j & 3) * (dB * k16);
+        }
+        float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+            for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
         // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
         const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
         const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
-            const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
             uint32_t a[4], alo[4], ahi[4];
             ldmatrix_x4(a, a_addr + 32 * grp);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                alo[i] = a[i] & 0x0f0f0f0fu;
-                ahi[i] = (a[i] >> 4) & 0x0f0f0f0fu;
+                alo[i] = a[i] & 0x0f0f0f0fu;  // q of sub-block 2*grp
+                ahi[i] = a[i] & 0xf0f0f0f0u;  // 16 * q of sub-block 2*grp + 1 (unsigned operand)
             }
-            const int sAl = byte_u(scA[jl >> 2], jl & 3), sAh = byte_u(scA[jh >> 2], jh & 3);
-            const int sBl = byte_u(scB[jl >> 2], jl & 3), sBh = byte_u(scB[jh >> 2], jh & 3);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 if (nt < A.ntiles) {
                     uint32_t b[4];
                     ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
                     int p[4], q[4];
-                    mma_s8_k32_z(p, alo, b[0], b[1]);
-                    mma_s8_k32_z(q, ahi, b[2], b[3]);
-                    c[nt][0] += sAl * p[0] + sAh * q[0];
-                    c[nt][1] += sAl * p[1] + sAh * q[1];
-                    c[nt][2] += sBl * p[2] + sBh * q[2];
-                    c[nt][3] += sBl * p[3] + sBh * q[3];
+                    mma_s8_k32_m(p, alo, b[0], b[1]);
+                    mma_u8s8_k32_m(q, ahi, b[2], b[3]);
+                    acc[nt][0] = fmaf(unmagic(p[0]), SA[2 * grp], acc[nt][0]);
+                    acc[nt][1] = fmaf(unmagic(p[1]), SA[2 * grp], acc[nt][1]);
+                    acc[nt][2] = fmaf(unmagic(p[2]), SB[2 * grp], acc[nt][2]);
+                    acc[nt][3] = fmaf(unmagic(p[3]), SB[2 * grp], acc[nt][3]);
+                    acc[nt][0] = fmaf(unmagic(q[0]), SA[2 * grp + 1], acc[nt][0]);
+                    acc[nt][1] = fmaf(unmagic(q[1]), SA[2 * grp + 1], acc[nt][1]);
+                    acc[nt][2] = fmaf(unmagic(q[2]), SB[2 * grp + 1], acc[nt][2]);
+                    acc[nt][3] = fmaf(unmagic(q[3]), SB[2 * grp + 1], acc[nt][3]);
                 }
             }
         }
@@ -128,14 +142,15 @@ struct FmtQ4K {
                 const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
                 const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
                 int ch[4], cl[4];
-                mma_s8_k16_z(ch, am0, am1, bh);
-                mma_s8_k16_z(cl, am0, am1, bl);
+                mma_s8_k16_m(ch, am0, am1, bh);
+                mma_s8_k16_m(cl, am0, am1, bl);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float d8 = (i & 1) ? d8b : d8a;
-                    const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
-                    f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
-                    f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
+                    const float mw = (i >> 1) ? mnB : mnA;
+                    const float msum = fmaf(128.0f, unmagic(ch[i]), unmagic(cl[i]));  // sum_j min_j * bsum_j, exact
+                    f[nt][i] = fmaf(d8, acc[nt][i], f[nt][i]);
+                    f[nt][i] = fmaf(-(d8 * mw), msum, f[nt][i]);
                 }
             }
         }
@@ -187,11 +202,19 @@ struct FmtQ6K {
             scA[i] = ld32<ODD>(rowA + 192 + 4 * i);
             scB[i] = ld32<ODD>(rowB + 192 + 4 * i);
         }
-        int c[NT][4];
+        // float(scale) for the 16 sub-blocks of both rows: bias the int8 by 128, drop the byte into
+        // the mantissa of 2^23, subtract (exact small integers)
+        float SA[16], SB[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            SA[j] = __uint_as_float(__byte_perm(scA[j >> 2] ^ 0x80808080u, 0x4B000000u, 0x7650 | (j & 3))) - 8388736.0f;
+            SB[j] = __uint_as_float(__byte_perm(scB[j >> 2] ^ 0x80808080u, 0x4B000000u, 0x7650 | (j & 3))) - 8388736.0f;
+        }
+        float c[NT][4];  // sum_j scale_j * (q . a)_j as exact small-integer floats
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0.f;
         const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 
 #pragma unroll
@@ -223,7 +246,6 @@ struct FmtQ6K {
 #pragma unroll
             for (int y = 0; y < 2; ++y) {  // 64 elements = quarters 2y, 2y+1 = four 16-element sub-blocks
                 uint32_t aA[4], aB[4];  // [2*(x&1) + lr]
-                int sA[4], sB[4];
 #pragma unroll
                 for (int xo = 0; xo < 2; ++xo) {
                     const int x = 2 * y + xo;  // quarter: elements 128h + 32x .. +31; low nibbles for x < 2
@@ -233,9 +255,6 @@ struct FmtQ6K {
                         const uint32_t lb = (x >> 1) ? (qlB[x & 1][lr] >> 4) : qlB[x & 1][lr];
                         aA[2 * xo + lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
                         aB[2 * xo + lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
-                        const int j = 8 * h + 2 * x + lr;  // sub-block id
-                        sA[2 * xo + lr] = byte_s(scA[j >> 2], j & 3);
-                        sB[2 * xo + lr] = byte_s(scB[j >> 2], j & 3);
                     }
                 }
 #pragma unroll
@@ -245,12 +264,13 @@ struct FmtQ6K {
                         ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
 #pragma unroll
                         for (int s4 = 0; s4 < 4; ++s4) {
+                            const int j = 8 * h + 4 * y + s4;  // sub-block id: 16 consecutive elements
                             int p[4];
-                            mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
-                            c[nt][0] += sA[s4] * p[0];
-                            c[nt][1] += sA[s4] * p[1];
-                            c[nt][2] += sB[s4] * p[2];
-                            c[nt][3] += sB[s4] * p[3];
+                            mma_s8_k16_m(p, aA[s4], aB[s4], b[s4]);
+                            c[nt][0] = fmaf(unmagic(p[0]), SA[j], c[nt][0]);
+                            c[nt][1] = fmaf(unmagic(p[1]), SA[j], c[nt][1]);
+                            c[nt][2] = fmaf(unmagic(p[2]), SB[j], c[nt][2]);
+                            c[nt][3] = fmaf(unmagic(p[3]), SB[j], c[nt][3]);
                         }
                     }
                 }
@@ -265,15 +285,16 @@ struct FmtQ6K {
                 const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
                 const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
                 int ch[4], cl[4];
-                mma_s8_k16_z(ch, sa, sb, bh);
-                mma_s8u8_k16_z(cl, sa, sb, bl);
+                mma_s8_k16_m(ch, sa, sb, bh);
+                mma_s8u8_k16_m(cl, sa, sb, bl);
                 const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
                 const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
+                    const float corr = fmaf(256.0f, unmagic(ch[i]), unmagic(cl[i]));  // sum_j scale_j * bsum_j
+                    const float isum = fmaf(-32.0f, corr, c[nt][i]);
                     const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
-                    f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+                    f[nt][i] = fmaf(dd, isum, f[nt][i]);
                 }
             }
         }
@@ -394,12 +415,21 @@ struct Walker {
 };
 
 // CW = consumer warps = 256-element blocks per stage chunk.
+#ifdef CMOE_STREAM_TIMING
+#define TMARK(var) const long long var = clock64()
+#define TADD(slot, a, b) do { if (tprobe) tacc[slot] += (b) - (a); } while (0)
+#else
+#define TMARK(var)
+#define TADD(slot, a, b)
+#endif
+
 template <class F, bool GATE_UP, int NT, int CW>
 __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const __grid_constant__ StreamParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint64_t full_bar[8], empty_bar[8];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ int s_abort;
+    __shared__ int s_rows[16];  // activation row of each token of the resident group (-1: none)
     constexpr int MT = 8 * NT;
     constexpr int RS = F::row_stride(CW);
     constexpr int CHUNK_BYTES = CW * F::BLOCK_BYTES;
@@ -419,6 +449,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
     __syncthreads();
     volatile int* abort_flag = &s_abort;
 
+#ifdef CMOE_STREAM_TIMING
+    const bool tprobe = blockIdx.x == 40 && lane == 0 && (warp == 0 || warp == 3);
+    long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long t_begin = clock64();
+#endif
     Walker wk(P, s_offs, blockIdx.x, gridDim.x);
     const size_t row_bytes = (size_t)P.kb * F::BLOCK_BYTES;
     uint8_t* stage0 = smem + P.off_stage;
@@ -439,7 +474,10 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
                 const uint32_t ph = (it / P.stages) & 1;
+                TMARK(tp0);
                 if (it >= (uint32_t)P.stages) mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
+                TMARK(tp1);
+                TADD(0, tp0, tp1);
                 const int blocks = min(CW, P.kb - ch * CW);
                 const uint32_t bytes = (uint32_t)blocks * F::BLOCK_BYTES;
                 if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * TILE_ROWS);
@@ -480,35 +518,33 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                 cur_e = w.e;
                 cur_grp = w.grp;
                 cur_split = w.split;
+                TMARK(tq0);
+                consumer_sync(N_CONS);
+                if (ctid < MT) {
+                    const uint32_t pp = p_base + ctid;
+                    s_rows[ctid] = pp < p_end ? (P.row_of ? (int)P.row_of[pp] : (int)pp) : -1;
+                }
                 consumer_sync(N_CONS);
                 const int vec_per_row = nblk * 16;  // 16-byte vectors per token row
+#pragma unroll 4
                 for (int idx = ctid; idx < MT * vec_per_row; idx += N_CONS) {
                     const int j = idx / vec_per_row, v = idx - j * vec_per_row;
+                    const int row = s_rows[j];
                     int4 val = make_int4(0, 0, 0, 0);
-                    if (p_base + j < p_end) {
-                        const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
-                        val = *reinterpret_cast<const int4*>(P.aq + row * P.K + (int64_t)blk0 * 256 + 16 * v);
-                    }
+                    if (row >= 0) val = *reinterpret_cast<const int4*>(P.aq + (int64_t)row * P.K + (int64_t)blk0 * 256 + 16 * v);
                     *reinterpret_cast<int4*>(act + j * P.act_stride + 16 * v) = val;
                 }
                 for (int idx = ctid; idx < MT * nblk; idx += N_CONS) {
                     const int j = idx / nblk, b = idx - j * nblk;
-                    float sv = 0.f;
-                    if (p_base + j < p_end) {
-                        const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
-                        sv = P.ascale[row * P.kb + blk0 + b];
-                    }
-                    act_scale[j * P.scale_stride + b] = sv;
+                    const int row = s_rows[j];
+                    act_scale[j * P.scale_stride + b] = row >= 0 ? P.ascale[(int64_t)row * P.kb + blk0 + b] : 0.f;
                 }
                 {
                     const int per_row = nblk * F::BS_PER_BLOCK;
                     for (int idx = ctid; idx < MT * per_row; idx += N_CONS) {
                         const int j = idx / per_row, b = idx - j * per_row;
-                        int v = 0;
-                        if (p_base + j < p_end) {
-                            const int64_t row = P.row_of ? (int64_t)P.row_of[p_base + j] : (int64_t)(p_base + j);
-                            v = F::bs_value(P.absum + row * (P.K / 16) + blk0 * 16, b);
-                        }
+                        const int row = s_rows[j];
+                        const int v = row >= 0 ? F::bs_value(P.absum + (int64_t)row * (P.K / 16) + blk0 * 16, b) : 0;
                         uint8_t hi, lo;
                         F::bs_split(v, hi, lo);
                         bs_lo[j * P.bs_stride + b] = lo;
@@ -516,6 +552,8 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                     }
                 }
                 consumer_sync(N_CONS);
+                TMARK(tq1);
+                TADD(1, tq0, tq1);
             }
 
             BlockArgs bargs;
@@ -535,7 +573,10 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
 
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
+                TMARK(tc0);
                 const bool ok = mbar_wait(&full_bar[s], (it / P.stages) & 1, abort_flag);
+                TMARK(tc1);
+                TADD(2, tc0, tc1);
                 const int blk = ch * CW + cw;
                 if (ok && blk < P.kb) {
                     bargs.kblk_local = blk - blk0;
@@ -543,7 +584,10 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
+                TMARK(tc2);
+                TADD(3, tc1, tc2);
             }
+            TMARK(tr0);
 
             // ---- the CW K-slices of the tile meet in shared memory (two buffers, one barrier per
             // item: a buffer is rewritten only after every warp has passed the next item's barrier) ----
@@ -559,15 +603,26 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                     }
             }
             consumer_sync(N_CONS);
-            for (int idx = ctid; idx < MT * TILE_N; idx += N_CONS) {
-                const int tok = idx / TILE_N, row = idx - tok * TILE_N;
-                if (p_base + tok < p_end) {
-                    float va = 0.f, vb = 0.f;
+            TMARK(tr1);
+            TADD(4, tr0, tr1);
+            // four threads per output: each adds a quarter of the K-slices, two shuffles finish the sum
+            for (int idx = ctid; idx < MT * TILE_N * 4; idx += N_CONS) {
+                const int o4 = idx >> 2, part = idx & 3;
+                const int tok = o4 / TILE_N, row = o4 - tok * TILE_N;
+                float va = 0.f, vb = 0.f;
 #pragma unroll
-                    for (int sw = 0; sw < CW; ++sw) {
-                        va += red[(sw * MT + tok) * RED_PAD + row];
-                        if (GATE_UP) vb += red[(sw * MT + tok) * RED_PAD + row + 8];
-                    }
+                for (int sw = 0; sw < CW / 4; ++sw) {
+                    const int slice = part * (CW / 4) + sw;
+                    va += red[(slice * MT + tok) * RED_PAD + row];
+                    if (GATE_UP) vb += red[(slice * MT + tok) * RED_PAD + row + 8];
+                }
+                va += __shfl_xor_sync(0xffffffffu, va, 1);
+                va += __shfl_xor_sync(0xffffffffu, va, 2);
+                if (GATE_UP) {
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 2);
+                }
+                if (part == 0 && p_base + tok < p_end) {
                     const int64_t o = (int64_t)(p_base + tok) * P.N + w.tile * TILE_N + row;
                     if (GATE_UP)
                         P.out[o] = silu_f(va) * vb;
@@ -575,8 +630,20 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                         P.out[(int64_t)w.split * P.out_split_stride + o] = va;
                 }
             }
+            TMARK(tr2);
+            TADD(5, tr1, tr2);
+#ifdef CMOE_STREAM_TIMING
+            if (tprobe) tacc[6] += 1;
+#endif
         }
     }
+#ifdef CMOE_STREAM_TIMING
+    if (tprobe) {
+        const int base = warp == 0 ? 0 : 16;
+        for (int i = 0; i < 8; ++i) g_stream_timing[base + i] = tacc[i];
+        g_stream_timing[base + 8] = clock64() - t_begin;
+    }
+#endif
     __syncthreads();
     if (threadIdx.x == 0 && s_abort) atomicOr(P.status, 1);
 }
@@ -617,6 +684,11 @@ cudaError_t launch_nt(cudaStream_t st, bool gate_up, int NT, const StreamParams&
 }  // namespace
 
 __device__ int g_stream_status = 0;
+#ifdef CMOE_STREAM_TIMING
+extern "C" __attribute__((visibility("default"))) int candle_moe_debug_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_stream_timing, sizeof(long long) * 32);
+}
+#endif
 
 // Plans and launches the streaming kernel; returns cudaErrorNotSupported when the shape is outside
 // what the streaming form takes (the caller then uses the row-per-warp form).

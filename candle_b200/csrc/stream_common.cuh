@@ -89,6 +89,37 @@ __device__ __forceinline__ void mma_s8u8_k16_z(int (&d)[4], uint32_t a0, uint32_
                  : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(0));
 }
+// Integer partial sums leave the tensor core as floats: the accumulator starts at the bit pattern
+// of 1.5 * 2^23, so `start + dot` re-read as a float is 12582912 + dot exactly (|dot| < 2^22),
+// and one FADD recovers float(dot).  Scaling then runs on the FP32 pipe instead of integer
+// multiplies, which are several times slower on this part.
+constexpr int MAGIC_I = 0x4B400000;
+constexpr float MAGIC_F = 12582912.0f;
+__device__ __forceinline__ void mma_s8_k32_m(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(MAGIC_I));
+}
+__device__ __forceinline__ void mma_u8s8_k32_m(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(MAGIC_I));
+}
+__device__ __forceinline__ void mma_s8_k16_m(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(MAGIC_I));
+}
+__device__ __forceinline__ void mma_s8u8_k16_m(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(MAGIC_I));
+}
+__device__ __forceinline__ float unmagic(int v) { return __int_as_float(v) - MAGIC_F; }
+// float(byte j of w) for an unsigned byte: the byte is dropped into the mantissa of 2^23
+__device__ __forceinline__ float byte_to_float(uint32_t w, int j) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650 | j)) - 8388608.0f;
+}
 // byte j of w, zero-extended / sign-extended, in one permute
 __device__ __forceinline__ int byte_u(uint32_t w, int j) { return (int)__byte_perm(w, 0, 0x4440 | j); }
 // (prmt with bit 3 of a selector nibble set copies the sign of the selected byte; the __byte_perm
