@@ -85,48 +85,38 @@ struct FmtQ4K {
         mB[0] = hb.z & 0x3f3f3f3fu;
         scB[1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
         mB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
-        // per-row, per-sub-block float scales d * sc_j (exact: 11-bit f16 mantissa times 6 bits); the
-        // high-nibble operand is used as 16 * q, so its scale carries the 1/16
-        float SA[8], SB[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float k16 = (j & 1) ? 0.0625f : 1.0f;
-            SA[j] = byte_to_float(scA[j >> 2], j & 3) * (dA * k16);
-            SB[j] = byte_to_float(scB[j >> 2], j & 3) * (dB * k16);
-        }
-        float acc[NT][4];
+        int c[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
         // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
         const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
         const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
+            const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
             uint32_t a[4], alo[4], ahi[4];
             ldmatrix_x4(a, a_addr + 32 * grp);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                alo[i] = a[i] & 0x0f0f0f0fu;  // q of sub-block 2*grp
-                ahi[i] = a[i] & 0xf0f0f0f0u;  // 16 * q of sub-block 2*grp + 1 (unsigned operand)
+                alo[i] = a[i] & 0x0f0f0f0fu;
+                ahi[i] = (a[i] >> 4) & 0x0f0f0f0fu;
             }
+            const int sAl = byte_u(scA[jl >> 2], jl & 3), sAh = byte_u(scA[jh >> 2], jh & 3);
+            const int sBl = byte_u(scB[jl >> 2], jl & 3), sBh = byte_u(scB[jh >> 2], jh & 3);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 if (nt < A.ntiles) {
                     uint32_t b[4];
                     ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
                     int p[4], q[4];
-                    mma_s8_k32_m(p, alo, b[0], b[1]);
-                    mma_u8s8_k32_m(q, ahi, b[2], b[3]);
-                    acc[nt][0] = fmaf(unmagic(p[0]), SA[2 * grp], acc[nt][0]);
-                    acc[nt][1] = fmaf(unmagic(p[1]), SA[2 * grp], acc[nt][1]);
-                    acc[nt][2] = fmaf(unmagic(p[2]), SB[2 * grp], acc[nt][2]);
-                    acc[nt][3] = fmaf(unmagic(p[3]), SB[2 * grp], acc[nt][3]);
-                    acc[nt][0] = fmaf(unmagic(q[0]), SA[2 * grp + 1], acc[nt][0]);
-                    acc[nt][1] = fmaf(unmagic(q[1]), SA[2 * grp + 1], acc[nt][1]);
-                    acc[nt][2] = fmaf(unmagic(q[2]), SB[2 * grp + 1], acc[nt][2]);
-                    acc[nt][3] = fmaf(unmagic(q[3]), SB[2 * grp + 1], acc[nt][3]);
+                    mma_s8_k32_z(p, alo, b[0], b[1]);
+                    mma_s8_k32_z(q, ahi, b[2], b[3]);
+                    c[nt][0] += sAl * p[0] + sAh * q[0];
+                    c[nt][1] += sAl * p[1] + sAh * q[1];
+                    c[nt][2] += sBl * p[2] + sBh * q[2];
+                    c[nt][3] += sBl * p[3] + sBh * q[3];
                 }
             }
         }
@@ -142,15 +132,14 @@ struct FmtQ4K {
                 const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
                 const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
                 int ch[4], cl[4];
-                mma_s8_k16_m(ch, am0, am1, bh);
-                mma_s8_k16_m(cl, am0, am1, bl);
+                mma_s8_k16_z(ch, am0, am1, bh);
+                mma_s8_k16_z(cl, am0, am1, bl);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float d8 = (i & 1) ? d8b : d8a;
-                    const float mw = (i >> 1) ? mnB : mnA;
-                    const float msum = fmaf(128.0f, unmagic(ch[i]), unmagic(cl[i]));  // sum_j min_j * bsum_j, exact
-                    f[nt][i] = fmaf(d8, acc[nt][i], f[nt][i]);
-                    f[nt][i] = fmaf(-(d8 * mw), msum, f[nt][i]);
+                    const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
+                    f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
+                    f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
                 }
             }
         }
@@ -202,19 +191,11 @@ struct FmtQ6K {
             scA[i] = ld32<ODD>(rowA + 192 + 4 * i);
             scB[i] = ld32<ODD>(rowB + 192 + 4 * i);
         }
-        // float(scale) for the 16 sub-blocks of both rows: bias the int8 by 128, drop the byte into
-        // the mantissa of 2^23, subtract (exact small integers)
-        float SA[16], SB[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            SA[j] = __uint_as_float(__byte_perm(scA[j >> 2] ^ 0x80808080u, 0x4B000000u, 0x7650 | (j & 3))) - 8388736.0f;
-            SB[j] = __uint_as_float(__byte_perm(scB[j >> 2] ^ 0x80808080u, 0x4B000000u, 0x7650 | (j & 3))) - 8388736.0f;
-        }
-        float c[NT][4];  // sum_j scale_j * (q . a)_j as exact small-integer floats
+        int c[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[nt][i] = 0.f;
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
         const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 
 #pragma unroll
@@ -246,6 +227,7 @@ struct FmtQ6K {
 #pragma unroll
             for (int y = 0; y < 2; ++y) {  // 64 elements = quarters 2y, 2y+1 = four 16-element sub-blocks
                 uint32_t aA[4], aB[4];  // [2*(x&1) + lr]
+                int sA[4], sB[4];
 #pragma unroll
                 for (int xo = 0; xo < 2; ++xo) {
                     const int x = 2 * y + xo;  // quarter: elements 128h + 32x .. +31; low nibbles for x < 2
@@ -255,6 +237,9 @@ struct FmtQ6K {
                         const uint32_t lb = (x >> 1) ? (qlB[x & 1][lr] >> 4) : qlB[x & 1][lr];
                         aA[2 * xo + lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
                         aB[2 * xo + lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
+                        const int j = 8 * h + 2 * x + lr;  // sub-block id
+                        sA[2 * xo + lr] = byte_s(scA[j >> 2], j & 3);
+                        sB[2 * xo + lr] = byte_s(scB[j >> 2], j & 3);
                     }
                 }
 #pragma unroll
@@ -264,13 +249,12 @@ struct FmtQ6K {
                         ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
 #pragma unroll
                         for (int s4 = 0; s4 < 4; ++s4) {
-                            const int j = 8 * h + 4 * y + s4;  // sub-block id: 16 consecutive elements
                             int p[4];
-                            mma_s8_k16_m(p, aA[s4], aB[s4], b[s4]);
-                            c[nt][0] = fmaf(unmagic(p[0]), SA[j], c[nt][0]);
-                            c[nt][1] = fmaf(unmagic(p[1]), SA[j], c[nt][1]);
-                            c[nt][2] = fmaf(unmagic(p[2]), SB[j], c[nt][2]);
-                            c[nt][3] = fmaf(unmagic(p[3]), SB[j], c[nt][3]);
+                            mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
+                            c[nt][0] += sA[s4] * p[0];
+                            c[nt][1] += sA[s4] * p[1];
+                            c[nt][2] += sB[s4] * p[2];
+                            c[nt][3] += sB[s4] * p[3];
                         }
                     }
                 }
@@ -285,16 +269,15 @@ struct FmtQ6K {
                 const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
                 const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
                 int ch[4], cl[4];
-                mma_s8_k16_m(ch, sa, sb, bh);
-                mma_s8u8_k16_m(cl, sa, sb, bl);
+                mma_s8_k16_z(ch, sa, sb, bh);
+                mma_s8u8_k16_z(cl, sa, sb, bl);
                 const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
                 const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float corr = fmaf(256.0f, unmagic(ch[i]), unmagic(cl[i]));  // sum_j scale_j * bsum_j
-                    const float isum = fmaf(-32.0f, corr, c[nt][i]);
+                    const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
                     const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
-                    f[nt][i] = fmaf(dd, isum, f[nt][i]);
+                    f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
                 }
             }
         }
