@@ -36,15 +36,14 @@ namespace {
 constexpr int TILE_ROWS = 16;         // weight rows per stage (gate_up: 8 rows of W1 followed by the same 8 rows of W3)
 constexpr int RED_PAD = 17;           // floats per (warp, token) in the reduction buffer
 
-// Everything a consumer warp needs besides the weight tile itself.
+// Everything a consumer warp needs besides the weight tile itself (32-bit shared-window addresses).
 struct BlockArgs {
-    const uint8_t* act;      // int8 rows of the token group, [MT][act_stride]
-    const float* act_scale;  // per (token, block) scale d8, [MT][scale_stride]
-    const uint8_t* bs_hi;    // activation block sums split into two byte planes, [MT][bs_stride]
-    const uint8_t* bs_lo;
-    int act_stride, scale_stride, bs_stride;
-    int kblk_local;          // block index inside the resident K-range
-    int ntiles;              // token tiles (of 8) that hold rows; the others are skipped
+    uint32_t act;        // int8 rows of the token group, [MT][act_stride]
+    uint32_t act_scale;  // per (token, block) scale d8 (f32), [MT][scale_stride]
+    uint32_t bs_hi;      // activation block sums split into two byte planes, [MT][bs_stride]
+    uint32_t bs_lo;
+    int act_stride, scale_stride, bs_stride;  // act/bs in bytes, scale in floats
+    int kblk_local;      // block index inside the resident K-range
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -67,13 +66,12 @@ struct FmtQ4K {
         hi = (uint8_t)((v >> 7) & 0xff);
     }
 
-    template <int NT, int RS>
-    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
-                                                 float (&f)[NT][4]) {
+    // NTL = token tiles (of 8) that hold rows
+    template <int NT, int NTL, int RS>
+    __device__ static __forceinline__ void block(uint32_t tile, int wblk, const BlockArgs& A, int lane, float (&f)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint8_t* rowA = tile + g * RS + wblk * BLOCK_BYTES;
-        const uint8_t* rowB = rowA + 8 * RS;
-        const uint4 ha = *reinterpret_cast<const uint4*>(rowA), hb = *reinterpret_cast<const uint4*>(rowB);
+        const uint32_t rowA = tile + g * RS + wblk * BLOCK_BYTES;
+        const uint4 ha = lds128(rowA), hb = lds128(rowA + 8 * RS);
         const float dA = half_bits_to_float((uint16_t)(ha.x & 0xffff)), mnA = half_bits_to_float((uint16_t)(ha.x >> 16));
         const float dB = half_bits_to_float((uint16_t)(hb.x & 0xffff)), mnB = half_bits_to_float((uint16_t)(hb.x >> 16));
         uint32_t scA[2], mA[2], scB[2], mB[2];  // [0]: sub-blocks 0..3, [1]: 4..7, one byte each
@@ -85,14 +83,14 @@ struct FmtQ4K {
         mB[0] = hb.z & 0x3f3f3f3fu;
         scB[1] = (hb.w & 0x0f0f0f0fu) | (((hb.y >> 6) & 0x03030303u) << 4);
         mB[1] = ((hb.w >> 4) & 0x0f0f0f0fu) | (((hb.z >> 6) & 0x03030303u) << 4);
-        int c[NT][4];
+        int c[NTL][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
         // ldmatrix lane addressing: matrices = (rows 0-7 | rows 8-15) x (bytes 0-15 | 16-31) of a 64-element group
-        const uint8_t* a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
-        const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
+        const uint32_t a_addr = tile + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + wblk * BLOCK_BYTES + 16 + 16 * (lane >> 4);
+        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
             const int jl = 2 * grp, jh = 2 * grp + 1;  // sub-block ids of the low / high nibbles
@@ -106,41 +104,36 @@ struct FmtQ4K {
             const int sAl = byte_u(scA[jl >> 2], jl & 3), sAh = byte_u(scA[jh >> 2], jh & 3);
             const int sBl = byte_u(scB[jl >> 2], jl & 3), sBh = byte_u(scB[jh >> 2], jh & 3);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                if (nt < A.ntiles) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
-                    int p[4], q[4];
-                    mma_s8_k32_z(p, alo, b[0], b[1]);
-                    mma_s8_k32_z(q, ahi, b[2], b[3]);
-                    c[nt][0] += sAl * p[0] + sAh * q[0];
-                    c[nt][1] += sAl * p[1] + sAh * q[1];
-                    c[nt][2] += sBl * p[2] + sBh * q[2];
-                    c[nt][3] += sBl * p[3] + sBh * q[3];
-                }
+            for (int nt = 0; nt < NTL; ++nt) {
+                uint32_t b[4];
+                ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
+                int p[4], q[4];
+                mma_s8_k32_z(p, alo, b[0], b[1]);
+                mma_s8_k32_z(q, ahi, b[2], b[3]);
+                c[nt][0] += sAl * p[0] + sAh * q[0];
+                c[nt][1] += sAl * p[1] + sAh * q[1];
+                c[nt][2] += sBl * p[2] + sBh * q[2];
+                c[nt][3] += sBl * p[3] + sBh * q[3];
             }
         }
         // A operand of the min product: k = sub-block id, lanes t = 0, 1 carry the 8 packed mins
         const uint32_t am0 = t == 0 ? mA[0] : (t == 1 ? mA[1] : 0u);
         const uint32_t am1 = t == 0 ? mB[0] : (t == 1 ? mB[1] : 0u);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            if (nt < A.ntiles) {
-                const int boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 8 + 4 * (t & 1);
-                const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
-                const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
-                const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
-                const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
-                int ch[4], cl[4];
-                mma_s8_k16_z(ch, am0, am1, bh);
-                mma_s8_k16_z(cl, am0, am1, bl);
+        for (int nt = 0; nt < NTL; ++nt) {
+            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 8 + 4 * (t & 1);
+            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
+            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
+            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
+            int ch[4], cl[4];
+            mma_s8_k16_z(ch, am0, am1, bh);
+            mma_s8_k16_z(cl, am0, am1, bl);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float d8 = (i & 1) ? d8b : d8a;
-                    const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
-                    f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
-                    f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
-                }
+            for (int i = 0; i < 4; ++i) {
+                const float d8 = (i & 1) ? d8b : d8a;
+                const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
+                f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
+                f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
             }
         }
     }
@@ -169,34 +162,30 @@ struct FmtQ6K {
     }
 
     template <bool ODD>
-    __device__ static __forceinline__ uint32_t ld32(const uint8_t* p) {
-        if (ODD) {
-            const uint16_t* h = reinterpret_cast<const uint16_t*>(p);
-            return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
-        }
-        return *reinterpret_cast<const uint32_t*>(p);
+    __device__ static __forceinline__ uint32_t ld32(uint32_t addr) {
+        if (ODD) return lds16(addr) | (lds16(addr + 2) << 16);
+        return lds32(addr);
     }
 
-    template <int NT, int RS, bool ODD>
-    __device__ static __forceinline__ void block_impl(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
-                                                      float (&f)[NT][4]) {
+    template <int NT, int NTL, int RS, bool ODD>
+    __device__ static __forceinline__ void block_impl(uint32_t tile, int wblk, const BlockArgs& A, int lane, float (&f)[NT][4]) {
         const int g = lane >> 2, t = lane & 3;
-        const uint8_t* rowA = tile + g * RS + wblk * BLOCK_BYTES;
-        const uint8_t* rowB = rowA + 8 * RS;
-        const float dA = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowA + 208));
-        const float dB = half_bits_to_float(*reinterpret_cast<const uint16_t*>(rowB + 208));
+        const uint32_t rowA = tile + g * RS + wblk * BLOCK_BYTES;
+        const uint32_t rowB = rowA + 8 * RS;
+        const float dA = half_bits_to_float((uint16_t)lds16(rowA + 208));
+        const float dB = half_bits_to_float((uint16_t)lds16(rowB + 208));
         uint32_t scA[4], scB[4];  // 16 int8 scales per row
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             scA[i] = ld32<ODD>(rowA + 192 + 4 * i);
             scB[i] = ld32<ODD>(rowB + 192 + 4 * i);
         }
-        int c[NT][4];
+        int c[NTL][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
-        const uint8_t* b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
+        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
 
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -243,53 +232,47 @@ struct FmtQ6K {
                     }
                 }
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    if (nt < A.ntiles) {
-                        uint32_t b[4];  // int8 activations of the four sub-blocks
-                        ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
+                for (int nt = 0; nt < NTL; ++nt) {
+                    uint32_t b[4];  // int8 activations of the four sub-blocks
+                    ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
 #pragma unroll
-                        for (int s4 = 0; s4 < 4; ++s4) {
-                            int p[4];
-                            mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
-                            c[nt][0] += sA[s4] * p[0];
-                            c[nt][1] += sA[s4] * p[1];
-                            c[nt][2] += sB[s4] * p[2];
-                            c[nt][3] += sB[s4] * p[3];
-                        }
+                    for (int s4 = 0; s4 < 4; ++s4) {
+                        int p[4];
+                        mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
+                        c[nt][0] += sA[s4] * p[0];
+                        c[nt][1] += sA[s4] * p[1];
+                        c[nt][2] += sB[s4] * p[2];
+                        c[nt][3] += sB[s4] * p[3];
                     }
                 }
             }
         }
         // offset term: corr[row][tok] = sum_j scale[row][j] * bsum[tok][j], bsum = 256 * hi + lo
-        const uint32_t sa = ld32<ODD>(rowA + 192 + 4 * t), sb = ld32<ODD>(rowB + 192 + 4 * t);
+        const uint32_t sa = scA[t], sb = scB[t];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            if (nt < A.ntiles) {
-                const int boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 16 + 4 * t;
-                const uint32_t bh = *reinterpret_cast<const uint32_t*>(A.bs_hi + boff);
-                const uint32_t bl = *reinterpret_cast<const uint32_t*>(A.bs_lo + boff);
-                int ch[4], cl[4];
-                mma_s8_k16_z(ch, sa, sb, bh);
-                mma_s8u8_k16_z(cl, sa, sb, bl);
-                const float d8a = A.act_scale[(nt * 8 + 2 * t) * A.scale_stride + A.kblk_local];
-                const float d8b = A.act_scale[(nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local];
+        for (int nt = 0; nt < NTL; ++nt) {
+            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 16 + 4 * t;
+            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
+            int ch[4], cl[4];
+            mma_s8_k16_z(ch, sa, sb, bh);
+            mma_s8u8_k16_z(cl, sa, sb, bl);
+            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
+            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
-                    const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
-                    f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
-                }
+            for (int i = 0; i < 4; ++i) {
+                const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
+                const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
+                f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
             }
         }
     }
 
-    template <int NT, int RS>
-    __device__ static __forceinline__ void block(const uint8_t* tile, int wblk, const BlockArgs& A, int lane,
-                                                 float (&f)[NT][4]) {
+    template <int NT, int NTL, int RS>
+    __device__ static __forceinline__ void block(uint32_t tile, int wblk, const BlockArgs& A, int lane, float (&f)[NT][4]) {
         if ((wblk & 1) || (RS & 3))
-            block_impl<NT, RS, true>(tile, wblk, A, lane, f);
+            block_impl<NT, NTL, RS, true>(tile, wblk, A, lane, f);
         else
-            block_impl<NT, RS, false>(tile, wblk, A, lane, f);
+            block_impl<NT, NTL, RS, false>(tile, wblk, A, lane, f);
     }
 };
 
@@ -440,6 +423,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
     Walker wk(P, s_offs, blockIdx.x, gridDim.x);
     const size_t row_bytes = (size_t)P.kb * F::BLOCK_BYTES;
     uint8_t* stage0 = smem + P.off_stage;
+    const uint32_t stage_addr0 = smem_u32(stage0);
 
     if (warp == 0) {
         // ================= producer: lane r < 16 copies weight row r of the tile =================
@@ -540,14 +524,14 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
             }
 
             BlockArgs bargs;
-            bargs.act = act;
-            bargs.act_scale = act_scale;
-            bargs.bs_hi = bs_hi;
-            bargs.bs_lo = bs_lo;
+            bargs.act = smem_u32(act);
+            bargs.act_scale = smem_u32(act_scale);
+            bargs.bs_hi = smem_u32(bs_hi);
+            bargs.bs_lo = smem_u32(bs_lo);
             bargs.act_stride = P.act_stride;
             bargs.scale_stride = P.scale_stride;
             bargs.bs_stride = P.bs_stride;
-            bargs.ntiles = (int)(p_end - p_base + 7) / 8;
+            const int ntiles = (int)(p_end - p_base + 7) / 8;  // token tiles that hold rows
             float f[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
@@ -563,7 +547,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                 const int blk = ch * CW + cw;
                 if (ok && blk < P.kb) {
                     bargs.kblk_local = blk - blk0;
-                    F::template block<NT, RS>(stage0 + (size_t)s * P.stage_bytes, cw, bargs, lane, f);
+                    const uint32_t tile_addr = stage_addr0 + (uint32_t)s * P.stage_bytes;
+                    if (NT == 1 || ntiles == 1)
+                        F::template block<NT, 1, RS>(tile_addr, cw, bargs, lane, f);
+                    else
+                        F::template block<NT, NT, RS>(tile_addr, cw, bargs, lane, f);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
