@@ -187,6 +187,9 @@ def config_dict(args, cfg):
         "tokens_per_step_per_gpu": args.tokens,
         "l2_policy": "inputs larger than L2: the expert weights streamed each step exceed the 126 MB L2"
         if weights_bytes(cfg) > 200e6 else "L2 flushed between steps by writing a 256 MB buffer",
+        "decode_weights": "GGUF blocks" if (args.no_prepack or args.tokens > 64) else
+        "prepacked copies made once at load (candle_moe_prepack; Q4_K +2.8 % bytes, Q6_K same size); "
+        "roofline bytes are the GGUF bytes",
         "parallelism": "single GPU" if args.gpus == 1 else f"{args.gpus} token-sharded replicas (no collective)",
     }
 
@@ -199,7 +202,7 @@ def weights_bytes(cfg):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
-def build_block(torch, cfg, device, seed=0):
+def build_block(torch, cfg, device, seed=0, prepack=True):
     from candle_b200 import GgmlDType, Mlp, MlpOrMoe, QMatMul, QTensor
     g = torch.Generator(device=device).manual_seed(seed)
     d, ff, E = cfg["d"], cfg["ff"], cfg["E"]
@@ -217,7 +220,10 @@ def build_block(torch, cfg, device, seed=0):
         kw["shared_expert_gate"] = torch.randn(d, generator=g, device=device) * 0.02
     if cfg.get("zipf_bias"):
         kw["router_bias"] = torch.log(1.0 / (torch.arange(E, dtype=torch.float32) + 1.0))
-    return MlpOrMoe.moe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], **kw)
+    blk = MlpOrMoe.moe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], **kw)
+    if prepack and cfg["dt13"] in (12, 14) and cfg["dt2"] in (12, 14):
+        blk.prepack()
+    return blk
 
 
 def oracle_view(torch, blk, cfg):
@@ -316,7 +322,7 @@ def run_ours(args, cfg):
     import candle_b200  # noqa: F401  loads libcandle_moe_sm100.so or raises
 
     T, d = args.tokens, cfg["d"]
-    blk = build_block(torch, cfg, dev, seed=0)
+    blk = build_block(torch, cfg, dev, seed=0, prepack=not args.no_prepack and T <= 64)
     blk.reserve(T)
     gx = torch.Generator(device=dev).manual_seed(1 + rank)
     x = torch.randn((T, d), generator=gx, device=dev, dtype=torch.float32)
@@ -456,6 +462,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--no-prepack", action="store_true",
+                    help="decode straight from the GGUF blocks instead of the one-time prepacked copies")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     if args.workload == "c5":

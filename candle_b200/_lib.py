@@ -44,6 +44,8 @@ class MoeWeightsC(C.Structure):
         ("w1", C.POINTER(C.c_void_p)), ("w3", C.POINTER(C.c_void_p)), ("w2", C.POINTER(C.c_void_p)),
         ("shared_w1", C.c_void_p), ("shared_w3", C.c_void_p), ("shared_w2", C.c_void_p),
         ("shared_gate", C.c_void_p),
+        ("w1_prepacked", C.POINTER(C.c_void_p)), ("w3_prepacked", C.POINTER(C.c_void_p)),
+        ("w2_prepacked", C.POINTER(C.c_void_p)),
     ]
 
 
@@ -62,6 +64,10 @@ SYMBOLS = {
     "candle_moe_forward": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ]),
     "candle_moe_forward_static": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P]),
     "candle_moe_workspace_views": (C.c_int, [C.POINTER(MoeWeightsC), _I64, _P, _PP, _PP, _PP, _PP]),
+    "candle_moe_prepacked_bytes": (C.c_int, [_I32, _I64, _I32, C.POINTER(_SZ)]),
+    "candle_moe_prepack": (C.c_int, [_P, _I32, _P, _I64, _I32, _P]),
+    "candle_moe_grouped_gate_up_prepacked": (C.c_int, [_P, _PP, _PP, _I32, _I32, _I32, _I32, _P, _P, _I64, _P, _P, _P, _P]),
+    "candle_moe_grouped_down_prepacked": (C.c_int, [_P, _PP, _I32, _I32, _I32, _I32, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_device_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "candle_moe_quantize_weights": (C.c_int, [_P, _I32, _P, _I64, _P]),
     "candle_moe_dequantize": (C.c_int, [_P, _I32, _P, _I64, _P]),

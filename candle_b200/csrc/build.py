@@ -21,6 +21,7 @@ SOURCES = {
     "weight_quantize.cu": ["-fmad=false"],
     "expert_rows.cu": [],
     "expert_stream.cu": [],
+    "expert_direct.cu": [],
 }
 # extra nvcc flags for local experiments, e.g. CANDLE_MOE_NVCC_FLAGS="-DCMOE_STREAM_TIMING"
 EXTRA = os.environ.get("CANDLE_MOE_NVCC_FLAGS", "").split()

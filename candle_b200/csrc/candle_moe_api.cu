@@ -239,12 +239,38 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
     CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
     // a token selects an expert at most once: no expert sees more than T rows
-    CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
-                                     ws.xb, ws.hidden)));
-    CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
+    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && T <= 64;
     int eo_splits = 1, so_splits = 1;
-    CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
-                                  k_split_slots(T), &eo_splits)));
+    bool gate_done = false, down_done = false;
+    ExpertPtrs q1, q3, q2;
+    if (use_prepacked) {
+        CM_TRY(fill_ptrs(w->w1_prepacked, E, q1));
+        CM_TRY(fill_ptrs(w->w3_prepacked, E, q3));
+        CM_TRY(fill_ptrs(w->w2_prepacked, E, q2));
+        const cudaError_t ce = launch_expert_direct(st, true, q1, q3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T,
+                                                    ws.xq, ws.xs, ws.xb, ws.hidden, nullptr, 0, 1);
+        if (ce == cudaSuccess)
+            gate_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+    }
+    if (!gate_done)
+        CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
+                                         ws.xb, ws.hidden)));
+    CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
+    if (use_prepacked) {
+        const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, T, ws.hq,
+                                                    ws.hs, ws.hb, ws.eo, &eo_splits, Tk * d, k_split_slots(T));
+        if (ce == cudaSuccess)
+            down_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+        else
+            eo_splits = 1;
+    }
+    if (!down_done)
+        CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
+                                      k_split_slots(T), &eo_splits)));
 
     const float* shared_out = nullptr;
     if (w->d_ff_shared > 0) {
@@ -317,6 +343,53 @@ int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* w
     if (expert_counts) *expert_counts = ws.counts;
     if (perm_token) *perm_token = ws.perm_token;
     return CANDLE_MOE_OK;
+}
+
+int candle_moe_prepacked_bytes(int32_t dtype, int64_t n_rows, int32_t k, size_t* out_bytes) {
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
+    if (n_rows < 0 || k <= 0) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = prepacked_bytes(dtype, n_rows, k);
+    return *out_bytes || n_rows == 0 ? CANDLE_MOE_OK : CANDLE_MOE_E_SHAPE;
+}
+
+int candle_moe_prepack(void* stream, int32_t dtype, const void* src_blocks, int64_t n_rows, int32_t k, void* dst) {
+    if (!src_blocks || !dst) return CANDLE_MOE_E_NULL;
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
+    if (n_rows < 0 || k <= 0 || k % 256 || n_rows % 8) return CANDLE_MOE_E_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(src_blocks) | reinterpret_cast<uintptr_t>(dst)) & 15) return CANDLE_MOE_E_ALIGN;
+    if (dtype == CANDLE_GGML_Q6K && (k / 256) % 2) return CANDLE_MOE_E_SHAPE;  // rows must stay 4-byte aligned
+    return rc(launch_prepack((cudaStream_t)stream, dtype, src_blocks, n_rows, k, dst));
+}
+
+int candle_moe_grouped_gate_up_prepacked(void* stream, const void* const* w1p, const void* const* w3p, int32_t dtype,
+                                         int32_t E, int32_t d, int32_t ff, const uint32_t* expert_offsets,
+                                         const uint32_t* row_of, int64_t max_rows, const int8_t* xq,
+                                         const float* xscales, const int16_t* xbsums, float* hidden) {
+    if (!expert_offsets || !xq || !xscales || !xbsums || !hidden) return CANDLE_MOE_E_NULL;
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || d % 256 || max_rows < 0 || max_rows > 64)
+        return CANDLE_MOE_E_SHAPE;
+    ExpertPtrs p1, p3;
+    CM_TRY(fill_ptrs(w1p, E, p1));
+    CM_TRY(fill_ptrs(w3p, E, p3));
+    const cudaError_t e = launch_expert_direct((cudaStream_t)stream, true, p1, p3, dtype, E, d, ff, expert_offsets, row_of,
+                                               max_rows, xq, xscales, xbsums, hidden, nullptr, 0, 1);
+    return e == cudaErrorNotSupported ? CANDLE_MOE_E_SHAPE : rc(e);
+}
+
+int candle_moe_grouped_down_prepacked(void* stream, const void* const* w2p, int32_t dtype, int32_t E, int32_t d,
+                                      int32_t ff, const uint32_t* expert_offsets, int64_t max_rows, const int8_t* hq,
+                                      const float* hscales, const int16_t* hbsums, float* out) {
+    if (!expert_offsets || !hq || !hscales || !hbsums || !out) return CANDLE_MOE_E_NULL;
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || ff % 256 || max_rows < 0 || max_rows > 64)
+        return CANDLE_MOE_E_SHAPE;
+    ExpertPtrs p2;
+    CM_TRY(fill_ptrs(w2p, E, p2));
+    const cudaError_t e = launch_expert_direct((cudaStream_t)stream, false, p2, p2, dtype, E, ff, d, expert_offsets,
+                                               nullptr, max_rows, hq, hscales, hbsums, out, nullptr, 0, 1);
+    return e == cudaErrorNotSupported ? CANDLE_MOE_E_SHAPE : rc(e);
 }
 
 int candle_moe_device_status(int32_t* flags) {

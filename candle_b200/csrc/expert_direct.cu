@@ -1,0 +1,568 @@
+// Grouped expert products for decode-sized batches over PREPACKED weights.
+//
+// A one-time repack (candle_moe_prepack) lays every 8-row x 256-element piece of a Q4_K / Q6_K
+// matrix out in the order the tensor-core fragments want it, so that in the hot loop every lane
+// fetches its share of a block with a few fully coalesced 128-bit loads straight into registers:
+// no shared-memory staging of weights, no K-split across warps, no cross-warp reduction.  Each warp
+// owns a 16-row MMA tile (gate_up: 8 rows of W1 and the same 8 rows of W3) over the whole K-range
+// and keeps the next block's loads in flight while it multiplies the current one.  Only the int8
+// activations of the expert's rows live in shared memory (read with ldmatrix).
+//
+// The arithmetic is the one of the streaming kernel (expert_stream.cu): exact integer sub-block
+// dots on mma.sync s8, sub-block scales in int32, block scales in f32, i.e. the integers of the
+// reference's vec_dot (candle-core/src/quantized/k_quants.rs:1205-1285, 1616-1673).
+//
+// Prepacked layout, per matrix [N rows, K]: [N / 8 half-tiles][K / 256 blocks][HTB bytes], where a
+// half-tile block (8 rows x 256 elements) is
+//   Q4_K (1184 B): quants [2][32 lanes][16 B]  lane (g = row, t): for u: {qs[32*(2u)+4t], qs[32*(2u)+16+4t],
+//                                               qs[32*(2u+1)+4t], qs[32*(2u+1)+16+4t]} (4-byte words of the raw qs)
+//                  d|dmin [8] u32, scales [8][8] u8, mins [8][8] u8 (the 6-bit fields widened to bytes)
+//   Q6_K (1680 B): [3][32 lanes][16 B]: u = 0,1: ql words of half u {ql[64u+4t], +16, +32, +48};
+//                  u = 2: qh words {qh[4t], qh[16+4t], qh[32+4t], qh[48+4t]}; scales [8][16] i8; d [8] f16
+// Q4_K grows by 2.8 % (the 12-byte packed scales become 16 bytes); Q6_K keeps its size.
+#include "common.cuh"
+#include "stream_common.cuh"
+
+namespace cmoe {
+
+namespace {
+
+constexpr int Q4K_HTB = 1184;
+constexpr int Q6K_HTB = 1680;
+constexpr int DIRECT_WARPS = 16;
+constexpr int DIRECT_THREADS = 32 * DIRECT_WARPS;
+
+__device__ __forceinline__ uint4 ldg128_stream(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg64_stream(const uint8_t* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg32_stream(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg16_stream(const uint8_t* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return (uint32_t)v;
+}
+
+// Shared-memory side of a block product (32-bit shared-window addresses)
+struct ActArgs {
+    uint32_t act, act_scale, bs_hi, bs_lo;
+    int act_stride, scale_stride, bs_stride;
+    int kblk_local;
+};
+
+// ------------------------------------------------------------------------------------------------
+struct DirQ4K {
+    static constexpr int HTB = Q4K_HTB;
+    static constexpr int BS_PER_BLOCK = 8;
+    __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[2 * i] + (int)bs16[2 * i + 1]; }
+    __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
+        lo = (uint8_t)(v & 127);
+        hi = (uint8_t)((v >> 7) & 0xff);
+    }
+    struct Frag {
+        uint4 qa[2], qb[2];  // nibble words of rows g (half-tile A) and g + 8 (half-tile B)
+        uint32_t dmA, dmB;   // f16 d | f16 dmin
+        uint2 scA, scB, mA, mB;
+    };
+    __device__ static __forceinline__ void load(Frag& F, const uint8_t* hta, const uint8_t* htb, int lane) {
+        const int g = lane >> 2;
+        F.qa[0] = ldg128_stream(hta + lane * 16);
+        F.qa[1] = ldg128_stream(hta + 512 + lane * 16);
+        F.qb[0] = ldg128_stream(htb + lane * 16);
+        F.qb[1] = ldg128_stream(htb + 512 + lane * 16);
+        F.dmA = ldg32_stream(hta + 1024 + 4 * g);
+        F.dmB = ldg32_stream(htb + 1024 + 4 * g);
+        F.scA = ldg64_stream(hta + 1056 + 8 * g);
+        F.scB = ldg64_stream(htb + 1056 + 8 * g);
+        F.mA = ldg64_stream(hta + 1120 + 8 * g);
+        F.mB = ldg64_stream(htb + 1120 + 8 * g);
+    }
+    template <int NT, int NTL>
+    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
+        const int g = lane >> 2, t = lane & 3;
+        const float dA = half_bits_to_float((uint16_t)(F.dmA & 0xffff)), mnA = half_bits_to_float((uint16_t)(F.dmA >> 16));
+        const float dB = half_bits_to_float((uint16_t)(F.dmB & 0xffff)), mnB = half_bits_to_float((uint16_t)(F.dmB >> 16));
+        const uint32_t scA[2] = {F.scA.x, F.scA.y}, scB[2] = {F.scB.x, F.scB.y};
+        int c[NTL][4];
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+            const int jl = 2 * grp, jh = 2 * grp + 1;
+            const uint4 wa = F.qa[grp >> 1], wb = F.qb[grp >> 1];
+            // fragment order a0 (row g, k 0-15), a1 (row g+8, k 0-15), a2 (row g, k 16-31), a3 (row g+8, k 16-31)
+            const uint32_t a0 = (grp & 1) ? wa.z : wa.x, a2 = (grp & 1) ? wa.w : wa.y;
+            const uint32_t a1 = (grp & 1) ? wb.z : wb.x, a3 = (grp & 1) ? wb.w : wb.y;
+            const uint32_t alo[4] = {a0 & 0x0f0f0f0fu, a1 & 0x0f0f0f0fu, a2 & 0x0f0f0f0fu, a3 & 0x0f0f0f0fu};
+            const uint32_t ahi[4] = {(a0 >> 4) & 0x0f0f0f0fu, (a1 >> 4) & 0x0f0f0f0fu, (a2 >> 4) & 0x0f0f0f0fu,
+                                     (a3 >> 4) & 0x0f0f0f0fu};
+            const int sAl = byte_u(scA[jl >> 2], jl & 3), sAh = byte_u(scA[jh >> 2], jh & 3);
+            const int sBl = byte_u(scB[jl >> 2], jl & 3), sBh = byte_u(scB[jh >> 2], jh & 3);
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) {
+                uint32_t b[4];
+                ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
+                int p[4], q[4];
+                mma_s8_k32_z(p, alo, b[0], b[1]);
+                mma_s8_k32_z(q, ahi, b[2], b[3]);
+                c[nt][0] += sAl * p[0] + sAh * q[0];
+                c[nt][1] += sAl * p[1] + sAh * q[1];
+                c[nt][2] += sBl * p[2] + sBh * q[2];
+                c[nt][3] += sBl * p[3] + sBh * q[3];
+            }
+        }
+        // min term: sum_j min_j * bsum_j as a [16 x 8] by [8 x 8] product (lanes t = 0, 1 carry the mins)
+        const uint32_t am0 = t == 0 ? F.mA.x : (t == 1 ? F.mA.y : 0u);
+        const uint32_t am1 = t == 0 ? F.mB.x : (t == 1 ? F.mB.y : 0u);
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) {
+            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 8 + 4 * (t & 1);
+            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
+            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
+            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
+            int ch[4], cl[4];
+            mma_s8_k16_z(ch, am0, am1, bh);
+            mma_s8_k16_z(cl, am0, am1, bl);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float d8 = (i & 1) ? d8b : d8a;
+                const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
+                f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
+                f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
+            }
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+struct DirQ6K {
+    static constexpr int HTB = Q6K_HTB;
+    static constexpr int BS_PER_BLOCK = 16;
+    __device__ static __forceinline__ int bs_value(const int16_t* bs16, int i) { return (int)bs16[i]; }
+    __device__ static __forceinline__ void bs_split(int v, uint8_t& hi, uint8_t& lo) {
+        lo = (uint8_t)(v & 0xff);
+        hi = (uint8_t)((v >> 8) & 0xff);
+    }
+    struct Frag {
+        uint4 qlA[2], qlB[2];  // [half]: words {xo0 lr0, xo0 lr1, xo1 lr0, xo1 lr1}
+        uint4 qhA, qhB;        // {h0 lr0, h0 lr1, h1 lr0, h1 lr1}
+        uint4 scA, scB;        // 16 int8 scales
+        uint32_t dA, dB;       // f16 d
+    };
+    __device__ static __forceinline__ void load(Frag& F, const uint8_t* hta, const uint8_t* htb, int lane) {
+        const int g = lane >> 2;
+        F.qlA[0] = ldg128_stream(hta + lane * 16);
+        F.qlA[1] = ldg128_stream(hta + 512 + lane * 16);
+        F.qhA = ldg128_stream(hta + 1024 + lane * 16);
+        F.qlB[0] = ldg128_stream(htb + lane * 16);
+        F.qlB[1] = ldg128_stream(htb + 512 + lane * 16);
+        F.qhB = ldg128_stream(htb + 1024 + lane * 16);
+        F.scA = ldg128_stream(hta + 1536 + 16 * g);
+        F.scB = ldg128_stream(htb + 1536 + 16 * g);
+        F.dA = ldg16_stream(hta + 1664 + 2 * g);
+        F.dB = ldg16_stream(htb + 1664 + 2 * g);
+    }
+    __device__ static __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
+
+    template <int NT, int NTL>
+    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
+        const int g = lane >> 2, t = lane & 3;
+        const float dA = half_bits_to_float((uint16_t)F.dA), dB = half_bits_to_float((uint16_t)F.dB);
+        const uint32_t scA[4] = {F.scA.x, F.scA.y, F.scA.z, F.scA.w}, scB[4] = {F.scB.x, F.scB.y, F.scB.z, F.scB.w};
+        int c[NTL][4];
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[nt][i] = 0;
+        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t hqA[2][4], hqB[2][4];  // [lr][quarter]: the 2-bit highs moved to bits 4..5
+#pragma unroll
+            for (int lr = 0; lr < 2; ++lr) {
+                const uint32_t qa = w4(F.qhA, 2 * h + lr), qb = w4(F.qhB, 2 * h + lr);
+                hqA[lr][0] = (qa << 4) & 0x30303030u;
+                hqA[lr][1] = (qa << 2) & 0x30303030u;
+                hqA[lr][2] = qa & 0x30303030u;
+                hqA[lr][3] = (qa >> 2) & 0x30303030u;
+                hqB[lr][0] = (qb << 4) & 0x30303030u;
+                hqB[lr][1] = (qb << 2) & 0x30303030u;
+                hqB[lr][2] = qb & 0x30303030u;
+                hqB[lr][3] = (qb >> 2) & 0x30303030u;
+            }
+#pragma unroll
+            for (int y = 0; y < 2; ++y) {  // 64 elements = quarters 2y, 2y+1
+                uint32_t aA[4], aB[4];
+                int sA[4], sB[4];
+#pragma unroll
+                for (int xo = 0; xo < 2; ++xo) {
+                    const int x = 2 * y + xo;
+#pragma unroll
+                    for (int lr = 0; lr < 2; ++lr) {
+                        const uint32_t wla = w4(F.qlA[h], 2 * (x & 1) + lr), wlb = w4(F.qlB[h], 2 * (x & 1) + lr);
+                        const uint32_t la = (x >> 1) ? (wla >> 4) : wla, lb = (x >> 1) ? (wlb >> 4) : wlb;
+                        aA[2 * xo + lr] = (la & 0x0f0f0f0fu) | hqA[lr][x];
+                        aB[2 * xo + lr] = (lb & 0x0f0f0f0fu) | hqB[lr][x];
+                        const int j = 8 * h + 2 * x + lr;
+                        sA[2 * xo + lr] = byte_s(scA[j >> 2], j & 3);
+                        sB[2 * xo + lr] = byte_s(scB[j >> 2], j & 3);
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NTL; ++nt) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
+#pragma unroll
+                    for (int s4 = 0; s4 < 4; ++s4) {
+                        int p[4];
+                        mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
+                        c[nt][0] += sA[s4] * p[0];
+                        c[nt][1] += sA[s4] * p[1];
+                        c[nt][2] += sB[s4] * p[2];
+                        c[nt][3] += sB[s4] * p[3];
+                    }
+                }
+            }
+        }
+        const uint32_t sa = scA[t], sb = scB[t];
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) {
+            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 16 + 4 * t;
+            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
+            int ch[4], cl[4];
+            mma_s8_k16_z(ch, sa, sb, bh);
+            mma_s8u8_k16_z(cl, sa, sb, bl);
+            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
+            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
+                const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
+                f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+            }
+        }
+    }
+};
+
+struct DirectParams {
+    ExpertPtrs wa, wb;  // prepacked matrices
+    const uint32_t* offsets;
+    const uint32_t* row_of;
+    const int8_t* aq;
+    const float* ascale;
+    const int16_t* absum;
+    float* out;
+    int64_t out_split_stride;
+    int E, K, N, kb, splits, MT;
+    int blk_start[5];  // split s covers blocks [blk_start[s], blk_start[s + 1])
+    int act_stride, scale_stride, bs_stride;
+    uint32_t off_act, off_scale, off_bs_hi, off_bs_lo;
+};
+
+template <class F, bool GATE_UP, int NT>
+__global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const __grid_constant__ DirectParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
+    __shared__ int s_rows[16];
+    constexpr int MT = 8 * NT;
+    constexpr int TILE_N = GATE_UP ? 8 : 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    for (int i = tid; i <= P.E; i += DIRECT_THREADS) s_offs[i] = P.offsets[i];
+    __syncthreads();
+
+    uint8_t* act = smem + P.off_act;
+    float* act_scale = reinterpret_cast<float*>(smem + P.off_scale);
+    uint8_t* bs_hi = smem + P.off_bs_hi;
+    uint8_t* bs_lo = smem + P.off_bs_lo;
+    ActArgs A;
+    A.act = smem_u32(act);
+    A.act_scale = smem_u32(act_scale);
+    A.bs_hi = smem_u32(bs_hi);
+    A.bs_lo = smem_u32(bs_lo);
+    A.act_stride = P.act_stride;
+    A.scale_stride = P.scale_stride;
+    A.bs_stride = P.bs_stride;
+
+    // cost-balanced contiguous share of the (token group, split, tile) sequence, cost = blocks streamed
+    const int tiles = P.N / TILE_N;
+    int gtot = 0;
+    for (int i = 0; i < P.E; ++i) gtot += (int)((s_offs[i + 1] - s_offs[i] + MT - 1) / MT);
+    const long long gcost = (long long)tiles * P.kb;
+    const long long ctot = gcost * gtot;
+    const long long lo = ctot * blockIdx.x / gridDim.x, hi = ctot * (blockIdx.x + 1) / gridDim.x;
+    if (lo >= hi) return;
+    const size_t ht_stride = (size_t)P.kb * F::HTB;  // bytes of one half-tile over the whole K
+
+    int e = 0, acc_groups = 0;
+    for (int gidx = (int)(lo / gcost); gidx <= (int)((hi - 1) / gcost); ++gidx) {
+        // (expert, token group) of gidx
+        while (e < P.E) {
+            const int ng = (int)((s_offs[e + 1] - s_offs[e] + MT - 1) / MT);
+            if (gidx < acc_groups + ng) break;
+            acc_groups += ng;
+            ++e;
+        }
+        if (e >= P.E) break;
+        const int grp = gidx - acc_groups;
+        const uint32_t p_base = s_offs[e] + (uint32_t)grp * MT;
+        const uint32_t p_end = min(s_offs[e + 1], p_base + MT);
+        const int ntiles = (int)(p_end - p_base + 7) / 8;
+        for (int sp = 0; sp < P.splits; ++sp) {
+            const int blk0 = P.blk_start[sp], nblk = P.blk_start[sp + 1] - blk0;
+            const long long ph_lo = (long long)gidx * gcost + (long long)tiles * blk0;
+            const long long ph_hi = ph_lo + (long long)tiles * nblk;
+            const long long a = lo > ph_lo ? lo : ph_lo, b = hi < ph_hi ? hi : ph_hi;
+            if (a >= b) continue;
+            const int tile_lo = (int)((a - ph_lo + nblk - 1) / nblk), tile_hi = (int)((b - ph_lo + nblk - 1) / nblk);
+            if (tile_lo >= tile_hi) continue;
+
+            // ---- make the token group's int8 rows, scales and block sums resident ----
+            __syncthreads();
+            if (tid < MT) {
+                const uint32_t pp = p_base + tid;
+                s_rows[tid] = pp < p_end ? (P.row_of ? (int)P.row_of[pp] : (int)pp) : -1;
+            }
+            __syncthreads();
+            {
+                const int vec_per_row = nblk * 16;
+#pragma unroll 4
+                for (int idx = tid; idx < MT * vec_per_row; idx += DIRECT_THREADS) {
+                    const int j = idx / vec_per_row, v = idx - j * vec_per_row;
+                    const int row = s_rows[j];
+                    int4 val = make_int4(0, 0, 0, 0);
+                    if (row >= 0) val = *reinterpret_cast<const int4*>(P.aq + (int64_t)row * P.K + (int64_t)blk0 * 256 + 16 * v);
+                    *reinterpret_cast<int4*>(act + j * P.act_stride + 16 * v) = val;
+                }
+                for (int idx = tid; idx < MT * nblk; idx += DIRECT_THREADS) {
+                    const int j = idx / nblk, bb = idx - j * nblk;
+                    const int row = s_rows[j];
+                    act_scale[j * P.scale_stride + bb] = row >= 0 ? P.ascale[(int64_t)row * P.kb + blk0 + bb] : 0.f;
+                }
+                const int per_row = nblk * F::BS_PER_BLOCK;
+                for (int idx = tid; idx < MT * per_row; idx += DIRECT_THREADS) {
+                    const int j = idx / per_row, bb = idx - j * per_row;
+                    const int row = s_rows[j];
+                    const int v = row >= 0 ? F::bs_value(P.absum + (int64_t)row * (P.K / 16) + blk0 * 16, bb) : 0;
+                    uint8_t h8, l8;
+                    F::bs_split(v, h8, l8);
+                    bs_lo[j * P.bs_stride + bb] = l8;
+                    bs_hi[j * P.bs_stride + bb] = h8;
+                }
+            }
+            __syncthreads();
+
+            // ---- every warp streams its own tiles over the whole K-range of this split ----
+            for (int tile = tile_lo + warp; tile < tile_hi; tile += DIRECT_WARPS) {
+                const uint8_t* hta;
+                const uint8_t* htb;
+                if (GATE_UP) {
+                    hta = P.wa.p[e] + (size_t)tile * ht_stride + (size_t)blk0 * F::HTB;
+                    htb = P.wb.p[e] + (size_t)tile * ht_stride + (size_t)blk0 * F::HTB;
+                } else {
+                    hta = P.wa.p[e] + (size_t)(2 * tile) * ht_stride + (size_t)blk0 * F::HTB;
+                    htb = hta + ht_stride;
+                }
+                float f[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) f[nt][i] = 0.f;
+                typename F::Frag cur, nxt;
+                F::load(cur, hta, htb, lane);
+                for (int bk = 0; bk < nblk; ++bk) {
+                    if (bk + 1 < nblk) F::load(nxt, hta + (size_t)(bk + 1) * F::HTB, htb + (size_t)(bk + 1) * F::HTB, lane);
+                    A.kblk_local = bk;
+                    if (NT == 1 || ntiles == 1)
+                        F::template compute<NT, 1>(cur, A, lane, f);
+                    else
+                        F::template compute<NT, NT>(cur, A, lane, f);
+                    cur = nxt;
+                }
+                const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const uint32_t p = p_base + nt * 8 + 2 * t + cc;
+                        if (p < p_end) {
+                            if (GATE_UP) {
+                                P.out[(int64_t)p * P.N + tile * 8 + g] = silu_f(f[nt][cc]) * f[nt][2 + cc];
+                            } else {
+                                float* o = P.out + (int64_t)sp * P.out_split_stride + (int64_t)p * P.N + tile * 16 + g;
+                                o[0] = f[nt][cc];
+                                o[8] = f[nt][2 + cc];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---- prepack kernels: one CTA per (half-tile, block) ----
+__global__ void __launch_bounds__(256) prepack_q4k_kernel(const uint8_t* __restrict__ raw, int kb, uint8_t* __restrict__ dst) {
+    const int ht = blockIdx.x / kb, blk = blockIdx.x - ht * kb;
+    const size_t row_bytes = (size_t)kb * Q4K_BYTES;
+    const uint8_t* src = raw + (size_t)ht * 8 * row_bytes + (size_t)blk * Q4K_BYTES;  // row g at + g * row_bytes
+    uint8_t* out = dst + ((size_t)ht * kb + blk) * Q4K_HTB;
+    const int w = threadIdx.x;  // output word 0..255 of the quant region
+    {
+        const int u = w >> 7, lane = (w >> 2) & 31, cw = w & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const int grp = 2 * u + (cw >> 1), isb = cw & 1;
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + (size_t)g * row_bytes + 16 + 32 * grp + 16 * isb + 4 * t);
+        reinterpret_cast<uint32_t*>(out)[w] = v;
+    }
+    if (w < 8) reinterpret_cast<uint32_t*>(out + 1024)[w] = *reinterpret_cast<const uint32_t*>(src + (size_t)w * row_bytes);
+    if (w < 64) {
+        const int g = w >> 3, j = w & 7;
+        int sc, m;
+        q4k_scale_min(j, src + (size_t)g * row_bytes + 4, sc, m);
+        out[1056 + w] = (uint8_t)sc;
+        out[1120 + w] = (uint8_t)m;
+    }
+}
+
+__global__ void __launch_bounds__(384) prepack_q6k_kernel(const uint8_t* __restrict__ raw, int kb, uint8_t* __restrict__ dst) {
+    const int ht = blockIdx.x / kb, blk = blockIdx.x - ht * kb;
+    const size_t row_bytes = (size_t)kb * Q6K_BYTES;
+    const uint8_t* src = raw + (size_t)ht * 8 * row_bytes + (size_t)blk * Q6K_BYTES;
+    uint8_t* out = dst + ((size_t)ht * kb + blk) * Q6K_HTB;
+    const int w = threadIdx.x;  // output word 0..383
+    {
+        const int u = w >> 7, lane = (w >> 2) & 31, cw = w & 3;
+        const int g = lane >> 2, t = lane & 3;
+        int off;
+        if (u < 2)
+            off = 64 * u + 32 * (cw >> 1) + 16 * (cw & 1) + 4 * t;  // ql, half u, xo = cw >> 1, lr = cw & 1
+        else
+            off = 128 + 32 * (cw >> 1) + 16 * (cw & 1) + 4 * t;     // qh, half cw >> 1, lr = cw & 1
+        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src + (size_t)g * row_bytes + off);
+        reinterpret_cast<uint32_t*>(out)[w] = (uint32_t)s16[0] | ((uint32_t)s16[1] << 16);
+    }
+    if (w < 128) out[1536 + w] = src[(size_t)(w >> 4) * row_bytes + 192 + (w & 15)];
+    if (w < 8) reinterpret_cast<uint16_t*>(out + 1664)[w] = *reinterpret_cast<const uint16_t*>(src + (size_t)w * row_bytes + 208);
+}
+
+int g_dir_max_smem = -1, g_dir_sms = -1;
+
+template <class F, bool GATE_UP, int NT>
+cudaError_t launch_dir(cudaStream_t st, const DirectParams& P, size_t smem_bytes) {
+    auto kfn = expert_direct_kernel<F, GATE_UP, NT>;
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    if (e != cudaSuccess) return e;
+    kfn<<<g_dir_sms, DIRECT_THREADS, smem_bytes, st>>>(P);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t prepacked_bytes(int dtype, int64_t n_rows, int k) {
+    if (k % 256 || n_rows % 8) return 0;
+    const size_t htb = dtype == CANDLE_GGML_Q4K ? Q4K_HTB : (dtype == CANDLE_GGML_Q6K ? Q6K_HTB : 0);
+    return (size_t)(n_rows / 8) * (size_t)(k / 256) * htb;
+}
+
+cudaError_t launch_prepack(cudaStream_t st, int dtype, const void* raw, int64_t n_rows, int k, void* dst) {
+    const int kb = k / 256;
+    const unsigned grid = (unsigned)((n_rows / 8) * kb);
+    if (grid == 0) return cudaSuccess;
+    if (dtype == CANDLE_GGML_Q4K)
+        prepack_q4k_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(raw), kb, static_cast<uint8_t*>(dst));
+    else if (dtype == CANDLE_GGML_Q6K)
+        prepack_q6k_kernel<<<grid, 384, 0, st>>>(static_cast<const uint8_t*>(raw), kb, static_cast<uint8_t*>(dst));
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+// Plans and launches the prepacked-weight kernel; cudaErrorNotSupported when the shape is not taken.
+cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
+                                 int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
+                                 int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
+                                 const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
+                                 int max_splits) {
+    if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return cudaErrorNotSupported;
+    const int tile_n = gate_up ? 8 : 16;
+    if (N % tile_n != 0 || K % 256 != 0) return cudaErrorNotSupported;
+    if (g_dir_max_smem < 0) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&g_dir_max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (e != cudaSuccess) return e;
+        e = cudaDeviceGetAttribute(&g_dir_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+    }
+    const int kb = K / 256;
+    const int NT = max_rows_per_expert <= 8 ? 1 : 2;
+    const int MT = 8 * NT;
+    const int bs_per_block = dtype == CANDLE_GGML_Q4K ? 8 : 16;
+    DirectParams P{};
+    P.wa = wa;
+    P.wb = wb;
+    for (int splits = 1; splits <= max_splits && splits <= kb; ++splits) {
+        if (gate_up && splits > 1) break;
+        const int ks_blocks = (kb + splits - 1) / splits;
+        uint32_t off = 0;
+        auto take = [&](uint32_t bytes) {
+            off = (off + 127u) & ~127u;
+            const uint32_t o = off;
+            off += bytes;
+            return o;
+        };
+        P.act_stride = ks_blocks * 256 + 16;
+        P.scale_stride = ks_blocks;
+        P.bs_stride = ks_blocks * bs_per_block + 16;
+        while ((P.bs_stride / 4) % 8 != 4) P.bs_stride += 4;
+        P.off_act = take((uint32_t)MT * P.act_stride);
+        P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
+        P.off_bs_hi = take((uint32_t)MT * P.bs_stride);
+        P.off_bs_lo = take((uint32_t)MT * P.bs_stride);
+        if ((int)off > g_dir_max_smem - 1024) continue;
+        P.splits = splits;
+        int bs = 0;
+        for (int s = 0; s < splits; ++s) {
+            P.blk_start[s] = bs;
+            const int rem = kb - bs, rs = splits - s;
+            bs += (rem + rs - 1) / rs;
+        }
+        P.blk_start[splits] = kb;
+        P.offsets = offsets;
+        P.row_of = row_of;
+        P.aq = aq;
+        P.ascale = ascale;
+        P.absum = absum;
+        P.out = out;
+        P.out_split_stride = split_stride;
+        P.E = E;
+        P.K = K;
+        P.N = N;
+        P.kb = kb;
+        P.MT = MT;
+        if (n_splits_out) *n_splits_out = splits;
+        if (dtype == CANDLE_GGML_Q4K) {
+            if (gate_up) return NT == 1 ? launch_dir<DirQ4K, true, 1>(st, P, off) : launch_dir<DirQ4K, true, 2>(st, P, off);
+            return NT == 1 ? launch_dir<DirQ4K, false, 1>(st, P, off) : launch_dir<DirQ4K, false, 2>(st, P, off);
+        }
+        if (gate_up) return NT == 1 ? launch_dir<DirQ6K, true, 1>(st, P, off) : launch_dir<DirQ6K, true, 2>(st, P, off);
+        return NT == 1 ? launch_dir<DirQ6K, false, 1>(st, P, off) : launch_dir<DirQ6K, false, 2>(st, P, off);
+    }
+    return cudaErrorNotSupported;
+}
+
+}  // namespace cmoe

@@ -103,6 +103,16 @@ class MlpOrMoe:
     def moe(cls, n_expert_used: int, feed_forward_gate_inp: torch.Tensor, experts: List[Mlp], **kw) -> "MlpOrMoe":
         return cls(n_expert_used, feed_forward_gate_inp, experts, **kw)
 
+    def prepack(self) -> "MlpOrMoe":
+        """Make the optional decode-path copies of every expert matrix (one-time, doubles the weight
+        memory of this block).  Batches of up to 64 rows then read the prepacked copies."""
+        E = len(self.experts)
+        self._p1 = self._arr(*[m.feed_forward_w1.inner.prepack().data_ptr() for m in self.experts])
+        self._p3 = self._arr(*[m.feed_forward_w3.inner.prepack().data_ptr() for m in self.experts])
+        self._p2 = self._arr(*[m.feed_forward_w2.inner.prepack().data_ptr() for m in self.experts])
+        self._cw.w1_prepacked, self._cw.w3_prepacked, self._cw.w2_prepacked = self._p1, self._p3, self._p2
+        return self
+
     @property
     def n_experts(self) -> int:
         return len(self.experts)

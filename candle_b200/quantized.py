@@ -91,6 +91,22 @@ class QTensor:
     def device_ptr(self) -> int:
         return self.data.data_ptr()
 
+    def prepack(self) -> torch.Tensor:
+        """Decode-path copy in register-fragment order (`candle_moe_prepack`); cached on the tensor."""
+        if getattr(self, "_prepacked", None) is None:
+            import ctypes as C
+            n, k = self._shape
+            need = C.c_size_t(0)
+            _lib.check("candle_moe_prepacked_bytes",
+                       _lib.load().candle_moe_prepacked_bytes(int(self._dtype), n, k, C.byref(need)))
+            out = torch.empty(need.value, dtype=torch.uint8, device=self.data.device)
+            with torch.cuda.device(self.data.device):
+                st = _lib.load().candle_moe_prepack(_stream_ptr(self.data.device), int(self._dtype), self.data.data_ptr(),
+                                                    n, k, out.data_ptr())
+            _lib.check("candle_moe_prepack", st)
+            self._prepacked = out
+        return self._prepacked
+
     def dequantize(self) -> torch.Tensor:
         """`QTensor::dequantize` (mod.rs:349-353)."""
         n, k = self._shape

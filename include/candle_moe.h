@@ -77,6 +77,12 @@ typedef struct candle_moe_weights {
     const void* shared_w3;
     const void* shared_w2;        /* device, [d_model, d_ff_shared] */
     const float* shared_gate;     /* device f32 [d_model] (shared_expert_gate) */
+    /* Optional decode-path copies made by candle_moe_prepack (host arrays of device pointers, or
+     * NULL): when all three are given, batches of up to 64 rows read these instead of the GGUF
+     * blocks.  The GGUF pointers above stay required (larger batches use them). */
+    const void* const* w1_prepacked;
+    const void* const* w3_prepacked;
+    const void* const* w2_prepacked;
 } candle_moe_weights_t;
 
 /* Library identification: returns a static string "candle_moe_sm100 <version>". */
@@ -179,6 +185,29 @@ CANDLE_MOE_API int candle_moe_forward_static(void* stream, const candle_moe_weig
  * perm_token [T*k].  Any output pointer may be NULL. */
 CANDLE_MOE_API int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,
                                float** topk_w, uint32_t** expert_counts, uint32_t** perm_token);
+
+/* One-time repack of a Q4_K / Q6_K matrix [n_rows, k] (n_rows a multiple of 8 -- 16 for w2 --, k a
+ * multiple of 256) into the register-fragment order the decode kernels read with coalesced
+ * 128-bit loads.  Q4_K grows by 2.8 % (its 12-byte packed 6-bit scales are widened to 16 bytes),
+ * Q6_K keeps its size.  No counterpart in the reference, whose kernels read the GGUF layout
+ * directly (candle-kernels/src/quantized.cu:2626-2698); optional here as well.
+ *   candle_moe_prepacked_bytes: size of the destination buffer (0 bytes = shape or dtype not supported)
+ *   candle_moe_prepack: src raw blocks -> dst, both device memory, 16-byte aligned */
+CANDLE_MOE_API int candle_moe_prepacked_bytes(int32_t dtype, int64_t n_rows, int32_t k, size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_prepack(void* stream, int32_t dtype, const void* src_blocks, int64_t n_rows, int32_t k,
+                                      void* dst);
+
+/* The grouped expert products over prepacked weights (same contracts as candle_moe_grouped_gate_up /
+ * candle_moe_grouped_down; at most 64 rows per expert; CANDLE_MOE_E_SHAPE when the shape is not taken). */
+CANDLE_MOE_API int candle_moe_grouped_gate_up_prepacked(void* stream, const void* const* w1p, const void* const* w3p,
+                                                        int32_t dtype, int32_t E, int32_t d, int32_t ff,
+                                                        const uint32_t* expert_offsets, const uint32_t* row_of,
+                                                        int64_t max_rows, const int8_t* xq, const float* xscales,
+                                                        const int16_t* xbsums, float* hidden);
+CANDLE_MOE_API int candle_moe_grouped_down_prepacked(void* stream, const void* const* w2p, int32_t dtype, int32_t E,
+                                                     int32_t d, int32_t ff, const uint32_t* expert_offsets,
+                                                     int64_t max_rows, const int8_t* hq, const float* hscales,
+                                                     const int16_t* hbsums, float* out);
 
 /* Health word of the device-side kernels.  Every wait inside a kernel (on a copy in flight) has an
  * iteration limit; a kernel whose wait expired raises bit 0 here and finishes without hanging.

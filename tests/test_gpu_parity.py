@@ -324,11 +324,67 @@ def test_streaming_form_equals_row_form(orc, torch_cuda, name, rows_per_expert, 
         assert H.rel_l2(outs[mode], want) < 2e-6 and H.max_rel(outs[mode], want) < 1e-5, f"mode {mode}"
 
 
+@pytest.mark.parametrize("name,rows_per_expert,k,n,gate_up", [
+    ("Q4K", [3, 0, 8, 1], 4096, 64, True), ("Q4K", [16, 5], 1024, 48, True), ("Q4K", [37, 2, 9], 2048, 32, True),
+    ("Q4K", [7, 1, 0, 12], 3584, 64, False), ("Q6K", [5, 8, 0, 1], 14336, 64, False), ("Q6K", [16, 23], 2048, 32, False),
+    ("Q6K", [3, 4], 4096, 32, True), ("Q4K", [1], 6144, 128, True), ("Q6K", [9], 4096, 32, False), ("Q4K", [64], 512, 16, False)])
+def test_prepacked_form_matches_oracle(orc, torch_cuda, name, rows_per_expert, k, n, gate_up):
+    """Decode kernels over the prepacked (register-fragment order) copy of the weights: same integers
+    as the oracle's vec_dot, f32 sums in a different order."""
+    torch = torch_cuda
+    from candle_b200 import GgmlDType, QTensor, _lib
+    L = _lib.load()
+    dt = getattr(orc, name)
+    E = len(rows_per_expert)
+    rng = np.random.default_rng(k + n + E + 1)
+    P = int(sum(rows_per_expert))
+    x = rng.standard_normal((P, k), dtype=np.float32)
+    wa = [orc.quantize(dt, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)) for _ in range(E)]
+    wb = [orc.quantize(dt, rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)) for _ in range(E)]
+    offs_h = np.concatenate([[0], np.cumsum(rows_per_expert)]).astype(np.int32)
+    perm_h = rng.permutation(P).astype(np.int32)
+    xd = torch.from_numpy(x).cuda()
+    qa = [QTensor.from_blocks(w, GgmlDType(dt), (n, k)) for w in wa]
+    qb = [QTensor.from_blocks(w, GgmlDType(dt), (n, k)) for w in wb]
+    qs = torch.empty((P, k), dtype=torch.int8, device="cuda")
+    sc = torch.empty((P, k // 256), dtype=torch.float32, device="cuda")
+    bs = torch.empty((P, k // 16), dtype=torch.int16, device="cuda")
+    offs = torch.from_numpy(offs_h).cuda()
+    perm = torch.from_numpy(perm_h).cuda()
+    st = _st(torch)
+    assert L.candle_moe_quantize_act(st, xd.data_ptr(), P, k, dt, qs.data_ptr(), sc.data_ptr(), bs.data_ptr()) == 0
+    pa = (C.c_void_p * E)(*[q.prepack().data_ptr() for q in qa])
+    pb = (C.c_void_p * E)(*[q.prepack().data_ptr() for q in qb])
+    out = torch.full((P, n), float("nan"), dtype=torch.float32, device="cuda")
+    if gate_up:
+        rc = L.candle_moe_grouped_gate_up_prepacked(st, pa, pb, dt, E, k, n, offs.data_ptr(), perm.data_ptr(),
+                                                    min(64, max(rows_per_expert)), qs.data_ptr(), sc.data_ptr(), bs.data_ptr(),
+                                                    out.data_ptr())
+    else:
+        rc = L.candle_moe_grouped_down_prepacked(st, pa, dt, E, n, k, offs.data_ptr(), min(64, max(rows_per_expert)),
+                                                 qs.data_ptr(), sc.data_ptr(), bs.data_ptr(), out.data_ptr())
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = np.empty((P, n), np.float32)
+    for e in range(E):
+        for p in range(offs_h[e], offs_h[e + 1]):
+            row = x[perm_h[p]] if gate_up else x[p]
+            a = orc.matmul(dt, row[None, :], wa[e], n)[0]
+            if gate_up:
+                a = orc.silu(a) * orc.matmul(dt, row[None, :], wb[e], n)[0]
+            want[p] = a
+    assert np.isfinite(got).all(), "rows not written"
+    assert H.rel_l2(got, want) < 2e-6 and H.max_rel(got, want) < 1e-5
+
+
 # ------------------------------------------------------------------------------------------------
 # the whole block
 # ------------------------------------------------------------------------------------------------
-def _run_block(orc, torch, mw, x):
+def _run_block(orc, torch, mw, x, prepack=False):
     blk = H.device_block(orc, mw)
+    if prepack:
+        blk.prepack()
     y = blk.forward(torch.from_numpy(x).cuda().reshape(1, x.shape[0], x.shape[1]))
     assert y.shape == (1, x.shape[0], x.shape[1])
     T = x.shape[0]
@@ -336,10 +392,10 @@ def _run_block(orc, torch, mw, x):
     return blk, y.reshape(T, -1).cpu().numpy(), ids.numpy().astype(np.uint32), tw.numpy(), counts.numpy(), perm.numpy()
 
 
-def _check_block(orc, torch, mw, x, label=""):
+def _check_block(orc, torch, mw, x, label="", prepack=False):
     ref = orc.moe_forward(mw, x)
     probs, _, _ = orc.router_topk(x, mw.router, mw.top_k, mw.renorm, mw.router_bias)
-    blk, y, ids, tw, counts, perm = _run_block(orc, torch, mw, x)
+    blk, y, ids, tw, counts, perm = _run_block(orc, torch, mw, x, prepack)
     n_tie = H.check_routing(probs, ref.topk_ids, ids)
     if n_tie == 0:
         assert np.array_equal(counts, ref.expert_counts), label
@@ -356,11 +412,12 @@ def _check_block(orc, torch, mw, x, label=""):
     return blk, y, ref
 
 
+@pytest.mark.parametrize("prepack", [False, True])
 @pytest.mark.parametrize("T", [1, 2, 8, 37])
-def test_block_small_ragged_q4k_q6k(orc, torch_cuda, T):
-    mw = orc.make_moe_weights(10, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+def test_block_small_ragged_q4k_q6k(orc, torch_cuda, T, prepack):
+    mw = orc.make_moe_weights(10, 512, 2048, 8, 2, orc.Q4K, orc.Q6K)
     x = orc.make_activations(20 + T, T, 512)
-    _check_block(orc, torch_cuda, mw, x, f"small T={T}")
+    _check_block(orc, torch_cuda, mw, x, f"small T={T} prepack={prepack}", prepack)
 
 
 def test_block_config1_shape(orc, torch_cuda):
@@ -408,10 +465,14 @@ def test_block_mixtral_layer_decode_sizes(orc, torch_cuda):
     router = (np.random.default_rng(0).standard_normal((E, d), dtype=np.float32) * np.float32(0.02))
     blk = MlpOrMoe.moe(k, torch.from_numpy(router).cuda(), experts)
     mw = orc.MoeWeights(d, ff, k, orc.Q4K, orc.Q6K, router, host["w1"], host["w3"], host["w2"])
-    for T in (1, 8, 32):
+    for T in (1, 8, 32, 1, 8, 32):
+        if T == 1 and blk._cw.w1_prepacked:
+            pass
         x = orc.make_activations(1, T, d)
         ref = orc.moe_forward(mw, x)
         y = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+        if T == 32:
+            blk.prepack()  # second round: the same sizes over the prepacked copies
         ids, tw, counts, perm = blk.last_routing(T)
         probs, _, _ = orc.router_topk(x, router, k)
         assert H.check_routing(probs, ref.topk_ids, ids.numpy().astype(np.uint32)) == 0
