@@ -9,7 +9,7 @@ using namespace cmoe;
 
 namespace {
 
-constexpr int MAX_K_SPLITS = 4;  // partial outputs the down product may leave for the combine kernel
+constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Only the decode-sized streaming form splits K; larger batches get a single output slot.
 inline int k_split_slots(int64_t T) { return T <= 64 ? MAX_K_SPLITS : 1; }
 

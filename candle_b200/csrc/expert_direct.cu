@@ -3,10 +3,12 @@
 // A one-time repack (candle_moe_prepack) lays every 8-row x 256-element piece of a Q4_K / Q6_K
 // matrix out in the order the tensor-core fragments want it, so that in the hot loop every lane
 // fetches its share of a block with a few fully coalesced 128-bit loads straight into registers:
-// no shared-memory staging of weights, no K-split across warps, no cross-warp reduction.  Each warp
+// no K-split across warps, no cross-warp reduction, no CTA-wide barrier in the hot loop.  Each warp
 // owns a 16-row MMA tile (gate_up: 8 rows of W1 and the same 8 rows of W3) over the whole K-range
-// and keeps the next block's loads in flight while it multiplies the current one.  Only the int8
-// activations of the expert's rows live in shared memory (read with ldmatrix).
+// and runs a private ring of a few blocks in shared memory filled by 16-byte cp.async copies, so
+// that several blocks per warp (> 100 KB per SM) are in flight while it multiplies the current one;
+// the fragments come back out of the ring with conflict-free 128-bit shared loads.  The int8
+// activations of the expert's rows also live in shared memory (read with ldmatrix).
 //
 // The arithmetic is the one of the streaming kernel (expert_stream.cu): exact integer sub-block
 // dots on mma.sync s8, sub-block scales in int32, block scales in f32, i.e. the integers of the
@@ -32,27 +34,6 @@ constexpr int Q6K_HTB = 1680;
 constexpr int DIRECT_WARPS = 16;
 constexpr int DIRECT_THREADS = 32 * DIRECT_WARPS;
 
-__device__ __forceinline__ uint4 ldg128_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg64_stream(const uint8_t* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg32_stream(const uint8_t* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg16_stream(const uint8_t* p) {
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return (uint32_t)v;
-}
-
 // Shared-memory side of a block product (32-bit shared-window addresses)
 struct ActArgs {
     uint32_t act, act_scale, bs_hi, bs_lo;
@@ -74,18 +55,19 @@ struct DirQ4K {
         uint32_t dmA, dmB;   // f16 d | f16 dmin
         uint2 scA, scB, mA, mB;
     };
-    __device__ static __forceinline__ void load(Frag& F, const uint8_t* hta, const uint8_t* htb, int lane) {
+    // hta / htb: shared-window addresses of the two half-tile blocks inside the warp's ring slot
+    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, uint32_t htb, int lane) {
         const int g = lane >> 2;
-        F.qa[0] = ldg128_stream(hta + lane * 16);
-        F.qa[1] = ldg128_stream(hta + 512 + lane * 16);
-        F.qb[0] = ldg128_stream(htb + lane * 16);
-        F.qb[1] = ldg128_stream(htb + 512 + lane * 16);
-        F.dmA = ldg32_stream(hta + 1024 + 4 * g);
-        F.dmB = ldg32_stream(htb + 1024 + 4 * g);
-        F.scA = ldg64_stream(hta + 1056 + 8 * g);
-        F.scB = ldg64_stream(htb + 1056 + 8 * g);
-        F.mA = ldg64_stream(hta + 1120 + 8 * g);
-        F.mB = ldg64_stream(htb + 1120 + 8 * g);
+        F.qa[0] = lds128(hta + lane * 16);
+        F.qa[1] = lds128(hta + 512 + lane * 16);
+        F.qb[0] = lds128(htb + lane * 16);
+        F.qb[1] = lds128(htb + 512 + lane * 16);
+        F.dmA = lds32(hta + 1024 + 4 * g);
+        F.dmB = lds32(htb + 1024 + 4 * g);
+        F.scA = lds64(hta + 1056 + 8 * g);
+        F.scB = lds64(htb + 1056 + 8 * g);
+        F.mA = lds64(hta + 1120 + 8 * g);
+        F.mB = lds64(htb + 1120 + 8 * g);
     }
     template <int NT, int NTL>
     __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
@@ -162,18 +144,18 @@ struct DirQ6K {
         uint4 scA, scB;        // 16 int8 scales
         uint32_t dA, dB;       // f16 d
     };
-    __device__ static __forceinline__ void load(Frag& F, const uint8_t* hta, const uint8_t* htb, int lane) {
+    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, uint32_t htb, int lane) {
         const int g = lane >> 2;
-        F.qlA[0] = ldg128_stream(hta + lane * 16);
-        F.qlA[1] = ldg128_stream(hta + 512 + lane * 16);
-        F.qhA = ldg128_stream(hta + 1024 + lane * 16);
-        F.qlB[0] = ldg128_stream(htb + lane * 16);
-        F.qlB[1] = ldg128_stream(htb + 512 + lane * 16);
-        F.qhB = ldg128_stream(htb + 1024 + lane * 16);
-        F.scA = ldg128_stream(hta + 1536 + 16 * g);
-        F.scB = ldg128_stream(htb + 1536 + 16 * g);
-        F.dA = ldg16_stream(hta + 1664 + 2 * g);
-        F.dB = ldg16_stream(htb + 1664 + 2 * g);
+        F.qlA[0] = lds128(hta + lane * 16);
+        F.qlA[1] = lds128(hta + 512 + lane * 16);
+        F.qhA = lds128(hta + 1024 + lane * 16);
+        F.qlB[0] = lds128(htb + lane * 16);
+        F.qlB[1] = lds128(htb + 512 + lane * 16);
+        F.qhB = lds128(htb + 1024 + lane * 16);
+        F.scA = lds128(hta + 1536 + 16 * g);
+        F.scB = lds128(htb + 1536 + 16 * g);
+        F.dA = lds16(hta + 1664 + 2 * g);
+        F.dB = lds16(htb + 1664 + 2 * g);
     }
     __device__ static __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
@@ -267,12 +249,13 @@ struct DirectParams {
     float* out;
     int64_t out_split_stride;
     int E, K, N, kb, splits, MT;
-    int blk_start[5];  // split s covers blocks [blk_start[s], blk_start[s + 1])
+    int blk_start[9];  // split s covers blocks [blk_start[s], blk_start[s + 1])
     int act_stride, scale_stride, bs_stride;
-    uint32_t off_act, off_scale, off_bs_hi, off_bs_lo;
+    uint32_t off_act, off_scale, off_bs_hi, off_bs_lo, off_ring;
 };
 
-template <class F, bool GATE_UP, int NT>
+// DEPTH = ring slots per warp (DEPTH - 1 blocks in flight while one is multiplied)
+template <class F, bool GATE_UP, int NT, int DEPTH>
 __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const __grid_constant__ DirectParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
@@ -295,6 +278,9 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
     A.act_stride = P.act_stride;
     A.scale_stride = P.scale_stride;
     A.bs_stride = P.bs_stride;
+    constexpr int SLOT_BYTES = 2 * F::HTB;       // both half-tile blocks of one K-block
+    constexpr int VEC_PER_HT = F::HTB / 16;      // 16-byte vectors per half-tile block
+    const uint32_t ring = smem_u32(smem + P.off_ring) + (uint32_t)warp * (DEPTH * SLOT_BYTES);
 
     // cost-balanced contiguous share of the (token group, split, tile) sequence, cost = blocks streamed
     const int tiles = P.N / TILE_N;
@@ -380,16 +366,35 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) f[nt][i] = 0.f;
-                typename F::Frag cur, nxt;
-                F::load(cur, hta, htb, lane);
+                // fill one ring slot with block bk of both half-tiles (16-byte cp.async per lane)
+                auto issue = [&](int bk) {
+                    if (bk < nblk) {
+                        const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
+                        const uint8_t* sa = hta + (size_t)bk * F::HTB;
+                        const uint8_t* sb = htb + (size_t)bk * F::HTB;
+                        for (int v = lane; v < 2 * VEC_PER_HT; v += 32) {
+                            const bool second = v >= VEC_PER_HT;
+                            const int vv = second ? v - VEC_PER_HT : v;
+                            cp_async16(slot + 16 * v, (second ? sb : sa) + 16 * vv);
+                        }
+                    }
+                    cp_async_commit();  // one group per block, empty past the end: the count stays in step
+                };
+                __syncwarp();  // the previous tile's last slot reads are done in every lane
+#pragma unroll
+                for (int i = 0; i < DEPTH - 1; ++i) issue(i);
                 for (int bk = 0; bk < nblk; ++bk) {
-                    if (bk + 1 < nblk) F::load(nxt, hta + (size_t)(bk + 1) * F::HTB, htb + (size_t)(bk + 1) * F::HTB, lane);
+                    cp_async_wait<DEPTH - 2>();  // this lane's copies of block bk have landed
+                    __syncwarp();                // ... and everyone else's; slot (bk - 1) % DEPTH is free again
+                    issue(bk + DEPTH - 1);
+                    typename F::Frag cur;
+                    const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
+                    F::load(cur, slot, slot + F::HTB, lane);
                     A.kblk_local = bk;
                     if (NT == 1 || ntiles == 1)
                         F::template compute<NT, 1>(cur, A, lane, f);
                     else
                         F::template compute<NT, NT>(cur, A, lane, f);
-                    cur = nxt;
                 }
                 const int g = lane >> 2, t = lane & 3;
 #pragma unroll
@@ -460,9 +465,9 @@ __global__ void __launch_bounds__(384) prepack_q6k_kernel(const uint8_t* __restr
 
 int g_dir_max_smem = -1, g_dir_sms = -1;
 
-template <class F, bool GATE_UP, int NT>
+template <class F, bool GATE_UP, int NT, int DEPTH>
 cudaError_t launch_dir(cudaStream_t st, const DirectParams& P, size_t smem_bytes) {
-    auto kfn = expert_direct_kernel<F, GATE_UP, NT>;
+    auto kfn = expert_direct_kernel<F, GATE_UP, NT, DEPTH>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (e != cudaSuccess) return e;
     kfn<<<g_dir_sms, DIRECT_THREADS, smem_bytes, st>>>(P);
@@ -533,6 +538,10 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
         P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
         P.off_bs_hi = take((uint32_t)MT * P.bs_stride);
         P.off_bs_lo = take((uint32_t)MT * P.bs_stride);
+        // per-warp rings of DEPTH K-blocks: 4 slots for Q4_K (2368 B each), 3 for Q6_K (3360 B each)
+        const int depth = dtype == CANDLE_GGML_Q4K ? 4 : 3;
+        const uint32_t slot_bytes = 2u * (dtype == CANDLE_GGML_Q4K ? Q4K_HTB : Q6K_HTB);
+        P.off_ring = take((uint32_t)DIRECT_WARPS * depth * slot_bytes);
         if ((int)off > g_dir_max_smem - 1024) continue;
         P.splits = splits;
         int bs = 0;
@@ -556,11 +565,11 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
         P.MT = MT;
         if (n_splits_out) *n_splits_out = splits;
         if (dtype == CANDLE_GGML_Q4K) {
-            if (gate_up) return NT == 1 ? launch_dir<DirQ4K, true, 1>(st, P, off) : launch_dir<DirQ4K, true, 2>(st, P, off);
-            return NT == 1 ? launch_dir<DirQ4K, false, 1>(st, P, off) : launch_dir<DirQ4K, false, 2>(st, P, off);
+            if (gate_up) return NT == 1 ? launch_dir<DirQ4K, true, 1, 4>(st, P, off) : launch_dir<DirQ4K, true, 2, 4>(st, P, off);
+            return NT == 1 ? launch_dir<DirQ4K, false, 1, 4>(st, P, off) : launch_dir<DirQ4K, false, 2, 4>(st, P, off);
         }
-        if (gate_up) return NT == 1 ? launch_dir<DirQ6K, true, 1>(st, P, off) : launch_dir<DirQ6K, true, 2>(st, P, off);
-        return NT == 1 ? launch_dir<DirQ6K, false, 1>(st, P, off) : launch_dir<DirQ6K, false, 2>(st, P, off);
+        if (gate_up) return NT == 1 ? launch_dir<DirQ6K, true, 1, 3>(st, P, off) : launch_dir<DirQ6K, true, 2, 3>(st, P, off);
+        return NT == 1 ? launch_dir<DirQ6K, false, 1, 3>(st, P, off) : launch_dir<DirQ6K, false, 2, 3>(st, P, off);
     }
     return cudaErrorNotSupported;
 }
