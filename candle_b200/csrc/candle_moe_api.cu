@@ -235,9 +235,12 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t Tk = T * k;
 
-    CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w)));
+    // k-quant experts: the router kernel also quantizes x (Q8K); Q8_0 experts keep the separate pass
+    const bool fuse_q = w->dtype_w13 != CANDLE_GGML_Q8_0;
+    CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w,
+                                 fuse_q ? ws.xq : nullptr, fuse_q ? ws.xs : nullptr, fuse_q ? ws.xb : nullptr)));
     CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
-    CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
+    if (!fuse_q) CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
     // a token selects an expert at most once: no expert sees more than T rows
     const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && T <= 64;
     int eo_splits = 1, so_splits = 1;

@@ -58,15 +58,97 @@ __device__ __forceinline__ void q4k_scale_min(int j, const uint8_t* q, int& sc, 
     }
 }
 
+// BlockQ8K::from_float (candle-core/src/quantized/k_quants.rs:1819-1856) for one 256-element block
+// by one warp, 8 consecutive elements per lane.  `max` is the signed value of the first element with
+// the largest magnitude; IEEE division, roundf = round half away from zero like f32::round.
+__device__ __forceinline__ void quantize_q8k_block(const float* __restrict__ xblk, int lane, int8_t* __restrict__ qs,
+                                                   float* __restrict__ scale, int16_t* __restrict__ bsums) {
+    const float4* src = reinterpret_cast<const float4*>(xblk) + lane * 2;
+    const float4 a = src[0], b = src[1];
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float amax = 0.f, mx = 0.f;
+    int idx = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (amax < fabsf(v[i])) {
+            amax = fabsf(v[i]);
+            mx = v[i];
+            idx = i;
+        }
+    }
+    idx += lane * 8;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        if (oa > amax || (oa == amax && oi < idx)) {
+            amax = oa;
+            idx = oi;
+            mx = om;
+        }
+    }
+    int q[8];
+    float d;
+    if (amax == 0.f) {
+        d = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = 0;
+    } else {
+        const float iscale = __fdiv_rn(-128.0f, mx);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = (int)fminf(roundf(__fmul_rn(iscale, v[i])), 127.f);
+        d = __fdiv_rn(1.0f, iscale);
+    }
+    int s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += q[i];
+    s += __shfl_xor_sync(0xffffffffu, s, 1);  // 16 elements = two lanes
+    const uint32_t lo = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
+                        ((uint32_t)(q[3] & 0xff) << 24);
+    const uint32_t hi = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
+                        ((uint32_t)(q[7] & 0xff) << 24);
+    reinterpret_cast<uint2*>(qs)[lane] = make_uint2(lo, hi);
+    if ((lane & 1) == 0) bsums[lane >> 1] = (int16_t)s;
+    if (lane == 0) *scale = d;
+}
+
 // candle-core/src/op.rs:645-648 and candle-nn/src/ops.rs:59-61; IEEE division, libm-grade expf.
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (expf(-v) + 1.0f); }
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Programmatic dependent launch.  Every kernel of the block starts with pdl_trigger() (the next
+// kernel in the stream may be made resident right away, hiding its launch latency) followed by
+// pdl_wait() (nothing produced by earlier kernels is touched before they have completed and
+// flushed).  Because every kernel waits before it exits, completion is transitive along the chain.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool pdl_enabled();  // CANDLE_MOE_PDL=0 turns the launch attribute off
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- launchers implemented in the other translation units (all enqueue on `st`) ----
+// qs / scales / bsums non-null: also quantize every row of x the Q8K way (fused, one pass over x)
 cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
-                               int d, int E, int k, int renorm, uint32_t* ids, float* w);
+                               int d, int E, int k, int renorm, uint32_t* ids, float* w, int8_t* qs = nullptr,
+                               float* scales = nullptr, int16_t* bsums = nullptr);
 cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
                            uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos);
 // offsets[0..2) = {0, rows}: one group holding every row (used for the always-on shared expert)

@@ -263,6 +263,8 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
     constexpr int MT = 8 * NT;
     constexpr int TILE_N = GATE_UP ? 8 : 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
     for (int i = tid; i <= P.E; i += DIRECT_THREADS) s_offs[i] = P.offsets[i];
     __syncthreads();
 
@@ -470,8 +472,7 @@ cudaError_t launch_dir(cudaStream_t st, const DirectParams& P, size_t smem_bytes
     auto kfn = expert_direct_kernel<F, GATE_UP, NT, DEPTH>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (e != cudaSuccess) return e;
-    kfn<<<g_dir_sms, DIRECT_THREADS, smem_bytes, st>>>(P);
-    return cudaGetLastError();
+    return launch_k(kfn, dim3(g_dir_sms), dim3(DIRECT_THREADS), smem_bytes, st, P);
 }
 
 }  // namespace

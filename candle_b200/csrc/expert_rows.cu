@@ -158,6 +158,8 @@ template <class Fmt, bool GATE_UP>
 __global__ void __launch_bounds__(ROWS_WARPS * 32)
 grouped_rows_kernel(ExpertPtrs wa, ExpertPtrs wb, int K, int N, const uint32_t* __restrict__ offsets,
                     const uint32_t* __restrict__ row_of, ActView act, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int e = blockIdx.y;
     const uint32_t p0 = offsets[e], p1 = offsets[e + 1];
     if (p0 == p1) return;
@@ -201,14 +203,11 @@ static cudaError_t launch_rows(cudaStream_t st, const ExpertPtrs& wa, const Expe
     dim3 block(ROWS_WARPS * 32);
     switch (dtype) {
         case CANDLE_GGML_Q4K:
-            grouped_rows_kernel<Q4KRow, GATE_UP><<<grid, block, 0, st>>>(wa, wb, K, N, offsets, row_of, act, out);
-            break;
+            return launch_k(grouped_rows_kernel<Q4KRow, GATE_UP>, grid, block, 0, st, wa, wb, K, N, offsets, row_of, act, out);
         case CANDLE_GGML_Q6K:
-            grouped_rows_kernel<Q6KRow, GATE_UP><<<grid, block, 0, st>>>(wa, wb, K, N, offsets, row_of, act, out);
-            break;
+            return launch_k(grouped_rows_kernel<Q6KRow, GATE_UP>, grid, block, 0, st, wa, wb, K, N, offsets, row_of, act, out);
         case CANDLE_GGML_Q8_0:
-            grouped_rows_kernel<Q80Row, GATE_UP><<<grid, block, 0, st>>>(wa, wb, K, N, offsets, row_of, act, out);
-            break;
+            return launch_k(grouped_rows_kernel<Q80Row, GATE_UP>, grid, block, 0, st, wa, wb, K, N, offsets, row_of, act, out);
         default:
             return cudaErrorInvalidValue;
     }

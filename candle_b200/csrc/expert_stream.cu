@@ -402,6 +402,8 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
     constexpr int N_CONS = 32 * CW;
     constexpr int TILE_N = GATE_UP ? 8 : 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
 
     for (int i = threadIdx.x; i <= P.E; i += blockDim.x) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
@@ -642,8 +644,7 @@ cudaError_t launch_one(cudaStream_t st, const StreamParams& P, size_t smem_bytes
     auto kfn = expert_stream_kernel<F, GATE_UP, NT, CW>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (e != cudaSuccess) return e;
-    kfn<<<g_num_sms, 32 * (1 + CW), smem_bytes, st>>>(P);
-    return cudaGetLastError();
+    return launch_k(kfn, dim3(g_num_sms), dim3(32 * (1 + CW)), smem_bytes, st, P);
 }
 
 template <class F, int CW>

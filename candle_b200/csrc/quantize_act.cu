@@ -13,62 +13,16 @@
 
 namespace cmoe {
 
-// BlockQ8K::from_float (k_quants.rs:1819-1856).  One warp per 256-element block, 8 consecutive
-// elements per lane.  `max` is the signed value of the first element with the largest magnitude.
+// BlockQ8K::from_float: one warp per 256-element block (quantize_q8k_block in common.cuh).
 __global__ void __launch_bounds__(256)
 quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __restrict__ qs,
                     float* __restrict__ scales, int16_t* __restrict__ bsums) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (blk >= n_blocks) return;
-    const float4* src = reinterpret_cast<const float4*>(x + blk * QK_K) + lane * 2;
-    const float4 a = src[0], b = src[1];
-    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float amax = 0.f, mx = 0.f;
-    int idx = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (amax < fabsf(v[i])) {
-            amax = fabsf(v[i]);
-            mx = v[i];
-            idx = i;
-        }
-    }
-    idx += lane * 8;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
-        if (oa > amax || (oa == amax && oi < idx)) {
-            amax = oa;
-            idx = oi;
-            mx = om;
-        }
-    }
-    int q[8];
-    float d;
-    if (amax == 0.f) {
-        d = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = 0;
-    } else {
-        const float iscale = -128.0f / mx;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = (int)fminf(roundf(iscale * v[i]), 127.f);
-        d = 1.0f / iscale;
-    }
-    int s = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s += q[i];
-    s += __shfl_xor_sync(0xffffffffu, s, 1);  // 16 elements = two lanes
-    uint32_t lo = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) |
-                  ((uint32_t)(q[3] & 0xff) << 24);
-    uint32_t hi = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) |
-                  ((uint32_t)(q[7] & 0xff) << 24);
-    reinterpret_cast<uint2*>(qs + blk * QK_K)[lane] = make_uint2(lo, hi);
-    if ((lane & 1) == 0) bsums[blk * 16 + (lane >> 1)] = (int16_t)s;
-    if (lane == 0) scales[blk] = d;
+    quantize_q8k_block(x + blk * QK_K, lane, qs + blk * QK_K, scales + blk, bsums + blk * 16);
 }
 
 // BlockQ8_0::from_float (k_quants.rs:605-634).  One warp per 8 blocks of 32: 4 lanes per block,
@@ -77,6 +31,8 @@ quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __res
 __global__ void __launch_bounds__(256)
 quantize_q8_0_kernel(const float* __restrict__ x, int64_t n_elems, int8_t* __restrict__ qs,
                      float* __restrict__ scales) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t grp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // 256 elements
     if (grp * 256 >= n_elems) return;
@@ -114,10 +70,8 @@ cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, i
     if (n256 == 0) return cudaSuccess;
     const unsigned grid = (unsigned)((n256 + 7) / 8);
     if (for_dtype == CANDLE_GGML_Q8_0)
-        quantize_q8_0_kernel<<<grid, 256, 0, st>>>(x, n, qs, scales);
-    else
-        quantize_q8k_kernel<<<grid, 256, 0, st>>>(x, n256, qs, scales, bsums);
-    return cudaGetLastError();
+        return launch_k(quantize_q8_0_kernel, dim3(grid), dim3(256), 0, st, x, n, qs, scales);
+    return launch_k(quantize_q8k_kernel, dim3(grid), dim3(256), 0, st, x, n256, qs, scales, bsums);
 }
 
 }  // namespace cmoe

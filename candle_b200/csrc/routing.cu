@@ -2,23 +2,39 @@
 // combine of the quantized MoE block.  All three are small, latency- or HBM-bound kernels.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace cmoe {
 
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("CANDLE_MOE_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
 // ------------------------------------------------------------------------------------------------
-// Router.  One CTA of 128 threads per token: the four warps split d with 128-bit loads, 8 experts
-// at a time; partial sums meet through warp shuffles and a 4-entry shared array.  Warp 0 then does
-// the softmax over all E experts and k rounds of arg-max with "lower expert id wins a tie", which
-// is what a stable descending sort followed by take(k) yields
-// (candle-transformers/src/models/quantized_llama.rs:162-179).
-// Arithmetic is plain f32 FMA (no TF32): the reference's router product is full f32.
+// Router (+ activation quantization).  One CTA of 1024 threads per token: for d = 4096 every thread
+// issues its single 128-bit load of x and its 8 loads of the router rows at once, so the whole
+// product costs about one memory latency; partial sums meet through warp shuffles and shared
+// memory in a fixed order.  Warp 0 then does the softmax over all E experts and k rounds of arg-max
+// with "lower expert id wins a tie", which is what a stable descending sort followed by take(k)
+// yields (candle-transformers/src/models/quantized_llama.rs:162-179).  Meanwhile the other warps
+// quantize the same row of x the Q8K way for the expert products (one pass over x instead of two
+// kernels).  Arithmetic is plain f32 FMA (no TF32): the reference's router product is full f32.
 // ------------------------------------------------------------------------------------------------
-constexpr int ROUTER_THREADS = 128;
+constexpr int ROUTER_THREADS = 1024;
+constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
 
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, const float* __restrict__ bias,
-                   int d, int E, int k, int renorm, uint32_t* __restrict__ ids, float* __restrict__ wout) {
+                   int d, int E, int k, int renorm, uint32_t* __restrict__ ids, float* __restrict__ wout,
+                   int8_t* __restrict__ qs, float* __restrict__ scales, int16_t* __restrict__ bsums) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float s_logits[CANDLE_MOE_MAX_EXPERTS];
-    __shared__ float s_part[ROUTER_THREADS / 32][8];
+    __shared__ float s_part[ROUTER_WARPS][8];
     const int64_t t = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float4* xr = reinterpret_cast<const float4*>(x + t * (int64_t)d);
@@ -48,13 +64,24 @@ router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, co
         }
         __syncthreads();
         if (tid < 8 && e0 + tid < E) {
-            float v = (s_part[0][tid] + s_part[1][tid]) + (s_part[2][tid] + s_part[3][tid]);
+            float v = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < ROUTER_WARPS; ++w8) v += s_part[w8][tid];
             if (bias) v += bias[e0 + tid];
             s_logits[e0 + tid] = v;
         }
         __syncthreads();
     }
-    if (warp != 0) return;
+    if (warp != 0) {
+        // warps 1.. quantize the row (each 256-element block by one warp)
+        if (qs) {
+            const int nb = d >> 8;
+            for (int b = warp - 1; b < nb; b += ROUTER_WARPS - 1)
+                quantize_q8k_block(x + t * (int64_t)d + b * 256, lane, qs + t * (int64_t)d + b * 256, scales + t * nb + b,
+                                   bsums + (t * nb + b) * 16);
+        }
+        return;
+    }
 
     // softmax over E (candle-nn/src/ops.rs:326-339): exp(v - max) / sum, true division
     constexpr int PER = CANDLE_MOE_MAX_EXPERTS / 32;
@@ -122,10 +149,11 @@ router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, co
 }
 
 cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
-                               int d, int E, int k, int renorm, uint32_t* ids, float* w) {
+                               int d, int E, int k, int renorm, uint32_t* ids, float* w, int8_t* qs, float* scales,
+                               int16_t* bsums) {
     if (T == 0) return cudaSuccess;
-    router_topk_kernel<<<(unsigned)T, ROUTER_THREADS, 0, st>>>(x, router, bias, d, E, k, renorm, ids, w);
-    return cudaGetLastError();
+    return launch_k(router_topk_kernel, dim3((unsigned)T), dim3(ROUTER_THREADS), 0, st, x, router, bias, d, E, k, renorm,
+                    ids, w, qs, scales, bsums);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -139,6 +167,8 @@ constexpr int PERMUTE_THREADS = 1024;
 __global__ void __launch_bounds__(PERMUTE_THREADS)
 permute_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int k, int E, uint32_t* __restrict__ counts,
                uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm_token, uint32_t* __restrict__ pair_pos) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ uint32_t s_count[CANDLE_MOE_MAX_EXPERTS];
     __shared__ uint32_t s_off[CANDLE_MOE_MAX_EXPERTS + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = PERMUTE_THREADS / 32;
@@ -181,17 +211,18 @@ permute_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int k, int E, 
 
 cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
                            uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos) {
-    permute_kernel<<<1, PERMUTE_THREADS, 0, st>>>(ids, T * k, k, E, counts, offsets, perm_token, pair_pos);
-    return cudaGetLastError();
+    return launch_k(permute_kernel, dim3(1), dim3(PERMUTE_THREADS), 0, st, ids, T * k, k, E, counts, offsets, perm_token,
+                    pair_pos);
 }
 
 __global__ void single_group_kernel(uint32_t* offsets, uint32_t rows) {
+    pdl_trigger();
+    pdl_wait();
     offsets[0] = 0u;
     offsets[1] = rows;
 }
 cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows) {
-    single_group_kernel<<<1, 1, 0, st>>>(offsets, rows);
-    return cudaGetLastError();
+    return launch_k(single_group_kernel, dim3(1), dim3(1), 0, st, offsets, rows);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -207,6 +238,8 @@ combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride,
                const float* __restrict__ w, const uint32_t* __restrict__ pair_pos, int k, int d,
                const float* __restrict__ shared_out, int shared_splits, int64_t shared_split_stride,
                const float* __restrict__ x, const float* __restrict__ gate, float* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float s_red[COMBINE_THREADS / 32];
     __shared__ float s_gate;
     const int64_t t = blockIdx.x;
@@ -303,10 +336,8 @@ cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_split
                            const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
                            const float* shared_gate, float* y) {
     if (T == 0) return cudaSuccess;
-    combine_kernel<<<(unsigned)T, COMBINE_THREADS, 0, st>>>(expert_out, n_splits, split_stride, ids, w, pair_pos, k, d,
-                                                            shared_out, shared_splits, shared_split_stride, x,
-                                                            shared_gate, y);
-    return cudaGetLastError();
+    return launch_k(combine_kernel, dim3((unsigned)T), dim3(COMBINE_THREADS), 0, st, expert_out, n_splits, split_stride,
+                    ids, w, pair_pos, k, d, shared_out, shared_splits, shared_split_stride, x, shared_gate, y);
 }
 
 }  // namespace cmoe
