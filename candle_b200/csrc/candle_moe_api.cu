@@ -263,7 +263,8 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
     if (use_prepacked) {
         const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, T, ws.hq,
-                                                    ws.hs, ws.hb, ws.eo, &eo_splits, Tk * d, k_split_slots(T));
+                                                    ws.hs, ws.hb, ws.eo, &eo_splits, Tk * d, k_split_slots(T),
+                                                    (int)(Tk < E ? Tk : E));
         if (ce == cudaSuccess)
             down_done = true;
         else if (ce != cudaErrorNotSupported)

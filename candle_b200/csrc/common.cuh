@@ -181,7 +181,7 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
                                  int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
                                  const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
-                                 int max_splits);
+                                 int max_splits, int max_active_experts = 0);
 // flags raised by kernels whose bounded waits expired (0 = none); synchronises the device
 cudaError_t read_stream_status(int* out);
 cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);

@@ -501,7 +501,7 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
                                  int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
                                  const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
-                                 int max_splits) {
+                                 int max_splits, int max_active_experts) {
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return cudaErrorNotSupported;
     const int tile_n = gate_up ? 8 : 16;
     if (N % tile_n != 0 || K % 256 != 0) return cudaErrorNotSupported;
@@ -521,7 +521,17 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
     DirectParams P{};
     P.wa = wa;
     P.wb = wb;
-    for (int splits = 1; splits <= max_splits && splits <= kb; ++splits) {
+    // With few active experts there are fewer 16-row tiles than warps on the GPU: split K further (the
+    // down product only; partial sums meet in the combine kernel) until every warp has ~2 items.
+    int min_splits = 1;
+    if (!gate_up && max_active_experts > 0) {
+        const long long items = (long long)max_active_experts * (N / tile_n);
+        const long long want = 2LL * g_dir_sms * DIRECT_WARPS;
+        min_splits = (int)((want + items - 1) / items);
+        if (min_splits > max_splits) min_splits = max_splits;
+        if (min_splits < 1) min_splits = 1;
+    }
+    for (int splits = min_splits; splits <= max_splits && splits <= kb; ++splits) {
         if (gate_up && splits > 1) break;
         const int ks_blocks = (kb + splits - 1) / splits;
         uint32_t off = 0;

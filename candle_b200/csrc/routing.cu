@@ -226,7 +226,7 @@ cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t row
 }
 
 // ------------------------------------------------------------------------------------------------
-// Combine.  One CTA per token, threads over d with 128-bit accesses.  The k contributions are added
+// Combine.  CTAs of 256 threads over (token, 1024-column slab) with 128-bit accesses.  The k contributions are added
 // in ascending expert id, each product rounded first (no FMA), starting from +0.0: the order of the
 // reference's expert loop with broadcast_mul followed by index_add (quantized_llama.rs:185-203).
 // Optional shared expert: y += shared_out * sigmoid(x . g) (qwen2_moe.rs:315-319).
@@ -293,7 +293,7 @@ combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride,
     }
 
     float4* yr = reinterpret_cast<float4*>(y + t * (int64_t)d);
-    for (int i = threadIdx.x; i < (d >> 2); i += COMBINE_THREADS) {
+    for (int i = blockIdx.y * COMBINE_THREADS + threadIdx.x; i < (d >> 2); i += COMBINE_THREADS * gridDim.y) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
@@ -336,7 +336,8 @@ cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_split
                            const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
                            const float* shared_gate, float* y) {
     if (T == 0) return cudaSuccess;
-    return launch_k(combine_kernel, dim3((unsigned)T), dim3(COMBINE_THREADS), 0, st, expert_out, n_splits, split_stride,
+    const unsigned slabs = (unsigned)((d / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS);
+    return launch_k(combine_kernel, dim3((unsigned)T, slabs), dim3(COMBINE_THREADS), 0, st, expert_out, n_splits, split_stride,
                     ids, w, pair_pos, k, d, shared_out, shared_splits, shared_split_stride, x, shared_gate, y);
 }
 
