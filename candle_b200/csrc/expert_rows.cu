@@ -17,9 +17,15 @@
 
 namespace cmoe {
 
-// Rows per expert up to which the streaming form is used; beyond it its per-expert token groups
-// would re-stream the weights too often.
-constexpr int64_t STREAM_MAX_ROWS = 64;
+// Rows per expert up to which the streaming form is used.  Beyond 16 rows per expert it walks the
+// expert's rows in groups of 16 and re-streams the weights for each group (mostly from L2), which
+// is still far faster than the row-per-warp form; CANDLE_MOE_STREAM_MAX_ROWS lowers the limit.
+constexpr int64_t STREAM_MAX_ROWS_DEFAULT = (int64_t)1 << 40;
+
+static int64_t stream_max_rows() {
+    const char* v = std::getenv("CANDLE_MOE_STREAM_MAX_ROWS");
+    return v ? std::atoll(v) : STREAM_MAX_ROWS_DEFAULT;
+}
 
 static bool force_rows() {
     const char* v = std::getenv("CANDLE_MOE_FORCE_ROWS");
@@ -217,7 +223,7 @@ static cudaError_t launch_rows(cudaStream_t st, const ExpertPtrs& wa, const Expe
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
                                    int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden) {
-    if (!force_rows() && max_rows <= STREAM_MAX_ROWS) {
+    if (!force_rows() && max_rows <= stream_max_rows()) {
         const cudaError_t e = launch_expert_stream(st, true, w1, w3, dtype, E, d, ff, offsets, row_of, max_rows, xq, xs,
                                                    xb, hidden, nullptr, 0, 1);
         if (e != cudaErrorNotSupported) return e;
@@ -230,7 +236,7 @@ cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype
                                 const uint32_t* offsets, int64_t max_rows, const int8_t* hq, const float* hs,
                                 const int16_t* hb, float* out, int64_t split_stride, int max_splits, int* n_splits) {
     if (n_splits) *n_splits = 1;
-    if (!force_rows() && max_rows <= STREAM_MAX_ROWS) {
+    if (!force_rows() && max_rows <= stream_max_rows()) {
         const cudaError_t e = launch_expert_stream(st, false, w2, w2, dtype, E, ff, d, offsets, nullptr, max_rows, hq, hs,
                                                    hb, out, n_splits, split_stride, max_splits);
         if (e != cudaErrorNotSupported) return e;

@@ -49,8 +49,8 @@ def test_workspace_query_is_host_only_and_monotonic(lib):
         assert L.candle_moe_workspace_bytes(C.byref(_weights(lib)), T, C.byref(out)) == 0
         sizes.append(out.value)
     assert sizes == sorted(sizes) and sizes[-1] > 2048 * 2 * 14336 * 4
-    # hidden f32 + its int8 copy dominate: [T*k, ff] * 5 bytes
-    assert sizes[-1] < 2048 * 2 * (14336 * 6 + 4096 * 8) + (1 << 20)
+    # hidden f32 + its int8 copy dominate: [T*k, ff] * 5 bytes; two K-split slots of [T*k, d] f32
+    assert sizes[-1] < 2048 * 2 * (14336 * 6 + 4096 * 12) + (1 << 20)
 
 
 @pytest.mark.parametrize("field,value,code", [
