@@ -11,8 +11,8 @@ namespace {
 
 constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
-// larger batches get two slots, enough for the streaming form's activation rows to fit.
-inline int k_split_slots(int64_t T) { return T <= 64 ? MAX_K_SPLITS : 2; }
+// larger batches get four slots, enough for the streaming form's activation rows to fit.
+inline int k_split_slots(int64_t T) { return T <= 64 ? MAX_K_SPLITS : 4; }
 
 struct Workspace {
     // routing
