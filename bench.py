@@ -243,66 +243,21 @@ def oracle_view(torch, blk, cfg):
     return mw
 
 
-def time_stages(torch, blk, cfg, x, steps):
-    """Per-kernel device times of the same launch sequence candle_moe_forward runs, each stage called
-    through its own C-ABI entry point between CUDA events on the launching stream."""
-    from candle_b200 import _lib
-    L = _lib.load()
-    dev = x.device
-    T, d, ff, E, k = x.shape[0], cfg["d"], cfg["ff"], cfg["E"], cfg["k"]
-    Tk = T * k
-    ab13 = 32 if cfg["dt13"] == 8 else 256
-    ab2 = 32 if cfg["dt2"] == 8 else 256
-    i32, f32, i8, i16 = torch.int32, torch.float32, torch.int8, torch.int16
-    ids = torch.empty((T, k), dtype=i32, device=dev)
-    tw = torch.empty((T, k), dtype=f32, device=dev)
-    counts = torch.empty(E, dtype=i32, device=dev)
-    offs = torch.empty(E + 1, dtype=i32, device=dev)
-    perm = torch.empty(Tk, dtype=i32, device=dev)
-    pos = torch.empty(Tk, dtype=i32, device=dev)
-    xq = torch.empty((T, d), dtype=i8, device=dev)
-    xs = torch.empty((T, d // ab13), dtype=f32, device=dev)
-    xb = torch.empty((T, d // 16), dtype=i16, device=dev)
-    hid = torch.empty((Tk, ff), dtype=f32, device=dev)
-    hq = torch.empty((Tk, ff), dtype=i8, device=dev)
-    hs = torch.empty((Tk, ff // ab2), dtype=f32, device=dev)
-    hb = torch.empty((Tk, ff // 16), dtype=i16, device=dev)
-    eo = torch.empty((Tk, d), dtype=f32, device=dev)
-    y = torch.empty((T, d), dtype=f32, device=dev)
-    st = torch.cuda.current_stream(dev).cuda_stream
-    bias = None if blk.router_bias is None else blk.router_bias.data_ptr()
-    stages = [
-        ("router_topk", lambda: L.candle_moe_router_topk(st, x.data_ptr(), blk.feed_forward_gate_inp.data_ptr(), bias, T, d, E,
-                                                         k, int(cfg["renorm"]), ids.data_ptr(), tw.data_ptr())),
-        ("permute", lambda: L.candle_moe_permute(st, ids.data_ptr(), T, k, E, counts.data_ptr(), offs.data_ptr(),
-                                                 perm.data_ptr(), pos.data_ptr())),
-        ("quantize_x", lambda: L.candle_moe_quantize_act(st, x.data_ptr(), T, d, cfg["dt13"], xq.data_ptr(), xs.data_ptr(),
-                                                         xb.data_ptr())),
-        ("gate_up", lambda: L.candle_moe_grouped_gate_up(st, blk._w1, blk._w3, cfg["dt13"], E, d, ff, offs.data_ptr(),
-                                                         perm.data_ptr(), Tk, xq.data_ptr(), xs.data_ptr(), xb.data_ptr(),
-                                                         hid.data_ptr())),
-        ("quantize_h", lambda: L.candle_moe_quantize_act(st, hid.data_ptr(), Tk, ff, cfg["dt2"], hq.data_ptr(), hs.data_ptr(),
-                                                         hb.data_ptr())),
-        ("down", lambda: L.candle_moe_grouped_down(st, blk._w2, cfg["dt2"], E, d, ff, offs.data_ptr(), Tk, hq.data_ptr(),
-                                                   hs.data_ptr(), hb.data_ptr(), eo.data_ptr())),
-        ("combine", lambda: L.candle_moe_combine(st, eo.data_ptr(), ids.data_ptr(), tw.data_ptr(), pos.data_ptr(), T, k, d,
-                                                 None, None, None, y.data_ptr())),
-    ]
-    acc = {n: 0.0 for n, _ in stages}
+# DRAM traffic (dram__bytes_read + dram__bytes_write) per launch of the dominant kernel from one ncu
+# --set full capture of the default workload (profiles/expert_direct_c2_t32.md); other workloads: null.
+NCU_TRAFFIC_BYTES = {("c2", 32, "gate_up"): 551.5e6, ("c2", 32, "down"): 396.8e6}
+
+
+def time_stages(torch, blk, x, steps):
+    """Per-kernel device times of the block: the forward itself with CUDA events recorded on the
+    launching stream between its launches (candle_moe_forward_timed), averaged over `steps`."""
+    acc = None
     for it in range(steps + 2):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
-        evs[0].record()
-        for i, (n, fn) in enumerate(stages):
-            rc = fn()
-            if rc != 0:
-                raise RuntimeError(f"{n} returned {rc}")
-            evs[i + 1].record()
-        torch.cuda.synchronize(dev)
+        _, ms = blk.forward_timed(x)
         if it >= 2:
-            for i, (n, _) in enumerate(stages):
-                acc[n] += evs[i].elapsed_time(evs[i + 1])
-    active = int((counts > 0).sum().item())
-    return {n: v / steps for n, v in acc.items()}, active
+            acc = ms if acc is None else {k: acc[k] + v for k, v in ms.items()}
+    _, _, counts, _ = blk.last_routing(x.shape[0])
+    return {k: v / steps for k, v in acc.items()}, int((counts > 0).sum())
 
 
 def run_ours(args, cfg):
@@ -400,7 +355,7 @@ def run_ours(args, cfg):
 
     if rank == 0:
         x.copy_(torch.randn((T, d), generator=torch.Generator().manual_seed(1), dtype=torch.float32))
-        stage_ms, active = time_stages(torch, blk, cfg, x, max(args.steps, 10))
+        stage_ms, active = time_stages(torch, blk, x, max(min(args.steps, 50), 10))
         per_expert13 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], cfg["d"])
         per_expert2 = mat_bytes(cfg["dt2"], cfg["d"], cfg["ff"])
         # algorithmic bytes of the block: active experts' blocks + router + x read + y write
@@ -432,7 +387,8 @@ def run_ours(args, cfg):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
             "roofline": {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s",
-                         "frac": ach / peak, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                         "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
+                         "peak_source": f"{peak_kind} copy bandwidth",
                          "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]},
             "block_roofline": {"bound": "hbm", "algorithmic_bytes": block_bytes, "achieved": blk_gbs,
                                "frac": blk_gbs / peak, "frac_of_nominal_8TBps": blk_gbs / 8000.0,
@@ -445,7 +401,7 @@ def run_ours(args, cfg):
             "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": (7 + (5 if cfg["ff_shared"] else 0)) * args.steps,
+            "gpu_launches": ((6 if cfg["dt13"] != 8 else 7) + (5 if cfg["ff_shared"] else 0)) * args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line))

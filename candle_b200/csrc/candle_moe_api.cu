@@ -125,6 +125,20 @@ int fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
 
 inline int rc(cudaError_t e) { return e == cudaSuccess ? CANDLE_MOE_OK : (int)e; }
 
+// Optional per-stage event marks for candle_moe_forward_timed (null in normal calls).
+constexpr int N_STAGES = 8;  // router, permute, quantize_x, gate_up, quantize_h, down, shared expert, combine
+struct StageProbe {
+    cudaEvent_t ev[N_STAGES + 1];
+    bool hit[N_STAGES + 1];
+};
+thread_local StageProbe* g_probe = nullptr;
+inline void mark(cudaStream_t st, int stage_done) {
+    if (g_probe) {
+        cudaEventRecord(g_probe->ev[stage_done + 1], st);
+        g_probe->hit[stage_done + 1] = true;
+    }
+}
+
 #define CM_TRY(expr)                    \
     do {                                \
         const int _r = (expr);          \
@@ -238,10 +252,17 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
 
     // k-quant experts: the router kernel also quantizes x (Q8K); Q8_0 experts keep the separate pass
     const bool fuse_q = w->dtype_w13 != CANDLE_GGML_Q8_0;
+    if (g_probe) {
+        cudaEventRecord(g_probe->ev[0], st);
+        g_probe->hit[0] = true;
+    }
     CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w,
                                  fuse_q ? ws.xq : nullptr, fuse_q ? ws.xs : nullptr, fuse_q ? ws.xb : nullptr)));
+    mark(st, 0);
     CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
+    mark(st, 1);
     if (!fuse_q) CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
+    mark(st, 2);
     // a token selects an expert at most once: no expert sees more than T rows
     const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && T <= 64;
     int eo_splits = 1, so_splits = 1;
@@ -261,7 +282,9 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     if (!gate_done)
         CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
                                          ws.xb, ws.hidden)));
+    mark(st, 3);
     CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
+    mark(st, 4);
     if (use_prepacked) {
         const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, T, ws.hq,
                                                     ws.hs, ws.hb, ws.eo, &eo_splits, Tk * d, k_split_slots(T),
@@ -276,6 +299,7 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     if (!down_done)
         CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
                                       k_split_slots(T), &eo_splits)));
+    mark(st, 5);
 
     const float* shared_out = nullptr;
     if (w->d_ff_shared > 0) {
@@ -294,9 +318,32 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
                                       ws.so, T * (int64_t)d, k_split_slots(T), &so_splits)));
         shared_out = ws.so;
     }
+    mark(st, 6);
     CM_TRY(rc(launch_combine(st, ws.eo, eo_splits, Tk * d, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out,
                              so_splits, T * (int64_t)d, x, w->shared_gate, y)));
+    mark(st, 7);
     return CANDLE_MOE_OK;
+}
+
+int candle_moe_forward_timed(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
+                             void* workspace, size_t workspace_bytes, float* stage_ms) {
+    if (!stage_ms) return CANDLE_MOE_E_NULL;
+    StageProbe probe{};
+    for (int i = 0; i <= N_STAGES; ++i) {
+        const cudaError_t e = cudaEventCreate(&probe.ev[i]);
+        if (e != cudaSuccess) return (int)e;
+    }
+    g_probe = &probe;
+    const int st = candle_moe_forward(stream, w, x, T, y, workspace, workspace_bytes);
+    g_probe = nullptr;
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    for (int i = 0; i < N_STAGES; ++i) {
+        stage_ms[i] = 0.f;
+        if (st == CANDLE_MOE_OK && e == cudaSuccess && probe.hit[i] && probe.hit[i + 1])
+            cudaEventElapsedTime(&stage_ms[i], probe.ev[i], probe.ev[i + 1]);
+    }
+    for (int i = 0; i <= N_STAGES; ++i) cudaEventDestroy(probe.ev[i]);
+    return st != CANDLE_MOE_OK ? st : rc(e);
 }
 
 // ---- allocation-free variant -------------------------------------------------------------------

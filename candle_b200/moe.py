@@ -150,6 +150,21 @@ class MlpOrMoe:
 
     __call__ = forward
 
+    STAGES = ("router_topk", "permute", "quantize_x", "gate_up", "quantize_h", "down", "shared_expert", "combine")
+
+    def forward_timed(self, xs: torch.Tensor):
+        """One forward with CUDA events between its launches: (y, {stage: milliseconds})."""
+        x2 = xs.reshape(-1, self.d_model).contiguous()
+        T = x2.shape[0]
+        self.reserve(max(T, 1))
+        y = torch.empty_like(x2)
+        ms = (C.c_float * 8)()
+        with torch.cuda.device(self.device):
+            st = _lib.load().candle_moe_forward_timed(_stream_ptr(self.device), C.byref(self._cw), x2.data_ptr(), T,
+                                                      y.data_ptr(), self._ws_ptr(), self._ws.numel() - 256, ms)
+        _lib.check("candle_moe_forward_timed", st)
+        return y.reshape(xs.shape), {n: float(ms[i]) for i, n in enumerate(self.STAGES)}
+
     def last_routing(self, T: int):
         """Routing of the last forward over T rows, read back for tests and expert-parallel callers:
         (topk_ids [T,k] i64, topk_w [T,k] f32, expert_counts [E] i64, perm_token [T*k] i64)."""

@@ -155,6 +155,15 @@ CANDLE_MOE_API int candle_moe_grouped_down(void* stream, const void* const* w2, 
 CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
                        void* workspace, size_t workspace_bytes);
 
+/* candle_moe_forward with CUDA events recorded on `stream` between its launches; synchronises the
+ * stream and writes the device time of each stage in milliseconds to stage_ms[8]:
+ * {router (+ fused quantization of x), dispatch, separate quantization of x, gate_up, quantization
+ * of the hidden rows, down, shared expert, combine}.  For measurement only (it creates and destroys
+ * events); plays the part of the tracing spans around `QMatMul::forward` in the reference
+ * (candle-transformers/src/models/quantized_llama.rs:97-115). */
+CANDLE_MOE_API int candle_moe_forward_timed(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T,
+                                            float* y, void* workspace, size_t workspace_bytes, float* stage_ms);
+
 /* The same block as candle_moe_forward for callers that may not allocate device memory at all.
  * (No counterpart in the reference: candle allocates its temporaries per call.)
  *
@@ -169,7 +178,7 @@ CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* 
  * Rules:
  *   - a call whose scratch need (candle_moe_workspace_bytes(w, T)) exceeds
  *     CANDLE_MOE_STATIC_SCRATCH_BYTES is refused with CANDLE_MOE_E_STATIC_SCRATCH before anything is
- *     enqueued (the Mixtral-8x7B-shaped layer fits up to T = 56 rows);
+ *     enqueued (the Mixtral-8x7B-shaped layer fits up to T = 40 rows);
  *   - the first call on each device looks the array's device address up (a host-side query, no
  *     allocation); make that first call with the device current and before starting any stream
  *     capture;
