@@ -1,5 +1,7 @@
 // extern "C" entry points of libcandle_moe_sm100.so (declared in include/candle_moe.h): argument
 // validation on the host, workspace carving, and the launch sequence of the whole block.
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -9,6 +11,7 @@ using namespace cmoe;
 
 namespace {
 
+constexpr int64_t GEMM_MIN_TOKENS = 64;  // above this the tensor-core GEMM takes the Q4_K products
 constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
@@ -42,6 +45,7 @@ struct Workspace {
     float* shs;
     int16_t* shb;
     float* so;  // [T, d]
+    void* gemm;  // operand scratch of the large-batch tensor-core GEMM (null for decode-sized T)
     size_t total;
 };
 
@@ -90,6 +94,18 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
         ws.shb = carve<int16_t>(base, off, (size_t)T * fs / 16);
         ws.so = carve<float>(base, off, (size_t)T * d * k_split_slots(T));
     }
+    if (T > GEMM_MIN_TOKENS) {
+        // large batches: fp16 activation operand of the tcgen05 GEMM (Q4_K matrices), reused by gate_up and down
+        size_t g = 0;
+        if (w->dtype_w13 == CANDLE_GGML_Q4K) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d));
+        if (w->dtype_w2 == CANDLE_GGML_Q4K) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)ff));
+        if (g) {
+            off = align_up(off, 1024);
+            ws.gemm = base ? base + off : nullptr;
+            if (!base) ws.gemm = reinterpret_cast<void*>(1);  // size query: only the extent matters
+            off += g;
+        }
+    }
     ws.total = align_up(off, 256);
     return ws;
 }
@@ -124,6 +140,12 @@ int fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
 }
 
 inline int rc(cudaError_t e) { return e == cudaSuccess ? CANDLE_MOE_OK : (int)e; }
+
+// CANDLE_MOE_GEMM=0 keeps large batches on the streaming form (A/B checks)
+inline bool gemm_enabled() {
+    const char* v = std::getenv("CANDLE_MOE_GEMM");
+    return !(v && v[0] == '0');
+}
 
 // Optional per-stage event marks for candle_moe_forward_timed (null in normal calls).
 constexpr int N_STAGES = 8;  // router, permute, quantize_x, gate_up, quantize_h, down, shared expert, combine
@@ -279,6 +301,14 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
         else if (ce != cudaErrorNotSupported)
             return (int)ce;
     }
+    if (!gate_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
+        const cudaError_t ce = launch_expert_gemm(st, true, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, Tk,
+                                                  ws.xq, ws.xs, ws.xb, ws.hidden, ws.gemm);
+        if (ce == cudaSuccess)
+            gate_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+    }
     if (!gate_done)
         CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
                                          ws.xb, ws.hidden)));
@@ -295,6 +325,16 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
             return (int)ce;
         else
             eo_splits = 1;
+    }
+    if (!down_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
+        const cudaError_t ce = launch_expert_gemm(st, false, p2, p2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, Tk, ws.hq,
+                                                  ws.hs, ws.hb, ws.eo, ws.gemm);
+        if (ce == cudaSuccess) {
+            down_done = true;
+            eo_splits = 1;
+        } else if (ce != cudaErrorNotSupported) {
+            return (int)ce;
+        }
     }
     if (!down_done)
         CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,

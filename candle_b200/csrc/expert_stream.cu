@@ -752,6 +752,13 @@ cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs
     return cudaErrorNotSupported;
 }
 
+cudaError_t stream_status_ptr(int** out) {
+    void* sp = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&sp, g_stream_status);
+    *out = static_cast<int*>(sp);
+    return e;
+}
+
 cudaError_t read_stream_status(int* out) {
     return cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int));
 }
