@@ -187,7 +187,7 @@ def config_dict(args, cfg):
         "tokens_per_step_per_gpu": args.tokens,
         "l2_policy": "inputs larger than L2: the expert weights streamed each step exceed the 126 MB L2"
         if weights_bytes(cfg) > 200e6 else "L2 flushed between steps by writing a 256 MB buffer",
-        "decode_weights": "GGUF blocks" if (args.no_prepack or args.tokens > 64) else
+        "decode_weights": "GGUF blocks" if args.no_prepack else
         "prepacked copies made once at load (candle_moe_prepack; Q4_K +2.8 % bytes, Q6_K same size); "
         "roofline bytes are the GGUF bytes",
         "parallelism": "single GPU" if args.gpus == 1 else f"{args.gpus} token-sharded replicas (no collective)",
@@ -277,7 +277,7 @@ def run_ours(args, cfg):
     import candle_b200  # noqa: F401  loads libcandle_moe_sm100.so or raises
 
     T, d = args.tokens, cfg["d"]
-    blk = build_block(torch, cfg, dev, seed=0, prepack=not args.no_prepack and T <= 64)
+    blk = build_block(torch, cfg, dev, seed=0, prepack=not args.no_prepack)
     blk.reserve(T)
     gx = torch.Generator(device=dev).manual_seed(1 + rank)
     x = torch.randn((T, d), generator=gx, device=dev, dtype=torch.float32)

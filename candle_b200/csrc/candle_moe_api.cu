@@ -97,8 +97,11 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     if (T > GEMM_MIN_TOKENS) {
         // large batches: fp16 activation operand of the tcgen05 GEMM (Q4_K matrices), reused by gate_up and down
         size_t g = 0;
-        if (w->dtype_w13 == CANDLE_GGML_Q4K) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d));
-        if (w->dtype_w2 == CANDLE_GGML_Q4K) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)ff));
+        const auto takes = [](int dt, const void* const* packed) {
+            return dt == CANDLE_GGML_Q4K || (dt == CANDLE_GGML_Q6K && packed != nullptr);
+        };
+        if (takes(w->dtype_w13, w->w1_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d));
+        if (takes(w->dtype_w2, w->w2_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)ff));
         if (g) {
             off = align_up(off, 1024);
             ws.gemm = base ? base + off : nullptr;
@@ -302,8 +305,15 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
             return (int)ce;
     }
     if (!gate_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
-        const cudaError_t ce = launch_expert_gemm(st, true, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, Tk,
-                                                  ws.xq, ws.xs, ws.xb, ws.hidden, ws.gemm);
+        // Q6_K is read from the repacked copies (its GGUF blocks are only 2-byte aligned)
+        const bool rp = w->dtype_w13 == CANDLE_GGML_Q6K && w->w1_prepacked && w->w3_prepacked;
+        ExpertPtrs g1 = p1, g3 = p3;
+        if (rp) {
+            CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
+            CM_TRY(fill_ptrs(w->w3_prepacked, E, g3));
+        }
+        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, ws.offsets, ws.perm_token,
+                                                  Tk, ws.xq, ws.xs, ws.xb, ws.hidden, ws.gemm);
         if (ce == cudaSuccess)
             gate_done = true;
         else if (ce != cudaErrorNotSupported)
@@ -327,8 +337,11 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
             eo_splits = 1;
     }
     if (!down_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
-        const cudaError_t ce = launch_expert_gemm(st, false, p2, p2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, Tk, ws.hq,
-                                                  ws.hs, ws.hb, ws.eo, ws.gemm);
+        const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
+        ExpertPtrs g2 = p2;
+        if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
+        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, ws.offsets, nullptr, Tk,
+                                                  ws.hq, ws.hs, ws.hb, ws.eo, ws.gemm);
         if (ce == cudaSuccess) {
             down_done = true;
             eo_splits = 1;

@@ -182,10 +182,11 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
                                  const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
                                  int max_splits, int max_active_experts = 0);
-// large-batch grouped GEMM on tcgen05 / TMEM (Q4_K); `scratch` of expert_gemm_scratch_bytes(P, K) bytes
+// large-batch grouped GEMM on tcgen05 / TMEM: Q4_K in GGUF layout (repacked = false), Q6_K in the repacked
+// layout (repacked = true); `scratch` of expert_gemm_scratch_bytes(P, K) bytes
 size_t expert_gemm_scratch_bytes(int64_t P, int K);
-cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype, int E,
-                               int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
+cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
+                               bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                const int8_t* aq, const float* ascale, const int16_t* absum, float* out, void* scratch);
 // flags raised by kernels whose bounded waits expired (0 = none); synchronises the device
 cudaError_t read_stream_status(int* out);

@@ -1,24 +1,31 @@
-// Grouped expert products for large batches (prefill): tcgen05 tensor cores with TMEM accumulators.
+// Grouped expert products for large batches (prefill): tcgen05 tensor cores, operands and accumulators
+// in tensor memory.
 //
 // out[p, n] = W_e[n, :] . act[row(p), :] for all grouped positions p of every expert, as a grouped GEMM
 // over tiles of 128 weight rows x 128 grouped positions.  The integers are the reference's
-// (candle-core/src/quantized/k_quants.rs:1205-1285): activations are the int8 Q8K rows, and the weight
-// operand holds sc_j * q (Q4_K: at most 63 * 15 = 945), both exact in fp16, multiplied by
+// (candle-core/src/quantized/k_quants.rs:1205-1285 Q4_K, :1520-1600 Q6_K): activations are the int8
+// Q8K rows, and the weight operand holds (sub-block scale) x (quant), both exact in fp16, multiplied by
 // `tcgen05.mma kind::f16` with fp32 accumulation in tensor memory -- exact while a 256-element block's
-// sum stays below 2^24, which it does by a wide margin for real data.  After every 256-element
-// block the accumulator is drained and scaled by d_w(row, block) * d8(position, block) on the CUDA
-// cores; the Q4_K min term sum_j m_j * bsum_j is one more K=16 MMA per block (mins against the int16
-// block sums, both exact in fp16) into a second accumulator scaled by dmin_w * d8.
+// sum stays below 2^24, which it does by a wide margin for real data.  After every 256-element block
+// the accumulator is drained and scaled by d_w(row, block) * d8(position, block) on the CUDA cores.
+//   Q4_K: operand sc_j * q (at most 63 * 15); the min term sum_j m_j * bsum_j is one more K=16 MMA per
+//         block (mins against the int16 block sums) into a second accumulator scaled by dmin_w * d8.
+//   Q6_K: sc_j * (q - 32) reaches 4096 and is not always an fp16 integer, so the int8 scale is split
+//         into ceil(sc/2) + floor(sc/2) and the slab is multiplied twice (each half at most 32 * 64 =
+//         2048: exact).  Reads the repacked layout of the decode kernels (16-byte aligned pieces; the
+//         210-byte GGUF blocks are only 2-byte aligned).
 //
 // One CTA per SM, persistent over tiles, warp-specialised:
-//   warps 0-7   epilogue: drain TMEM (tcgen05.ld) once per block, scale, accumulate 64 columns per
-//               thread in registers; at the end of a tile apply the SiLU gate and store
-//   warp  8     TMA: the activation operand, [128 positions x 64 k] fp16 boxes, 128-byte swizzle
-//   warp  9     one thread issues the MMAs and commits them to mbarriers
-//   warps 10-17 unpack the Q4_K nibbles of [128 rows x 64 k] to fp16 (x sub-block scale, one HFMA2
-//               per two elements) straight into the swizzled shared-memory operand
-// A ring of 6 stages (32 KB each) decouples the three producers from the MMA thread; two TMEM
-// accumulator sets (2 x 256 columns) decouple the MMA thread from the epilogue.  gate_up interleaves
+//   warps 0-7   epilogue: drain TMEM (tcgen05.ld) once per block, scale (packed fp32 pairs), keep 64
+//               columns per thread in registers; at the end of a tile apply the SiLU gate and store
+//   warps 8-15  unpack the weight nibbles of [128 rows x 64 k] to fp16 x scale with one HFMA2 per two
+//               elements and store them straight into TENSOR MEMORY (tcgen05.st): the A operand never
+//               touches shared memory, whose bandwidth the B operand needs
+//   warp  16    TMA: the activation operand, [128 positions x 64 k] fp16 boxes, 128-byte swizzle
+//   warp  17    one thread issues the MMAs (A from TMEM, B from shared memory) and commits to mbarriers
+// Rings: 4 A stages in TMEM, 8 B stages in shared memory; two main accumulators (2 x 128 columns) let
+// the MMAs of block b+1 overlap the drain of block b; the Q4_K min accumulator is single (its MMA is
+// issued last in a block, when the drain of the block before has long finished).  gate_up interleaves
 // rows of W1 and W3 (tile row 2i = W1 row, 2i+1 = W3 row) so the two factors of silu(w1 x) * (w3 x)
 // sit in neighbouring lanes and meet with one shuffle.
 // Every mbarrier wait is bounded (see stream_common.cuh); nothing here uses cluster multicast.
@@ -30,17 +37,37 @@
 
 namespace cmoe {
 
+#ifdef CMOE_GEMM_TIMING
+__device__ long long g_gemm_timing[32];
+extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timing(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_timing, sizeof(long long) * 32);
+}
+#endif
+
 namespace {
 
 constexpr int G_TILE_M = 128, G_TILE_N = 128, G_SLAB_K = 64;
-constexpr int G_STAGES = 6;
-constexpr int G_STAGE_A = G_TILE_M * G_SLAB_K * 2;  // 16 KB
-constexpr int G_STAGE_B = G_TILE_N * G_SLAB_K * 2;  // 16 KB
-constexpr int G_STAGE = G_STAGE_A + G_STAGE_B;
+constexpr int G_A_STAGES = 4, G_B_STAGES = 8;
+constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
-constexpr int G_THREADS = 32 * (G_EPI_WARPS + 2 + G_DQ_WARPS);  // 576
+constexpr int G_WARP_TMA = G_EPI_WARPS + G_DQ_WARPS, G_WARP_MMA = G_WARP_TMA + 1;
+constexpr int G_THREADS = 32 * (G_WARP_MMA + 1);  // 576
 constexpr int G_TMEM_COLS = 512;
-constexpr int G_SMEM_BYTES = G_STAGES * G_STAGE + 1024 /* alignment slack */;
+constexpr int G_TM_MAIN = 0;    // + 128 * buffer
+constexpr int G_TM_MIN = 256;   // Q4_K only
+constexpr int Q6K_HTB_BYTES = 1680;
+
+// Cycle counters of CTA 0 (local experiments only, -DCMOE_GEMM_TIMING): where each role waits.
+#ifdef CMOE_GEMM_TIMING
+#define GT_BEGIN() long long gt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long gt0_ = clock64()
+#define GT(i, stmt) do { const long long t_ = clock64(); stmt; gt_[i] += clock64() - t_; } while (0)
+#define GT_END(base, leader) do { if (blockIdx.x == 0 && (leader)) { for (int i_ = 0; i_ < 7; ++i_) g_gemm_timing[(base) + i_] = gt_[i_]; \
+    g_gemm_timing[(base) + 7] = clock64() - gt0_; } } while (0)
+#else
+#define GT_BEGIN() do { } while (0)
+#define GT(i, stmt) do { stmt; } while (0)
+#define GT_END(base, leader) do { } while (0)
+#endif  // repacked half-tile block: 8 rows x 256 elements (expert_direct.cu)
 
 // ---------------------------------------------------------------------------------------------
 // Operand preparation: the int8 activation rows in grouped order as fp16 (B operand), their int16
@@ -87,7 +114,7 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
 }
 
 struct GemmParams {
-    ExpertPtrs wa, wb;            // GGUF blocks: gate_up W1 / W3, down W2 (wb unused)
+    ExpertPtrs wa, wb;            // gate_up: W1 / W3, down: W2 (wb unused); GGUF blocks (Q4_K) or repacked (Q6_K)
     const uint32_t* offsets;      // [E + 1]
     const float* d8t;             // [kb][P_pad]
     float* out;                   // gate_up: hidden [P, N]; down: [P, N]
@@ -96,38 +123,180 @@ struct GemmParams {
     int m_tiles;                  // tiles along the weight rows (N / 64 for gate_up, N / 128 for down)
 };
 
-// 6-bit scales / mins of a Q4_K block as bytes: sc[0] = sub-blocks 0..3, sc[1] = 4..7 (utils.rs:50-60)
-__device__ __forceinline__ void q4k_unpack_scales(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t (&sc)[2], uint32_t (&mn)[2]) {
-    sc[0] = s0 & 0x3f3f3f3fu;
-    mn[0] = s1 & 0x3f3f3f3fu;
-    sc[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
-    mn[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+__device__ __forceinline__ __half2 h2_bits(uint32_t v) { return *reinterpret_cast<const __half2*>(&v); }
+__device__ __forceinline__ uint32_t bits_h2(__half2 v) { return *reinterpret_cast<const uint32_t*>(&v); }
+// (1024 + byte b of w) in both halves: 0x64xx is 1024 + xx in fp16
+__device__ __forceinline__ __half2 byte_magic2(uint32_t w, int b) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0x64646464u), "r"(0x4040u | (uint32_t)b | ((uint32_t)b << 8)));
+    return h2_bits(r);
 }
+__device__ __forceinline__ uint4 ldg128(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
-// two nibbles (bits 0-3 and 16-19 of x) -> half2 of (nibble * scale): 0x6400 | n is 1024 + n in fp16,
-// and fma(1024 + n, sc, -1024 * sc) rounds the exact n * sc once (it is an integer <= 945: exact)
-__device__ __forceinline__ uint32_t nib2_to_scaled_half2(uint32_t x, __half2 sc2, __half2 off2) {
-    const uint32_t v = (x & 0x000F000Fu) | 0x64006400u;
-    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&v), sc2, off2);
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
+// ------------------------------------------------------------------------------------------------
+// Q4_K, GGUF layout (144-byte blocks: d, dmin, 12 scale bytes, 128 nibble bytes).  Thread (row, h) owns
+// bytes 16h..16h+15 of each 32-byte group: low nibbles are k = 16h.. of the 64-wide slab, high
+// nibbles k = 32 + 16h..; one TMEM column holds two k, so the 16 + 16 values are columns 8h.. and 16+8h..
+// ------------------------------------------------------------------------------------------------
+struct GemmQ4K {
+    static constexpr bool HAS_MIN = true;
+    static constexpr int A_COLS = 32, A_BASE = 384, A_PARTS = 1;
+    struct Row {
+        const uint8_t* p;
+    };
+    __device__ static __forceinline__ Row row(const uint8_t* w, int n, int kb) { return Row{w + (size_t)n * kb * Q4K_BYTES}; }
+    struct Pre {
+        uint4 hdr, q[4];
+    };
+    __device__ static __forceinline__ void load(Pre& pr, const Row& r, int blk, int h) {
+        const uint8_t* b = r.p + (size_t)blk * Q4K_BYTES;
+        pr.hdr = ldg128(b);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) pr.q[s] = ldg128(b + 16 + 32 * s + 16 * h);
+    }
+    // d (low half) and dmin (high half) of the block, fp16 bits
+    __device__ static __forceinline__ uint32_t load_hdr(const Row& r, int blk) {
+        return __ldg(reinterpret_cast<const uint32_t*>(r.p + (size_t)blk * Q4K_BYTES));
+    }
+    struct Ctx {
+        uint32_t sc[2], mn[2];  // 6-bit scales / mins as bytes: [0] = sub-blocks 0..3, [1] = 4..7 (utils.rs:50-60)
+    };
+    __device__ static __forceinline__ void begin(const Pre& pr, Ctx& c) {
+        const uint32_t s0 = pr.hdr.y, s1 = pr.hdr.z, s2 = pr.hdr.w;
+        c.sc[0] = s0 & 0x3f3f3f3fu;
+        c.mn[0] = s1 & 0x3f3f3f3fu;
+        c.sc[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
+        c.mn[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+    }
+    // slab s = sub-blocks 2s (low nibbles) and 2s+1 (high nibbles).  0x6400 | n is 1024 + n and
+    // fma(1024 + n, sc, -1024 sc) rounds the exact n * sc once; 0x6400 | (n << 4) is 1024 + 16 n and
+    // fma(1024 + 16 n, sc / 16, -64 sc) does the same for a nibble left in the high half of its byte.
+    __device__ static __forceinline__ void emit(int s, const Pre& pr, const Ctx& c, uint32_t ta, int h) {
+        const int jl = 2 * s, jh = 2 * s + 1;
+        const __half2 k1024 = __float2half2_rn(1024.f);
+        const __half2 scl = __hsub2(byte_magic2(c.sc[jl >> 2], jl & 3), k1024);
+        const __half2 sch = __hsub2(byte_magic2(c.sc[jh >> 2], jh & 3), k1024);
+        const __half2 offl = __hmul2(scl, __float2half2_rn(-1024.f));
+        const __half2 sch16 = __hmul2(sch, __float2half2_rn(0.0625f)), offh = __hmul2(sch, __float2half2_rn(-64.f));
+        const uint32_t w[4] = {pr.q[s].x, pr.q[s].y, pr.q[s].z, pr.q[s].w};
+        uint32_t lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t x = w[i], y = w[i] >> 8;  // bytes (0, 2) and (1, 3) of the four
+            lo[2 * i] = bits_h2(__hfma2(h2_bits((x & 0x000F000Fu) | 0x64006400u), scl, offl));
+            lo[2 * i + 1] = bits_h2(__hfma2(h2_bits((y & 0x000F000Fu) | 0x64006400u), scl, offl));
+            hi[2 * i] = bits_h2(__hfma2(h2_bits((x & 0x00F000F0u) | 0x64006400u), sch16, offh));
+            hi[2 * i + 1] = bits_h2(__hfma2(h2_bits((y & 0x00F000F0u) | 0x64006400u), sch16, offh));
+        }
+        tmem_st8(ta + 8 * h, lo);
+        tmem_st8(ta + 16 + 8 * h, hi);
+    }
+    // min operand in shared memory: k = 2j, 2j+1 both carry m_j (against the two 16-element sums of sub-block j)
+    __device__ static __forceinline__ void emit_min(const Ctx& c, uint8_t* arow, int h, int sw) {
+        const __half2 k1024 = __float2half2_rn(1024.f);
+        uint32_t mw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mw[i] = bits_h2(__hsub2(byte_magic2(c.mn[h], i), k1024));
+        *reinterpret_cast<uint4*>(arow + ((h ^ sw) << 4)) = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// Q6_K, repacked layout (expert_direct.cu: per 8 rows x 256 elements, 1680 bytes: low nibbles 2 x 512,
+// high bit pairs 512, 128 scales, 8 d).  Row g's 64 nibble bytes of half n sit at 512 n + 64 g in four
+// 16-byte chunks t; word cw of chunk t holds elements k0 = 16 cw + 4 t .. + 3 of the half's two slabs
+// (low nibbles: even slab, high nibbles: odd slab).  Thread (row, h) takes chunks t = 2h, 2h + 1.
+// The quant is placed at mantissa bits 4..9 (0x6400 | q << 4 = 1024 + 16 q); minus 1536 leaves
+// 16 (q - 32), times ceil(sc/2)/16 and floor(sc/2)/16 gives the two exact operand parts.
+// ------------------------------------------------------------------------------------------------
+struct GemmQ6K {
+    static constexpr bool HAS_MIN = false;
+    static constexpr int A_COLS = 64, A_BASE = 256, A_PARTS = 2;
+    struct Row {
+        const uint8_t* p;  // half-tile block 0 of the row's group of 8
+        int g;
+    };
+    __device__ static __forceinline__ Row row(const uint8_t* w, int n, int kb) {
+        return Row{w + (size_t)(n >> 3) * kb * Q6K_HTB_BYTES, n & 7};
+    }
+    struct Pre {
+        uint4 ql[2][2], qh[2], sc;
+    };
+    __device__ static __forceinline__ void load(Pre& pr, const Row& r, int blk, int h) {
+        const uint8_t* b = r.p + (size_t)blk * Q6K_HTB_BYTES + 64 * r.g + 32 * h;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            pr.ql[0][j] = ldg128(b + 16 * j);
+            pr.ql[1][j] = ldg128(b + 512 + 16 * j);
+            pr.qh[j] = ldg128(b + 1024 + 16 * j);
+        }
+        pr.sc = ldg128(r.p + (size_t)blk * Q6K_HTB_BYTES + 1536 + 16 * r.g);
+    }
+    __device__ static __forceinline__ uint32_t load_hdr(const Row& r, int blk) {
+        return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r.p + (size_t)blk * Q6K_HTB_BYTES + 1664 + 2 * r.g));
+    }
+    struct Ctx {
+        uint32_t xc[4], xh[4];  // per scale byte: ceil(sc/2) + 64 and floor(sc/2) + 64
+    };
+    __device__ static __forceinline__ void begin(const Pre& pr, Ctx& c) {
+        const uint32_t w[4] = {pr.sc.x, pr.sc.y, pr.sc.z, pr.sc.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t x = w[i] ^ 0x80808080u;  // sc + 128 per byte
+            c.xh[i] = (x >> 1) & 0x7f7f7f7fu;
+            c.xc[i] = c.xh[i] + (x & 0x01010101u);
+        }
+    }
+    __device__ static __forceinline__ void emit(int s, const Pre& pr, const Ctx& c, uint32_t ta, int h) {
+        const int n = s >> 1, odd = s & 1;
+        const __half2 k16th = __float2half2_rn(0.0625f), km68 = __float2half2_rn(-68.f), km1536 = __float2half2_rn(-1536.f);
+#pragma unroll
+        for (int cw = 0; cw < 4; ++cw) {
+            const int idx = 4 * s + cw;
+            // (1024 + x) / 16 - 68 = (x - 64) / 16: the half scale over 16
+            const __half2 m1 = __hfma2(byte_magic2(c.xc[idx >> 2], idx & 3), k16th, km68);
+            const __half2 m2 = __hfma2(byte_magic2(c.xh[idx >> 2], idx & 3), k16th, km68);
+            const int bq = 2 * ((cw >> 1) + 2 * odd);  // bit position of this quarter's pair in the qh byte
+            uint32_t o1[4], o2[4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t qlw = w4(pr.ql[n][j], cw), qhw = w4(pr.qh[j], 2 * n + (cw & 1));
+                const uint32_t a02 = odd ? qlw : (qlw << 4), a13 = odd ? (qlw >> 8) : (qlw >> 4);
+                const uint32_t b02 = qhw << (8 - bq), b13 = qhw >> bq;
+                const uint32_t v02 = ((a02 & 0x00F000F0u) | 0x64006400u) | (b02 & 0x03000300u);
+                const uint32_t v13 = ((a13 & 0x00F000F0u) | 0x64006400u) | (b13 & 0x03000300u);
+                const __half2 x02 = __hadd2(h2_bits(v02), km1536), x13 = __hadd2(h2_bits(v13), km1536);
+                o1[2 * j] = bits_h2(__hmul2(x02, m1));
+                o1[2 * j + 1] = bits_h2(__hmul2(x13, m1));
+                o2[2 * j] = bits_h2(__hmul2(x02, m2));
+                o2[2 * j + 1] = bits_h2(__hmul2(x13, m2));
+            }
+            tmem_st4(ta + 8 * cw + 4 * h, o1[0], o1[1], o1[2], o1[3]);
+            tmem_st4(ta + 32 + 8 * cw + 4 * h, o2[0], o2[1], o2[2], o2[3]);
+        }
+    }
+    __device__ static __forceinline__ void emit_min(const Ctx&, uint8_t*, int, int) {}
+};
 
 struct TileCoord {
     int e, nt, mt;
     uint32_t p0, p_end;
 };
 
-// tile id -> (expert, position tile, row tile); m-tiles are fastest so neighbouring CTAs share B
+// tile id -> (expert, row tile, position tile); position tiles are fastest, so the CTAs that run at
+// the same time share a weight tile (fetched from HBM once) and each expert's activations stay in L2
 __device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs, int E, int m_tiles, TileCoord& tc) {
     long long cum = 0;
     for (int e = 0; e < E; ++e) {
         const uint32_t cnt = offs[e + 1] - offs[e];
-        const long long te = (long long)((cnt + G_TILE_N - 1) / G_TILE_N) * m_tiles;
+        const int n_tiles = (int)((cnt + G_TILE_N - 1) / G_TILE_N);
+        const long long te = (long long)n_tiles * m_tiles;
         if (tile < cum + te) {
             const long long local = tile - cum;
             tc.e = e;
-            tc.nt = (int)(local / m_tiles);
-            tc.mt = (int)(local - (long long)tc.nt * m_tiles);
+            tc.mt = (int)(local / n_tiles);
+            tc.nt = (int)(local - (long long)tc.mt * n_tiles);
             tc.p0 = offs[e] + (uint32_t)tc.nt * G_TILE_N;
             tc.p_end = offs[e + 1];
             return true;
@@ -137,12 +306,13 @@ __device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs
     return false;
 }
 
-template <bool GATE_UP>
+template <class F, bool GATE_UP>
 __global__ void __launch_bounds__(G_THREADS, 1)
-expert_gemm_q4k_kernel(const __grid_constant__ GemmParams P, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ CUtensorMap map_bs) {
+expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_bs) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[G_STAGES], empty_bar[G_STAGES], tmem_full[2], tmem_empty[2];
+    __shared__ uint64_t full_a[G_A_STAGES], empty_a[G_A_STAGES], full_b[G_B_STAGES], empty_b[G_B_STAGES];
+    __shared__ uint64_t full_m[2], empty_m[2], tmem_full[2], epi_done[2], min_free;
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ __align__(16) float s_d8[2][G_TILE_N];
     __shared__ uint32_t s_tmem_base;
@@ -151,26 +321,34 @@ expert_gemm_q4k_kernel(const __grid_constant__ GemmParams P, const __grid_consta
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_min_a = smem + G_B_STAGES * G_TILE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
+    uint8_t* smem_min_b = smem_min_a + 2 * G_TILE_BYTES;     //       2 slots of the block sums (activation side)
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < G_STAGES; ++s) {
-            mbar_init(&full_bar[s], G_DQ_WARPS + 1);  // 8 unpack warps + the TMA thread's expect_tx arrival
-            mbar_init(&empty_bar[s], 1);              // one tcgen05.commit
+        for (int s = 0; s < G_A_STAGES; ++s) {
+            mbar_init(&full_a[s], G_DQ_WARPS);
+            mbar_init(&empty_a[s], 1);
+        }
+        for (int s = 0; s < G_B_STAGES; ++s) {
+            mbar_init(&full_b[s], 1);
+            mbar_init(&empty_b[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
+            mbar_init(&full_m[b], G_DQ_WARPS + 1);  // 8 unpack warps + the TMA thread's expect_tx arrival
+            mbar_init(&empty_m[b], 1);
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], G_EPI_WARPS);
+            mbar_init(&epi_done[b], G_EPI_WARPS);
         }
+        mbar_init(&min_free, G_EPI_WARPS);
         fence_barrier_init();
     }
-    if (warp == G_EPI_WARPS) tmem_alloc(&s_tmem_base, G_TMEM_COLS);
+    if (warp == G_WARP_TMA) tmem_alloc(&s_tmem_base, G_TMEM_COLS);
     tc5_fence_before_sync();
     __syncthreads();
     tc5_fence_after_sync();
     const uint32_t tmem_base = s_tmem_base;
     volatile int* abort_flag = &s_abort;
-    const size_t row_bytes = (size_t)P.kb * Q4K_BYTES;
     constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, G_TILE_N);
 
     if (warp < G_EPI_WARPS) {
@@ -178,180 +356,264 @@ expert_gemm_q4k_kernel(const __grid_constant__ GemmParams P, const __grid_consta
         const int quarter = warp & 3, colhalf = warp >> 2;
         const int r = 32 * quarter + lane;  // tile row = TMEM lane
         const int etid = threadIdx.x;       // 0..255
+        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(colhalf * 64);
         uint32_t ab = 0;
-        TileCoord tc;
-        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
+        long long tile = blockIdx.x;
+        TileCoord tc, tcn;
+        bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+        typename F::Row rowc{}, rown{};
+        uint32_t hdr_c = 0, hdr_n = 0;
+        GT_BEGIN();
+        if (have) {
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
-            const uint8_t* wrow = ((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e]) + (size_t)n * row_bytes;
-            float acc[64];
+            rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
+            hdr_c = F::load_hdr(rowc, 0);
+            if (etid < G_TILE_N) s_d8[0][etid] = P.d8t[tc.p0 + etid];
+        }
+        while (have) {
+            const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            if (have_n) {
+                const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
+                rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
+            }
+            uint64_t acc[32];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 const int buf = ab & 1;
-                if (etid < G_TILE_N) {
-                    const uint32_t p = tc.p0 + etid;
-                    s_d8[buf][etid] = p < (uint32_t)P.P_pad ? P.d8t[(size_t)blk * P.P_pad + p] : 0.f;
+                GT(1, named_bar_sync(2, 32 * G_EPI_WARPS));  // s_d8[buf] is complete; s_d8[buf ^ 1] is no longer read
+                // scales of the next block (maybe of the next tile): in flight while this block is drained
+                float d8_n = 0.f;
+                bool pre = false;
+                if (blk + 1 < P.kb) {
+                    hdr_n = F::load_hdr(rowc, blk + 1);
+                    if (etid < G_TILE_N) d8_n = P.d8t[(size_t)(blk + 1) * P.P_pad + tc.p0 + etid];
+                    pre = true;
+                } else if (have_n) {
+                    hdr_n = F::load_hdr(rown, 0);
+                    if (etid < G_TILE_N) d8_n = P.d8t[tcn.p0 + etid];
+                    pre = true;
                 }
-                const uint32_t hdr = *reinterpret_cast<const uint32_t*>(wrow + (size_t)blk * Q4K_BYTES);
-                const float dw = half_bits_to_float((uint16_t)(hdr & 0xffff)), dmw = half_bits_to_float((uint16_t)(hdr >> 16));
-                named_bar_sync(2, 32 * G_EPI_WARPS);
-                mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag);
+                const float dw = half_bits_to_float((uint16_t)(hdr_c & 0xffff));
+                const uint64_t dw2 = f32x2_pack(dw, dw);
+                uint64_t ndm2 = 0ull;
+                if (F::HAS_MIN) {
+                    const float ndm = -half_bits_to_float((uint16_t)(hdr_c >> 16));
+                    ndm2 = f32x2_pack(ndm, ndm);
+                }
+                GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
                 tc5_fence_after_sync();
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(buf * 256 + colhalf * 64);
+                const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128), t_min = ta_lane + (uint32_t)G_TM_MIN;
+                const uint32_t d8_addr = smem_u32(&s_d8[buf][colhalf * 64]);
+                // Steps of 16 columns: (Q4_K) the min accumulator first, so that it is released to the MMA
+                // thread as early as possible, then the main accumulator.  The load of step i+1 is in
+                // flight while step i is scaled into the register accumulators.
+                constexpr int NSTEP = F::HAS_MIN ? 8 : 4;
+                uint32_t stg[2][16];
+                tmem_ld16((F::HAS_MIN ? t_min : t_main), stg[0]);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t vm[16], vn[16];
-                    tmem_ld16(taddr + 16 * c, vm);
-                    tmem_ld16(taddr + 128 + 16 * c, vn);
-                    tmem_ld_wait();
+                for (int step = 0; step < NSTEP; ++step) {
+                    const bool is_min = F::HAS_MIN && step < 4;
+                    const int c = step & 3;
+                    if (step + 1 < NSTEP) {
+                        const bool nm = F::HAS_MIN && step + 1 < 4;
+                        tmem_ld16((nm ? t_min : t_main) + 16 * ((step + 1) & 3), stg[(step + 1) & 1]);
+                    }
+                    const uint64_t sc2 = is_min ? ndm2 : dw2;
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const float4 d8 = *reinterpret_cast<const float4*>(&s_d8[buf][colhalf * 64 + 16 * c + 4 * q4]);
-                        const float d8v[4] = {d8.x, d8.y, d8.z, d8.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float t = fmaf(dw, __uint_as_float(vm[4 * q4 + i]), -(dmw * __uint_as_float(vn[4 * q4 + i])));
-                            acc[16 * c + 4 * q4 + i] = fmaf(d8v[i], t, acc[16 * c + 4 * q4 + i]);
-                        }
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 dv = lds128(d8_addr + 64 * c + 16 * q);
+                        const uint64_t d8a = f32x2_pack_bits(dv.x, dv.y), d8b = f32x2_pack_bits(dv.z, dv.w);
+                        const uint64_t ta = f32x2_mul(sc2, f32x2_pack_bits(stg[step & 1][4 * q], stg[step & 1][4 * q + 1]));
+                        const uint64_t tb = f32x2_mul(sc2, f32x2_pack_bits(stg[step & 1][4 * q + 2], stg[step & 1][4 * q + 3]));
+                        acc[8 * c + 2 * q] = f32x2_fma(d8a, ta, acc[8 * c + 2 * q]);
+                        acc[8 * c + 2 * q + 1] = f32x2_fma(d8b, tb, acc[8 * c + 2 * q + 1]);
+                    }
+                    if (step + 1 < NSTEP) tmem_ld_wait();
+                    if (F::HAS_MIN && step == 2) {  // every min column of this thread has been read
+                        tc5_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&min_free);
+                    }
+                    if (step == NSTEP - 2) {  // every main column has been read: the buffer may be overwritten
+                        tc5_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&epi_done[buf]);
                     }
                 }
-                tc5_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                if (pre && etid < G_TILE_N) s_d8[buf ^ 1][etid] = d8_n;
+                hdr_c = hdr_n;
             }
             // ---- store the tile ----
+#ifdef CMOE_GEMM_TIMING
+            const long long ts_ = clock64();
+#endif
+            const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             const uint32_t pc0 = tc.p0 + colhalf * 64;
-            if (GATE_UP) {
+            float v[64];
 #pragma unroll
-                for (int c = 0; c < 64; ++c) {
-                    const float other = __shfl_xor_sync(0xffffffffu, acc[c], 1);
-                    // even lane holds w1 x, odd lane w3 x of the same output row; even lanes store the first 32
-                    // columns of this half, odd lanes the last 32
-                    const bool mine = ((lane & 1) == 0) ? (c < 32) : (c >= 32);
-                    if (mine && pc0 + c < tc.p_end) {
-                        const float gv = (lane & 1) ? other : acc[c], uv = (lane & 1) ? acc[c] : other;
-                        P.out[(size_t)(pc0 + c) * P.N + n] = silu_f(gv) * uv;
-                    }
+            for (int c2 = 0; c2 < 32; ++c2) f32x2_unpack(acc[c2], v[2 * c2], v[2 * c2 + 1]);
+            if (GATE_UP) {
+                // even lane holds w1 x, odd lane w3 x of the same output row: the even lane finishes columns
+                // 0..31 of this half, the odd lane columns 32..63, one exchange per pair of columns
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? v[c] : v[c + 32], 1);
+                    const float gv = (lane & 1) ? recv : v[c], uv = (lane & 1) ? v[c + 32] : recv;
+                    const uint32_t p = pc0 + c + ((lane & 1) ? 32 : 0);
+                    if (p < tc.p_end) P.out[(size_t)p * P.N + n] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                 }
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; ++c)
-                    if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = acc[c];
+                    if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = v[c];
             }
+#ifdef CMOE_GEMM_TIMING
+            gt_[4] += clock64() - ts_;
+#endif
+            tile += gridDim.x;
+            tc = tcn;
+            rowc = rown;
+            have = have_n;
         }
-    } else if (warp == G_EPI_WARPS) {
+        GT_END(16, threadIdx.x == 0);
+    } else if (warp < G_WARP_TMA) {
+        // ===================== weight unpack -> fp16 operand in tensor memory =====================
+        const int quarter = warp & 3, h = (warp - G_EPI_WARPS) >> 2;
+        const int r = 32 * quarter + lane;
+        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)F::A_BASE;
+        const uint32_t min_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        uint32_t ita = 0, ab = 0;
+        long long tile = blockIdx.x;
+        TileCoord tc, tcn;
+        bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+        typename F::Row rowc{}, rown{};
+        typename F::Pre cur, nxt;
+        GT_BEGIN();
+        if (have) {
+            const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
+            rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
+            F::load(cur, rowc, 0, h);
+            nxt = cur;
+        }
+        while (have) {
+            const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            if (have_n) {
+                const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
+                rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
+            }
+            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                if (blk + 1 < P.kb)
+                    F::load(nxt, rowc, blk + 1, h);
+                else if (have_n)
+                    F::load(nxt, rown, 0, h);
+                typename F::Ctx ctx;
+                F::begin(cur, ctx);
+#pragma unroll
+                for (int s = 0; s < 4; ++s, ++ita) {
+                    const int st = ita % G_A_STAGES;
+                    if (ita >= G_A_STAGES) GT(0, mbar_wait(&empty_a[st], ((ita / G_A_STAGES) & 1) ^ 1, abort_flag));
+                    tc5_fence_after_sync();
+                    GT(2, F::emit(s, cur, ctx, ta_lane + (uint32_t)(st * F::A_COLS), h));
+                    GT(3, tmem_st_wait());
+                    tc5_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_a[st]);
+                }
+                if (F::HAS_MIN) {
+                    const int ms = ab & 1;
+                    if (ab >= 2) GT(1, mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag));
+                    F::emit_min(ctx, smem_min_a + (size_t)ms * G_TILE_BYTES + min_row_off, h, r & 7);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_m[ms]);
+                }
+                cur = nxt;
+            }
+            tile += gridDim.x;
+            tc = tcn;
+            rowc = rown;
+            have = have_n;
+        }
+        GT_END(8, threadIdx.x == 32 * G_EPI_WARPS);
+    } else if (warp == G_WARP_TMA) {
         // ===================== TMA: activation operand =====================
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t itb = 0, ab = 0;
             TileCoord tc;
+            GT_BEGIN();
             for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-                for (int blk = 0; blk < P.kb; ++blk) {
-                    for (int s = 0; s < 5; ++s, ++it) {
-                        const int st = it % G_STAGES;
-                        if (it >= G_STAGES) mbar_wait(&empty_bar[st], ((it / G_STAGES) & 1) ^ 1, abort_flag);
-                        mbar_expect_tx(&full_bar[st], G_STAGE_B);
-                        uint8_t* dst = smem + (size_t)st * G_STAGE + G_STAGE_A;
-                        if (s < 4)
-                            tma_load_2d(dst, &map_b, blk * 256 + s * 64, (int)tc.p0, &full_bar[st]);
-                        else
-                            tma_load_2d(dst, &map_bs, blk * 64, (int)tc.p0, &full_bar[st]);
+                for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                    for (int s = 0; s < 4; ++s, ++itb) {
+                        const int st = itb % G_B_STAGES;
+                        if (itb >= G_B_STAGES) GT(0, mbar_wait(&empty_b[st], ((itb / G_B_STAGES) & 1) ^ 1, abort_flag));
+                        mbar_expect_tx(&full_b[st], G_TILE_BYTES);
+                        tma_load_2d(smem + (size_t)st * G_TILE_BYTES, &map_b, blk * 256 + s * 64, (int)tc.p0, &full_b[st]);
+                    }
+                    if (F::HAS_MIN) {
+                        const int ms = ab & 1;
+                        if (ab >= 2) mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag);
+                        mbar_expect_tx(&full_m[ms], G_TILE_BYTES);
+                        tma_load_2d(smem_min_b + (size_t)ms * G_TILE_BYTES, &map_bs, blk * 64, (int)tc.p0, &full_m[ms]);
                     }
                 }
             }
+            GT_END(24, true);
         }
-    } else if (warp == G_EPI_WARPS + 1) {
+    } else {
         // ===================== MMA issue =====================
         if (lane == 0) {
-            uint32_t it = 0, ab = 0;
+            uint32_t ita = 0, itb = 0, ab = 0;
             TileCoord tc;
+            GT_BEGIN();
             for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
                 for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                     const int buf = ab & 1;
-                    if (ab >= 2) mbar_wait(&tmem_empty[buf], ((ab >> 1) & 1) ^ 1, abort_flag);
+                    // the drain of block ab - 2 has released this main accumulator
+                    if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
                     tc5_fence_after_sync();
-                    const uint32_t d_main = tmem_base + (uint32_t)(buf * 256), d_min = d_main + 128;
-                    for (int s = 0; s < 5; ++s, ++it) {
-                        const int st = it % G_STAGES;
-                        mbar_wait(&full_bar[st], (it / G_STAGES) & 1, abort_flag);
+                    const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * 128);
+                    for (int s = 0; s < 4; ++s, ++ita, ++itb) {
+                        const int sa = ita % G_A_STAGES, sb = itb % G_B_STAGES;
+                        GT(0, mbar_wait(&full_a[sa], (ita / G_A_STAGES) & 1, abort_flag));
+                        GT(1, mbar_wait(&full_b[sb], (itb / G_B_STAGES) & 1, abort_flag));
                         tc5_fence_after_sync();
-                        const uint32_t a_addr = smem_u32(smem + (size_t)st * G_STAGE);
-                        const uint64_t da = umma_desc_sw128(a_addr), db = umma_desc_sw128(a_addr + G_STAGE_A);
-                        if (s < 4) {
+                        const uint32_t a_t = tmem_base + (uint32_t)(F::A_BASE + sa * F::A_COLS);
+                        const uint64_t db = umma_desc_sw128(smem_u32(smem + (size_t)sb * G_TILE_BYTES));
+#ifdef CMOE_GEMM_TIMING
+                        const long long tm_ = clock64();
+#endif
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) umma_f16(d_main, da + 2 * k, db + 2 * k, IDESC, (s | k) != 0);
-                        } else {
-                            umma_f16(d_min, da, db, IDESC, false);
+                        for (int k = 0; k < 4; ++k) {
+                            umma_f16_ts(d_main, a_t + 8 * k, db + 2 * k, IDESC, (s | k) != 0);
+                            if (F::A_PARTS == 2) umma_f16_ts(d_main, a_t + 32 + 8 * k, db + 2 * k, IDESC, true);
                         }
-                        umma_commit(&empty_bar[st]);  // the stage may be refilled once these MMAs have read it
+#ifdef CMOE_GEMM_TIMING
+                        gt_[5] += clock64() - tm_;
+#endif
+                        GT(6, umma_commit(&empty_a[sa]); umma_commit(&empty_b[sb]));  // stages refillable once read
+                    }
+                    if (F::HAS_MIN) {
+                        const int ms = ab & 1;
+                        // the single min accumulator: the drain of block ab - 1 must have read it
+                        if (ab >= 1) GT(3, mbar_wait(&min_free, (ab - 1) & 1, abort_flag));
+                        GT(4, mbar_wait(&full_m[ms], (ab >> 1) & 1, abort_flag));
+                        tc5_fence_after_sync();
+                        const uint64_t da = umma_desc_sw128(smem_u32(smem_min_a + (size_t)ms * G_TILE_BYTES));
+                        const uint64_t db = umma_desc_sw128(smem_u32(smem_min_b + (size_t)ms * G_TILE_BYTES));
+                        umma_f16(tmem_base + (uint32_t)G_TM_MIN, da, db, IDESC, false);
+                        umma_commit(&empty_m[ms]);
                     }
                     umma_commit(&tmem_full[buf]);
                 }
             }
-        }
-    } else {
-        // ===================== weight unpack: Q4_K nibbles -> fp16 (x sub-block scale) =====================
-        const int dt = threadIdx.x - 32 * (G_EPI_WARPS + 2);  // 0..255
-        const int r = dt >> 1, h = dt & 1;                    // tile row, 16-byte half of the row's 32 bytes per slab
-        const uint32_t row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        const int sw = r & 7;
-        uint32_t it = 0;
-        TileCoord tc;
-        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-            const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
-            const uint8_t* wrow = ((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e]) + (size_t)n * row_bytes;
-            for (int blk = 0; blk < P.kb; ++blk) {
-                const uint8_t* wb = wrow + (size_t)blk * Q4K_BYTES;
-                const uint4 hdr = *reinterpret_cast<const uint4*>(wb);
-                uint32_t sc[2], mn[2];
-                q4k_unpack_scales(hdr.y, hdr.z, hdr.w, sc, mn);
-                uint4 q[4];
-#pragma unroll
-                for (int s = 0; s < 4; ++s) q[s] = *reinterpret_cast<const uint4*>(wb + 16 + 32 * s + 16 * h);
-#pragma unroll
-                for (int s = 0; s < 5; ++s, ++it) {
-                    const int st = it % G_STAGES;
-                    if (it >= G_STAGES) mbar_wait(&empty_bar[st], ((it / G_STAGES) & 1) ^ 1, abort_flag);
-                    uint8_t* arow = smem + (size_t)st * G_STAGE + row_off;
-                    if (s < 4) {
-                        const int jl = 2 * s, jh = 2 * s + 1;
-                        const float fl = (float)byte_u(sc[jl >> 2], jl & 3), fh = (float)byte_u(sc[jh >> 2], jh & 3);
-                        const __half2 scl = __float2half2_rn(fl), offl = __float2half2_rn(-1024.f * fl);
-                        const __half2 sch = __float2half2_rn(fh), offh = __float2half2_rn(-1024.f * fh);
-                        const uint32_t w[4] = {q[s].x, q[s].y, q[s].z, q[s].w};
-                        uint32_t lo[8], hi[8];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            lo[2 * i] = nib2_to_scaled_half2(w[i], scl, offl);            // elements (0, 2) of the 4
-                            lo[2 * i + 1] = nib2_to_scaled_half2(w[i] >> 8, scl, offl);   // elements (1, 3)
-                            hi[2 * i] = nib2_to_scaled_half2(w[i] >> 4, sch, offh);
-                            hi[2 * i + 1] = nib2_to_scaled_half2(w[i] >> 12, sch, offh);
-                        }
-                        // 16-byte chunks of the 128-byte row: low nibbles -> k = 16h .. 16h+15 (chunks 2h, 2h+1),
-                        // high nibbles -> k = 32 + 16h .. (chunks 4+2h, 5+2h); chunk index XOR (row & 7) = 128B swizzle
-                        *reinterpret_cast<uint4*>(arow + (((2 * h) ^ sw) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        *reinterpret_cast<uint4*>(arow + (((2 * h + 1) ^ sw) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-                        *reinterpret_cast<uint4*>(arow + (((4 + 2 * h) ^ sw) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        *reinterpret_cast<uint4*>(arow + (((5 + 2 * h) ^ sw) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                    } else {
-                        // min operand: k = 2j, 2j+1 both carry m_j (against the two 16-element block sums of sub-block j)
-                        uint32_t mw[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const __half2 m2 = __float2half2_rn((float)byte_u(mn[h], i));
-                            mw[i] = *reinterpret_cast<const uint32_t*>(&m2);
-                        }
-                        *reinterpret_cast<uint4*>(arow + ((h ^ sw) << 4)) = make_uint4(mw[0], mw[1], mw[2], mw[3]);
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_bar[st]);
-                }
-            }
+            GT_END(0, true);
         }
     }
     tc5_fence_before_sync();
     __syncthreads();
-    if (warp == G_EPI_WARPS) {
+    if (warp == G_WARP_TMA) {
         tc5_fence_after_sync();
         tmem_dealloc(tmem_base, G_TMEM_COLS);
     }
@@ -390,6 +652,15 @@ bool make_map_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 
 int g_gemm_sms = -1;
 
+template <class F, bool GATE_UP>
+cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
+    const int smem_bytes = (G_B_STAGES + (F::HAS_MIN ? 4 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
+    auto kfn = expert_gemm_kernel<F, GATE_UP>;
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return e;
+    return launch_k(kfn, dim3(g_gemm_sms), dim3(G_THREADS), (size_t)smem_bytes, st, G, map_b, map_bs);
+}
+
 }  // namespace
 
 // Scratch the GEMM needs for P grouped rows of length K (fp16 operand, block-sum operand, scales).
@@ -398,11 +669,13 @@ size_t expert_gemm_scratch_bytes(int64_t P, int K) {
     return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256);
 }
 
-// cudaErrorNotSupported when the shape / dtype is not taken.
-cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype, int E,
-                               int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
+// Takes Q4_K weights in GGUF layout (repacked = false) and Q6_K weights in the repacked layout of the
+// decode kernels (repacked = true); cudaErrorNotSupported for every other shape / dtype / layout.
+cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
+                               bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                const int8_t* aq, const float* ascale, const int16_t* absum, float* out, void* scratch) {
-    if (dtype != CANDLE_GGML_Q4K || !scratch) return cudaErrorNotSupported;
+    if (!scratch) return cudaErrorNotSupported;
+    if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked))) return cudaErrorNotSupported;
     if (K % 256 != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
     if (!encode_tiled_fn()) return cudaErrorNotSupported;
     if (g_gemm_sms < 0) {
@@ -443,14 +716,9 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     G.m_tiles = gate_up ? N / 64 : N / 128;
     e = stream_status_ptr(&G.status);
     if (e != cudaSuccess) return e;
-    if (gate_up) {
-        e = cudaFuncSetAttribute(expert_gemm_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        return launch_k(expert_gemm_q4k_kernel<true>, dim3(g_gemm_sms), dim3(G_THREADS), G_SMEM_BYTES, st, G, map_b, map_bs);
-    }
-    e = cudaFuncSetAttribute(expert_gemm_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    return launch_k(expert_gemm_q4k_kernel<false>, dim3(g_gemm_sms), dim3(G_THREADS), G_SMEM_BYTES, st, G, map_b, map_bs);
+    if (dtype == CANDLE_GGML_Q4K)
+        return gate_up ? launch_gemm_kernel<GemmQ4K, true>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false>(st, G, map_b, map_bs);
+    return gate_up ? launch_gemm_kernel<GemmQ6K, true>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false>(st, G, map_b, map_bs);
 }
 
 }  // namespace cmoe

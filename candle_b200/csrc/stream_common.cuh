@@ -37,6 +37,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached, or
 // as soon as another thread of the CTA has raised the flag.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;  // the common case costs one instruction and a branch
     for (int i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;

@@ -509,3 +509,53 @@ def test_block_prefill_properties_at_full_size(orc, torch_cuda):
     assert H.rel_l2(small.cpu().numpy(), y[100:108].cpu().numpy()) < 5e-4
     again = blk.forward(x)
     assert torch.equal(again, y)  # determinism at full size
+
+
+def _device_status():
+    """Health word of the kernels' bounded waits (0 = no wait ever expired)."""
+    from candle_b200 import _lib
+    v = C.c_int32(-1)
+    assert _lib.load().candle_moe_device_status(C.byref(v)) == 0
+    return v.value
+
+
+@pytest.mark.parametrize("name13,name2", [("Q4K", "Q6K"), ("Q6K", "Q6K"), ("Q4K", "Q4K")])
+def test_block_large_batch_tensor_core_form(orc, torch_cuda, name13, name2, monkeypatch):
+    """More than 64 tokens take the tcgen05 grouped GEMM (Q4_K from the GGUF blocks, Q6_K from the
+    repacked copies).  Against the oracle, and against the streaming form of the same block: both
+    multiply the same integers, so they differ only by f32 summation order and the few one-step
+    flips that causes when the hidden rows are re-quantized."""
+    torch = torch_cuda
+    from candle_b200 import _lib
+    mw = orc.make_moe_weights(11, 512, 1024, 8, 2, getattr(orc, name13), getattr(orc, name2))
+    x = orc.make_activations(31, 300, 512)
+    blk, y, ref = _check_block(orc, torch, mw, x, f"tensor-core form {name13}/{name2}", prepack=True)
+    assert _device_status() == 0
+    monkeypatch.setenv("CANDLE_MOE_GEMM", "0")
+    y_stream = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    monkeypatch.delenv("CANDLE_MOE_GEMM")
+    assert H.rel_l2(y, y_stream) < 2e-4
+    y_again = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.array_equal(y, y_again)
+
+
+def test_block_prefill_over_repacked_weights(orc, torch_cuda):
+    """Config-2 shapes at T = 1024 over the repacked copies (w2 Q6_K then takes the tensor-core form
+    too): finite, deterministic, and the rows of a small batch agree with the same rows inside."""
+    torch = torch_cuda
+    from candle_b200 import GgmlDType, Mlp, MlpOrMoe, QMatMul, QTensor, _lib
+    d, ff, E, k, T = 4096, 14336, 8, 2, 1024
+    g = torch.Generator(device="cuda").manual_seed(2)
+    experts = []
+    for e in range(E):
+        mk = lambda shape, dt: QMatMul(QTensor.quantize(torch.randn(shape, generator=g, device="cuda") * 0.02, dt))
+        experts.append(Mlp(mk((ff, d), GgmlDType.Q4K), mk((d, ff), GgmlDType.Q6K), mk((ff, d), GgmlDType.Q4K)))
+    router = torch.randn((E, d), generator=g, device="cuda") * 0.02
+    blk = MlpOrMoe.moe(k, router, experts).prepack()
+    x = torch.randn((T, d), generator=g, device="cuda")
+    y = blk.forward(x)
+    assert torch.isfinite(y).all()
+    assert _device_status() == 0
+    small = blk.forward(x[500:508].clone())
+    assert H.rel_l2(small.cpu().numpy(), y[500:508].cpu().numpy()) < 5e-4
+    assert torch.equal(blk.forward(x), y)
