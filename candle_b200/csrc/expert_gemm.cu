@@ -37,6 +37,16 @@
 
 namespace cmoe {
 
+#ifdef CMOE_GEMM_TRACE
+// Event timeline of CTA 0 (local experiments only): g_gemm_trace[stream][index] = clock at the event.
+__device__ unsigned g_gemm_trace[16][1024];
+extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_trace(unsigned* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned) * 16 * 1024);
+}
+#define TR(stream, idx) do { if (blockIdx.x == 0 && (idx) < 1024u) g_gemm_trace[stream][idx] = (unsigned)clock(); } while (0)
+#else
+#define TR(stream, idx) do { } while (0)
+#endif
 #ifdef CMOE_GEMM_TIMING
 __device__ long long g_gemm_timing[32];
 extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timing(long long* out) {
@@ -47,15 +57,18 @@ extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timi
 namespace {
 
 constexpr int G_TILE_M = 128, G_TILE_N = 128, G_SLAB_K = 64;
-constexpr int G_A_STAGES = 4, G_B_STAGES = 8;
+constexpr int G_B_STAGES = 4;   // in shared memory, two slabs each
 constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
 constexpr int G_WARP_TMA = G_EPI_WARPS + G_DQ_WARPS, G_WARP_MMA = G_WARP_TMA + 1;
-constexpr int G_THREADS = 32 * (G_WARP_MMA + 1);  // 576
+constexpr int G_THREADS = 32 * 20;  // five warpgroups: 2 epilogue, 2 unpack, 1 with the TMA and MMA warps (+ 2 idle)
+constexpr int G_REGS_EPI = 128, G_REGS_MISC = 32;  // budgets after the trade: 2 * 128 + 2 * 96 + 32 = 5 * 96, the launch allocation
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_MAIN = 0;    // + 128 * buffer
 constexpr int G_TM_MIN = 256;   // Q4_K only
+constexpr int G_MIN_GROUP = 4;  // blocks whose min terms are summed in tensor memory before they are drained
 constexpr int Q6K_HTB_BYTES = 1680;
+
 
 // Cycle counters of CTA 0 (local experiments only, -DCMOE_GEMM_TIMING): where each role waits.
 #ifdef CMOE_GEMM_TIMING
@@ -70,17 +83,28 @@ constexpr int Q6K_HTB_BYTES = 1680;
 #endif  // repacked half-tile block: 8 rows x 256 elements (expert_direct.cu)
 
 // ---------------------------------------------------------------------------------------------
-// Operand preparation: the int8 activation rows in grouped order as fp16 (B operand), their int16
-// block sums as fp16 (B operand of the min product, 16 real + 48 zero columns per block so that it
-// uses the same 128-byte-swizzled box), and the block scales transposed to [block][position].
+// Operand preparation: the int8 activation rows in grouped order as fp16 (B operand), the block scales
+// transposed to [block][position], and the activation side of the Q4_K min term (below).
 // Inside every group of 4 k the order is (0, 2, 1, 3): the weight unpack produces that order for
 // free (nibbles of bytes 0,2 and 1,3 convert pairwise), and a dot product does not care.
 // Rows p >= P are zero padding so that a 128-row box never leaves the buffer.
+//
+// Min term of Q4_K (k_quants.rs:1262-1268): - sum_b d8[p,b] dmin[r,b] sum_j m[r,b,j] bsum32[p,b,j].
+// Both factors carry a float scale, so this is a plain GEMM over (b, j) with fp32-valued operands
+// A' = -dmin m (17 significant bits) and B' = d8 bsum32 (24).  It runs as kind::tf32 MMAs that
+// accumulate over the whole tile: each operand is split into tf32 terms (10-bit mantissa, fp32
+// exponent range: no overflow or underflow concerns), A' = a1 + a2 exactly, B' = b1 + b2 to 2^-23, and
+// the products a1 b1 + a1 b2 + a2 b1 are three K=8 steps per block.  Per (position, block) the buffer
+// holds 32 floats: [b1 (8) | b2 (8) | b1 (8) | 0 (8)], matched by [a1 | a1 | a2 | -] on the weight side.
+// The dropped terms are below 2^-22 of the min term: the order of the reference's own f32 rounding.
 // ---------------------------------------------------------------------------------------------
+// nearest value with a 10-bit mantissa (the 13 low bits of the fp32 container zero)
+__device__ __forceinline__ float tf32_head(float v) { return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u); }
+
 __global__ void __launch_bounds__(256)
 prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ ascale, const int16_t* __restrict__ absum,
                    const uint32_t* __restrict__ row_of, int P, int P_pad, int K, __half* __restrict__ bf16,
-                   __half* __restrict__ bs16, float* __restrict__ d8t) {
+                   float* __restrict__ bmin, float* __restrict__ d8t) {
     pdl_trigger();
     pdl_wait();
     const int kb = K >> 8;
@@ -89,8 +113,7 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
     if (unit >= (int64_t)P_pad * kb) return;
     const int p = (int)(unit / kb), blk = (int)(unit - (int64_t)p * kb);
     uint4 o = make_uint4(0, 0, 0, 0);
-    uint32_t s2 = 0;
-    float d8 = 0.f;
+    float bm = 0.f, d8 = 0.f;
     if (p < P) {
         const int64_t row = row_of ? (int64_t)row_of[p] : (int64_t)p;
         const uint2 v = *reinterpret_cast<const uint2*>(aq + row * K + blk * 256 + lane * 8);
@@ -101,15 +124,17 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
         h[2] = __halves2half2(__int2half_rn(b[4]), __int2half_rn(b[6]));
         h[3] = __halves2half2(__int2half_rn(b[5]), __int2half_rn(b[7]));
         o = *reinterpret_cast<uint4*>(h);
-        if (lane < 8) {
-            const int16_t* bs = absum + row * (K / 16) + blk * 16 + 2 * lane;
-            const __half2 t = __halves2half2(__int2half_rn((int)bs[0]), __int2half_rn((int)bs[1]));
-            s2 = *reinterpret_cast<const uint32_t*>(&t);
-        }
         d8 = ascale[row * kb + blk];
+        if (bmin) {
+            const int j = lane & 7, part = lane >> 3;  // word: part 0, 2 = b1_j; part 1 = b2_j; part 3 = 0
+            const int16_t* bs = absum + row * (K / 16) + blk * 16 + 2 * j;
+            const float bv = __fmul_rn(d8, (float)((int)bs[0] + (int)bs[1]));
+            const float b1 = tf32_head(bv), b2 = tf32_head(__fsub_rn(bv, b1));
+            bm = part == 1 ? b2 : (part == 3 ? 0.f : b1);
+        }
     }
     *reinterpret_cast<uint4*>(bf16 + (int64_t)p * K + blk * 256 + lane * 8) = o;
-    reinterpret_cast<uint32_t*>(bs16 + ((int64_t)p * kb + blk) * 64)[lane] = s2;  // 32 words = 64 halves
+    if (bmin) bmin[((int64_t)p * kb + blk) * 32 + lane] = bm;
     if (lane == 0) d8t[(int64_t)blk * P_pad + p] = d8;
 }
 
@@ -192,13 +217,27 @@ struct GemmQ4K {
         tmem_st8(ta + 8 * h, lo);
         tmem_st8(ta + 16 + 8 * h, hi);
     }
-    // min operand in shared memory: k = 2j, 2j+1 both carry m_j (against the two 16-element sums of sub-block j)
-    __device__ static __forceinline__ void emit_min(const Ctx& c, uint8_t* arow, int h, int sw) {
-        const __half2 k1024 = __float2half2_rn(1024.f);
-        uint32_t mw[4];
+    // weight side of the min term (see prep_gemm_b_kernel): a_j = -dmin * m_j split into tf32 terms.  One row is
+    // 32 floats [a1 (8) | a1 (8) | a2 (8) | unused]; thread h = 0 writes the four 16-byte chunks of a1, thread
+    // h = 1 the two of a2.  2^23 + m as float bits is 0x4B000000 | m.
+    __device__ static __forceinline__ void emit_min(const Pre& pr, const Ctx& c, uint8_t* arow, int h, int sw) {
+        const float ndm = -half_bits_to_float((uint16_t)(pr.hdr.x >> 16));
+        uint32_t o[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mw[i] = bits_h2(__hsub2(byte_magic2(c.mn[h], i), k1024));
-        *reinterpret_cast<uint4*>(arow + ((h ^ sw) << 4)) = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+        for (int j = 0; j < 8; ++j) {
+            const float mf = __uint_as_float(0x4B000000u | byte_u(c.mn[j >> 2], j & 3)) - 8388608.f;
+            const float a = __fmul_rn(ndm, mf), a1 = tf32_head(a);
+            o[j] = __float_as_uint(h == 0 ? a1 : __fsub_rn(a, a1));
+        }
+        if (h == 0) {
+            *reinterpret_cast<uint4*>(arow + ((0 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(arow + ((1 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+            *reinterpret_cast<uint4*>(arow + ((2 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(arow + ((3 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+            *reinterpret_cast<uint4*>(arow + ((4 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(arow + ((5 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
     }
 };
 
@@ -276,7 +315,7 @@ struct GemmQ6K {
             tmem_st4(ta + 32 + 8 * cw + 4 * h, o2[0], o2[1], o2[2], o2[3]);
         }
     }
-    __device__ static __forceinline__ void emit_min(const Ctx&, uint8_t*, int, int) {}
+    __device__ static __forceinline__ void emit_min(const Pre&, const Ctx&, uint8_t*, int, int) {}
 };
 
 struct TileCoord {
@@ -311,22 +350,22 @@ __global__ void __launch_bounds__(G_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_bs) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_a[G_A_STAGES], empty_a[G_A_STAGES], full_b[G_B_STAGES], empty_b[G_B_STAGES];
+    __shared__ uint64_t full_a[2], empty_a[2], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
     __shared__ uint64_t full_m[2], empty_m[2], tmem_full[2], epi_done[2], min_free;
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
-    __shared__ __align__(16) float s_d8[2][G_TILE_N];
+    __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* smem_min_a = smem + G_B_STAGES * G_TILE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
+    uint8_t* smem_min_a = smem + G_B_STAGES * 2 * G_TILE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
     uint8_t* smem_min_b = smem_min_a + 2 * G_TILE_BYTES;     //       2 slots of the block sums (activation side)
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < G_A_STAGES; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbar_init(&full_a[s], G_DQ_WARPS);
             mbar_init(&empty_a[s], 1);
         }
@@ -349,13 +388,17 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     tc5_fence_after_sync();
     const uint32_t tmem_base = s_tmem_base;
     volatile int* abort_flag = &s_abort;
-    constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, G_TILE_N);
+    constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, G_TILE_N), IDESC_TF32 = umma_idesc_tf32(G_TILE_M, G_TILE_N);
 
+    // Register budget: launched with 96 per thread; the TMA/MMA warpgroup hands 64 per thread back to the CTA's
+    // pool and the two epilogue warpgroups take 32 more each, so the total stays what the launch allocated (a
+    // request beyond the pool would wait forever).
+    if (warp >= G_WARP_TMA) reg_dealloc<G_REGS_MISC>();  // the whole last warpgroup (TMA, MMA and two idle warps)
     if (warp < G_EPI_WARPS) {
+        reg_alloc<G_REGS_EPI>();
         // ===================== epilogue =====================
         const int quarter = warp & 3, colhalf = warp >> 2;
         const int r = 32 * quarter + lane;  // tile row = TMEM lane
-        const int etid = threadIdx.x;       // 0..255
         const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(colhalf * 64);
         uint32_t ab = 0;
         long long tile = blockIdx.x;
@@ -368,7 +411,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
             hdr_c = F::load_hdr(rowc, 0);
-            if (etid < G_TILE_N) s_d8[0][etid] = P.d8t[tc.p0 + etid];
+            const float* dp = P.d8t + tc.p0 + colhalf * 64 + lane;
+            s_d8[warp][0][lane] = dp[0];
+            s_d8[warp][0][lane + 32] = dp[32];
+            __syncwarp();
         }
         while (have) {
             const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
@@ -376,74 +422,85 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
                 rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
             }
-            uint64_t acc[32];
+            float acc[64];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 const int buf = ab & 1;
-                GT(1, named_bar_sync(2, 32 * G_EPI_WARPS));  // s_d8[buf] is complete; s_d8[buf ^ 1] is no longer read
                 // scales of the next block (maybe of the next tile): in flight while this block is drained
-                float d8_n = 0.f;
+                float d8_n0 = 0.f, d8_n1 = 0.f;
                 bool pre = false;
                 if (blk + 1 < P.kb) {
                     hdr_n = F::load_hdr(rowc, blk + 1);
-                    if (etid < G_TILE_N) d8_n = P.d8t[(size_t)(blk + 1) * P.P_pad + tc.p0 + etid];
+                    const float* dp = P.d8t + (size_t)(blk + 1) * P.P_pad + tc.p0 + colhalf * 64 + lane;
+                    d8_n0 = dp[0];
+                    d8_n1 = dp[32];
                     pre = true;
                 } else if (have_n) {
                     hdr_n = F::load_hdr(rown, 0);
-                    if (etid < G_TILE_N) d8_n = P.d8t[tcn.p0 + etid];
+                    const float* dp = P.d8t + tcn.p0 + colhalf * 64 + lane;
+                    d8_n0 = dp[0];
+                    d8_n1 = dp[32];
                     pre = true;
                 }
                 const float dw = half_bits_to_float((uint16_t)(hdr_c & 0xffff));
                 const uint64_t dw2 = f32x2_pack(dw, dw);
-                uint64_t ndm2 = 0ull;
-                if (F::HAS_MIN) {
-                    const float ndm = -half_bits_to_float((uint16_t)(hdr_c >> 16));
-                    ndm2 = f32x2_pack(ndm, ndm);
-                }
+                if (threadIdx.x == 0) TR(0, ab);
                 GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
                 tc5_fence_after_sync();
-                const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128), t_min = ta_lane + (uint32_t)G_TM_MIN;
-                const uint32_t d8_addr = smem_u32(&s_d8[buf][colhalf * 64]);
-                // Steps of 16 columns: (Q4_K) the min accumulator first, so that it is released to the MMA
-                // thread as early as possible, then the main accumulator.  The load of step i+1 is in
-                // flight while step i is scaled into the register accumulators.
-                constexpr int NSTEP = F::HAS_MIN ? 8 : 4;
+                if (threadIdx.x == 0) TR(1, ab);
+                const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128);
+                const uint32_t d8_addr = smem_u32(&s_d8[warp][buf][0]);
+                // Four steps of 16 columns; the load of step i+1 is in flight while step i is scaled into
+                // the register accumulators: acc += (d8[col] * dw[row]) * v.
                 uint32_t stg[2][16];
-                tmem_ld16((F::HAS_MIN ? t_min : t_main), stg[0]);
+                tmem_ld16(t_main, stg[0]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int step = 0; step < NSTEP; ++step) {
-                    const bool is_min = F::HAS_MIN && step < 4;
-                    const int c = step & 3;
-                    if (step + 1 < NSTEP) {
-                        const bool nm = F::HAS_MIN && step + 1 < 4;
-                        tmem_ld16((nm ? t_min : t_main) + 16 * ((step + 1) & 3), stg[(step + 1) & 1]);
-                    }
-                    const uint64_t sc2 = is_min ? ndm2 : dw2;
+                for (int c = 0; c < 4; ++c) {
+                    if (c + 1 < 4) tmem_ld16(t_main + 16 * (c + 1), stg[(c + 1) & 1]);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint4 dv = lds128(d8_addr + 64 * c + 16 * q);
-                        const uint64_t d8a = f32x2_pack_bits(dv.x, dv.y), d8b = f32x2_pack_bits(dv.z, dv.w);
-                        const uint64_t ta = f32x2_mul(sc2, f32x2_pack_bits(stg[step & 1][4 * q], stg[step & 1][4 * q + 1]));
-                        const uint64_t tb = f32x2_mul(sc2, f32x2_pack_bits(stg[step & 1][4 * q + 2], stg[step & 1][4 * q + 3]));
-                        acc[8 * c + 2 * q] = f32x2_fma(d8a, ta, acc[8 * c + 2 * q]);
-                        acc[8 * c + 2 * q + 1] = f32x2_fma(d8b, tb, acc[8 * c + 2 * q + 1]);
+                        // the two scale products of a column pair in one packed multiply, then one fma per value
+                        float s0, s1, s2, s3;
+                        f32x2_unpack(f32x2_mul(dw2, f32x2_pack_bits(dv.x, dv.y)), s0, s1);
+                        f32x2_unpack(f32x2_mul(dw2, f32x2_pack_bits(dv.z, dv.w)), s2, s3);
+                        acc[16 * c + 4 * q] = fmaf(s0, __uint_as_float(stg[c & 1][4 * q]), acc[16 * c + 4 * q]);
+                        acc[16 * c + 4 * q + 1] = fmaf(s1, __uint_as_float(stg[c & 1][4 * q + 1]), acc[16 * c + 4 * q + 1]);
+                        acc[16 * c + 4 * q + 2] = fmaf(s2, __uint_as_float(stg[c & 1][4 * q + 2]), acc[16 * c + 4 * q + 2]);
+                        acc[16 * c + 4 * q + 3] = fmaf(s3, __uint_as_float(stg[c & 1][4 * q + 3]), acc[16 * c + 4 * q + 3]);
                     }
-                    if (step + 1 < NSTEP) tmem_ld_wait();
-                    if (F::HAS_MIN && step == 2) {  // every min column of this thread has been read
-                        tc5_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&min_free);
-                    }
-                    if (step == NSTEP - 2) {  // every main column has been read: the buffer may be overwritten
+                    if (c + 1 < 4) tmem_ld_wait();
+                    if (c == 2) {  // every column of this thread has been read: the buffer may be overwritten
                         tc5_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&epi_done[buf]);
                     }
                 }
-                if (pre && etid < G_TILE_N) s_d8[buf ^ 1][etid] = d8_n;
+                if (F::HAS_MIN && ((blk % G_MIN_GROUP) == G_MIN_GROUP - 1 || blk == P.kb - 1)) {
+                    // the min terms of this group of blocks (their MMAs were committed with this block's): a
+                    // short chain in the tensor core's truncating adder, then round-to-nearest adds here
+                    const uint32_t t_min = ta_lane + (uint32_t)G_TM_MIN;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t mv[16];
+                        tmem_ld16(t_min + 16 * c, mv);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) acc[16 * c + i] += __uint_as_float(mv[i]);
+                    }
+                    tc5_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&min_free);
+                }
+                if (pre) {
+                    s_d8[warp][buf ^ 1][lane] = d8_n0;
+                    s_d8[warp][buf ^ 1][lane + 32] = d8_n1;
+                }
+                __syncwarp();
                 hdr_c = hdr_n;
+                if (threadIdx.x == 0) TR(2, ab);
             }
             // ---- store the tile ----
 #ifdef CMOE_GEMM_TIMING
@@ -451,23 +508,20 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #endif
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             const uint32_t pc0 = tc.p0 + colhalf * 64;
-            float v[64];
-#pragma unroll
-            for (int c2 = 0; c2 < 32; ++c2) f32x2_unpack(acc[c2], v[2 * c2], v[2 * c2 + 1]);
             if (GATE_UP) {
                 // even lane holds w1 x, odd lane w3 x of the same output row: the even lane finishes columns
                 // 0..31 of this half, the odd lane columns 32..63, one exchange per pair of columns
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? v[c] : v[c + 32], 1);
-                    const float gv = (lane & 1) ? recv : v[c], uv = (lane & 1) ? v[c + 32] : recv;
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? acc[c] : acc[c + 32], 1);
+                    const float gv = (lane & 1) ? recv : acc[c], uv = (lane & 1) ? acc[c + 32] : recv;
                     const uint32_t p = pc0 + c + ((lane & 1) ? 32 : 0);
                     if (p < tc.p_end) P.out[(size_t)p * P.N + n] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                 }
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; ++c)
-                    if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = v[c];
+                    if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = acc[c];
             }
 #ifdef CMOE_GEMM_TIMING
             gt_[4] += clock64() - ts_;
@@ -511,20 +565,24 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 typename F::Ctx ctx;
                 F::begin(cur, ctx);
 #pragma unroll
-                for (int s = 0; s < 4; ++s, ++ita) {
-                    const int st = ita % G_A_STAGES;
-                    if (ita >= G_A_STAGES) GT(0, mbar_wait(&empty_a[st], ((ita / G_A_STAGES) & 1) ^ 1, abort_flag));
+                for (int pr = 0; pr < 2; ++pr, ita += 2) {
+                    // four slabs per block in four TMEM stages (stage = slab index), handed over in pairs
+                    if (lane == 0 && warp == 8) TR(3, ita);
+                    if (ab >= 1) GT(0, mbar_wait(&empty_a[pr], (ab & 1) ^ 1, abort_flag));
                     tc5_fence_after_sync();
-                    GT(2, F::emit(s, cur, ctx, ta_lane + (uint32_t)(st * F::A_COLS), h));
+                    if (lane == 0 && warp == 8) TR(4, ita);
+                    GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * pr * F::A_COLS), h));
+                    GT(2, F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * pr + 1) * F::A_COLS), h));
                     GT(3, tmem_st_wait());
                     tc5_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_a[st]);
+                    if (lane == 0) mbar_arrive(&full_a[pr]);
+                    if (lane == 0 && warp == 8) TR(5, ita);
                 }
                 if (F::HAS_MIN) {
                     const int ms = ab & 1;
                     if (ab >= 2) GT(1, mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag));
-                    F::emit_min(ctx, smem_min_a + (size_t)ms * G_TILE_BYTES + min_row_off, h, r & 7);
+                    F::emit_min(cur, ctx, smem_min_a + (size_t)ms * G_TILE_BYTES + min_row_off, h, r & 7);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_m[ms]);
@@ -539,77 +597,108 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         GT_END(8, threadIdx.x == 32 * G_EPI_WARPS);
     } else if (warp == G_WARP_TMA) {
         // ===================== TMA: activation operand =====================
-        if (lane == 0) {
-            uint32_t itb = 0, ab = 0;
-            TileCoord tc;
-            GT_BEGIN();
-            for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-                for (int blk = 0; blk < P.kb; ++blk, ++ab) {
-                    for (int s = 0; s < 4; ++s, ++itb) {
-                        const int st = itb % G_B_STAGES;
-                        if (itb >= G_B_STAGES) GT(0, mbar_wait(&empty_b[st], ((itb / G_B_STAGES) & 1) ^ 1, abort_flag));
-                        mbar_expect_tx(&full_b[st], G_TILE_BYTES);
-                        tma_load_2d(smem + (size_t)st * G_TILE_BYTES, &map_b, blk * 256 + s * 64, (int)tc.p0, &full_b[st]);
+        // the whole warp walks the loop (uniform control flow and addresses), one elected lane issues
+        uint32_t ab = 0;
+        TileCoord tc;
+        GT_BEGIN();
+        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
+            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                for (int s2 = 0; s2 < 2; ++s2) {  // one stage = two 64-wide slabs, one barrier
+                    const int st = 2 * (ab & 1) + s2;
+                    if (ab >= 2) GT(0, mbar_wait(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
+                    uint8_t* dst = smem + (size_t)st * 2 * G_TILE_BYTES;
+                    if (elect_one()) {
+                        mbar_expect_tx(&full_b[st], 2 * G_TILE_BYTES);
+                        tma_load_2d(dst, &map_b, blk * 256 + s2 * 128, (int)tc.p0, &full_b[st]);
+                        tma_load_2d(dst + G_TILE_BYTES, &map_b, blk * 256 + s2 * 128 + 64, (int)tc.p0, &full_b[st]);
                     }
-                    if (F::HAS_MIN) {
-                        const int ms = ab & 1;
-                        if (ab >= 2) mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag);
+                    __syncwarp();
+                }
+                if (F::HAS_MIN) {
+                    const int ms = ab & 1;
+                    if (ab >= 2) mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag);
+                    if (elect_one()) {
                         mbar_expect_tx(&full_m[ms], G_TILE_BYTES);
-                        tma_load_2d(smem_min_b + (size_t)ms * G_TILE_BYTES, &map_bs, blk * 64, (int)tc.p0, &full_m[ms]);
+                        tma_load_2d(smem_min_b + (size_t)ms * G_TILE_BYTES, &map_bs, blk * 32, (int)tc.p0, &full_m[ms]);
                     }
+                    __syncwarp();
                 }
             }
-            GT_END(24, true);
         }
-    } else {
+        GT_END(24, lane == 0);
+    } else if (warp == G_WARP_MMA) {
         // ===================== MMA issue =====================
-        if (lane == 0) {
-            uint32_t ita = 0, itb = 0, ab = 0;
-            TileCoord tc;
-            GT_BEGIN();
-            for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-                for (int blk = 0; blk < P.kb; ++blk, ++ab) {
-                    const int buf = ab & 1;
-                    // the drain of block ab - 2 has released this main accumulator
-                    if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
-                    tc5_fence_after_sync();
-                    const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * 128);
-                    for (int s = 0; s < 4; ++s, ++ita, ++itb) {
-                        const int sa = ita % G_A_STAGES, sb = itb % G_B_STAGES;
-                        GT(0, mbar_wait(&full_a[sa], (ita / G_A_STAGES) & 1, abort_flag));
-                        GT(1, mbar_wait(&full_b[sb], (itb / G_B_STAGES) & 1, abort_flag));
-                        tc5_fence_after_sync();
-                        const uint32_t a_t = tmem_base + (uint32_t)(F::A_BASE + sa * F::A_COLS);
-                        const uint64_t db = umma_desc_sw128(smem_u32(smem + (size_t)sb * G_TILE_BYTES));
-#ifdef CMOE_GEMM_TIMING
-                        const long long tm_ = clock64();
-#endif
+        uint32_t ita = 0, ab = 0, ng_done = 0;
+        TileCoord tc;
+        GT_BEGIN();
+        const uint32_t a_base = tmem_base + (uint32_t)F::A_BASE;
+        const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem));
+        const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a)), mb_desc0 = umma_desc_sw128(smem_u32(smem_min_b));
+        bool rdy_a = false;
+        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
+            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                const int buf = ab & 1;
+                // the drain of block ab - 2 has released this main accumulator
+                if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
+                tc5_fence_after_sync();
+                if (lane == 0) TR(13, ab);
+                const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * 128);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            umma_f16_ts(d_main, a_t + 8 * k, db + 2 * k, IDESC, (s | k) != 0);
-                            if (F::A_PARTS == 2) umma_f16_ts(d_main, a_t + 32 + 8 * k, db + 2 * k, IDESC, true);
+                for (int pr = 0; pr < 2; ++pr, ita += 2) {
+                    const int sb = 2 * (ab & 1) + pr;  // B stage: the same two slabs
+                    if (lane == 0) TR(9, ita);
+                    if (!rdy_a) GT(0, mbar_wait(&full_a[pr], ab & 1, abort_flag));
+                    if (lane == 0) TR(10, ita);
+                    GT(1, mbar_wait(&full_b[sb], (ab >> 1) & 1, abort_flag));
+                    if (lane == 0) TR(11, ita);
+                    tc5_fence_after_sync();
+                    // look at the next pair's barrier now: the answer arrives while the MMAs are issued
+                    rdy_a = mbar_test(&full_a[pr ^ 1], pr == 1 ? ((ab + 1) & 1) : (ab & 1));
+                    if (lane == 0) TR(6, ita);
+                    const uint32_t a_t = a_base + (uint32_t)(2 * pr * F::A_COLS);
+                    const uint64_t db = b_desc0 + (uint64_t)(2 * sb * (G_TILE_BYTES >> 4));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {  // two slabs of four K steps
+                            const uint32_t a_k = a_t + (uint32_t)((k >> 2) * F::A_COLS + 8 * (k & 3));
+                            const uint64_t b_k = db + (uint64_t)((k >> 2) * (G_TILE_BYTES >> 4) + 2 * (k & 3));
+                            umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
+                            if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
+                            if (k == 0) TR(15, ita);
+                            if (k == 3) TR(7, ita);
                         }
-#ifdef CMOE_GEMM_TIMING
-                        gt_[5] += clock64() - tm_;
-#endif
-                        GT(6, umma_commit(&empty_a[sa]); umma_commit(&empty_b[sb]));  // stages refillable once read
+                        TR(8, ita);
+                        umma_commit(&empty_a[pr]);  // the stages may be refilled once these MMAs have read them
+                        umma_commit(&empty_b[sb]);
                     }
-                    if (F::HAS_MIN) {
-                        const int ms = ab & 1;
-                        // the single min accumulator: the drain of block ab - 1 must have read it
-                        if (ab >= 1) GT(3, mbar_wait(&min_free, (ab - 1) & 1, abort_flag));
-                        GT(4, mbar_wait(&full_m[ms], (ab >> 1) & 1, abort_flag));
-                        tc5_fence_after_sync();
-                        const uint64_t da = umma_desc_sw128(smem_u32(smem_min_a + (size_t)ms * G_TILE_BYTES));
-                        const uint64_t db = umma_desc_sw128(smem_u32(smem_min_b + (size_t)ms * G_TILE_BYTES));
-                        umma_f16(tmem_base + (uint32_t)G_TM_MIN, da, db, IDESC, false);
+                    __syncwarp();
+                    if (lane == 0) TR(12, ita);
+                }
+                if (F::HAS_MIN) {
+                    const int ms = ab & 1;
+                    // the min accumulator runs over a group of G_MIN_GROUP blocks; before a new group overwrites
+                    // it, the epilogue must have read the previous group's
+                    if ((blk % G_MIN_GROUP) == 0) {
+                        if (ng_done > 0) GT(3, mbar_wait(&min_free, (ng_done - 1) & 1, abort_flag));
+                        ++ng_done;
+                    }
+                    GT(4, mbar_wait(&full_m[ms], (ab >> 1) & 1, abort_flag));
+                    tc5_fence_after_sync();
+                    const uint64_t da = ma_desc0 + (uint64_t)(ms * (G_TILE_BYTES >> 4)), db = mb_desc0 + (uint64_t)(ms * (G_TILE_BYTES >> 4));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < 3; ++k)
+                            umma_tf32(tmem_base + (uint32_t)G_TM_MIN, da + 2 * k, db + 2 * k, IDESC_TF32, ((blk % G_MIN_GROUP) | k) != 0);
                         umma_commit(&empty_m[ms]);
                     }
-                    umma_commit(&tmem_full[buf]);
+                    __syncwarp();
                 }
+                if (elect_one()) umma_commit(&tmem_full[buf]);
+                __syncwarp();
+                if (lane == 0) TR(14, ab);
             }
-            GT_END(0, true);
         }
+        GT_END(0, lane == 0);
     }
     tc5_fence_before_sync();
     __syncthreads();
@@ -637,24 +726,24 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 matrix [rows, cols] row-major -> boxes of [128 rows x 64 cols], 128-byte swizzle
-bool make_map_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+// row-major matrix [rows, cols] -> boxes of [128 rows x box_cols] (128 bytes wide), 128-byte swizzle
+bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint32_t box_cols) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {G_SLAB_K, G_TILE_N};
+    const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    const cuuint32_t box[2] = {box_cols, G_TILE_N};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int g_gemm_sms = -1;
 
 template <class F, bool GATE_UP>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = (G_B_STAGES + (F::HAS_MIN ? 4 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
+    const int smem_bytes = (2 * G_B_STAGES + (F::HAS_MIN ? 4 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
@@ -689,17 +778,18 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     const int64_t p_pad = P + G_TILE_N;
     uint8_t* base = static_cast<uint8_t*>(scratch);
     __half* bf16 = reinterpret_cast<__half*>(base);
-    __half* bs16 = reinterpret_cast<__half*>(base + align_up((size_t)p_pad * K * 2, 256));
-    float* d8t = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bs16) + align_up((size_t)p_pad * kb * 64 * 2, 256));
+    float* bmin = reinterpret_cast<float*>(base + align_up((size_t)p_pad * K * 2, 256));
+    float* d8t = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bmin) + align_up((size_t)p_pad * kb * 32 * 4, 256));
+    const bool has_min = dtype == CANDLE_GGML_Q4K;
 
     const int64_t units = p_pad * kb;
     cudaError_t e = launch_k(prep_gemm_b_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, absum,
-                             row_of, (int)P, (int)p_pad, K, bf16, bs16, d8t);
+                             row_of, (int)P, (int)p_pad, K, bf16, has_min ? bmin : (float*)nullptr, d8t);
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_b, map_bs;
-    if (!make_map_f16(&map_b, bf16, (uint64_t)p_pad, (uint64_t)K)) return cudaErrorNotSupported;
-    if (!make_map_f16(&map_bs, bs16, (uint64_t)p_pad, (uint64_t)kb * 64)) return cudaErrorNotSupported;
+    if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K, G_SLAB_K)) return cudaErrorNotSupported;
+    if (!make_map_2d(&map_bs, bmin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)p_pad, (uint64_t)kb * 32, 32)) return cudaErrorNotSupported;
 
     GemmParams G{};
     G.wa = wa;
