@@ -60,7 +60,9 @@ constexpr int G_TILE_M = 128, G_TILE_N = 128, G_SLAB_K = 64;
 constexpr int G_B_STAGES = 4;   // in shared memory, two slabs each
 constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
-constexpr int G_WARP_TMA = G_EPI_WARPS + G_DQ_WARPS, G_WARP_MMA = G_WARP_TMA + 1;
+// Warp roles.  The MMA and TMA warps take the highest indices: measured, their short instruction streams
+// are served far better there than at the lowest ones (1.75x on the whole kernel).
+constexpr int G_WARP_EPI0 = 0, G_WARP_DQ0 = G_WARP_EPI0 + G_EPI_WARPS, G_WARP_TMA = 18, G_WARP_MMA = 19;
 constexpr int G_THREADS = 32 * 20;  // five warpgroups: 2 epilogue, 2 unpack, 1 with the TMA and MMA warps (+ 2 idle)
 constexpr int G_REGS_EPI = 128, G_REGS_MISC = 32;  // budgets after the trade: 2 * 128 + 2 * 96 + 32 = 5 * 96, the launch allocation
 constexpr int G_TMEM_COLS = 512;
@@ -356,7 +358,9 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a shuffle: the compiler then knows that it is warp-uniform and keeps role
+    // dispatch, loop counters and MMA / TMA operands in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -386,18 +390,18 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     tc5_fence_before_sync();
     __syncthreads();
     tc5_fence_after_sync();
-    const uint32_t tmem_base = s_tmem_base;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, s_tmem_base, 0);
     volatile int* abort_flag = &s_abort;
     constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, G_TILE_N), IDESC_TF32 = umma_idesc_tf32(G_TILE_M, G_TILE_N);
 
     // Register budget: launched with 96 per thread; the TMA/MMA warpgroup hands 64 per thread back to the CTA's
     // pool and the two epilogue warpgroups take 32 more each, so the total stays what the launch allocated (a
     // request beyond the pool would wait forever).
-    if (warp >= G_WARP_TMA) reg_dealloc<G_REGS_MISC>();  // the whole last warpgroup (TMA, MMA and two idle warps)
-    if (warp < G_EPI_WARPS) {
+    if (warp >= G_WARP_DQ0 + G_DQ_WARPS) reg_dealloc<G_REGS_MISC>();  // the whole last warpgroup (two idle warps, TMA, MMA)
+    if (warp < G_WARP_DQ0) {
         reg_alloc<G_REGS_EPI>();
         // ===================== epilogue =====================
-        const int quarter = warp & 3, colhalf = warp >> 2;
+        const int quarter = warp & 3, colhalf = (warp - G_WARP_EPI0) >> 2, ew = warp - G_WARP_EPI0;
         const int r = 32 * quarter + lane;  // tile row = TMEM lane
         const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(colhalf * 64);
         uint32_t ab = 0;
@@ -412,8 +416,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
             hdr_c = F::load_hdr(rowc, 0);
             const float* dp = P.d8t + tc.p0 + colhalf * 64 + lane;
-            s_d8[warp][0][lane] = dp[0];
-            s_d8[warp][0][lane + 32] = dp[32];
+            s_d8[ew][0][lane] = dp[0];
+            s_d8[ew][0][lane + 32] = dp[32];
             __syncwarp();
         }
         while (have) {
@@ -445,12 +449,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 }
                 const float dw = half_bits_to_float((uint16_t)(hdr_c & 0xffff));
                 const uint64_t dw2 = f32x2_pack(dw, dw);
-                if (threadIdx.x == 0) TR(0, ab);
+                if (threadIdx.x == 32 * G_WARP_EPI0) TR(0, ab);
                 GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
                 tc5_fence_after_sync();
-                if (threadIdx.x == 0) TR(1, ab);
+                if (threadIdx.x == 32 * G_WARP_EPI0) TR(1, ab);
                 const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128);
-                const uint32_t d8_addr = smem_u32(&s_d8[warp][buf][0]);
+                const uint32_t d8_addr = smem_u32(&s_d8[ew][buf][0]);
                 // Four steps of 16 columns; the load of step i+1 is in flight while step i is scaled into
                 // the register accumulators: acc += (d8[col] * dw[row]) * v.
                 uint32_t stg[2][16];
@@ -495,12 +499,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     if (lane == 0) mbar_arrive(&min_free);
                 }
                 if (pre) {
-                    s_d8[warp][buf ^ 1][lane] = d8_n0;
-                    s_d8[warp][buf ^ 1][lane + 32] = d8_n1;
+                    s_d8[ew][buf ^ 1][lane] = d8_n0;
+                    s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
                 }
                 __syncwarp();
                 hdr_c = hdr_n;
-                if (threadIdx.x == 0) TR(2, ab);
+                if (threadIdx.x == 32 * G_WARP_EPI0) TR(2, ab);
             }
             // ---- store the tile ----
 #ifdef CMOE_GEMM_TIMING
@@ -531,10 +535,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             rowc = rown;
             have = have_n;
         }
-        GT_END(16, threadIdx.x == 0);
-    } else if (warp < G_WARP_TMA) {
+        GT_END(16, threadIdx.x == 32 * G_WARP_EPI0);
+    } else if (warp < G_WARP_DQ0 + G_DQ_WARPS) {
         // ===================== weight unpack -> fp16 operand in tensor memory =====================
-        const int quarter = warp & 3, h = (warp - G_EPI_WARPS) >> 2;
+        const int quarter = warp & 3, h = (warp - G_WARP_DQ0) >> 2;
         const int r = 32 * quarter + lane;
         const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)F::A_BASE;
         const uint32_t min_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
@@ -567,17 +571,17 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
                     // four slabs per block in four TMEM stages (stage = slab index), handed over in pairs
-                    if (lane == 0 && warp == 8) TR(3, ita);
+                    if (lane == 0 && warp == G_WARP_DQ0) TR(3, ita);
                     if (ab >= 1) GT(0, mbar_wait(&empty_a[pr], (ab & 1) ^ 1, abort_flag));
                     tc5_fence_after_sync();
-                    if (lane == 0 && warp == 8) TR(4, ita);
+                    if (lane == 0 && warp == G_WARP_DQ0) TR(4, ita);
                     GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * pr * F::A_COLS), h));
                     GT(2, F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * pr + 1) * F::A_COLS), h));
                     GT(3, tmem_st_wait());
                     tc5_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_a[pr]);
-                    if (lane == 0 && warp == 8) TR(5, ita);
+                    if (lane == 0 && warp == G_WARP_DQ0) TR(5, ita);
                 }
                 if (F::HAS_MIN) {
                     const int ms = ab & 1;
@@ -594,7 +598,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             rowc = rown;
             have = have_n;
         }
-        GT_END(8, threadIdx.x == 32 * G_EPI_WARPS);
+        GT_END(8, threadIdx.x == 32 * G_WARP_DQ0);
     } else if (warp == G_WARP_TMA) {
         // ===================== TMA: activation operand =====================
         // the whole warp walks the loop (uniform control flow and addresses), one elected lane issues
