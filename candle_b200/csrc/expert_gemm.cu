@@ -57,7 +57,7 @@ extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timi
 namespace {
 
 constexpr int G_TILE_M = 128, G_TILE_N = 128, G_SLAB_K = 64;
-constexpr int G_B_STAGES = 4;   // in shared memory, two slabs each
+constexpr int G_B_STAGES = 2;   // in shared memory, one 256-wide block each (four slabs + the min-term box for Q4_K)
 constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
 // Warp roles.  The MMA and TMA warps take the highest indices: measured, their short instruction streams
@@ -67,8 +67,7 @@ constexpr int G_THREADS = 32 * 20;  // five warpgroups: 2 epilogue, 2 unpack, 1 
 constexpr int G_REGS_EPI = 128, G_REGS_MISC = 32;  // budgets after the trade: 2 * 128 + 2 * 96 + 32 = 5 * 96, the launch allocation
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_MAIN = 0;    // + 128 * buffer
-constexpr int G_TM_MIN = 256;   // Q4_K only
-constexpr int G_MIN_GROUP = 4;  // blocks whose min terms are summed in tensor memory before they are drained
+constexpr int G_TM_A = 256;     // weight operand ring: columns 256..511
 constexpr int Q6K_HTB_BYTES = 1680;
 
 
@@ -91,14 +90,14 @@ constexpr int Q6K_HTB_BYTES = 1680;
 // free (nibbles of bytes 0,2 and 1,3 convert pairwise), and a dot product does not care.
 // Rows p >= P are zero padding so that a 128-row box never leaves the buffer.
 //
-// Min term of Q4_K (k_quants.rs:1262-1268): - sum_b d8[p,b] dmin[r,b] sum_j m[r,b,j] bsum32[p,b,j].
-// Both factors carry a float scale, so this is a plain GEMM over (b, j) with fp32-valued operands
-// A' = -dmin m (17 significant bits) and B' = d8 bsum32 (24).  It runs as kind::tf32 MMAs that
-// accumulate over the whole tile: each operand is split into tf32 terms (10-bit mantissa, fp32
-// exponent range: no overflow or underflow concerns), A' = a1 + a2 exactly, B' = b1 + b2 to 2^-23, and
-// the products a1 b1 + a1 b2 + a2 b1 are three K=8 steps per block.  Per (position, block) the buffer
-// holds 32 floats: [b1 (8) | b2 (8) | b1 (8) | 0 (8)], matched by [a1 | a1 | a2 | -] on the weight side.
-// The dropped terms are below 2^-22 of the min term: the order of the reference's own f32 rounding.
+// Min term of Q4_K (k_quants.rs:1262-1268): block b contributes d8[p,b] * (d[r,b] * M - dmin[r,b] * sum_j m_j bsum32_j)
+// = d8 * d * (M - sum_j rho_j bsum32_j) with rho_j = dmin * m_j / d, so the min term joins the SAME accumulator
+// as the integer main sum M: three more K=8 steps per block, kind::tf32 (fp32 exponent range, 10-bit
+// mantissa).  rho_j (fp32) is split into tf32 terms r1 + r2 (to 2^-23), the integer bsum32 (at most 32 * 127,
+// 12 bits) exactly into b1 + b2; the steps are r1 b1 + r2 b1 + r1 b2.  Per (position, block) the buffer holds
+// 32 floats [b1 (8) | b1 (8) | b2 (8) | 0 (8)], matched by [r1 | r2 | r1 | -] on the weight side.  The main
+// sum stays an exact integer until these last three steps; what they add in error is of the order of the
+// reference's own f32 rounding (2^-23 of the min term).
 // ---------------------------------------------------------------------------------------------
 // nearest value with a 10-bit mantissa (the 13 low bits of the fp32 container zero)
 __device__ __forceinline__ float tf32_head(float v) { return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xffffe000u); }
@@ -128,11 +127,11 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
         o = *reinterpret_cast<uint4*>(h);
         d8 = ascale[row * kb + blk];
         if (bmin) {
-            const int j = lane & 7, part = lane >> 3;  // word: part 0, 2 = b1_j; part 1 = b2_j; part 3 = 0
+            const int j = lane & 7, part = lane >> 3;  // word: part 0, 1 = b1_j; part 2 = b2_j; part 3 = 0
             const int16_t* bs = absum + row * (K / 16) + blk * 16 + 2 * j;
-            const float bv = __fmul_rn(d8, (float)((int)bs[0] + (int)bs[1]));
-            const float b1 = tf32_head(bv), b2 = tf32_head(__fsub_rn(bv, b1));
-            bm = part == 1 ? b2 : (part == 3 ? 0.f : b1);
+            const float bv = (float)((int)bs[0] + (int)bs[1]);
+            const float b1 = tf32_head(bv), b2 = bv - b1;  // exact: |bv| < 4096, so b2 is -1, 0 or 1
+            bm = part == 2 ? b2 : (part == 3 ? 0.f : b1);
         }
     }
     *reinterpret_cast<uint4*>(bf16 + (int64_t)p * K + blk * 256 + lane * 8) = o;
@@ -168,7 +167,7 @@ __device__ __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? 
 // ------------------------------------------------------------------------------------------------
 struct GemmQ4K {
     static constexpr bool HAS_MIN = true;
-    static constexpr int A_COLS = 32, A_BASE = 384, A_PARTS = 1;
+    static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;  // 8 slabs of 32 columns: two blocks in flight
     struct Row {
         const uint8_t* p;
     };
@@ -195,6 +194,13 @@ struct GemmQ4K {
         c.mn[0] = s1 & 0x3f3f3f3fu;
         c.sc[1] = (s2 & 0x0f0f0f0fu) | (((s0 >> 6) & 0x03030303u) << 4);
         c.mn[1] = ((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4);
+        if ((pr.hdr.x & 0x7fffu) == 0) c.sc[0] = c.sc[1] = 0;  // d = 0: the block is its min term alone (see scale_of)
+    }
+    // The epilogue multiplies the block's accumulator by d; a block with d = 0 (and no main sum, above) is
+    // scaled by dmin instead so that its min term survives, or by 1 if both are zero.
+    __device__ static __forceinline__ float scale_of(uint32_t hdr) {
+        const uint32_t hb = (hdr & 0x7fffu) ? (hdr & 0xffffu) : (((hdr >> 16) & 0x7fffu) ? (hdr >> 16) : 0x3c00u);
+        return half_bits_to_float((uint16_t)hb);
     }
     // slab s = sub-blocks 2s (low nibbles) and 2s+1 (high nibbles).  0x6400 | n is 1024 + n and
     // fma(1024 + n, sc, -1024 sc) rounds the exact n * sc once; 0x6400 | (n << 4) is 1024 + 16 n and
@@ -219,26 +225,26 @@ struct GemmQ4K {
         tmem_st8(ta + 8 * h, lo);
         tmem_st8(ta + 16 + 8 * h, hi);
     }
-    // weight side of the min term (see prep_gemm_b_kernel): a_j = -dmin * m_j split into tf32 terms.  One row is
-    // 32 floats [a1 (8) | a1 (8) | a2 (8) | unused]; thread h = 0 writes the four 16-byte chunks of a1, thread
-    // h = 1 the two of a2.  2^23 + m as float bits is 0x4B000000 | m.
+    // weight side of the min term (see prep_gemm_b_kernel): -rho_j = -dmin m_j / d split into tf32 terms.  One
+    // row is 32 floats [r1 (8) | r2 (8) | r1 (8) | unused]; thread h = 0 writes the four 16-byte chunks of r1,
+    // thread h = 1 the two of r2.  2^23 + m as float bits is 0x4B000000 | m.
     __device__ static __forceinline__ void emit_min(const Pre& pr, const Ctx& c, uint8_t* arow, int h, int sw) {
-        const float ndm = -half_bits_to_float((uint16_t)(pr.hdr.x >> 16));
+        const float ratio = -__fdividef(half_bits_to_float((uint16_t)(pr.hdr.x >> 16)), scale_of(pr.hdr.x));
         uint32_t o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float mf = __uint_as_float(0x4B000000u | byte_u(c.mn[j >> 2], j & 3)) - 8388608.f;
-            const float a = __fmul_rn(ndm, mf), a1 = tf32_head(a);
-            o[j] = __float_as_uint(h == 0 ? a1 : __fsub_rn(a, a1));
+            const float a = __fmul_rn(ratio, mf), a1 = tf32_head(a);
+            o[j] = __float_as_uint(h == 0 ? a1 : tf32_head(__fsub_rn(a, a1)));
         }
         if (h == 0) {
             *reinterpret_cast<uint4*>(arow + ((0 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             *reinterpret_cast<uint4*>(arow + ((1 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-            *reinterpret_cast<uint4*>(arow + ((2 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-            *reinterpret_cast<uint4*>(arow + ((3 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-        } else {
             *reinterpret_cast<uint4*>(arow + ((4 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
             *reinterpret_cast<uint4*>(arow + ((5 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+            *reinterpret_cast<uint4*>(arow + ((2 ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4*>(arow + ((3 ^ sw) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
         }
     }
 };
@@ -253,7 +259,7 @@ struct GemmQ4K {
 // ------------------------------------------------------------------------------------------------
 struct GemmQ6K {
     static constexpr bool HAS_MIN = false;
-    static constexpr int A_COLS = 64, A_BASE = 256, A_PARTS = 2;
+    static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;  // 4 slabs of 64 columns (two operand parts each)
     struct Row {
         const uint8_t* p;  // half-tile block 0 of the row's group of 8
         int g;
@@ -318,6 +324,7 @@ struct GemmQ6K {
         }
     }
     __device__ static __forceinline__ void emit_min(const Pre&, const Ctx&, uint8_t*, int, int) {}
+    __device__ static __forceinline__ float scale_of(uint32_t hdr) { return half_bits_to_float((uint16_t)hdr); }
 };
 
 struct TileCoord {
@@ -352,8 +359,8 @@ __global__ void __launch_bounds__(G_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_bs) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_a[2], empty_a[2], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
-    __shared__ uint64_t full_m[2], empty_m[2], tmem_full[2], epi_done[2], min_free;
+    __shared__ uint64_t full_a[4], empty_a[4], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
+    __shared__ uint64_t tmem_full[2], epi_done[2];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
     __shared__ uint32_t s_tmem_base;
@@ -364,12 +371,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* smem_min_a = smem + G_B_STAGES * 2 * G_TILE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
-    uint8_t* smem_min_b = smem_min_a + 2 * G_TILE_BYTES;     //       2 slots of the block sums (activation side)
+    constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * G_TILE_BYTES;
+    uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < 4; ++s) {
             mbar_init(&full_a[s], G_DQ_WARPS);
             mbar_init(&empty_a[s], 1);
         }
@@ -378,12 +385,9 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             mbar_init(&empty_b[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&full_m[b], G_DQ_WARPS + 1);  // 8 unpack warps + the TMA thread's expect_tx arrival
-            mbar_init(&empty_m[b], 1);
             mbar_init(&tmem_full[b], 1);
             mbar_init(&epi_done[b], G_EPI_WARPS);
         }
-        mbar_init(&min_free, G_EPI_WARPS);
         fence_barrier_init();
     }
     if (warp == G_WARP_TMA) tmem_alloc(&s_tmem_base, G_TMEM_COLS);
@@ -447,7 +451,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     d8_n1 = dp[32];
                     pre = true;
                 }
-                const float dw = half_bits_to_float((uint16_t)(hdr_c & 0xffff));
+                const float dw = F::scale_of(hdr_c);
                 const uint64_t dw2 = f32x2_pack(dw, dw);
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(0, ab);
                 GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
@@ -481,22 +485,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&epi_done[buf]);
                     }
-                }
-                if (F::HAS_MIN && ((blk % G_MIN_GROUP) == G_MIN_GROUP - 1 || blk == P.kb - 1)) {
-                    // the min terms of this group of blocks (their MMAs were committed with this block's): a
-                    // short chain in the tensor core's truncating adder, then round-to-nearest adds here
-                    const uint32_t t_min = ta_lane + (uint32_t)G_TM_MIN;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t mv[16];
-                        tmem_ld16(t_min + 16 * c, mv);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) acc[16 * c + i] += __uint_as_float(mv[i]);
-                    }
-                    tc5_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&min_free);
                 }
                 if (pre) {
                     s_d8[ew][buf ^ 1][lane] = d8_n0;
@@ -540,7 +528,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         // ===================== weight unpack -> fp16 operand in tensor memory =====================
         const int quarter = warp & 3, h = (warp - G_WARP_DQ0) >> 2;
         const int r = 32 * quarter + lane;
-        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)F::A_BASE;
+        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)G_TM_A;
         const uint32_t min_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
         uint32_t ita = 0, ab = 0;
         long long tile = blockIdx.x;
@@ -570,26 +558,25 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 F::begin(cur, ctx);
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
-                    // four slabs per block in four TMEM stages (stage = slab index), handed over in pairs
+                    // slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks)
+                    const uint32_t np = 2 * ab + pr, slot = np % F::A_PAIRS, use = np / F::A_PAIRS;
                     if (lane == 0 && warp == G_WARP_DQ0) TR(3, ita);
-                    if (ab >= 1) GT(0, mbar_wait(&empty_a[pr], (ab & 1) ^ 1, abort_flag));
+                    if (use >= 1) GT(0, mbar_wait(&empty_a[slot], (use & 1) ^ 1, abort_flag));
                     tc5_fence_after_sync();
                     if (lane == 0 && warp == G_WARP_DQ0) TR(4, ita);
-                    GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * pr * F::A_COLS), h));
-                    GT(2, F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * pr + 1) * F::A_COLS), h));
+                    GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * slot * F::A_COLS), h));
+                    GT(2, F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * slot + 1) * F::A_COLS), h));
+                    if (F::HAS_MIN && pr == 1) {
+                        // weight side of the min term, handed over with the second pair.  Its slot was last read by
+                        // the min MMAs of block ab - 2, issued before the commit whose completion the wait above saw.
+                        F::emit_min(cur, ctx, smem_min_a + (size_t)(ab & 1) * G_TILE_BYTES + min_row_off, h, r & 7);
+                        fence_proxy_async_smem();
+                    }
                     GT(3, tmem_st_wait());
                     tc5_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_a[pr]);
+                    if (lane == 0) mbar_arrive(&full_a[slot]);
                     if (lane == 0 && warp == G_WARP_DQ0) TR(5, ita);
-                }
-                if (F::HAS_MIN) {
-                    const int ms = ab & 1;
-                    if (ab >= 2) GT(1, mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag));
-                    F::emit_min(cur, ctx, smem_min_a + (size_t)ms * G_TILE_BYTES + min_row_off, h, r & 7);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_m[ms]);
                 }
                 cur = nxt;
             }
@@ -607,98 +594,78 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         GT_BEGIN();
         for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
-                for (int s2 = 0; s2 < 2; ++s2) {  // one stage = two 64-wide slabs, one barrier
-                    const int st = 2 * (ab & 1) + s2;
-                    if (ab >= 2) GT(0, mbar_wait(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
-                    uint8_t* dst = smem + (size_t)st * 2 * G_TILE_BYTES;
-                    if (elect_one()) {
-                        mbar_expect_tx(&full_b[st], 2 * G_TILE_BYTES);
-                        tma_load_2d(dst, &map_b, blk * 256 + s2 * 128, (int)tc.p0, &full_b[st]);
-                        tma_load_2d(dst + G_TILE_BYTES, &map_b, blk * 256 + s2 * 128 + 64, (int)tc.p0, &full_b[st]);
-                    }
-                    __syncwarp();
+                // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
+                const int st = ab & 1;
+                if (ab >= 2) GT(0, mbar_wait(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
+                uint8_t* dst = smem + (size_t)st * G_STAGE_BYTES;
+                if (elect_one()) {
+                    mbar_expect_tx(&full_b[st], G_STAGE_BYTES);
+#pragma unroll
+                    for (int s4 = 0; s4 < 4; ++s4)
+                        tma_load_2d(dst + s4 * G_TILE_BYTES, &map_b, blk * 256 + s4 * 64, (int)tc.p0, &full_b[st]);
+                    if (F::HAS_MIN) tma_load_2d(dst + 4 * G_TILE_BYTES, &map_bs, blk * 32, (int)tc.p0, &full_b[st]);
                 }
-                if (F::HAS_MIN) {
-                    const int ms = ab & 1;
-                    if (ab >= 2) mbar_wait(&empty_m[ms], ((ab >> 1) & 1) ^ 1, abort_flag);
-                    if (elect_one()) {
-                        mbar_expect_tx(&full_m[ms], G_TILE_BYTES);
-                        tma_load_2d(smem_min_b + (size_t)ms * G_TILE_BYTES, &map_bs, blk * 32, (int)tc.p0, &full_m[ms]);
-                    }
-                    __syncwarp();
-                }
+                __syncwarp();
             }
         }
         GT_END(24, lane == 0);
     } else if (warp == G_WARP_MMA) {
         // ===================== MMA issue =====================
-        uint32_t ita = 0, ab = 0, ng_done = 0;
+        uint32_t ita = 0, ab = 0;
         TileCoord tc;
         GT_BEGIN();
-        const uint32_t a_base = tmem_base + (uint32_t)F::A_BASE;
+        const uint32_t a_base = tmem_base + (uint32_t)G_TM_A;
         const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem));
-        const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a)), mb_desc0 = umma_desc_sw128(smem_u32(smem_min_b));
-        bool rdy_a = false;
+        const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a));
+        bool rdy_a = false, rdy_b = false;
         for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
-                const int buf = ab & 1;
+                const int buf = ab & 1;  // main accumulator and B stage of this block
                 // the drain of block ab - 2 has released this main accumulator
                 if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
-                tc5_fence_after_sync();
                 if (lane == 0) TR(13, ab);
                 const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * 128);
+                const uint64_t db = b_desc0 + (uint64_t)(buf * (G_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
-                    const int sb = 2 * (ab & 1) + pr;  // B stage: the same two slabs
+                    const uint32_t np = 2 * ab + pr, slot = np % F::A_PAIRS, use = np / F::A_PAIRS;
                     if (lane == 0) TR(9, ita);
-                    if (!rdy_a) GT(0, mbar_wait(&full_a[pr], ab & 1, abort_flag));
+                    if (!rdy_a) GT(0, mbar_wait(&full_a[slot], use & 1, abort_flag));
                     if (lane == 0) TR(10, ita);
-                    GT(1, mbar_wait(&full_b[sb], (ab >> 1) & 1, abort_flag));
+                    if (pr == 0 && !rdy_b) GT(1, mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag));
                     if (lane == 0) TR(11, ita);
                     tc5_fence_after_sync();
-                    // look at the next pair's barrier now: the answer arrives while the MMAs are issued
-                    rdy_a = mbar_test(&full_a[pr ^ 1], pr == 1 ? ((ab + 1) & 1) : (ab & 1));
+                    // look at the next barriers now: the answers arrive while the MMAs are issued
+                    rdy_a = mbar_test(&full_a[(np + 1) % F::A_PAIRS], ((np + 1) / F::A_PAIRS) & 1);
+                    if (pr == 1) rdy_b = mbar_test(&full_b[buf ^ 1], ((ab + 1) >> 1) & 1);
                     if (lane == 0) TR(6, ita);
-                    const uint32_t a_t = a_base + (uint32_t)(2 * pr * F::A_COLS);
-                    const uint64_t db = b_desc0 + (uint64_t)(2 * sb * (G_TILE_BYTES >> 4));
+                    const uint32_t a_t = a_base + (uint32_t)(2 * slot * F::A_COLS);
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {  // two slabs of four K steps
                             const uint32_t a_k = a_t + (uint32_t)((k >> 2) * F::A_COLS + 8 * (k & 3));
-                            const uint64_t b_k = db + (uint64_t)((k >> 2) * (G_TILE_BYTES >> 4) + 2 * (k & 3));
+                            const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (G_TILE_BYTES >> 4) + 2 * (k & 3));
                             umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
                             if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
                             if (k == 0) TR(15, ita);
                             if (k == 3) TR(7, ita);
                         }
                         TR(8, ita);
-                        umma_commit(&empty_a[pr]);  // the stages may be refilled once these MMAs have read them
-                        umma_commit(&empty_b[sb]);
+                        if (pr == 1 && F::HAS_MIN) {
+                            // the min term joins the same accumulator: three tf32 steps, last in the block
+                            const uint64_t da = ma_desc0 + (uint64_t)(buf * (G_TILE_BYTES >> 4)), dm = db + (uint64_t)(4 * (G_TILE_BYTES >> 4));
+#pragma unroll
+                            for (int k = 0; k < 3; ++k) umma_tf32(d_main, da + 2 * k, dm + 2 * k, IDESC_TF32, true);
+                        }
+                        umma_commit(&empty_a[slot]);  // the stages may be refilled once these MMAs have read them
+                        if (pr == 1) {
+                            umma_commit(&empty_b[buf]);
+                            umma_commit(&tmem_full[buf]);
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) TR(12, ita);
                 }
-                if (F::HAS_MIN) {
-                    const int ms = ab & 1;
-                    // the min accumulator runs over a group of G_MIN_GROUP blocks; before a new group overwrites
-                    // it, the epilogue must have read the previous group's
-                    if ((blk % G_MIN_GROUP) == 0) {
-                        if (ng_done > 0) GT(3, mbar_wait(&min_free, (ng_done - 1) & 1, abort_flag));
-                        ++ng_done;
-                    }
-                    GT(4, mbar_wait(&full_m[ms], (ab >> 1) & 1, abort_flag));
-                    tc5_fence_after_sync();
-                    const uint64_t da = ma_desc0 + (uint64_t)(ms * (G_TILE_BYTES >> 4)), db = mb_desc0 + (uint64_t)(ms * (G_TILE_BYTES >> 4));
-                    if (elect_one()) {
-#pragma unroll
-                        for (int k = 0; k < 3; ++k)
-                            umma_tf32(tmem_base + (uint32_t)G_TM_MIN, da + 2 * k, db + 2 * k, IDESC_TF32, ((blk % G_MIN_GROUP) | k) != 0);
-                        umma_commit(&empty_m[ms]);
-                    }
-                    __syncwarp();
-                }
-                if (elect_one()) umma_commit(&tmem_full[buf]);
-                __syncwarp();
                 if (lane == 0) TR(14, ab);
             }
         }
@@ -747,7 +714,7 @@ int g_gemm_sms = -1;
 
 template <class F, bool GATE_UP>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = (2 * G_B_STAGES + (F::HAS_MIN ? 4 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
+    const int smem_bytes = (G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) + (F::HAS_MIN ? 2 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
