@@ -8,24 +8,26 @@
 // `tcgen05.mma kind::f16` with fp32 accumulation in tensor memory -- exact while a 256-element block's
 // sum stays below 2^24, which it does by a wide margin for real data.  After every 256-element block
 // the accumulator is drained and scaled by d_w(row, block) * d8(position, block) on the CUDA cores.
-//   Q4_K: operand sc_j * q (at most 63 * 15); the min term sum_j m_j * bsum_j is one more K=16 MMA per
-//         block (mins against the int16 block sums) into a second accumulator scaled by dmin_w * d8.
+//   Q4_K: operand sc_j * q (at most 63 * 15); the min term joins the same accumulator as three tf32
+//         steps per block against dmin / d (see prep_gemm_b_kernel).
 //   Q6_K: sc_j * (q - 32) reaches 4096 and is not always an fp16 integer, so the int8 scale is split
 //         into ceil(sc/2) + floor(sc/2) and the slab is multiplied twice (each half at most 32 * 64 =
 //         2048: exact).  Reads the repacked layout of the decode kernels (16-byte aligned pieces; the
 //         210-byte GGUF blocks are only 2-byte aligned).
 //
-// One CTA per SM, persistent over tiles, warp-specialised:
-//   warps 0-7   epilogue: drain TMEM (tcgen05.ld) once per block, scale (packed fp32 pairs), keep 64
-//               columns per thread in registers; at the end of a tile apply the SiLU gate and store
+// One CTA per SM, persistent over tiles, warp-specialised (20 warps, five warpgroups):
+//   warps 0-7   epilogue: drain TMEM (tcgen05.ld, next load in flight) once per block, scale, keep 64
+//               columns per thread in registers (128 registers per thread, taken from the last
+//               warpgroup with setmaxnreg); at the end of a tile apply the SiLU gate and store
 //   warps 8-15  unpack the weight nibbles of [128 rows x 64 k] to fp16 x scale with one HFMA2 per two
 //               elements and store them straight into TENSOR MEMORY (tcgen05.st): the A operand never
 //               touches shared memory, whose bandwidth the B operand needs
-//   warp  16    TMA: the activation operand, [128 positions x 64 k] fp16 boxes, 128-byte swizzle
-//   warp  17    one thread issues the MMAs (A from TMEM, B from shared memory) and commits to mbarriers
-// Rings: 4 A stages in TMEM, 8 B stages in shared memory; two main accumulators (2 x 128 columns) let
-// the MMAs of block b+1 overlap the drain of block b; the Q4_K min accumulator is single (its MMA is
-// issued last in a block, when the drain of the block before has long finished).  gate_up interleaves
+//   warp  18    TMA: the activation operand, [128 positions x 64 k] fp16 boxes, 128-byte swizzle; one
+//               stage is a whole 256-wide block (four boxes + the min-term box), two stages
+//   warp  19    issues the MMAs (A from TMEM, B from shared memory) and commits to mbarriers; the whole
+//               warp walks the loop with warp-uniform operands, one elected lane issues
+// Tensor memory: two main accumulators (2 x 128 columns: the MMAs of block b+1 overlap the drain of
+// block b) and a 256-column ring of weight-operand slabs, handed over in pairs.  gate_up interleaves
 // rows of W1 and W3 (tile row 2i = W1 row, 2i+1 = W3 row) so the two factors of silu(w1 x) * (w3 x)
 // sit in neighbouring lanes and meet with one shuffle.
 // Every mbarrier wait is bounded (see stream_common.cuh); nothing here uses cluster multicast.
@@ -561,7 +563,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     // slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks)
                     const uint32_t np = 2 * ab + pr, slot = np % F::A_PAIRS, use = np / F::A_PAIRS;
                     if (lane == 0 && warp == G_WARP_DQ0) TR(3, ita);
-                    if (use >= 1) GT(0, mbar_wait(&empty_a[slot], (use & 1) ^ 1, abort_flag));
+                    if (use >= 1) GT(0, mbar_wait_relaxed(&empty_a[slot], (use & 1) ^ 1, abort_flag));
                     tc5_fence_after_sync();
                     if (lane == 0 && warp == G_WARP_DQ0) TR(4, ita);
                     GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * slot * F::A_COLS), h));
@@ -596,7 +598,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
                 const int st = ab & 1;
-                if (ab >= 2) GT(0, mbar_wait(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
+                if (ab >= 2) GT(0, mbar_wait_relaxed(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
                 uint8_t* dst = smem + (size_t)st * G_STAGE_BYTES;
                 if (elect_one()) {
                     mbar_expect_tx(&full_b[st], G_STAGE_BYTES);

@@ -58,6 +58,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     return false;
 }
+// The same wait for warps that run ahead of their consumer (producers waiting for a free stage): they sleep
+// between polls so that their polling does not take issue slots from the warps that work.  (try_wait with a
+// suspend-time hint is no alternative: it is expanded into exactly such a loop.)
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < SPIN_LIMIT; ++i) {
+        __nanosleep(100);
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
 // global -> shared bulk copy (16-byte aligned addresses, size a multiple of 16), completion counted
 // in bytes on `bar`.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
