@@ -11,5 +11,6 @@ _lib.load()  # fail loudly: there is no fallback implementation
 from ._lib import CandleMoeError  # noqa: E402
 from .quantized import GgmlDType, QMatMul, QTensor  # noqa: E402
 from .moe import Mlp, MlpOrMoe  # noqa: E402
+from .expert_parallel import ExpertParallelMoe  # noqa: E402
 
-__all__ = ["CandleMoeError", "GgmlDType", "QMatMul", "QTensor", "Mlp", "MlpOrMoe"]
+__all__ = ["CandleMoeError", "GgmlDType", "QMatMul", "QTensor", "Mlp", "MlpOrMoe", "ExpertParallelMoe"]

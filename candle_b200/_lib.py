@@ -70,6 +70,10 @@ SYMBOLS = {
     "candle_moe_grouped_gate_up_prepacked": (C.c_int, [_P, _PP, _PP, _I32, _I32, _I32, _I32, _P, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_grouped_down_prepacked": (C.c_int, [_P, _PP, _I32, _I32, _I32, _I32, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_device_status": (C.c_int, [C.POINTER(C.c_int32)]),
+    "candle_moe_ep_row_bytes": (C.c_int, [_I32, C.POINTER(C.c_size_t)]),
+    "candle_moe_ep_pack": (C.c_int, [_P, _P, _I64, _I32, _P, _P, _P, _P]),
+    "candle_moe_ep_workspace_bytes": (C.c_int, [C.POINTER(MoeWeightsC), _I64, C.POINTER(C.c_size_t)]),
+    "candle_moe_ep_experts": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _P, _I32, _I64, _I64, _P, _P, C.c_size_t]),
     "candle_moe_quantize_weights": (C.c_int, [_P, _I32, _P, _I64, _P]),
     "candle_moe_dequantize": (C.c_int, [_P, _I32, _P, _I64, _P]),
 }

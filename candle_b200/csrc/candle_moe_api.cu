@@ -251,6 +251,132 @@ int candle_moe_grouped_down(void* stream, const void* const* w2, int32_t dtype, 
                                   hbsums, out, 0, 1, nullptr));
 }
 
+namespace {
+struct ExpertBufs {
+    float* hidden;  // [P, ff]
+    int8_t* hq;
+    float* hs;
+    int16_t* hb;
+    float* eo;      // [slots][P, d]
+    void* gemm;     // scratch of the large-batch GEMM (may be null)
+};
+
+// The routed experts over P rows grouped by expert (device offsets [E + 1]); no expert has more than max_rows
+// rows.  Picks, per product, the decode kernels over the repacked copies (max_rows <= 64), the tensor-core GEMM
+// (more than that, scratch present), or the streaming / row forms.  Leaves *eo_splits partial outputs in b.eo.
+int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs& p1, const ExpertPtrs& p3,
+                const ExpertPtrs& p2, int64_t max_rows, int64_t P, const uint32_t* offsets, const uint32_t* row_of,
+                const int8_t* xq, const float* xs, const int16_t* xb, const ExpertBufs& b, int slots, int* eo_splits,
+                bool marks) {
+    const int E = w->n_experts, d = w->d_model, ff = w->d_ff;
+    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= 64;
+    const bool large = b.gemm && max_rows > GEMM_MIN_TOKENS && gemm_enabled();
+    bool gate_done = false, down_done = false;
+    *eo_splits = 1;
+    ExpertPtrs q1, q3, q2;
+    if (use_prepacked) {
+        CM_TRY(fill_ptrs(w->w1_prepacked, E, q1));
+        CM_TRY(fill_ptrs(w->w3_prepacked, E, q3));
+        CM_TRY(fill_ptrs(w->w2_prepacked, E, q2));
+        const cudaError_t ce = launch_expert_direct(st, true, q1, q3, w->dtype_w13, E, d, ff, offsets, row_of, max_rows, xq,
+                                                    xs, xb, b.hidden, nullptr, 0, 1);
+        if (ce == cudaSuccess)
+            gate_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+    }
+    if (!gate_done && large) {
+        // Q6_K is read from the repacked copies (its GGUF blocks are only 2-byte aligned)
+        const bool rp = w->dtype_w13 == CANDLE_GGML_Q6K && w->w1_prepacked && w->w3_prepacked;
+        ExpertPtrs g1 = p1, g3 = p3;
+        if (rp) {
+            CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
+            CM_TRY(fill_ptrs(w->w3_prepacked, E, g3));
+        }
+        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, offsets, row_of, P, xq, xs,
+                                                  xb, b.hidden, b.gemm);
+        if (ce == cudaSuccess)
+            gate_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+    }
+    if (!gate_done)
+        CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, offsets, row_of, max_rows, xq, xs, xb,
+                                         b.hidden)));
+    if (marks) mark(st, 3);
+    CM_TRY(rc(launch_quantize_act(st, b.hidden, P, ff, w->dtype_w2, b.hq, b.hs, b.hb)));
+    if (marks) mark(st, 4);
+    if (use_prepacked) {
+        const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, offsets, nullptr, max_rows, b.hq,
+                                                    b.hs, b.hb, b.eo, eo_splits, P * d, slots, (int)(P < E ? P : E));
+        if (ce == cudaSuccess)
+            down_done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+        else
+            *eo_splits = 1;
+    }
+    if (!down_done && large) {
+        const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
+        ExpertPtrs g2 = p2;
+        if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
+        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, b.hq, b.hs,
+                                                  b.hb, b.eo, b.gemm);
+        if (ce == cudaSuccess) {
+            down_done = true;
+            *eo_splits = 1;
+        } else if (ce != cudaErrorNotSupported) {
+            return (int)ce;
+        }
+    }
+    if (!down_done)
+        CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, offsets, max_rows, b.hq, b.hs, b.hb, b.eo, P * d, slots,
+                                      eo_splits)));
+    return CANDLE_MOE_OK;
+}
+
+// Scratch of the expert-parallel local phase for up to P rows
+struct EpWorkspace {
+    uint32_t* plan;     // [2 * 1024]
+    uint32_t* offsets;  // [E + 1]
+    uint32_t* back;     // [P]
+    int8_t* xq;
+    float* xs;
+    int16_t* xb;
+    ExpertBufs eb;
+    int64_t eo_rows;    // rows x slots the eo region holds
+    size_t total;
+};
+EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
+    uint8_t* base = static_cast<uint8_t*>(base_);
+    EpWorkspace ws{};
+    size_t off = 0;
+    const size_t d = w->d_model, ff = w->d_ff, E = w->n_experts;
+    ws.plan = carve<uint32_t>(base, off, 2048);
+    ws.offsets = carve<uint32_t>(base, off, E + 1);
+    ws.back = carve<uint32_t>(base, off, (size_t)P);
+    ws.xq = carve<int8_t>(base, off, (size_t)P * d);
+    ws.xs = carve<float>(base, off, (size_t)P * d / 256);
+    ws.xb = carve<int16_t>(base, off, (size_t)P * d / 16);
+    ws.eb.hidden = carve<float>(base, off, (size_t)P * ff);
+    ws.eb.hq = carve<int8_t>(base, off, (size_t)P * ff);
+    ws.eb.hs = carve<float>(base, off, (size_t)P * ff / 256);
+    ws.eb.hb = carve<int16_t>(base, off, (size_t)P * ff / 16);
+    // K-split slots: 8 while no expert has more than 64 rows (then P <= 64 E), 4 beyond
+    const size_t small_rows = std::min<size_t>((size_t)P, 64 * E);
+    ws.eo_rows = (int64_t)std::max<size_t>((size_t)P * 4, small_rows * MAX_K_SPLITS);
+    ws.eb.eo = carve<float>(base, off, (size_t)ws.eo_rows * d);
+    if (P > GEMM_MIN_TOKENS) {
+        const size_t g = std::max(expert_gemm_scratch_bytes(P, (int)d), expert_gemm_scratch_bytes(P, (int)ff));
+        off = align_up(off, 1024);
+        ws.eb.gemm = base ? base + off : reinterpret_cast<void*>(1);
+        off += g;
+    }
+    ws.total = align_up(off, 256);
+    return ws;
+}
+}  // namespace
+
 int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
                        void* workspace, size_t workspace_bytes) {
     CM_TRY(check_weights(w));
@@ -289,69 +415,10 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     if (!fuse_q) CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
     mark(st, 2);
     // a token selects an expert at most once: no expert sees more than T rows
-    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && T <= 64;
     int eo_splits = 1, so_splits = 1;
-    bool gate_done = false, down_done = false;
-    ExpertPtrs q1, q3, q2;
-    if (use_prepacked) {
-        CM_TRY(fill_ptrs(w->w1_prepacked, E, q1));
-        CM_TRY(fill_ptrs(w->w3_prepacked, E, q3));
-        CM_TRY(fill_ptrs(w->w2_prepacked, E, q2));
-        const cudaError_t ce = launch_expert_direct(st, true, q1, q3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T,
-                                                    ws.xq, ws.xs, ws.xb, ws.hidden, nullptr, 0, 1);
-        if (ce == cudaSuccess)
-            gate_done = true;
-        else if (ce != cudaErrorNotSupported)
-            return (int)ce;
-    }
-    if (!gate_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
-        // Q6_K is read from the repacked copies (its GGUF blocks are only 2-byte aligned)
-        const bool rp = w->dtype_w13 == CANDLE_GGML_Q6K && w->w1_prepacked && w->w3_prepacked;
-        ExpertPtrs g1 = p1, g3 = p3;
-        if (rp) {
-            CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
-            CM_TRY(fill_ptrs(w->w3_prepacked, E, g3));
-        }
-        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, ws.offsets, ws.perm_token,
-                                                  Tk, ws.xq, ws.xs, ws.xb, ws.hidden, ws.gemm);
-        if (ce == cudaSuccess)
-            gate_done = true;
-        else if (ce != cudaErrorNotSupported)
-            return (int)ce;
-    }
-    if (!gate_done)
-        CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, ws.offsets, ws.perm_token, T, ws.xq, ws.xs,
-                                         ws.xb, ws.hidden)));
-    mark(st, 3);
-    CM_TRY(rc(launch_quantize_act(st, ws.hidden, Tk, ff, w->dtype_w2, ws.hq, ws.hs, ws.hb)));
-    mark(st, 4);
-    if (use_prepacked) {
-        const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, ws.offsets, nullptr, T, ws.hq,
-                                                    ws.hs, ws.hb, ws.eo, &eo_splits, Tk * d, k_split_slots(T),
-                                                    (int)(Tk < E ? Tk : E));
-        if (ce == cudaSuccess)
-            down_done = true;
-        else if (ce != cudaErrorNotSupported)
-            return (int)ce;
-        else
-            eo_splits = 1;
-    }
-    if (!down_done && ws.gemm && T > GEMM_MIN_TOKENS && gemm_enabled()) {
-        const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
-        ExpertPtrs g2 = p2;
-        if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
-        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, ws.offsets, nullptr, Tk,
-                                                  ws.hq, ws.hs, ws.hb, ws.eo, ws.gemm);
-        if (ce == cudaSuccess) {
-            down_done = true;
-            eo_splits = 1;
-        } else if (ce != cudaErrorNotSupported) {
-            return (int)ce;
-        }
-    }
-    if (!down_done)
-        CM_TRY(rc(launch_grouped_down(st, p2, w->dtype_w2, E, d, ff, ws.offsets, T, ws.hq, ws.hs, ws.hb, ws.eo, Tk * d,
-                                      k_split_slots(T), &eo_splits)));
+    const ExpertBufs eb{ws.hidden, ws.hq, ws.hs, ws.hb, ws.eo, ws.gemm};
+    CM_TRY(run_experts(st, w, p1, p3, p2, T, Tk, ws.offsets, ws.perm_token, ws.xq, ws.xs, ws.xb, eb, k_split_slots(T),
+                       &eo_splits, true));
     mark(st, 5);
 
     const float* shared_out = nullptr;
@@ -518,6 +585,64 @@ int candle_moe_dequantize(void* stream, int32_t dtype, const void* blocks, int64
     if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
     if (n_elems < 0 || n_elems % block_elems(dtype)) return CANDLE_MOE_E_SHAPE;
     return rc(launch_dequantize((cudaStream_t)stream, dtype, blocks, n_elems, dst));
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Expert parallelism (experts sharded over ranks; the host issues the all-to-alls between these calls)
+// ---------------------------------------------------------------------------------------------------------
+int candle_moe_ep_row_bytes(int32_t d_model, size_t* out_bytes) {
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (d_model <= 0 || d_model % 256) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = ep_row_bytes(d_model);
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_ep_pack(void* stream, const uint32_t* perm_token, int64_t n_rows, int32_t d_model, const int8_t* xq,
+                       const float* xscales, const int16_t* xbsums, void* send_rows) {
+    if (n_rows < 0 || d_model <= 0 || d_model % 256) return CANDLE_MOE_E_SHAPE;
+    if (n_rows == 0) return CANDLE_MOE_OK;
+    if (!xq || !xscales || !xbsums || !send_rows) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(send_rows) & 15)) return CANDLE_MOE_E_ALIGN;
+    return rc(launch_ep_pack((cudaStream_t)stream, perm_token, n_rows, d_model, xq, xscales, xbsums, send_rows));
+}
+
+int candle_moe_ep_workspace_bytes(const candle_moe_weights_t* w, int64_t max_rows_total, size_t* out_bytes) {
+    CM_TRY(check_weights(w));
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (max_rows_total < 0 || max_rows_total > (int64_t)1 << 26) return CANDLE_MOE_E_SHAPE;
+    if (w->dtype_w13 == CANDLE_GGML_Q8_0 || w->dtype_w2 == CANDLE_GGML_Q8_0) return CANDLE_MOE_E_DTYPE;
+    *out_bytes = ep_layout(w, max_rows_total, nullptr).total;
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_ep_experts(void* stream, const candle_moe_weights_t* w, const void* recv_rows, const uint32_t* recv_counts,
+                          int32_t n_src, int64_t n_rows, int64_t max_rows_per_expert, float* out_rows, void* workspace,
+                          size_t workspace_bytes) {
+    CM_TRY(check_weights(w));
+    if (w->dtype_w13 == CANDLE_GGML_Q8_0 || w->dtype_w2 == CANDLE_GGML_Q8_0) return CANDLE_MOE_E_DTYPE;
+    if (n_rows < 0 || n_src <= 0 || (int64_t)n_src * w->n_experts > 1024 || max_rows_per_expert < 0 ||
+        max_rows_per_expert > n_rows)
+        return CANDLE_MOE_E_SHAPE;
+    if (n_rows == 0) return CANDLE_MOE_OK;
+    if (!recv_rows || !recv_counts || !out_rows || !workspace) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(recv_rows) & 15) ||
+        (reinterpret_cast<uintptr_t>(out_rows) & 15))
+        return CANDLE_MOE_E_ALIGN;
+    const EpWorkspace ws = ep_layout(w, n_rows, workspace);
+    if (workspace_bytes < ws.total) return CANDLE_MOE_E_WORKSPACE;
+    const int E = w->n_experts, d = w->d_model;
+    ExpertPtrs p1, p3, p2;
+    CM_TRY(fill_ptrs(w->w1, E, p1));
+    CM_TRY(fill_ptrs(w->w3, E, p3));
+    CM_TRY(fill_ptrs(w->w2, E, p2));
+    cudaStream_t st = (cudaStream_t)stream;
+    CM_TRY(rc(launch_ep_regroup(st, recv_rows, recv_counts, n_src, E, n_rows, d, ws.plan, ws.xq, ws.xs, ws.xb, ws.offsets,
+                                ws.back)));
+    int eo_splits = 1;
+    const int slots = max_rows_per_expert <= 64 ? MAX_K_SPLITS : 4;
+    CM_TRY(run_experts(st, w, p1, p3, p2, max_rows_per_expert, n_rows, ws.offsets, nullptr, ws.xq, ws.xs, ws.xb, ws.eb, slots,
+                       &eo_splits, false));
+    return rc(launch_ep_scatter(st, ws.eb.eo, eo_splits, n_rows * d, ws.back, n_rows, d, out_rows));
 }
 
 }  // extern "C"

@@ -188,6 +188,14 @@ size_t expert_gemm_scratch_bytes(int64_t P, int K);
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                const int8_t* aq, const float* ascale, const int16_t* absum, float* out, void* scratch);
+// expert parallelism: packed quantized rows either side of the all-to-all (expert_parallel.cu)
+size_t ep_row_bytes(int d);
+cudaError_t launch_ep_pack(cudaStream_t st, const uint32_t* row_of, int64_t n_rows, int d, const int8_t* xq, const float* xs,
+                           const int16_t* xb, void* send);
+cudaError_t launch_ep_regroup(cudaStream_t st, const void* recv, const uint32_t* counts, int n_src, int E, int64_t n_rows, int d,
+                              uint32_t* plan, int8_t* xq, float* xs, int16_t* xb, uint32_t* offsets, uint32_t* back_index);
+cudaError_t launch_ep_scatter(cudaStream_t st, const float* eo, int n_splits, int64_t split_stride, const uint32_t* back_index,
+                              int64_t n_rows, int d, float* out);
 // flags raised by kernels whose bounded waits expired (0 = none); synchronises the device
 cudaError_t read_stream_status(int* out);
 cudaError_t stream_status_ptr(int** out);  // device address of that health word

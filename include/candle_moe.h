@@ -195,6 +195,35 @@ CANDLE_MOE_API int candle_moe_forward_static(void* stream, const candle_moe_weig
 CANDLE_MOE_API int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* workspace, uint32_t** topk_ids,
                                float** topk_w, uint32_t** expert_counts, uint32_t** perm_token);
 
+/* Expert parallelism over ranks (one process per GPU): rank r owns a contiguous range of the experts and
+ * every rank routes its own tokens.  The reference has no multi-device form of this block (it runs every
+ * expert where the block lives, quantized_llama.rs:185-203); these calls are what an NCCL all-to-all of
+ * permuted token rows needs either side of it, and they reproduce the single-device results bit for bit:
+ * what travels is the quantized activation row that `VecDotType::from_float` (k_quants.rs:1898-1902) would
+ * produce on the receiving side anyway.  K-quant experts only (Q4_K / Q6_K; activations Q8K).
+ *
+ * Sender:   candle_moe_router_topk, candle_moe_quantize_act, candle_moe_permute as on one device (the
+ *           dispatch order, ascending global expert id, is also ascending destination rank), then
+ *   candle_moe_ep_pack: send_rows[p] = packed row of grouped position p, candle_moe_ep_row_bytes(d) bytes:
+ *           int8 values [d] | int16 block sums [d/16] | f32 block scales [d/256] | padding to 16 bytes.
+ * Host:     exchange the per-expert counts, then the rows (all-to-all with those split sizes).
+ * Receiver: candle_moe_ep_experts over the n_rows received rows, laid out source-major, each source's
+ *           rows ordered by local expert id; recv_counts is the device array [n_src][n_local_experts] of
+ *           row counts (w->n_experts is the LOCAL expert count here and w->w1/w3/w2 the local experts'
+ *           matrices; router and top_k are ignored).  max_rows_per_expert is a host-side bound on the
+ *           rows of any one local expert (n_rows is always valid; a tight bound picks better kernels).
+ *           out_rows [n_rows, d] f32: the experts' outputs in the order the rows arrived, ready for the
+ *           return all-to-all.  Workspace: candle_moe_ep_workspace_bytes(w, n_rows) bytes.
+ * Sender:   candle_moe_combine over the returned rows (they are back in grouped order). */
+CANDLE_MOE_API int candle_moe_ep_row_bytes(int32_t d_model, size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_ep_pack(void* stream, const uint32_t* perm_token, int64_t n_rows, int32_t d_model,
+                                      const int8_t* xq, const float* xscales, const int16_t* xbsums, void* send_rows);
+CANDLE_MOE_API int candle_moe_ep_workspace_bytes(const candle_moe_weights_t* w, int64_t max_rows_total, size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_ep_experts(void* stream, const candle_moe_weights_t* w, const void* recv_rows,
+                                         const uint32_t* recv_counts, int32_t n_src, int64_t n_rows,
+                                         int64_t max_rows_per_expert, float* out_rows, void* workspace,
+                                         size_t workspace_bytes);
+
 /* One-time repack of a Q4_K / Q6_K matrix [n_rows, k] (n_rows a multiple of 8 -- 16 for w2 --, k a
  * multiple of 256) into the register-fragment order the decode kernels read with coalesced
  * 128-bit loads.  Q4_K grows by 2.8 % (its 12-byte packed 6-bit scales are widened to 16 bytes),

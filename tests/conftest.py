@@ -18,3 +18,11 @@ def orc():
     from oracle import oracle
     oracle.build()
     return oracle
+
+
+@pytest.fixture(scope="session")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import candle_b200  # noqa: F401  (raises if the CUDA library is missing: no fallback)
+    return torch

@@ -1,0 +1,174 @@
+"""Expert parallelism: the exchange logic of candle_b200.expert_parallel.ExpertParallelMoe.
+
+CPU part (world size 2, gloo): the class runs with a stand-in for the four device steps that computes
+them with the oracle, so what is tested is the host logic -- counts exchange, split sizes, the order in
+which received rows are regrouped and sent back.  Every rank's result must equal the oracle's
+single-process block on that rank's tokens bit for bit.
+
+GPU part (one GPU): the same class over the CUDA library with a single rank, with and without a
+process group, against the oracle and against the single-device block.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests import helpers as H
+
+
+class OracleOps:
+    """The device steps of ExpertParallelMoe computed on the CPU by the oracle (f32 rows travel)."""
+
+    def __init__(self, orc, mw, rank, world):
+        self.orc, self.mw = orc, mw
+        self.d, self.k, self.E = mw.d_model, mw.top_k, mw.n_experts
+        self.El = self.E // world
+        self.lo = rank * self.El
+
+    def route(self, x):
+        from candle_b200.expert_parallel import Routed
+        xn = x.numpy()
+        T = xn.shape[0]
+        _, ids, tw = self.orc.router_topk(xn, self.mw.router, self.k, self.mw.renorm, self.mw.router_bias)
+        ids = np.asarray(ids).astype(np.int64)
+        flat = ids.reshape(-1)
+        order = np.argsort(flat, kind="stable")            # by expert, tokens ascending inside an expert
+        perm_token = (order // self.k).astype(np.int32)
+        pair_pos = np.empty(T * self.k, dtype=np.int32)
+        pair_pos[order] = np.arange(T * self.k, dtype=np.int32)
+        counts = np.bincount(flat, minlength=self.E).astype(np.int32)
+        return Routed(T, torch.from_numpy(ids.astype(np.int32)), torch.from_numpy(np.asarray(tw, np.float32)),
+                      torch.from_numpy(counts), torch.from_numpy(perm_token), torch.from_numpy(pair_pos), xn)
+
+    def pack(self, r):
+        return torch.from_numpy(r.extra[r.perm_token.numpy()].copy())
+
+    def empty_rows(self, n):
+        return torch.empty((n, self.d), dtype=torch.float32)
+
+    empty_out = empty_rows
+
+    def experts(self, recv_rows, recv_counts, n_rows, max_rows):
+        rows, cnt = recv_rows.numpy(), recv_counts.numpy()
+        assert cnt.sum() == n_rows and (n_rows == 0 or cnt.sum(0).max() <= max_rows)
+        out = np.zeros((n_rows, self.d), dtype=np.float32)
+        base = np.concatenate([[0], np.cumsum(cnt.reshape(-1))])  # arrival order: source-major, expert-minor
+        for e in range(self.El):
+            idx = np.concatenate([np.arange(base[s * self.El + e], base[s * self.El + e + 1]) for s in range(cnt.shape[0])])
+            if len(idx) == 0:
+                continue
+            g = self.lo + e
+            o, _ = self.orc.mlp_forward(self.mw.dtype_w13, self.mw.dtype_w2, rows[idx], self.mw.w1[g], self.mw.w3[g],
+                                        self.mw.w2[g], self.mw.d_ff)
+            out[idx] = o
+        return torch.from_numpy(out)
+
+    def combine(self, r, ret_rows, x):
+        ret, ids, tw, pos = ret_rows.numpy(), r.topk_ids.numpy(), r.topk_w.numpy(), r.pair_pos.numpy().reshape(r.T, self.k)
+        y = np.zeros((r.T, self.d), dtype=np.float32)
+        for t in range(r.T):
+            for j in np.argsort(ids[t], kind="stable"):  # ascending expert id, product rounded before the add
+                y[t] = y[t] + np.float32(tw[t, j]) * ret[pos[t, j]]
+        return torch.from_numpy(y)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cpu_rank(rank, world, port, tokens, fail):
+    try:
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        from oracle import oracle as orc
+        from candle_b200.expert_parallel import ExpertParallelMoe
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+        mw = orc.make_moe_weights(3, 256, 512, 8, 2, orc.Q4K, orc.Q6K,
+                                  router_bias=np.log(1.0 / (np.arange(8) + 1)).astype(np.float32))  # skewed load
+        x = orc.make_activations(100 + rank, tokens[rank], 256)
+        blk = ExpertParallelMoe(2, torch.from_numpy(mw.router), [], ops=OracleOps(orc, mw, rank, world))
+        y = blk.forward(torch.from_numpy(x)).numpy()
+        ref = orc.moe_forward(mw, x)
+        assert np.array_equal(y, ref.y), f"rank {rank}: max diff {np.abs(y - ref.y).max()}"
+        # a second step with other sizes reuses the object
+        x2 = orc.make_activations(200 + rank, 5 + 3 * rank, 256)
+        assert np.array_equal(blk.forward(torch.from_numpy(x2)).numpy(), orc.moe_forward(mw, x2).y)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        fail.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+
+
+@pytest.mark.parametrize("tokens", [(37, 12), (1, 0)])
+def test_exchange_logic_two_ranks_gloo(tokens):
+    ctx = mp.get_context("spawn")
+    fail = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_rank, args=(r, 2, port, tokens, fail)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    msgs = []
+    while not fail.empty():
+        msgs.append(fail.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            msgs.append("a rank did not finish")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs
+
+
+# ------------------------------------------------------------------------------------------------
+# one GPU
+# ------------------------------------------------------------------------------------------------
+def _device_block_and_ep(orc, torch, mw, prepack):
+    from candle_b200 import ExpertParallelMoe
+    blk = H.device_block(orc, mw)
+    if prepack:
+        blk.prepack()
+    ep = ExpertParallelMoe(mw.top_k, blk.feed_forward_gate_inp, blk.experts, norm_topk_prob=mw.renorm, prepack=prepack)
+    return blk, ep
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,prepack", [(1, True), (19, False), (19, True), (300, True)])
+def test_single_rank_equals_the_single_device_block(orc, torch_cuda, T, prepack):
+    torch = torch_cuda
+    mw = orc.make_moe_weights(21, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    x = orc.make_activations(40 + T, T, 512)
+    blk, ep = _device_block_and_ep(orc, torch, mw, prepack)
+    xd = torch.from_numpy(x).cuda()
+    y_ep = ep.forward(xd).cpu().numpy()
+    y_one = blk.forward(xd).cpu().numpy()
+    ref = orc.moe_forward(mw, x)
+    assert H.rel_l2(y_ep, ref.y) <= H.REL_L2_TOL and H.max_rel(y_ep, ref.y) <= H.MAX_REL_TOL
+    # same kernels over the same quantized rows: the expert-parallel path changes no arithmetic
+    assert H.rel_l2(y_ep, y_one) < 1e-6
+    assert ep.last_rows == T * 2
+
+
+@pytest.mark.gpu
+def test_single_rank_over_a_nccl_group(orc, torch_cuda):
+    torch = torch_cuda
+    if dist.is_initialized():
+        pytest.skip("a process group already exists in this process")
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{_free_port()}", rank=0, world_size=1,
+                            device_id=torch.device("cuda:0"))
+    try:
+        mw = orc.make_moe_weights(22, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+        x = orc.make_activations(77, 64, 512)
+        blk, ep = _device_block_and_ep(orc, torch, mw, True)
+        y = ep.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+        ref = orc.moe_forward(mw, x)
+        assert H.rel_l2(y, ref.y) <= H.REL_L2_TOL and H.max_rel(y, ref.y) <= H.MAX_REL_TOL
+    finally:
+        dist.destroy_process_group()
