@@ -53,6 +53,15 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peaks():
+    """(sustained, burst) dense bf16/fp16 TFLOP/s of this pool's B200s and where the numbers come from."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), float(j["bf16_tflops"]), "measured"
+    return 1400.0, 1590.0, "fallback"
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -190,7 +199,9 @@ def config_dict(args, cfg):
         "decode_weights": "GGUF blocks" if args.no_prepack else
         "prepacked copies made once at load (candle_moe_prepack; Q4_K +2.8 % bytes, Q6_K same size); "
         "roofline bytes are the GGUF bytes",
-        "parallelism": "single GPU" if args.gpus == 1 else f"{args.gpus} token-sharded replicas (no collective)",
+        "parallelism": "single GPU" if args.gpus == 1 else
+        f"ep{args.gpus}: {cfg['E'] // args.gpus} expert(s) per rank, every rank routes its own {args.tokens} rows; "
+        "NCCL all-to-all of the packed quantized rows and of the expert outputs",
     }
 
 
@@ -202,6 +213,27 @@ def weights_bytes(cfg):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
+def build_ep_block(torch, cfg, device, rank, world, prepack=True):
+    """Expert-parallel block: this rank's E/world experts (expert e is seeded by e, whatever the rank count) and
+    the replicated router."""
+    from candle_b200 import ExpertParallelMoe, GgmlDType, Mlp, QMatMul, QTensor
+    d, ff, E = cfg["d"], cfg["ff"], cfg["E"]
+    El = E // world
+
+    def q(g, shape, dt):
+        w = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02
+        return QMatMul(QTensor.quantize(w, GgmlDType(dt)))
+
+    experts = []
+    for e in range(rank * El, (rank + 1) * El):
+        g = torch.Generator(device=device).manual_seed(1000 + e)
+        experts.append(Mlp(q(g, (ff, d), cfg["dt13"]), q(g, (d, ff), cfg["dt2"]), q(g, (ff, d), cfg["dt13"])))
+    g = torch.Generator(device=device).manual_seed(999)
+    router = torch.randn((E, d), generator=g, device=device, dtype=torch.float32) * 0.02
+    bias = torch.log(1.0 / (torch.arange(E, dtype=torch.float32) + 1.0)) if cfg.get("zipf_bias") else None
+    return ExpertParallelMoe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], router_bias=bias, prepack=prepack)
+
+
 def build_block(torch, cfg, device, seed=0, prepack=True):
     from candle_b200 import GgmlDType, Mlp, MlpOrMoe, QMatMul, QTensor
     g = torch.Generator(device=device).manual_seed(seed)
@@ -273,10 +305,14 @@ def run_ours(args, cfg):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a rank that falls out of step must end the run with an error, not hang it
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     import candle_b200  # noqa: F401  loads libcandle_moe_sm100.so or raises
 
     T, d = args.tokens, cfg["d"]
+    if world > 1:
+        return run_ep(args, cfg, torch, dist, rank, world, local, dev)
     blk = build_block(torch, cfg, dev, seed=0, prepack=not args.no_prepack)
     blk.reserve(T)
     gx = torch.Generator(device=dev).manual_seed(1 + rank)
@@ -381,15 +417,25 @@ def run_ours(args, cfg):
         got = blk.forward(x[:Ts].clone()).cpu().numpy()
         rel_l2 = float(np.linalg.norm(got.astype(np.float64) - ref.y) / max(np.linalg.norm(ref.y), 1e-30))
 
+        roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s",
+                "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
+                "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]}
+        if T > 64 and cfg["dt13"] != 8:
+            # large batches run the tcgen05 grouped GEMM: the bound is the tensor pipe.  Algorithmic flops of the
+            # dominant product (the second multiply of every Q6_K slab is not counted).
+            sus, burst, kind = tensor_peaks()
+            flops = 2.0 * T * cfg["k"] * d * cfg["ff"] * (2 if top == "gate_up" else 1)
+            tf = flops / (stage_ms[top] * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": top, "achieved": tf, "peak": sus, "unit": "TFLOP/s", "frac": tf / sus,
+                    "traffic": None, "peak_source": f"{kind} cuBLAS bf16, sustained (burst {burst:.0f})",
+                    "algorithmic_flops_per_launch": flops, "kernel_ms": stage_ms[top]}
         line = {
             "metric": "moe_layer_tokens_per_s", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
-            "roofline": {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s",
-                         "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
-                         "peak_source": f"{peak_kind} copy bandwidth",
-                         "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]},
+            "roofline": roof,
             "block_roofline": {"bound": "hbm", "algorithmic_bytes": block_bytes, "achieved": blk_gbs,
                                "frac": blk_gbs / peak, "frac_of_nominal_8TBps": blk_gbs / 8000.0,
                                "active_experts": active, "tensor_ops": block_ops,
@@ -408,6 +454,119 @@ def run_ours(args, cfg):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_ep(args, cfg, torch, dist, rank, world, local, dev):
+    """N > 1: expert parallelism.  Every rank holds E / N experts and routes its own T rows per step."""
+    if cfg["E"] % world or cfg["dt13"] == 8 or cfg["ff_shared"]:
+        raise SystemExit(f"workload {args.workload} has no expert-parallel form over {world} ranks")
+    T, d = args.tokens, cfg["d"]
+    blk = build_ep_block(torch, cfg, dev, rank, world, prepack=not args.no_prepack)
+    gx = torch.Generator(device=dev).manual_seed(1 + rank)
+    x = torch.randn((T, d), generator=gx, device=dev, dtype=torch.float32)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t_load0 = time.perf_counter()
+    for _ in range(args.warmup):
+        y = blk.forward(x)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        y = blk.forward(x)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+
+    hx = torch.randn((T, d), dtype=torch.float32).pin_memory()
+    hy = torch.empty((T, d), dtype=torch.float32).pin_memory()
+    for _ in range(3):
+        x.copy_(hx, non_blocking=True)
+        hy.copy_(blk.forward(x), non_blocking=True)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(args.steps):
+        x.copy_(hx, non_blocking=True)
+        hy.copy_(blk.forward(x), non_blocking=True)
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+
+    # per-phase device times (events between the phases of a step), outside the timed regions above
+    n_ph = len(blk.PHASES)
+    acc = [0.0] * n_ph
+    reps = max(min(args.steps, 20), 5)
+    for _ in range(reps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph + 1)]
+        it = iter(evs[1:])
+        evs[0].record()
+        blk.forward(x, mark=lambda: next(it).record())
+        torch.cuda.synchronize(dev)
+        for i in range(n_ph):
+            acc[i] += evs[i].elapsed_time(evs[i + 1]) / reps
+    rows_here = blk.last_rows
+    # keep the GPUs under the same load until the clock sampler has seen it.  Every forward holds collectives,
+    # so all ranks must run the SAME number of extra steps: rank 0's estimate, agreed through an all-reduce.
+    left = max(0.0, 1.5 - (time.perf_counter() - t_load0))
+    n_extra = torch.tensor([int(left / max(ms_total / args.steps * 1e-3, 1e-5)) + 1 if rank == 0 else 0],
+                           dtype=torch.int64, device=dev)
+    dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)
+    for _ in range(min(int(n_extra), 20000)):
+        blk.forward(x)
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms_total, ms_e2e] + acc + [float(blk.last_max_rows), float(rows_here)], dtype=torch.float64, device=dev)
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = float(tmax[0]), float(tmax[1])
+    phase_ms = {n: float(tmax[2 + i]) for i, n in enumerate(blk.PHASES)}
+    if rank == 0:
+        ms_step = ms_total / args.steps
+        rows_max, rows_expert_max = int(tmax[-1]), int(tmax[-2])
+        El = cfg["E"] // world
+        per13, per2 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], d), mat_bytes(cfg["dt2"], d, cfg["ff"])
+        ex_ms = phase_ms["experts"]
+        if rows_expert_max > 64:  # the tensor-core form; up to 64 rows per expert take the decode kernels
+            sus, burst, kind = tensor_peaks()
+            flops = 2.0 * rows_max * 3 * d * cfg["ff"]
+            tf = flops / (ex_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "local experts (gate_up + down) on the busiest rank", "achieved": tf,
+                    "peak": sus, "unit": "TFLOP/s", "frac": tf / sus, "traffic": None,
+                    "peak_source": f"{kind} cuBLAS bf16, sustained (burst {burst:.0f})",
+                    "algorithmic_flops_per_launch": flops, "kernel_ms": ex_ms}
+        else:
+            peak, peak_kind = peaks()
+            byts = El * (per13 + per2)
+            gbs = byts / (ex_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": "local experts (gate_up + down)", "achieved": gbs, "peak": peak,
+                    "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                    "algorithmic_bytes_per_launch": byts, "kernel_ms": ex_ms}
+        row_b = d + d // 8 + d // 64
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
+            "roofline": roof, "stage_ms": phase_ms,
+            "exchange": {"rows_sent_per_rank": T * cfg["k"], "row_bytes_forward": row_b, "row_bytes_back": 4 * d,
+                         "rows_on_busiest_rank": rows_max, "rows_of_busiest_expert": rows_expert_max},
+            "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": 12 * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def main():

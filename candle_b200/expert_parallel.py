@@ -160,11 +160,16 @@ class ExpertParallelMoe:
             return
         dist.all_to_all_single(out, inp, out_split, in_split, group=self.group)
 
-    def forward(self, xs: torch.Tensor) -> torch.Tensor:
+    PHASES = ("route_pack", "exchange_rows", "experts", "exchange_results", "combine")
+
+    def forward(self, xs: torch.Tensor, mark=None) -> torch.Tensor:
+        """One step.  `mark`, if given, is called after each of PHASES (for per-phase timing)."""
+        mark = mark or (lambda: None)
         x2 = xs.reshape(-1, self.d_model).contiguous()
         N, El = self.world, self.E_local
         r = self.ops.route(x2)
         send_rows = self.ops.pack(r)
+        mark()
         # rows per (destination rank, its local expert) -> rows per (source rank, my local expert)
         recv_counts = torch.empty((N, El), dtype=r.counts.dtype, device=r.counts.device)
         self._a2a(recv_counts.view(-1), r.counts.view(-1))
@@ -175,11 +180,15 @@ class ExpertParallelMoe:
         max_rows = int(both[1].sum(0).max()) if n_rows else 0
         recv_rows = self.ops.empty_rows(n_rows)
         self._a2a(recv_rows, send_rows, recv_split, send_split)
+        mark()
         out_rows = self.ops.experts(recv_rows, recv_counts, n_rows, max_rows)
+        mark()
         ret_rows = self.ops.empty_out(r.T * self.k)
         self._a2a(ret_rows, out_rows, send_split, recv_split)
+        mark()
         y = self.ops.combine(r, ret_rows, x2)
-        self.last_rows = n_rows
+        mark()
+        self.last_rows, self.last_max_rows = n_rows, max_rows
         return y.reshape(xs.shape)
 
     __call__ = forward
