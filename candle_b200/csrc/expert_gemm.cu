@@ -184,9 +184,7 @@ struct GemmQ4K {
         for (int s = 0; s < 4; ++s) pr.q[s] = ldg128(b + 16 + 32 * s + 16 * h);
     }
     // d (low half) and dmin (high half) of the block, fp16 bits
-    __device__ static __forceinline__ uint32_t load_hdr(const Row& r, int blk) {
-        return __ldg(reinterpret_cast<const uint32_t*>(r.p + (size_t)blk * Q4K_BYTES));
-    }
+    __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.hdr.x; }
     struct Ctx {
         uint32_t sc[2], mn[2];  // 6-bit scales / mins as bytes: [0] = sub-blocks 0..3, [1] = 4..7 (utils.rs:50-60)
     };
@@ -271,7 +269,9 @@ struct GemmQ6K {
     }
     struct Pre {
         uint4 ql[2][2], qh[2], sc;
+        uint32_t d;  // fp16 bits
     };
+    __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.d; }
     __device__ static __forceinline__ void load(Pre& pr, const Row& r, int blk, int h) {
         const uint8_t* b = r.p + (size_t)blk * Q6K_HTB_BYTES + 64 * r.g + 32 * h;
 #pragma unroll
@@ -281,9 +281,7 @@ struct GemmQ6K {
             pr.qh[j] = ldg128(b + 1024 + 16 * j);
         }
         pr.sc = ldg128(r.p + (size_t)blk * Q6K_HTB_BYTES + 1536 + 16 * r.g);
-    }
-    __device__ static __forceinline__ uint32_t load_hdr(const Row& r, int blk) {
-        return (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r.p + (size_t)blk * Q6K_HTB_BYTES + 1664 + 2 * r.g));
+        pr.d = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(r.p + (size_t)blk * Q6K_HTB_BYTES + 1664 + 2 * r.g));
     }
     struct Ctx {
         uint32_t xc[4], xh[4];  // per scale byte: ceil(sc/2) + 64 and floor(sc/2) + 64
@@ -365,6 +363,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     __shared__ uint64_t tmem_full[2], epi_done[2];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
+    __shared__ float s_dw[8][G_TILE_M];  // per block (ring of 8) and tile row: the weight scale the drain multiplies by
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     // the warp index through a shuffle: the compiler then knows that it is warp-uniform and keeps role
@@ -414,13 +413,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
         bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
-        typename F::Row rowc{}, rown{};
-        uint32_t hdr_c = 0, hdr_n = 0;
         GT_BEGIN();
         if (have) {
-            const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
-            rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
-            hdr_c = F::load_hdr(rowc, 0);
             const float* dp = P.d8t + tc.p0 + colhalf * 64 + lane;
             s_d8[ew][0][lane] = dp[0];
             s_d8[ew][0][lane + 32] = dp[32];
@@ -428,10 +422,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         }
         while (have) {
             const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
-            if (have_n) {
-                const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
-                rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
-            }
             float acc[64];
 #pragma unroll
             for (int i = 0; i < 64; ++i) acc[i] = 0.f;
@@ -441,23 +431,21 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 float d8_n0 = 0.f, d8_n1 = 0.f;
                 bool pre = false;
                 if (blk + 1 < P.kb) {
-                    hdr_n = F::load_hdr(rowc, blk + 1);
                     const float* dp = P.d8t + (size_t)(blk + 1) * P.P_pad + tc.p0 + colhalf * 64 + lane;
                     d8_n0 = dp[0];
                     d8_n1 = dp[32];
                     pre = true;
                 } else if (have_n) {
-                    hdr_n = F::load_hdr(rown, 0);
                     const float* dp = P.d8t + tcn.p0 + colhalf * 64 + lane;
                     d8_n0 = dp[0];
                     d8_n1 = dp[32];
                     pre = true;
                 }
-                const float dw = F::scale_of(hdr_c);
-                const uint64_t dw2 = f32x2_pack(dw, dw);
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(0, ab);
                 GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
                 tc5_fence_after_sync();
+                const float dw = s_dw[ab & 7][r];  // left by the unpack warps when they produced this block
+                const uint64_t dw2 = f32x2_pack(dw, dw);
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(1, ab);
                 const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128);
                 const uint32_t d8_addr = smem_u32(&s_d8[ew][buf][0]);
@@ -493,7 +481,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
                 }
                 __syncwarp();
-                hdr_c = hdr_n;
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(2, ab);
             }
             // ---- store the tile ----
@@ -522,7 +509,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #endif
             tile += gridDim.x;
             tc = tcn;
-            rowc = rown;
             have = have_n;
         }
         GT_END(16, threadIdx.x == 32 * G_WARP_EPI0);
@@ -558,6 +544,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     F::load(nxt, rown, 0, h);
                 typename F::Ctx ctx;
                 F::begin(cur, ctx);
+                if (h == 0) s_dw[ab & 7][r] = F::scale_of(F::hdr_of(cur));  // read by the epilogue when it drains this block
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
                     // slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks)
