@@ -64,7 +64,7 @@ constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 op
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
 // Warp roles.  The MMA and TMA warps take the highest indices: measured, their short instruction streams
 // are served far better there than at the lowest ones (1.75x on the whole kernel).
-constexpr int G_WARP_EPI0 = 0, G_WARP_DQ0 = G_WARP_EPI0 + G_EPI_WARPS, G_WARP_TMA = 18, G_WARP_MMA = 19;
+constexpr int G_WARP_EPI0 = 0, G_WARP_DQ0 = G_WARP_EPI0 + G_EPI_WARPS, G_WARP_LOAD = 16, G_WARP_TMA = 18, G_WARP_MMA = 19;
 constexpr int G_THREADS = 32 * 20;  // five warpgroups: 2 epilogue, 2 unpack, 1 with the TMA and MMA warps (+ 2 idle)
 constexpr int G_REGS_EPI = 128, G_REGS_MISC = 32;  // budgets after the trade: 2 * 128 + 2 * 96 + 32 = 5 * 96, the launch allocation
 constexpr int G_TMEM_COLS = 512;
@@ -146,6 +146,7 @@ struct GemmParams {
     const uint32_t* offsets;      // [E + 1]
     const float* d8t;             // [kb][P_pad]
     float* out;                   // gate_up: hidden [P, N]; down: [P, N]
+    const CUtensorMap* wmaps;     // device array [E][2]: raw blocks of W1 / W3 (or W2, second unused) as byte matrices
     int* status;
     int E, K, N, kb, P, P_pad;
     int m_tiles;                  // tiles along the weight rows (N / 64 for gate_up, N / 128 for down)
@@ -170,6 +171,8 @@ __device__ __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? 
 struct GemmQ4K {
     static constexpr bool HAS_MIN = true;
     static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;  // 8 slabs of 32 columns: two blocks in flight
+    static constexpr bool STAGE_W = true;                         // raw blocks of the tile pass through shared memory
+    static constexpr int W_ROW_BYTES = Q4K_BYTES;
     struct Row {
         const uint8_t* p;
     };
@@ -182,6 +185,13 @@ struct GemmQ4K {
         pr.hdr = ldg128(b);
 #pragma unroll
         for (int s = 0; s < 4; ++s) pr.q[s] = ldg128(b + 16 + 32 * s + 16 * h);
+    }
+    // the same pieces from the staged copy of the block (row_addr: shared-window address of the row's 144 bytes;
+    // rows are 36 words apart, so the eight lanes of a 16-byte load phase cover all 32 banks once)
+    __device__ static __forceinline__ void load_staged(Pre& pr, uint32_t row_addr, int h) {
+        pr.hdr = lds128(row_addr);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) pr.q[s] = lds128(row_addr + 16 + 32 * s + 16 * h);
     }
     // d (low half) and dmin (high half) of the block, fp16 bits
     __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.hdr.x; }
@@ -260,6 +270,8 @@ struct GemmQ4K {
 struct GemmQ6K {
     static constexpr bool HAS_MIN = false;
     static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;  // 4 slabs of 64 columns (two operand parts each)
+    static constexpr bool STAGE_W = false;
+    static constexpr int W_ROW_BYTES = 0;
     struct Row {
         const uint8_t* p;  // half-tile block 0 of the row's group of 8
         int g;
@@ -272,6 +284,7 @@ struct GemmQ6K {
         uint32_t d;  // fp16 bits
     };
     __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.d; }
+    __device__ static __forceinline__ void load_staged(Pre&, uint32_t, int) {}
     __device__ static __forceinline__ void load(Pre& pr, const Row& r, int blk, int h) {
         const uint8_t* b = r.p + (size_t)blk * Q6K_HTB_BYTES + 64 * r.g + 32 * h;
 #pragma unroll
@@ -360,7 +373,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                    const __grid_constant__ CUtensorMap map_bs) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_a[4], empty_a[4], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
-    __shared__ uint64_t tmem_full[2], epi_done[2];
+    __shared__ uint64_t tmem_full[2], epi_done[2], full_w, empty_w;
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
     __shared__ float s_dw[8][G_TILE_M];  // per block (ring of 8) and tile row: the weight scale the drain multiplies by
@@ -374,6 +387,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * G_TILE_BYTES;
     uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
+    uint8_t* smem_w = smem_min_a + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES;  // staged raw blocks of the tile rows (one block deep)
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -389,6 +403,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             mbar_init(&tmem_full[b], 1);
             mbar_init(&epi_done[b], G_EPI_WARPS);
         }
+        mbar_init(&full_w, 1);
+        mbar_init(&empty_w, G_DQ_WARPS);
         fence_barrier_init();
     }
     if (warp == G_WARP_TMA) tmem_alloc(&s_tmem_base, G_TMEM_COLS);
@@ -525,7 +541,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         typename F::Row rowc{}, rown{};
         typename F::Pre cur, nxt;
         GT_BEGIN();
-        if (have) {
+        // staged row of tile row r: gate_up keeps the W1 rows first, then the W3 rows
+        const uint32_t w_row = smem_u32(smem_w) + (GATE_UP ? (uint32_t)((r & 1) * (G_TILE_M / 2 * F::W_ROW_BYTES) + (r >> 1) * F::W_ROW_BYTES)
+                                                           : (uint32_t)(r * F::W_ROW_BYTES));
+        if (have && !F::STAGE_W) {
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
             F::load(cur, rowc, 0, h);
@@ -533,18 +552,27 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         }
         while (have) {
             const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
-            if (have_n) {
+            if (have_n && !F::STAGE_W) {
                 const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
                 rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
             }
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
-                if (blk + 1 < P.kb)
+                if (F::STAGE_W) {
+                    // this block's raw bytes were copied to shared memory by the loader warp
+                    GT(1, mbar_wait(&full_w, ab & 1, abort_flag));
+                    F::load_staged(cur, w_row, h);
+                } else if (blk + 1 < P.kb) {
                     F::load(nxt, rowc, blk + 1, h);
-                else if (have_n)
+                } else if (have_n) {
                     F::load(nxt, rown, 0, h);
+                }
                 typename F::Ctx ctx;
                 F::begin(cur, ctx);
                 if (h == 0) s_dw[ab & 7][r] = F::scale_of(F::hdr_of(cur));  // read by the epilogue when it drains this block
+                if (F::STAGE_W) {  // the staged copy is in registers: the loader may refill it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_w);
+                }
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
                     // slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks)
@@ -567,7 +595,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     if (lane == 0) mbar_arrive(&full_a[slot]);
                     if (lane == 0 && warp == G_WARP_DQ0) TR(5, ita);
                 }
-                cur = nxt;
+                if (!F::STAGE_W) cur = nxt;
             }
             tile += gridDim.x;
             tc = tcn;
@@ -575,6 +603,51 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             have = have_n;
         }
         GT_END(8, threadIdx.x == 32 * G_WARP_DQ0);
+    } else if (warp == G_WARP_LOAD) {
+        // ===================== weight loader: raw blocks of the tile rows -> shared memory =====================
+        // One TMA box per matrix and block: [64 or 128 rows x 144 bytes] of the byte matrix [n_rows, row_bytes]
+        // (gate_up: the W1 rows, then the W3 rows; a TMA destination must be 128-byte aligned, so the halves cannot
+        // be skewed against each other and neighbouring lanes, which alternate between them, share banks two by
+        // two).  Two blocks ahead the same boxes are requested into L2, so the copy into the one-block-deep stage
+        // finds them there.
+        if (F::STAGE_W) {
+            uint32_t ab = 0;
+            long long tile = blockIdx.x;
+            TileCoord tc, tcn;
+            bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+            constexpr int HALF = G_TILE_M / 2 * F::W_ROW_BYTES;  // 9216
+            while (have) {
+                const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+                const CUtensorMap* m0 = P.wmaps + 2 * tc.e;
+                const int y0 = GATE_UP ? tc.mt * 64 : tc.mt * 128;
+                for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                    if (ab >= 1) mbar_wait(&empty_w, (ab - 1) & 1, abort_flag);
+                    if (elect_one()) {
+                        mbar_expect_tx(&full_w, G_TILE_M * F::W_ROW_BYTES);
+                        if (GATE_UP) {
+                            tma_load_2d(smem_w, m0, blk * F::W_ROW_BYTES, y0, &full_w);
+                            tma_load_2d(smem_w + HALF, m0 + 1, blk * F::W_ROW_BYTES, y0, &full_w);
+                        } else {
+                            tma_load_2d(smem_w, m0, blk * F::W_ROW_BYTES, y0, &full_w);
+                            tma_load_2d(smem_w + HALF, m0, blk * F::W_ROW_BYTES, y0 + 64, &full_w);
+                        }
+                        // two blocks ahead, possibly in the next tile
+                        const bool same = blk + 2 < P.kb;
+                        if (same || have_n) {
+                            const CUtensorMap* mp = same ? m0 : P.wmaps + 2 * tcn.e;
+                            const int yp = same ? y0 : (GATE_UP ? tcn.mt * 64 : tcn.mt * 128);
+                            const int xp = (same ? blk + 2 : blk + 2 - P.kb) * F::W_ROW_BYTES;
+                            tma_prefetch_2d(mp, xp, yp);
+                            tma_prefetch_2d(GATE_UP ? mp + 1 : mp, xp, GATE_UP ? yp : yp + 64);
+                        }
+                    }
+                    __syncwarp();
+                }
+                tile += gridDim.x;
+                tc = tcn;
+                have = have_n;
+            }
+        }
     } else if (warp == G_WARP_TMA) {
         // ===================== TMA: activation operand =====================
         // the whole warp walks the loop (uniform control flow and addresses), one elected lane issues
@@ -699,11 +772,25 @@ bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// byte matrix [rows, row_bytes] -> boxes of [box_rows x box_bytes], no swizzle
+bool make_map_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int g_gemm_sms = -1;
 
 template <class F, bool GATE_UP>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = (G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) + (F::HAS_MIN ? 2 : 0)) * G_TILE_BYTES + 1024 /* alignment slack */;
+    const int smem_bytes = (G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) + (F::HAS_MIN ? 2 : 0)) * G_TILE_BYTES +
+                           (F::STAGE_W ? G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
@@ -715,7 +802,8 @@ cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUten
 // Scratch the GEMM needs for P grouped rows of length K (fp16 operand, block-sum operand, scales).
 size_t expert_gemm_scratch_bytes(int64_t P, int K) {
     const size_t p_pad = (size_t)P + G_TILE_N, kb = (size_t)K / 256;
-    return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256);
+    return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256) +
+           sizeof(CUtensorMap) * 2 * CANDLE_MOE_MAX_EXPERTS;
 }
 
 // Takes Q4_K weights in GGUF layout (repacked = false) and Q6_K weights in the repacked layout of the
@@ -751,7 +839,23 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K, G_SLAB_K)) return cudaErrorNotSupported;
     if (!make_map_2d(&map_bs, bmin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)p_pad, (uint64_t)kb * 32, 32)) return cudaErrorNotSupported;
 
+    // byte-matrix tensor maps of the raw weight blocks (Q4_K): [n_rows, kb * 144] with boxes of 64 rows x one block,
+    // written to the head of the scratch on the stream before the kernel
+    CUtensorMap* wmaps_dev = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(d8t) + align_up((size_t)kb * p_pad * 4, 256));
+    if (dtype == CANDLE_GGML_Q4K) {
+        CUtensorMap host_maps[2 * CANDLE_MOE_MAX_EXPERTS];
+        const uint64_t n_rows = (uint64_t)N, rb = (uint64_t)kb * Q4K_BYTES;
+        for (int e2 = 0; e2 < E; ++e2) {
+            if (!make_map_bytes(&host_maps[2 * e2], wa.p[e2], n_rows, rb, Q4K_BYTES, 64)) return cudaErrorNotSupported;
+            if (!make_map_bytes(&host_maps[2 * e2 + 1], gate_up ? wb.p[e2] : wa.p[e2], n_rows, rb, Q4K_BYTES, 64))
+                return cudaErrorNotSupported;
+        }
+        e = cudaMemcpyAsync(wmaps_dev, host_maps, sizeof(CUtensorMap) * 2 * E, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return e;
+    }
+
     GemmParams G{};
+    G.wmaps = wmaps_dev;
     G.wa = wa;
     G.wb = wb;
     G.offsets = offsets;
