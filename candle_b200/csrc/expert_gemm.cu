@@ -314,9 +314,11 @@ struct GemmQ6K {
 #pragma unroll
         for (int cw = 0; cw < 4; ++cw) {
             const int idx = 4 * s + cw;
-            // (1024 + x) / 16 - 68 = (x - 64) / 16: the half scale over 16
+            // (1024 + x) / 16 - 68 = (x - 64) / 16: the half scale over 16; c = -1536 m, so that
+            // fma(1024 + 16 q, m, c) = (q - 32) * (half scale), an integer of at most 2048: exact
             const __half2 m1 = __hfma2(byte_magic2(c.xc[idx >> 2], idx & 3), k16th, km68);
             const __half2 m2 = __hfma2(byte_magic2(c.xh[idx >> 2], idx & 3), k16th, km68);
+            const __half2 c1 = __hmul2(m1, km1536), c2 = __hmul2(m2, km1536);
             const int bq = 2 * ((cw >> 1) + 2 * odd);  // bit position of this quarter's pair in the qh byte
             uint32_t o1[4], o2[4];
 #pragma unroll
@@ -324,13 +326,12 @@ struct GemmQ6K {
                 const uint32_t qlw = w4(pr.ql[n][j], cw), qhw = w4(pr.qh[j], 2 * n + (cw & 1));
                 const uint32_t a02 = odd ? qlw : (qlw << 4), a13 = odd ? (qlw >> 8) : (qlw >> 4);
                 const uint32_t b02 = qhw << (8 - bq), b13 = qhw >> bq;
-                const uint32_t v02 = ((a02 & 0x00F000F0u) | 0x64006400u) | (b02 & 0x03000300u);
-                const uint32_t v13 = ((a13 & 0x00F000F0u) | 0x64006400u) | (b13 & 0x03000300u);
-                const __half2 x02 = __hadd2(h2_bits(v02), km1536), x13 = __hadd2(h2_bits(v13), km1536);
-                o1[2 * j] = bits_h2(__hmul2(x02, m1));
-                o1[2 * j + 1] = bits_h2(__hmul2(x13, m1));
-                o2[2 * j] = bits_h2(__hmul2(x02, m2));
-                o2[2 * j + 1] = bits_h2(__hmul2(x13, m2));
+                const __half2 v02 = h2_bits(((a02 & 0x00F000F0u) | 0x64006400u) | (b02 & 0x03000300u));
+                const __half2 v13 = h2_bits(((a13 & 0x00F000F0u) | 0x64006400u) | (b13 & 0x03000300u));
+                o1[2 * j] = bits_h2(__hfma2(v02, m1, c1));
+                o1[2 * j + 1] = bits_h2(__hfma2(v13, m1, c1));
+                o2[2 * j] = bits_h2(__hfma2(v02, m2, c2));
+                o2[2 * j + 1] = bits_h2(__hfma2(v13, m2, c2));
             }
             tmem_st4(ta + 8 * cw + 4 * h, o1[0], o1[1], o1[2], o1[3]);
             tmem_st4(ta + 32 + 8 * cw + 4 * h, o2[0], o2[1], o2[2], o2[3]);
