@@ -11,7 +11,17 @@ using namespace cmoe;
 
 namespace {
 
-constexpr int64_t GEMM_MIN_TOKENS = 64;  // above this the tensor-core GEMM takes the Q4_K products
+// Above this bound on the rows of one expert the tensor-core GEMM takes the k-quant products (below, the decode
+// kernels); CANDLE_MOE_GEMM_MIN_ROWS overrides it (experiments).
+inline int64_t gemm_min_rows() {
+    const char* v = std::getenv("CANDLE_MOE_GEMM_MIN_ROWS");
+    return v && v[0] ? std::atoll(v) : 64;
+}
+// When the caller knows the ACTUAL largest row count of an expert (expert parallelism: the host has the counts), the
+// GEMM already pays off above 24 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
+// with 32-wide position tiles).  (A single-device
+// forward only knows the bound T, and its experts usually hold a fraction of that.)
+constexpr int64_t GEMM_MIN_ROWS_EXACT = 24;
 constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
@@ -94,7 +104,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
         ws.shb = carve<int16_t>(base, off, (size_t)T * fs / 16);
         ws.so = carve<float>(base, off, (size_t)T * d * k_split_slots(T));
     }
-    if (T > GEMM_MIN_TOKENS) {
+    if (T > gemm_min_rows()) {
         // large batches: fp16 activation operand of the tcgen05 GEMM (Q4_K matrices), reused by gate_up and down
         size_t g = 0;
         const auto takes = [](int dt, const void* const* packed) {
@@ -267,10 +277,10 @@ struct ExpertBufs {
 int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs& p1, const ExpertPtrs& p3,
                 const ExpertPtrs& p2, int64_t max_rows, int64_t P, const uint32_t* offsets, const uint32_t* row_of,
                 const int8_t* xq, const float* xs, const int16_t* xb, const ExpertBufs& b, int slots, int* eo_splits,
-                bool marks) {
+                bool marks, bool rows_exact = false) {
     const int E = w->n_experts, d = w->d_model, ff = w->d_ff;
-    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= 64;
-    const bool large = b.gemm && max_rows > GEMM_MIN_TOKENS && gemm_enabled();
+    const bool large = b.gemm && max_rows > (rows_exact ? GEMM_MIN_ROWS_EXACT : gemm_min_rows()) && gemm_enabled();
+    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= 64 && !large;
     bool gate_done = false, down_done = false;
     *eo_splits = 1;
     ExpertPtrs q1, q3, q2;
@@ -293,8 +303,8 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
             CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
             CM_TRY(fill_ptrs(w->w3_prepacked, E, g3));
         }
-        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, offsets, row_of, P, xq, xs,
-                                                  xb, b.hidden, b.gemm);
+        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, offsets, row_of, P, max_rows, xq,
+                                                  xs, xb, b.hidden, b.gemm);
         if (ce == cudaSuccess)
             gate_done = true;
         else if (ce != cudaErrorNotSupported)
@@ -320,8 +330,8 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
         ExpertPtrs g2 = p2;
         if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
-        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, b.hq, b.hs,
-                                                  b.hb, b.eo, b.gemm);
+        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, max_rows,
+                                                  b.hq, b.hs, b.hb, b.eo, b.gemm);
         if (ce == cudaSuccess) {
             down_done = true;
             *eo_splits = 1;
@@ -366,7 +376,7 @@ EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
     const size_t small_rows = std::min<size_t>((size_t)P, 64 * E);
     ws.eo_rows = (int64_t)std::max<size_t>((size_t)P * 4, small_rows * MAX_K_SPLITS);
     ws.eb.eo = carve<float>(base, off, (size_t)ws.eo_rows * d);
-    if (P > GEMM_MIN_TOKENS) {
+    if (P > GEMM_MIN_ROWS_EXACT) {
         const size_t g = std::max(expert_gemm_scratch_bytes(P, (int)d), expert_gemm_scratch_bytes(P, (int)ff));
         off = align_up(off, 1024);
         ws.eb.gemm = base ? base + off : reinterpret_cast<void*>(1);
@@ -641,7 +651,7 @@ int candle_moe_ep_experts(void* stream, const candle_moe_weights_t* w, const voi
     int eo_splits = 1;
     const int slots = max_rows_per_expert <= 64 ? MAX_K_SPLITS : 4;
     CM_TRY(run_experts(st, w, p1, p3, p2, max_rows_per_expert, n_rows, ws.offsets, nullptr, ws.xq, ws.xs, ws.xb, ws.eb, slots,
-                       &eo_splits, false));
+                       &eo_splits, false, true));
     return rc(launch_ep_scatter(st, ws.eb.eo, eo_splits, n_rows * d, ws.back, n_rows, d, out_rows));
 }
 

@@ -58,9 +58,10 @@ extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timi
 
 namespace {
 
-constexpr int G_TILE_M = 128, G_TILE_N = 128, G_SLAB_K = 64;
+constexpr int G_TILE_M = 128, G_SLAB_K = 64;  // the position tile (N) is a template parameter: 128, or 32 for small batches
+constexpr int G_PAD_ROWS = 128;                // zero rows after the last position, so that no box leaves the buffers
 constexpr int G_B_STAGES = 2;   // in shared memory, one 256-wide block each (four slabs + the min-term box for Q4_K)
-constexpr int G_TILE_BYTES = G_TILE_N * G_SLAB_K * 2;  // one [128 x 64] fp16 operand tile, 16 KB
+constexpr int G_TILE_BYTES = G_TILE_M * G_SLAB_K * 2;  // one [128 x 64] fp16 (or [128 x 32] tf32) operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
 // Warp roles.  The MMA and TMA warps take the highest indices: measured, their short instruction streams
 // are served far better there than at the lowest ones (1.75x on the whole kernel).
@@ -348,18 +349,19 @@ struct TileCoord {
 
 // tile id -> (expert, row tile, position tile); position tiles are fastest, so the CTAs that run at
 // the same time share a weight tile (fetched from HBM once) and each expert's activations stay in L2
+template <int TN>
 __device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs, int E, int m_tiles, TileCoord& tc) {
     long long cum = 0;
     for (int e = 0; e < E; ++e) {
         const uint32_t cnt = offs[e + 1] - offs[e];
-        const int n_tiles = (int)((cnt + G_TILE_N - 1) / G_TILE_N);
+        const int n_tiles = (int)((cnt + TN - 1) / TN);
         const long long te = (long long)n_tiles * m_tiles;
         if (tile < cum + te) {
             const long long local = tile - cum;
             tc.e = e;
             tc.mt = (int)(local / n_tiles);
             tc.nt = (int)(local - (long long)tc.mt * n_tiles);
-            tc.p0 = offs[e] + (uint32_t)tc.nt * G_TILE_N;
+            tc.p0 = offs[e] + (uint32_t)tc.nt * TN;
             tc.p_end = offs[e + 1];
             return true;
         }
@@ -368,7 +370,7 @@ __device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs
     return false;
 }
 
-template <class F, bool GATE_UP>
+template <class F, bool GATE_UP, int TN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_bs) {
@@ -376,7 +378,9 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     __shared__ uint64_t full_a[4], empty_a[4], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
     __shared__ uint64_t tmem_full[2], epi_done[2], full_w, empty_w;
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
-    __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][64];  // per epilogue warp: activation scales of its 64 columns
+    constexpr int CH = TN / 2;            // columns (positions) per epilogue warp: two warps share a TMEM lane quarter
+    constexpr int B_TILE = TN * G_SLAB_K * 2;  // one [TN x 64] fp16 activation slab
+    __shared__ __align__(16) float s_d8[G_EPI_WARPS][2][CH];  // per epilogue warp: activation scales of its columns
     __shared__ float s_dw[8][G_TILE_M];  // per block (ring of 8) and tile row: the weight scale the drain multiplies by
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -386,7 +390,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * G_TILE_BYTES;
+    constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * B_TILE;
     uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
     uint8_t* smem_w = smem_min_a + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES;  // staged raw blocks of the tile rows (one block deep)
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
@@ -414,7 +418,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     tc5_fence_after_sync();
     const uint32_t tmem_base = __shfl_sync(0xffffffffu, s_tmem_base, 0);
     volatile int* abort_flag = &s_abort;
-    constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, G_TILE_N), IDESC_TF32 = umma_idesc_tf32(G_TILE_M, G_TILE_N);
+    constexpr uint32_t IDESC = umma_idesc_f16(G_TILE_M, TN), IDESC_TF32 = umma_idesc_tf32(G_TILE_M, TN);
 
     // Register budget: launched with 96 per thread; the TMA/MMA warpgroup hands 64 per thread back to the CTA's
     // pool and the two epilogue warpgroups take 32 more each, so the total stays what the launch allocated (a
@@ -425,38 +429,35 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         // ===================== epilogue =====================
         const int quarter = warp & 3, colhalf = (warp - G_WARP_EPI0) >> 2, ew = warp - G_WARP_EPI0;
         const int r = 32 * quarter + lane;  // tile row = TMEM lane
-        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(colhalf * 64);
+        const uint32_t ta_lane = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(colhalf * CH);
         uint32_t ab = 0;
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
-        bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
         GT_BEGIN();
         if (have) {
-            const float* dp = P.d8t + tc.p0 + colhalf * 64 + lane;
-            s_d8[ew][0][lane] = dp[0];
-            s_d8[ew][0][lane + 32] = dp[32];
+            const float* dp = P.d8t + tc.p0 + colhalf * CH;
+            for (int i = lane; i < CH; i += 32) s_d8[ew][0][i] = dp[i];
             __syncwarp();
         }
         while (have) {
-            const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
-            float acc[64];
+            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            float acc[CH];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+            for (int i = 0; i < CH; ++i) acc[i] = 0.f;
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 const int buf = ab & 1;
                 // scales of the next block (maybe of the next tile): in flight while this block is drained
                 float d8_n0 = 0.f, d8_n1 = 0.f;
-                bool pre = false;
-                if (blk + 1 < P.kb) {
-                    const float* dp = P.d8t + (size_t)(blk + 1) * P.P_pad + tc.p0 + colhalf * 64 + lane;
-                    d8_n0 = dp[0];
-                    d8_n1 = dp[32];
-                    pre = true;
-                } else if (have_n) {
-                    const float* dp = P.d8t + tcn.p0 + colhalf * 64 + lane;
-                    d8_n0 = dp[0];
-                    d8_n1 = dp[32];
-                    pre = true;
+                const float* dp = nullptr;
+                if (blk + 1 < P.kb)
+                    dp = P.d8t + (size_t)(blk + 1) * P.P_pad + tc.p0 + colhalf * CH + lane;
+                else if (have_n)
+                    dp = P.d8t + tcn.p0 + colhalf * CH + lane;
+                const bool pre = dp != nullptr;
+                if (pre) {
+                    if (lane < CH) d8_n0 = dp[0];
+                    if (CH > 32) d8_n1 = dp[32];
                 }
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(0, ab);
                 GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
@@ -464,16 +465,17 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 const float dw = s_dw[ab & 7][r];  // left by the unpack warps when they produced this block
                 const uint64_t dw2 = f32x2_pack(dw, dw);
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(1, ab);
-                const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * 128);
+                const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * TN);
                 const uint32_t d8_addr = smem_u32(&s_d8[ew][buf][0]);
                 // Four steps of 16 columns; the load of step i+1 is in flight while step i is scaled into
                 // the register accumulators: acc += (d8[col] * dw[row]) * v.
+                constexpr int NS = CH / 16;  // steps of 16 columns
                 uint32_t stg[2][16];
                 tmem_ld16(t_main, stg[0]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    if (c + 1 < 4) tmem_ld16(t_main + 16 * (c + 1), stg[(c + 1) & 1]);
+                for (int c = 0; c < NS; ++c) {
+                    if (c + 1 < NS) tmem_ld16(t_main + 16 * (c + 1), stg[(c + 1) & 1]);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint4 dv = lds128(d8_addr + 64 * c + 16 * q);
@@ -486,16 +488,16 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         acc[16 * c + 4 * q + 2] = fmaf(s2, __uint_as_float(stg[c & 1][4 * q + 2]), acc[16 * c + 4 * q + 2]);
                         acc[16 * c + 4 * q + 3] = fmaf(s3, __uint_as_float(stg[c & 1][4 * q + 3]), acc[16 * c + 4 * q + 3]);
                     }
-                    if (c + 1 < 4) tmem_ld_wait();
-                    if (c == 2) {  // every column of this thread has been read: the buffer may be overwritten
+                    if (c + 1 < NS) tmem_ld_wait();
+                    if (c == (NS >= 2 ? NS - 2 : 0)) {  // every column of this thread has been read: the buffer may be overwritten
                         tc5_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&epi_done[buf]);
                     }
                 }
                 if (pre) {
-                    s_d8[ew][buf ^ 1][lane] = d8_n0;
-                    s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
+                    if (lane < CH) s_d8[ew][buf ^ 1][lane] = d8_n0;
+                    if (CH > 32) s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
                 }
                 __syncwarp();
                 if (threadIdx.x == 32 * G_WARP_EPI0) TR(2, ab);
@@ -505,20 +507,20 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             const long long ts_ = clock64();
 #endif
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
-            const uint32_t pc0 = tc.p0 + colhalf * 64;
+            const uint32_t pc0 = tc.p0 + colhalf * CH;
             if (GATE_UP) {
-                // even lane holds w1 x, odd lane w3 x of the same output row: the even lane finishes columns
-                // 0..31 of this half, the odd lane columns 32..63, one exchange per pair of columns
+                // even lane holds w1 x, odd lane w3 x of the same output row: the even lane finishes the first
+                // half of this warp's columns, the odd lane the second half, one exchange per pair of columns
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? acc[c] : acc[c + 32], 1);
-                    const float gv = (lane & 1) ? recv : acc[c], uv = (lane & 1) ? acc[c + 32] : recv;
-                    const uint32_t p = pc0 + c + ((lane & 1) ? 32 : 0);
+                for (int c = 0; c < CH / 2; ++c) {
+                    const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? acc[c] : acc[c + CH / 2], 1);
+                    const float gv = (lane & 1) ? recv : acc[c], uv = (lane & 1) ? acc[c + CH / 2] : recv;
+                    const uint32_t p = pc0 + c + ((lane & 1) ? CH / 2 : 0);
                     if (p < tc.p_end) P.out[(size_t)p * P.N + n] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < 64; ++c)
+                for (int c = 0; c < CH; ++c)
                     if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = acc[c];
             }
 #ifdef CMOE_GEMM_TIMING
@@ -538,7 +540,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         uint32_t ita = 0, ab = 0;
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
-        bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
         typename F::Row rowc{}, rown{};
         typename F::Pre cur, nxt;
         GT_BEGIN();
@@ -552,7 +554,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             nxt = cur;
         }
         while (have) {
-            const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
             if (have_n && !F::STAGE_W) {
                 const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
                 rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
@@ -615,10 +617,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             uint32_t ab = 0;
             long long tile = blockIdx.x;
             TileCoord tc, tcn;
-            bool have = decode_tile(tile, s_offs, P.E, P.m_tiles, tc);
+            bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
             constexpr int HALF = G_TILE_M / 2 * F::W_ROW_BYTES;  // 9216
             while (have) {
-                const bool have_n = decode_tile(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+                const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
                 const CUtensorMap* m0 = P.wmaps + 2 * tc.e;
                 const int y0 = GATE_UP ? tc.mt * 64 : tc.mt * 128;
                 for (int blk = 0; blk < P.kb; ++blk, ++ab) {
@@ -655,7 +657,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         uint32_t ab = 0;
         TileCoord tc;
         GT_BEGIN();
-        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
+        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
                 const int st = ab & 1;
@@ -665,8 +667,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     mbar_expect_tx(&full_b[st], G_STAGE_BYTES);
 #pragma unroll
                     for (int s4 = 0; s4 < 4; ++s4)
-                        tma_load_2d(dst + s4 * G_TILE_BYTES, &map_b, blk * 256 + s4 * 64, (int)tc.p0, &full_b[st]);
-                    if (F::HAS_MIN) tma_load_2d(dst + 4 * G_TILE_BYTES, &map_bs, blk * 32, (int)tc.p0, &full_b[st]);
+                        tma_load_2d(dst + s4 * B_TILE, &map_b, blk * 256 + s4 * 64, (int)tc.p0, &full_b[st]);
+                    if (F::HAS_MIN) tma_load_2d(dst + 4 * B_TILE, &map_bs, blk * 32, (int)tc.p0, &full_b[st]);
                 }
                 __syncwarp();
             }
@@ -681,13 +683,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem));
         const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a));
         bool rdy_a = false, rdy_b = false;
-        for (long long tile = blockIdx.x; decode_tile(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
+        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
             for (int blk = 0; blk < P.kb; ++blk, ++ab) {
                 const int buf = ab & 1;  // main accumulator and B stage of this block
                 // the drain of block ab - 2 has released this main accumulator
                 if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
                 if (lane == 0) TR(13, ab);
-                const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * 128);
+                const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * TN);
                 const uint64_t db = b_desc0 + (uint64_t)(buf * (G_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
@@ -707,7 +709,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {  // two slabs of four K steps
                             const uint32_t a_k = a_t + (uint32_t)((k >> 2) * F::A_COLS + 8 * (k & 3));
-                            const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (G_TILE_BYTES >> 4) + 2 * (k & 3));
+                            const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (B_TILE >> 4) + 2 * (k & 3));
                             umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
                             if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
                             if (k == 0) TR(15, ita);
@@ -716,7 +718,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         TR(8, ita);
                         if (pr == 1 && F::HAS_MIN) {
                             // the min term joins the same accumulator: three tf32 steps, last in the block
-                            const uint64_t da = ma_desc0 + (uint64_t)(buf * (G_TILE_BYTES >> 4)), dm = db + (uint64_t)(4 * (G_TILE_BYTES >> 4));
+                            const uint64_t da = ma_desc0 + (uint64_t)(buf * (G_TILE_BYTES >> 4)), dm = db + (uint64_t)(4 * (B_TILE >> 4));
 #pragma unroll
                             for (int k = 0; k < 3; ++k) umma_tf32(d_main, da + 2 * k, dm + 2 * k, IDESC_TF32, true);
                         }
@@ -760,14 +762,14 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// row-major matrix [rows, cols] -> boxes of [128 rows x box_cols] (128 bytes wide), 128-byte swizzle
+// row-major matrix [rows, cols] -> boxes of [box_rows x box_cols] (128 bytes wide), 128-byte swizzle
 bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
-                 uint32_t box_cols) {
+                 uint32_t box_cols, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
-    const cuuint32_t box[2] = {box_cols, G_TILE_N};
+    const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -788,11 +790,11 @@ bool make_map_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
 
 int g_gemm_sms = -1;
 
-template <class F, bool GATE_UP>
+template <class F, bool GATE_UP, int TN>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = (G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) + (F::HAS_MIN ? 2 : 0)) * G_TILE_BYTES +
+    const int smem_bytes = G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
                            (F::STAGE_W ? G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
-    auto kfn = expert_gemm_kernel<F, GATE_UP>;
+    auto kfn = expert_gemm_kernel<F, GATE_UP, TN>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
     return launch_k(kfn, dim3(g_gemm_sms), dim3(G_THREADS), (size_t)smem_bytes, st, G, map_b, map_bs);
@@ -802,7 +804,7 @@ cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUten
 
 // Scratch the GEMM needs for P grouped rows of length K (fp16 operand, block-sum operand, scales).
 size_t expert_gemm_scratch_bytes(int64_t P, int K) {
-    const size_t p_pad = (size_t)P + G_TILE_N, kb = (size_t)K / 256;
+    const size_t p_pad = (size_t)P + G_PAD_ROWS, kb = (size_t)K / 256;
     return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256) +
            sizeof(CUtensorMap) * 2 * CANDLE_MOE_MAX_EXPERTS;
 }
@@ -811,8 +813,10 @@ size_t expert_gemm_scratch_bytes(int64_t P, int K) {
 // decode kernels (repacked = true); cudaErrorNotSupported for every other shape / dtype / layout.
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
-                               const int8_t* aq, const float* ascale, const int16_t* absum, float* out, void* scratch) {
+                               int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
+                               void* scratch) {
     if (!scratch) return cudaErrorNotSupported;
+    const int tn = max_rows <= 32 ? 32 : 128;  // position tile: no expert has more than max_rows rows
     if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked))) return cudaErrorNotSupported;
     if (K % 256 != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
     if (!encode_tiled_fn()) return cudaErrorNotSupported;
@@ -824,7 +828,7 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
         if (e != cudaSuccess) return e;
     }
     const int kb = K / 256;
-    const int64_t p_pad = P + G_TILE_N;
+    const int64_t p_pad = P + G_PAD_ROWS;
     uint8_t* base = static_cast<uint8_t*>(scratch);
     __half* bf16 = reinterpret_cast<__half*>(base);
     float* bmin = reinterpret_cast<float*>(base + align_up((size_t)p_pad * K * 2, 256));
@@ -837,8 +841,10 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_b, map_bs;
-    if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K, G_SLAB_K)) return cudaErrorNotSupported;
-    if (!make_map_2d(&map_bs, bmin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)p_pad, (uint64_t)kb * 32, 32)) return cudaErrorNotSupported;
+    if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K, G_SLAB_K, tn))
+        return cudaErrorNotSupported;
+    if (!make_map_2d(&map_bs, bmin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)p_pad, (uint64_t)kb * 32, 32, tn))
+        return cudaErrorNotSupported;
 
     // byte-matrix tensor maps of the raw weight blocks (Q4_K): [n_rows, kb * 144] with boxes of 64 rows x one block,
     // written to the head of the scratch on the stream before the kernel
@@ -871,9 +877,14 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     G.m_tiles = gate_up ? N / 64 : N / 128;
     e = stream_status_ptr(&G.status);
     if (e != cudaSuccess) return e;
-    if (dtype == CANDLE_GGML_Q4K)
-        return gate_up ? launch_gemm_kernel<GemmQ4K, true>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false>(st, G, map_b, map_bs);
-    return gate_up ? launch_gemm_kernel<GemmQ6K, true>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false>(st, G, map_b, map_bs);
+    if (dtype == CANDLE_GGML_Q4K) {
+        if (tn == 32)
+            return gate_up ? launch_gemm_kernel<GemmQ4K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 32>(st, G, map_b, map_bs);
+        return gate_up ? launch_gemm_kernel<GemmQ4K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 128>(st, G, map_b, map_bs);
+    }
+    if (tn == 32)
+        return gate_up ? launch_gemm_kernel<GemmQ6K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 32>(st, G, map_b, map_bs);
+    return gate_up ? launch_gemm_kernel<GemmQ6K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 128>(st, G, map_b, map_bs);
 }
 
 }  // namespace cmoe

@@ -140,7 +140,7 @@ def _device_block_and_ep(orc, torch, mw, prepack):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("T,prepack", [(1, True), (19, False), (19, True), (300, True)])
+@pytest.mark.parametrize("T,prepack", [(1, True), (19, False), (19, True), (96, True), (110, True), (300, True)])
 def test_single_rank_equals_the_single_device_block(orc, torch_cuda, T, prepack):
     torch = torch_cuda
     mw = orc.make_moe_weights(21, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
