@@ -578,10 +578,16 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 }
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
-                    // slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks)
-                    const uint32_t np = 2 * ab + pr, slot = np % F::A_PAIRS, use = np / F::A_PAIRS;
+                    // Slabs go to tensor memory in pairs; the ring holds A_PAIRS pairs (Q4_K: two blocks).  The barriers
+                    // go by (block parity, pair) -- each has ONE waiting MMA warp that sees every phase, so a parity
+                    // wait is never ambiguous -- while the TMEM slot is the pair index modulo the ring size: before
+                    // writing it, wait for the MMAs of the block that used it last.
+                    const uint32_t bidx = 2 * (ab & 1) + pr, slot = bidx % F::A_PAIRS;
                     if (lane == 0 && warp == G_WARP_DQ0) TR(3, ita);
-                    if (use >= 1) GT(0, mbar_wait_relaxed(&empty_a[slot], (use & 1) ^ 1, abort_flag));
+                    if (ab >= F::A_PAIRS / 2) {
+                        const uint32_t abp = ab - F::A_PAIRS / 2;
+                        GT(0, mbar_wait_relaxed(&empty_a[2 * (abp & 1) + pr], (abp >> 1) & 1, abort_flag));
+                    }
                     tc5_fence_after_sync();
                     if (lane == 0 && warp == G_WARP_DQ0) TR(4, ita);
                     GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * slot * F::A_COLS), h));
@@ -595,7 +601,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     GT(3, tmem_st_wait());
                     tc5_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_a[slot]);
+                    if (lane == 0) mbar_arrive(&full_a[bidx]);
                     if (lane == 0 && warp == G_WARP_DQ0) TR(5, ita);
                 }
                 if (!F::STAGE_W) cur = nxt;
@@ -676,6 +682,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         GT_END(24, lane == 0);
     } else if (warp == G_WARP_MMA) {
         // ===================== MMA issue =====================
+        // (Splitting the blocks by parity over two issuing warps was measured: no gain.)
         uint32_t ita = 0, ab = 0;
         TileCoord tc;
         GT_BEGIN();
@@ -693,15 +700,16 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 const uint64_t db = b_desc0 + (uint64_t)(buf * (G_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
-                    const uint32_t np = 2 * ab + pr, slot = np % F::A_PAIRS, use = np / F::A_PAIRS;
+                    const uint32_t bidx = 2 * (ab & 1) + pr, slot = bidx % F::A_PAIRS;  // barrier, TMEM slot (see the unpack warps)
                     if (lane == 0) TR(9, ita);
-                    if (!rdy_a) GT(0, mbar_wait(&full_a[slot], use & 1, abort_flag));
+                    if (!rdy_a) GT(0, mbar_wait(&full_a[bidx], (ab >> 1) & 1, abort_flag));
                     if (lane == 0) TR(10, ita);
                     if (pr == 0 && !rdy_b) GT(1, mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag));
                     if (lane == 0) TR(11, ita);
                     tc5_fence_after_sync();
-                    // look at the next barriers now: the answers arrive while the MMAs are issued
-                    rdy_a = mbar_test(&full_a[(np + 1) % F::A_PAIRS], ((np + 1) / F::A_PAIRS) & 1);
+                    // look at this warp's next barriers now: the answers arrive while the MMAs are issued
+                    rdy_a = pr == 0 ? mbar_test(&full_a[bidx + 1], (ab >> 1) & 1)                    // second pair of this block
+                                    : mbar_test(&full_a[2 * ((ab + 1) & 1)], ((ab + 1) >> 1) & 1);  // first pair of the next
                     if (pr == 1) rdy_b = mbar_test(&full_b[buf ^ 1], ((ab + 1) >> 1) & 1);
                     if (lane == 0) TR(6, ita);
                     const uint32_t a_t = a_base + (uint32_t)(2 * slot * F::A_COLS);
@@ -722,7 +730,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #pragma unroll
                             for (int k = 0; k < 3; ++k) umma_tf32(d_main, da + 2 * k, dm + 2 * k, IDESC_TF32, true);
                         }
-                        umma_commit(&empty_a[slot]);  // the stages may be refilled once these MMAs have read them
+                        umma_commit(&empty_a[bidx]);  // the stages may be refilled once these MMAs have read them
                         if (pr == 1) {
                             umma_commit(&empty_b[buf]);
                             umma_commit(&tmem_full[buf]);
