@@ -24,6 +24,7 @@ SOURCES = {
     "expert_direct.cu": [],
     "expert_gemm.cu": [],
     "expert_parallel.cu": [],
+    "expert_q80.cu": [],
 }
 # extra nvcc flags for local experiments, e.g. CANDLE_MOE_NVCC_FLAGS="-DCMOE_STREAM_TIMING"
 EXTRA = os.environ.get("CANDLE_MOE_NVCC_FLAGS", "").split()

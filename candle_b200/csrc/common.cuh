@@ -189,6 +189,9 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
                                void* scratch);
+// Q8_0 grouped products for many rows per expert (expert_q80.cu); cudaErrorNotSupported for other shapes
+cudaError_t launch_expert_q80(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int E, int K, int N,
+                              const uint32_t* offsets, const uint32_t* row_of, const int8_t* aq, const float* ascale, float* out);
 // expert parallelism: packed quantized rows either side of the all-to-all (expert_parallel.cu)
 size_t ep_row_bytes(int d);
 cudaError_t launch_ep_pack(cudaStream_t st, const uint32_t* row_of, int64_t n_rows, int d, const int8_t* xq, const float* xs,

@@ -220,12 +220,19 @@ static cudaError_t launch_rows(cudaStream_t st, const ExpertPtrs& wa, const Expe
     return cudaGetLastError();
 }
 
+// Q8_0: above this bound on the rows of one expert the tensor-core tile kernel takes over from the row-per-warp form
+constexpr int64_t Q80_TILE_MIN_ROWS = 16;
+
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
                                    int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden) {
     if (!force_rows() && max_rows <= stream_max_rows()) {
         const cudaError_t e = launch_expert_stream(st, true, w1, w3, dtype, E, d, ff, offsets, row_of, max_rows, xq, xs,
                                                    xb, hidden, nullptr, 0, 1);
+        if (e != cudaErrorNotSupported) return e;
+    }
+    if (!force_rows() && dtype == CANDLE_GGML_Q8_0 && max_rows > Q80_TILE_MIN_ROWS) {
+        const cudaError_t e = launch_expert_q80(st, true, w1, w3, E, d, ff, offsets, row_of, xq, xs, hidden);
         if (e != cudaErrorNotSupported) return e;
     }
     ActView a{xq, xs, xb};
@@ -241,6 +248,10 @@ cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype
                                                    hb, out, n_splits, split_stride, max_splits);
         if (e != cudaErrorNotSupported) return e;
         if (n_splits) *n_splits = 1;
+    }
+    if (!force_rows() && dtype == CANDLE_GGML_Q8_0 && max_rows > Q80_TILE_MIN_ROWS) {
+        const cudaError_t e = launch_expert_q80(st, false, w2, w2, E, ff, d, offsets, nullptr, hq, hs, out);
+        if (e != cudaErrorNotSupported) return e;
     }
     ActView a{hq, hs, hb};
     return launch_rows<false>(st, w2, w2, dtype, E, ff, d, offsets, nullptr, a, out);

@@ -231,7 +231,8 @@ def test_qmatmul_forward_matches_oracle(orc, torch_cuda, name, m, k, n):
 
 
 @pytest.mark.parametrize("name13,name2,rows,d,ff", [("Q4K", "Q6K", 5, 512, 1024), ("Q4K", "Q4K", 13, 1024, 3584),
-                                                    ("Q8_0", "Q8_0", 9, 2048, 1408)])
+                                                    ("Q8_0", "Q8_0", 9, 2048, 1408), ("Q8_0", "Q8_0", 77, 2048, 1408),
+                                                    ("Q8_0", "Q8_0", 130, 256, 96)])
 def test_expert_hidden_before_requantization(orc, torch_cuda, name13, name2, rows, d, ff):
     """silu(W1 x) * (W3 x) in f32, before it is re-quantized for W2: same integers as the oracle, so
     only f32 summation order and the last bit of expf differ (Mlp::forward, quantized_llama.rs:125-128)."""
