@@ -145,7 +145,9 @@ class ExpertParallelMoe:
             dev = local_experts[0].feed_forward_w1.inner.device()
             router = feed_forward_gate_inp.to(dev, torch.float32).contiguous()
             lo = self.rank * self.E_local
-            local = MlpOrMoe(n_expert_used, router[lo:lo + self.E_local].contiguous(), local_experts,
+            # the local block only describes this rank's expert matrices to the C ABI (its router and top-k are not
+            # used there); a rank may hold fewer experts than a token selects
+            local = MlpOrMoe(min(self.k, self.E_local), router[lo:lo + self.E_local].contiguous(), local_experts,
                              norm_topk_prob=norm_topk_prob)
             if prepack:
                 local.prepack()

@@ -172,3 +172,36 @@ def test_single_rank_over_a_nccl_group(orc, torch_cuda):
         assert H.rel_l2(y, ref.y) <= H.REL_L2_TOL and H.max_rel(y, ref.y) <= H.MAX_REL_TOL
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_rank_holding_fewer_experts_than_top_k(orc, torch_cuda, monkeypatch):
+    """8 experts over 8 ranks with top-2: every rank holds ONE expert.  The construction and the local phase of
+    one such rank run on a single GPU (process-group queries stubbed); the rows come from eight made-up sources."""
+    torch = torch_cuda
+    from candle_b200 import ExpertParallelMoe
+    import candle_b200.expert_parallel as ep_mod
+    mw = orc.make_moe_weights(23, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    blk = H.device_block(orc, mw)
+    rank = 5
+    monkeypatch.setattr(ep_mod.dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(ep_mod.dist, "get_world_size", lambda group=None: 8)
+    monkeypatch.setattr(ep_mod.dist, "get_rank", lambda group=None: rank)
+    ep = ExpertParallelMoe(2, blk.feed_forward_gate_inp, [blk.experts[rank]], prepack=True)
+    assert ep.E_local == 1 and ep.world == 8
+    # rows "received" from 8 sources: quantize + pack them here, as a sender would
+    counts = [3, 0, 7, 1, 0, 12, 5, 2]
+    n = sum(counts)
+    x = orc.make_activations(9, n, 512)
+    xd = torch.from_numpy(x).cuda()
+    ops = ep.ops
+    r = ops.route(xd)  # only its quantized rows are used
+    r.perm_token = torch.arange(n, dtype=torch.int32, device="cuda")
+    r.T, ops_k = n, ops.k
+    ops.k = 1
+    send = ops.pack(r)
+    ops.k = ops_k
+    recv_counts = torch.tensor(counts, dtype=torch.int32, device="cuda").reshape(8, 1)
+    out = ops.experts(send, recv_counts, n, n).cpu().numpy()
+    ref, _ = orc.mlp_forward(mw.dtype_w13, mw.dtype_w2, x, mw.w1[rank], mw.w3[rank], mw.w2[rank], mw.d_ff)
+    assert H.rel_l2(out, ref) <= H.REL_L2_TOL and H.max_rel(out, ref) <= H.MAX_REL_TOL
