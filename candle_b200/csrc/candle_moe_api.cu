@@ -18,10 +18,10 @@ inline int64_t gemm_min_rows() {
     return v && v[0] ? std::atoll(v) : 64;
 }
 // When the caller knows the ACTUAL largest row count of an expert (expert parallelism: the host has the counts), the
-// GEMM already pays off above 24 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
+// GEMM already pays off above 16 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
 // with 32-wide position tiles).  (A single-device
 // forward only knows the bound T, and its experts usually hold a fraction of that.)
-constexpr int64_t GEMM_MIN_ROWS_EXACT = 24;
+constexpr int64_t GEMM_MIN_ROWS_EXACT = 16;
 constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
@@ -331,10 +331,9 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         ExpertPtrs g2 = p2;
         if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
         const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, max_rows,
-                                                  b.hq, b.hs, b.hb, b.eo, b.gemm);
+                                                  b.hq, b.hs, b.hb, b.eo, b.gemm, slots, eo_splits, P * d);
         if (ce == cudaSuccess) {
             down_done = true;
-            *eo_splits = 1;
         } else if (ce != cudaErrorNotSupported) {
             return (int)ce;
         }

@@ -188,7 +188,7 @@ size_t expert_gemm_scratch_bytes(int64_t P, int K);
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
-                               void* scratch);
+                               void* scratch, int max_splits = 1, int* n_splits_out = nullptr, int64_t split_stride = 0);
 // Q8_0 grouped products for many rows per expert (expert_q80.cu); cudaErrorNotSupported for other shapes
 cudaError_t launch_expert_q80(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int E, int K, int N,
                               const uint32_t* offsets, const uint32_t* row_of, const int8_t* aq, const float* ascale, float* out);

@@ -31,6 +31,7 @@
 // rows of W1 and W3 (tile row 2i = W1 row, 2i+1 = W3 row) so the two factors of silu(w1 x) * (w3 x)
 // sit in neighbouring lanes and meet with one shuffle.
 // Every mbarrier wait is bounded (see stream_common.cuh); nothing here uses cluster multicast.
+#include <algorithm>
 #include <cuda_fp16.h>
 #include <cudaTypedefs.h>
 
@@ -151,6 +152,8 @@ struct GemmParams {
     int* status;
     int E, K, N, kb, P, P_pad;
     int m_tiles;                  // tiles along the weight rows (N / 64 for gate_up, N / 128 for down)
+    int ksplit;                   // K splits (down only): partial outputs out + ks * split_stride, summed by the caller
+    long long split_stride;
 };
 
 __device__ __forceinline__ __half2 h2_bits(uint32_t v) { return *reinterpret_cast<const __half2*>(&v); }
@@ -344,23 +347,30 @@ struct GemmQ6K {
 
 struct TileCoord {
     int e, nt, mt;
+    int ks, kb0, kb1;  // K split: this work item covers the 256-blocks [kb0, kb1) and writes partial output ks
     uint32_t p0, p_end;
 };
 
 // tile id -> (expert, row tile, position tile); position tiles are fastest, so the CTAs that run at
 // the same time share a weight tile (fetched from HBM once) and each expert's activations stay in L2
 template <int TN>
-__device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs, int E, int m_tiles, TileCoord& tc) {
+__device__ __forceinline__ bool decode_tile(long long tile, const uint32_t* offs, int E, int m_tiles, int ksplit, int kb,
+                                            TileCoord& tc) {
     long long cum = 0;
     for (int e = 0; e < E; ++e) {
         const uint32_t cnt = offs[e + 1] - offs[e];
         const int n_tiles = (int)((cnt + TN - 1) / TN);
-        const long long te = (long long)n_tiles * m_tiles;
+        const long long te = (long long)n_tiles * m_tiles * ksplit;
         if (tile < cum + te) {
             const long long local = tile - cum;
+            const int per_mt = n_tiles * ksplit;
             tc.e = e;
-            tc.mt = (int)(local / n_tiles);
-            tc.nt = (int)(local - (long long)tc.mt * n_tiles);
+            tc.mt = (int)(local / per_mt);
+            const int rem = (int)(local - (long long)tc.mt * per_mt);
+            tc.ks = rem / n_tiles;
+            tc.nt = rem - tc.ks * n_tiles;
+            tc.kb0 = tc.ks * (kb / ksplit);
+            tc.kb1 = tc.kb0 + kb / ksplit;
             tc.p0 = offs[e] + (uint32_t)tc.nt * TN;
             tc.p_end = offs[e + 1];
             return true;
@@ -433,27 +443,27 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         uint32_t ab = 0;
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
-        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
+        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc);
         GT_BEGIN();
         if (have) {
-            const float* dp = P.d8t + tc.p0 + colhalf * CH;
+            const float* dp = P.d8t + (size_t)tc.kb0 * P.P_pad + tc.p0 + colhalf * CH;
             for (int i = lane; i < CH; i += 32) s_d8[ew][0][i] = dp[i];
             __syncwarp();
         }
         while (have) {
-            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
             float acc[CH];
 #pragma unroll
             for (int i = 0; i < CH; ++i) acc[i] = 0.f;
-            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+            for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 const int buf = ab & 1;
                 // scales of the next block (maybe of the next tile): in flight while this block is drained
                 float d8_n0 = 0.f, d8_n1 = 0.f;
                 const float* dp = nullptr;
-                if (blk + 1 < P.kb)
+                if (blk + 1 < tc.kb1)
                     dp = P.d8t + (size_t)(blk + 1) * P.P_pad + tc.p0 + colhalf * CH + lane;
                 else if (have_n)
-                    dp = P.d8t + tcn.p0 + colhalf * CH + lane;
+                    dp = P.d8t + (size_t)tcn.kb0 * P.P_pad + tcn.p0 + colhalf * CH + lane;
                 const bool pre = dp != nullptr;
                 if (pre) {
                     if (lane < CH) d8_n0 = dp[0];
@@ -508,6 +518,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
 #endif
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             const uint32_t pc0 = tc.p0 + colhalf * CH;
+            float* out_k = P.out + (size_t)tc.ks * P.split_stride;
             if (GATE_UP) {
                 // even lane holds w1 x, odd lane w3 x of the same output row: the even lane finishes the first
                 // half of this warp's columns, the odd lane the second half, one exchange per pair of columns
@@ -516,12 +527,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     const float recv = __shfl_xor_sync(0xffffffffu, (lane & 1) ? acc[c] : acc[c + CH / 2], 1);
                     const float gv = (lane & 1) ? recv : acc[c], uv = (lane & 1) ? acc[c + CH / 2] : recv;
                     const uint32_t p = pc0 + c + ((lane & 1) ? CH / 2 : 0);
-                    if (p < tc.p_end) P.out[(size_t)p * P.N + n] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+                    if (p < tc.p_end) out_k[(size_t)p * P.N + n] = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
                 }
             } else {
 #pragma unroll
                 for (int c = 0; c < CH; ++c)
-                    if (pc0 + c < tc.p_end) P.out[(size_t)(pc0 + c) * P.N + n] = acc[c];
+                    if (pc0 + c < tc.p_end) out_k[(size_t)(pc0 + c) * P.N + n] = acc[c];
             }
 #ifdef CMOE_GEMM_TIMING
             gt_[4] += clock64() - ts_;
@@ -540,7 +551,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         uint32_t ita = 0, ab = 0;
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
-        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
+        bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc);
         typename F::Row rowc{}, rown{};
         typename F::Pre cur, nxt;
         GT_BEGIN();
@@ -550,24 +561,24 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         if (have && !F::STAGE_W) {
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             rowc = F::row((GATE_UP && (r & 1)) ? P.wb.p[tc.e] : P.wa.p[tc.e], n, P.kb);
-            F::load(cur, rowc, 0, h);
+            F::load(cur, rowc, tc.kb0, h);
             nxt = cur;
         }
         while (have) {
-            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+            const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
             if (have_n && !F::STAGE_W) {
                 const int nn = GATE_UP ? tcn.mt * 64 + (r >> 1) : tcn.mt * 128 + r;
                 rown = F::row((GATE_UP && (r & 1)) ? P.wb.p[tcn.e] : P.wa.p[tcn.e], nn, P.kb);
             }
-            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+            for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 if (F::STAGE_W) {
                     // this block's raw bytes were copied to shared memory by the loader warp
                     GT(1, mbar_wait(&full_w, ab & 1, abort_flag));
                     F::load_staged(cur, w_row, h);
-                } else if (blk + 1 < P.kb) {
+                } else if (blk + 1 < tc.kb1) {
                     F::load(nxt, rowc, blk + 1, h);
                 } else if (have_n) {
-                    F::load(nxt, rown, 0, h);
+                    F::load(nxt, rown, tcn.kb0, h);
                 }
                 typename F::Ctx ctx;
                 F::begin(cur, ctx);
@@ -623,13 +634,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             uint32_t ab = 0;
             long long tile = blockIdx.x;
             TileCoord tc, tcn;
-            bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc);
+            bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc);
             constexpr int HALF = G_TILE_M / 2 * F::W_ROW_BYTES;  // 9216
             while (have) {
-                const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, tcn);
+                const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
                 const CUtensorMap* m0 = P.wmaps + 2 * tc.e;
                 const int y0 = GATE_UP ? tc.mt * 64 : tc.mt * 128;
-                for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+                for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                     if (ab >= 1) mbar_wait(&empty_w, (ab - 1) & 1, abort_flag);
                     if (elect_one()) {
                         mbar_expect_tx(&full_w, G_TILE_M * F::W_ROW_BYTES);
@@ -641,11 +652,11 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                             tma_load_2d(smem_w + HALF, m0, blk * F::W_ROW_BYTES, y0 + 64, &full_w);
                         }
                         // two blocks ahead, possibly in the next tile
-                        const bool same = blk + 2 < P.kb;
+                        const bool same = blk + 2 < tc.kb1;
                         if (same || have_n) {
                             const CUtensorMap* mp = same ? m0 : P.wmaps + 2 * tcn.e;
                             const int yp = same ? y0 : (GATE_UP ? tcn.mt * 64 : tcn.mt * 128);
-                            const int xp = (same ? blk + 2 : blk + 2 - P.kb) * F::W_ROW_BYTES;
+                            const int xp = (same ? blk + 2 : tcn.kb0 + blk + 2 - tc.kb1) * F::W_ROW_BYTES;
                             tma_prefetch_2d(mp, xp, yp);
                             tma_prefetch_2d(GATE_UP ? mp + 1 : mp, xp, GATE_UP ? yp : yp + 64);
                         }
@@ -663,8 +674,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         uint32_t ab = 0;
         TileCoord tc;
         GT_BEGIN();
-        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc); tile += gridDim.x) {
+            for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
                 const int st = ab & 1;
                 if (ab >= 2) GT(0, mbar_wait_relaxed(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
@@ -690,8 +701,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem));
         const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a));
         bool rdy_a = false, rdy_b = false;
-        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, tc); tile += gridDim.x) {
-            for (int blk = 0; blk < P.kb; ++blk, ++ab) {
+        for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc); tile += gridDim.x) {
+            for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 const int buf = ab & 1;  // main accumulator and B stage of this block
                 // the drain of block ab - 2 has released this main accumulator
                 if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
@@ -822,7 +833,8 @@ size_t expert_gemm_scratch_bytes(int64_t P, int K) {
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
-                               void* scratch) {
+                               void* scratch, int max_splits, int* n_splits_out, int64_t split_stride) {
+    if (n_splits_out) *n_splits_out = 1;
     if (!scratch) return cudaErrorNotSupported;
     const int tn = max_rows <= 32 ? 32 : 128;  // position tile: no expert has more than max_rows rows
     if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked))) return cudaErrorNotSupported;
@@ -883,6 +895,18 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     G.P = (int)P;
     G.P_pad = (int)p_pad;
     G.m_tiles = gate_up ? N / 64 : N / 128;
+    // down with few tiles (few experts with rows, narrow outputs): split K so that every SM has work; the partial
+    // outputs are summed by whoever consumes them (combine, or the expert-parallel scatter)
+    int ksplit = 1;
+    if (!gate_up && n_splits_out && max_splits > 1) {
+        const int64_t rows_per = std::max<int64_t>(1, std::min<int64_t>(max_rows, P));
+        const int64_t items = (int64_t)G.m_tiles * std::max<int64_t>(1, std::min<int64_t>(E, (P + rows_per - 1) / rows_per)) *
+                              ((rows_per + tn - 1) / tn);
+        while (ksplit * 2 <= max_splits && kb % (ksplit * 2) == 0 && items * ksplit < 2 * (int64_t)g_gemm_sms) ksplit *= 2;
+        *n_splits_out = ksplit;
+    }
+    G.ksplit = ksplit;
+    G.split_stride = split_stride;
     e = stream_status_ptr(&G.status);
     if (e != cudaSuccess) return e;
     if (dtype == CANDLE_GGML_Q4K) {
