@@ -62,6 +62,8 @@ SYMBOLS = {
     "candle_moe_grouped_gate_up": (C.c_int, [_P, _PP, _PP, _I32, _I32, _I32, _I32, _P, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_grouped_down": (C.c_int, [_P, _PP, _I32, _I32, _I32, _I32, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_forward": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ]),
+    "candle_moe_ffn_layer_workspace_bytes": (C.c_int, [C.POINTER(MoeWeightsC), _I64, C.POINTER(_SZ)]),
+    "candle_moe_ffn_layer": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, C.c_float, _P, _I64, _P, _P, _SZ]),
     "candle_moe_forward_timed": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ, _P]),
     "candle_moe_forward_static": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _I64, _P]),
     "candle_moe_workspace_views": (C.c_int, [C.POINTER(MoeWeightsC), _I64, _P, _PP, _PP, _PP, _PP]),

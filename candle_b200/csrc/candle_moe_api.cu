@@ -386,8 +386,8 @@ EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
 }
 }  // namespace
 
-int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
-                       void* workspace, size_t workspace_bytes) {
+static int forward_impl(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y, void* workspace,
+                        size_t workspace_bytes, const float* residual) {
     CM_TRY(check_weights(w));
     if (!x || !y || !w->router) return CANDLE_MOE_E_NULL;
     if (T < 0 || T > (int64_t)1 << 24) return CANDLE_MOE_E_SHAPE;
@@ -449,9 +449,40 @@ int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float*
     }
     mark(st, 6);
     CM_TRY(rc(launch_combine(st, ws.eo, eo_splits, Tk * d, ws.topk_ids, ws.topk_w, ws.pair_pos, T, k, d, shared_out,
-                             so_splits, T * (int64_t)d, x, w->shared_gate, y)));
+                             so_splits, T * (int64_t)d, x, w->shared_gate, y, residual)));
     mark(st, 7);
     return CANDLE_MOE_OK;
+}
+
+int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
+                       void* workspace, size_t workspace_bytes) {
+    return forward_impl(stream, w, x, T, y, workspace, workspace_bytes, nullptr);
+}
+
+int candle_moe_ffn_layer_workspace_bytes(const candle_moe_weights_t* w, int64_t T, size_t* out_bytes) {
+    CM_TRY(check_weights(w));
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (T < 0 || T > (int64_t)1 << 24) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = layout(w, T, nullptr).total + align_up((size_t)T * w->d_model * sizeof(float), 256);
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_ffn_layer(void* stream, const candle_moe_weights_t* w, const float* norm_weight, float eps, const float* x,
+                         int64_t T, float* y, void* workspace, size_t workspace_bytes) {
+    CM_TRY(check_weights(w));
+    if (!x || !y || !norm_weight) return CANDLE_MOE_E_NULL;
+    if (T < 0 || T > (int64_t)1 << 24) return CANDLE_MOE_E_SHAPE;
+    if (T == 0) return CANDLE_MOE_OK;
+    if (!workspace) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (reinterpret_cast<uintptr_t>(norm_weight) & 15))
+        return CANDLE_MOE_E_ALIGN;
+    const size_t inner = layout(w, T, nullptr).total;
+    const size_t need = inner + align_up((size_t)T * w->d_model * sizeof(float), 256);
+    if (workspace_bytes < need) return CANDLE_MOE_E_WORKSPACE;
+    float* xn = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + inner);
+    CM_TRY(rc(launch_rmsnorm((cudaStream_t)stream, x, norm_weight, eps, T, w->d_model, xn)));
+    return forward_impl(stream, w, xn, T, y, workspace, inner, x);
 }
 
 int candle_moe_forward_timed(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,

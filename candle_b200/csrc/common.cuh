@@ -167,7 +167,8 @@ cudaError_t launch_grouped_down(cudaStream_t st, const ExpertPtrs& w2, int dtype
 cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_splits, int64_t split_stride,
                            const uint32_t* ids, const float* w, const uint32_t* pair_pos, int64_t T, int k, int d,
                            const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
-                           const float* shared_gate, float* y);
+                           const float* shared_gate, float* y, const float* residual = nullptr);
+cudaError_t launch_rmsnorm(cudaStream_t st, const float* x, const float* alpha, float eps, int64_t T, int d, float* y);
 // streaming (TMA ring + tensor-core) form; cudaErrorNotSupported when the shape is not taken
 cudaError_t launch_expert_stream(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                  int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,

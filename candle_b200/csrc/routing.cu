@@ -237,7 +237,8 @@ __global__ void __launch_bounds__(COMBINE_THREADS)
 combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride, const uint32_t* __restrict__ ids,
                const float* __restrict__ w, const uint32_t* __restrict__ pair_pos, int k, int d,
                const float* __restrict__ shared_out, int shared_splits, int64_t shared_split_stride,
-               const float* __restrict__ x, const float* __restrict__ gate, float* __restrict__ y) {
+               const float* __restrict__ x, const float* __restrict__ gate, const float* __restrict__ residual,
+               float* __restrict__ y) {
     pdl_trigger();
     pdl_wait();
     __shared__ float s_red[COMBINE_THREADS / 32];
@@ -327,6 +328,13 @@ combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride,
             acc.z = __fadd_rn(acc.z, __fmul_rn(s.z, g));
             acc.w = __fadd_rn(acc.w, __fmul_rn(s.w, g));
         }
+        if (residual) {  // the layer's `x + residual` after the block (quantized_llama.rs:889-891)
+            const float4 rr = reinterpret_cast<const float4*>(residual + t * (int64_t)d)[i];
+            acc.x = __fadd_rn(acc.x, rr.x);
+            acc.y = __fadd_rn(acc.y, rr.y);
+            acc.z = __fadd_rn(acc.z, rr.z);
+            acc.w = __fadd_rn(acc.w, rr.w);
+        }
         yr[i] = acc;
     }
 }
@@ -334,11 +342,53 @@ combine_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride,
 cudaError_t launch_combine(cudaStream_t st, const float* expert_out, int n_splits, int64_t split_stride,
                            const uint32_t* ids, const float* w, const uint32_t* pair_pos, int64_t T, int k, int d,
                            const float* shared_out, int shared_splits, int64_t shared_split_stride, const float* x,
-                           const float* shared_gate, float* y) {
+                           const float* shared_gate, float* y, const float* residual) {
     if (T == 0) return cudaSuccess;
     const unsigned slabs = (unsigned)((d / 4 + COMBINE_THREADS - 1) / COMBINE_THREADS);
     return launch_k(combine_kernel, dim3((unsigned)T, slabs), dim3(COMBINE_THREADS), 0, st, expert_out, n_splits, split_stride,
-                    ids, w, pair_pos, k, d, shared_out, shared_splits, shared_split_stride, x, shared_gate, y);
+                    ids, w, pair_pos, k, d, shared_out, shared_splits, shared_split_stride, x, shared_gate, residual, y);
+}
+
+// RmsNorm of the rows feeding the block (candle-nn/src/ops.rs:504-514): y = x / sqrt(mean(x^2) + eps) * alpha, f32.
+// One CTA per row; the sum of squares is a fixed-order tree (the reference adds sequentially: last-bit
+// differences only).
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ alpha, float eps, int d, float* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float s_part[8];
+    __shared__ float s_m;
+    const float4* xr = reinterpret_cast<const float4*>(x + (int64_t)blockIdx.x * d);
+    float part = 0.f;
+    for (int i = threadIdx.x; i < (d >> 2); i += 256) {
+        const float4 v = xr[i];
+        part = fmaf(v.x, v.x, part);
+        part = fmaf(v.y, v.y, part);
+        part = fmaf(v.z, v.z, part);
+        part = fmaf(v.w, v.w, part);
+    }
+    part = warp_sum(part);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int i = 0; i < 8; ++i) t += s_part[i];
+        s_m = sqrtf(t / (float)d + eps);
+    }
+    __syncthreads();
+    const float m = s_m;
+    const float4* ar = reinterpret_cast<const float4*>(alpha);
+    float4* yr = reinterpret_cast<float4*>(y + (int64_t)blockIdx.x * d);
+    for (int i = threadIdx.x; i < (d >> 2); i += 256) {
+        const float4 v = xr[i], a = ar[i];
+        yr[i] = make_float4(__fmul_rn(__fdiv_rn(v.x, m), a.x), __fmul_rn(__fdiv_rn(v.y, m), a.y),
+                            __fmul_rn(__fdiv_rn(v.z, m), a.z), __fmul_rn(__fdiv_rn(v.w, m), a.w));
+    }
+}
+
+cudaError_t launch_rmsnorm(cudaStream_t st, const float* x, const float* alpha, float eps, int64_t T, int d, float* y) {
+    if (T == 0) return cudaSuccess;
+    return launch_k(rmsnorm_kernel, dim3((unsigned)T), dim3(256), 0, st, x, alpha, eps, d, y);
 }
 
 }  // namespace cmoe

@@ -150,6 +150,28 @@ class MlpOrMoe:
 
     __call__ = forward
 
+    def forward_layer(self, xs: torch.Tensor, ffn_norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """The FFN half of a decoder layer: `xs + self.forward(rms_norm(xs, ffn_norm_weight, eps))`
+        (quantized_llama.rs:887-891), one call into the C ABI."""
+        if not xs.is_cuda or xs.dtype != torch.float32 or xs.shape[-1] != self.d_model:
+            raise ValueError(f"expected a CUDA f32 [.., {self.d_model}] tensor")
+        x2 = xs.reshape(-1, self.d_model).contiguous()
+        T = x2.shape[0]
+        nw = ffn_norm_weight.to(self.device, torch.float32).contiguous()
+        need = C.c_size_t(0)
+        L = _lib.load()
+        _lib.check("candle_moe_ffn_layer_workspace_bytes", L.candle_moe_ffn_layer_workspace_bytes(C.byref(self._cw), max(T, 1),
+                                                                                             C.byref(need)))
+        if self._ws is None or self._ws.numel() - 256 < need.value:
+            self._ws = torch.empty(need.value + 256, dtype=torch.uint8, device=self.device)
+            self._ws_tokens = T
+        y = torch.empty_like(x2)
+        with torch.cuda.device(self.device):
+            st = L.candle_moe_ffn_layer(_stream_ptr(self.device), C.byref(self._cw), nw.data_ptr(), float(eps), x2.data_ptr(), T,
+                                        y.data_ptr(), self._ws_ptr(), self._ws.numel() - 256)
+        _lib.check("candle_moe_ffn_layer", st)
+        return y.reshape(xs.shape)
+
     STAGES = ("router_topk", "permute", "quantize_x", "gate_up", "quantize_h", "down", "shared_expert", "combine")
 
     def forward_timed(self, xs: torch.Tensor):

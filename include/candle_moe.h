@@ -155,6 +155,16 @@ CANDLE_MOE_API int candle_moe_grouped_down(void* stream, const void* const* w2, 
 CANDLE_MOE_API int candle_moe_forward(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y,
                        void* workspace, size_t workspace_bytes);
 
+/* The FFN half of a decoder layer around the block: y = x + MoE(RmsNorm(x)), i.e.
+ * `layer.ffn_norm.forward` -> `layer.mlp_or_moe.forward` -> `x + residual`
+ * (candle-transformers/src/models/quantized_llama.rs:887-891; RmsNorm arithmetic of
+ * candle-nn/src/ops.rs:504-514: x / sqrt(mean(x^2) + eps) * norm_weight in f32).  The residual add
+ * happens inside the combine kernel.  Workspace: candle_moe_ffn_layer_workspace_bytes(w, T) bytes
+ * (the block's workspace plus the normalised rows). */
+CANDLE_MOE_API int candle_moe_ffn_layer_workspace_bytes(const candle_moe_weights_t* w, int64_t T, size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_ffn_layer(void* stream, const candle_moe_weights_t* w, const float* norm_weight, float eps,
+                                        const float* x, int64_t T, float* y, void* workspace, size_t workspace_bytes);
+
 /* candle_moe_forward with CUDA events recorded on `stream` between its launches; synchronises the
  * stream and writes the device time of each stage in milliseconds to stage_ms[8]:
  * {router (+ fused quantization of x), dispatch, separate quantization of x, gate_up, quantization

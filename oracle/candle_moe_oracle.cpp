@@ -918,6 +918,19 @@ inline float sigmoid_f(float v) { return 1.0f / (std::exp(-v) + 1.0f); }    // c
 // C interface (ctypes)
 // ==========================================================================================
 
+// RmsNorm as candle's CPU op computes it (candle-nn/src/ops.rs:504-514): the squares are summed sequentially in
+// f32, m = sqrt(sum / dim + eps), and each element is x / m * alpha (division first).
+ORC_API int orc_rms_norm(const float* x, const float* alpha, float eps, size_t rows, size_t d, float* out) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float* s = x + r * d;
+        float sum2 = 0.f;
+        for (size_t i = 0; i < d; ++i) sum2 += s[i] * s[i];
+        const float m = std::sqrt(sum2 / (float)d + eps);
+        for (size_t i = 0; i < d; ++i) out[r * d + i] = s[i] / m * alpha[i];
+    }
+    return 0;
+}
+
 ORC_API size_t orc_block_bytes(int dtype) { return block_bytes(dtype); }
 ORC_API int orc_block_elems(int dtype) { return block_elems(dtype); }
 ORC_API int orc_vec_dot_dtype(int dtype) { return vec_dot_dtype(dtype); }

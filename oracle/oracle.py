@@ -250,6 +250,18 @@ def moe_forward(w: MoeWeights, x, order: int = ORDER_SIMD) -> MoeResult:
     return MoeResult(y, ids, tw, counts, rows)
 
 
+def rms_norm(x, alpha, eps: float):
+    """``candle_nn::ops::rms_norm`` on the CPU (ops.rs:504-514)."""
+    x, alpha = _f32(x), _f32(alpha)
+    rows, d = x.shape
+    out = np.empty_like(x)
+    L = lib()
+    L.orc_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_float, C.c_size_t, C.c_size_t, C.c_void_p]
+    rc = L.orc_rms_norm(_p(x), _p(alpha), C.c_float(eps), rows, d, _p(out))
+    assert rc == 0, rc
+    return out
+
+
 def mlp_forward(dt13: int, dt2: int, x, w1, w3, w2, ff: int, order: int = ORDER_SIMD):
     """One expert (``Mlp::forward``): returns (out [rows, d], hidden [rows, ff])."""
     x = _f32(x)

@@ -70,3 +70,10 @@ SILU_OUT = [[-0.1423, 0.7311, 3.9281, -0.0475, 0.3112], [2.53, -0.2553, -0.1205,
 # candle-core/tests/tensor_tests.rs:1008-1023: zeros(6,3).index_add([5,0,1,0], arange(12).reshape(4,3), dim 0)
 INDEX_ADD_IDS = [5, 0, 1, 0]
 INDEX_ADD_OUT = [[12.0, 14.0, 16.0], [6.0, 7.0, 8.0], [0.0, 0.0, 0.0], [0.0, 0.0, 0.0], [0.0, 0.0, 0.0], [0.0, 1.0, 2.0]]
+
+# candle-nn/tests/ops.rs:55-66: rms_norm(data, alpha = [1, 2, 3], eps = 1e-5), rounded to 4 decimals
+RMS_NORM_DATA = [[[3.0, 1.0, 4.0], [1.0, 5.0, 9.0]], [[2.0, 1.0, 7.0], [8.0, 2.0, 8.0]]]
+RMS_NORM_ALPHA = [1.0, 2.0, 3.0]
+RMS_NORM_EPS = 1e-5
+RMS_NORM_EXPECTED = [[[1.019, 0.6794, 4.0762], [0.1674, 1.6744, 4.521]],
+                     [[0.4714, 0.4714, 4.9497], [1.206, 0.603, 3.6181]]]

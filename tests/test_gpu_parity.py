@@ -560,3 +560,29 @@ def test_block_prefill_over_repacked_weights(orc, torch_cuda):
     small = blk.forward(x[500:508].clone())
     assert H.rel_l2(small.cpu().numpy(), y[500:508].cpu().numpy()) < 5e-4
     assert torch.equal(blk.forward(x), y)
+
+
+@pytest.mark.parametrize("T,prepack", [(5, False), (33, True), (200, True)])
+def test_ffn_layer_norm_block_residual(orc, torch_cuda, T, prepack):
+    """y = x + MoE(RmsNorm(x)): the FFN half of a decoder layer (quantized_llama.rs:887-891) in one call.  The
+    normalised rows agree with the oracle to the last bits (the device sums the squares as a tree), so routing is
+    compared with the near-tie allowance and the result with the block's bars."""
+    torch = torch_cuda
+    mw = orc.make_moe_weights(12, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    x = orc.make_activations(50 + T, T, 512) * np.float32(3.0)
+    alpha = (1.0 + 0.1 * np.random.default_rng(T).standard_normal(512)).astype(np.float32)
+    eps = 1e-5
+    xn = orc.rms_norm(x, alpha, eps)
+    ref = orc.moe_forward(mw, xn)
+    want = ref.y + x
+    blk = H.device_block(orc, mw)
+    if prepack:
+        blk.prepack()
+    y = blk.forward_layer(torch.from_numpy(x).cuda(), torch.from_numpy(alpha), eps).cpu().numpy()
+    probs, _, _ = orc.router_topk(xn, mw.router, mw.top_k, mw.renorm, mw.router_bias)
+    ids, _, _, _ = blk.last_routing(T)
+    n_tie = H.check_routing(probs, ref.topk_ids, ids.numpy().astype(np.uint32))
+    same = (ref.topk_ids == ids.numpy().astype(np.uint32)).all(axis=1) if n_tie else np.ones(T, bool)
+    ffn = y[same] - x[same]
+    assert H.rel_l2(ffn, ref.y[same]) <= H.REL_L2_TOL and H.max_rel(ffn, ref.y[same]) <= H.MAX_REL_TOL
+    assert H.rel_l2(y[same], want[same]) < 5e-4

@@ -176,3 +176,10 @@ def test_moe_block_matches_composition(orc):
         y = orc.index_add_dim0(y, rows, scaled)
     assert res.expert_rows.tolist() == rows_cat
     assert np.array_equal(y, res.y)
+
+
+def test_rms_norm_known_answers(orc):
+    """candle-nn/tests/ops.rs:55-66."""
+    x = np.array(KA.RMS_NORM_DATA, dtype=np.float32).reshape(-1, 3)
+    got = orc.rms_norm(x, np.array(KA.RMS_NORM_ALPHA, dtype=np.float32), KA.RMS_NORM_EPS)
+    assert np.array_equal(np.round(got.astype(np.float64), 4), np.array(KA.RMS_NORM_EXPECTED).reshape(-1, 3))
