@@ -569,17 +569,84 @@ def run_ep(args, cfg, torch, dist, rank, world, local, dev):
     dist.destroy_process_group()
 
 
+PROJECTIONS = {
+    # the dense matrices of the model the block sits in (quantized_llama.rs:275-277, 345, 897), Mixtral-8x7B shapes
+    "attn_q": (4096, 4096, 12), "attn_k": (1024, 4096, 12), "attn_output": (4096, 4096, 12), "output": (32000, 4096, 14),
+}
+
+
+def run_projections(args):
+    """`--workload proj`: QMatMul::forward of each dense projection at --tokens rows (default 1), device-timed,
+    weights rotated over copies that together exceed L2.  One JSON line; not the headline metric."""
+    import torch
+    from candle_b200 import GgmlDType, QMatMul, QTensor
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    T = args.tokens or 1
+    hbm, src = peaks()
+    rows = {}
+    g = torch.Generator(device=dev).manual_seed(0)
+    for name, (n, k, dt) in PROJECTIONS.items():
+        nbytes = mat_bytes(dt, n, k)
+        copies = max(2, -(-400_000_000 // nbytes))
+        w = torch.randn((n, k), generator=g, device=dev) * 0.02
+        base = QTensor.quantize(w, GgmlDType(dt))
+        mats = []
+        for _ in range(copies):
+            m = QMatMul.from_qtensor(QTensor(base.data.clone(), GgmlDType(dt), (n, k)))
+            if not args.no_prepack:
+                m.prepack()
+            mats.append(m)
+        x = torch.randn((T, k), generator=g, device=dev)
+        for i in range(max(args.warmup, 3, copies)):  # every copy once: its scratch is allocated on first use
+            mats[i % copies].forward(x)
+        torch.cuda.synchronize()
+        # the calls of the timed region are replayed from one CUDA graph, so that the figure is the device's time
+        # and not the host's launch rate (a call is four short launches)
+        graph = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(args.steps):
+                    mats[i % copies].forward(x)
+            graph.replay()
+        except Exception as exc:  # noqa: BLE001
+            print(f"# graph capture failed ({exc}); timing eager calls", file=sys.stderr)
+            graph = None
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(args.steps):
+                mats[i % copies].forward(x)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        gbs = nbytes / (us * 1e-6) / 1e9
+        rows[name] = {"n": n, "k": k, "dtype": DT_NAME[dt], "us": round(us, 2), "weight_GBps": round(gbs, 1),
+                      "frac_of_hbm_peak": round(gbs / hbm, 3), "TFLOPs": round(2.0 * T * n * k / (us * 1e-6) / 1e12, 2), "timed": "graph" if graph is not None else "eager"}
+        del mats, graph
+    print(json.dumps({"metric": "qmatmul_us", "unit": "us per call (quantize rows + product)", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "tokens": T, "data": "synthetic", "peak_GBps": hbm, "peak_source": src,
+                      "config": {"workload": "dense projections of a Mixtral-8x7B layer + lm head", "l2": "weights rotated over > 400 MB of copies",
+                                 "prepacked": not args.no_prepack}, "projections": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["proj"])
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-prepack", action="store_true",
                     help="decode straight from the GGUF blocks instead of the one-time prepacked copies")
     args = ap.parse_args()
+    if args.workload == "proj":
+        return run_projections(args)
     cfg = dict(WORKLOADS[args.workload])
     if args.workload == "c5":
         cfg["zipf_bias"] = True

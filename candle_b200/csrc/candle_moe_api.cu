@@ -685,4 +685,98 @@ int candle_moe_ep_experts(void* stream, const candle_moe_weights_t* w, const voi
     return rc(launch_ep_scatter(st, ws.eb.eo, eo_splits, n_rows * d, ws.back, n_rows, d, out_rows));
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// One quantized matrix over a batch of rows: QMatMul::forward for the dense projections of the model
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+struct QmmWorkspace {
+    int8_t* xq;
+    float* xs;
+    int16_t* xb;
+    uint32_t* offsets;
+    float* eo;    // K-split partial outputs (null: the product writes `out` itself)
+    int slots;
+    void* gemm;
+    size_t total;
+};
+QmmWorkspace qmm_layout(int dtype, int64_t rows, int n, int k, void* base_) {
+    uint8_t* base = static_cast<uint8_t*>(base_);
+    QmmWorkspace ws{};
+    size_t off = 0;
+    ws.xq = carve<int8_t>(base, off, (size_t)rows * k);
+    ws.xs = carve<float>(base, off, (size_t)rows * k / act_block(dtype));
+    ws.xb = carve<int16_t>(base, off, (size_t)rows * k / 16);
+    ws.offsets = carve<uint32_t>(base, off, 2);
+    // decode-sized batches split K to fill the device (a [4096, 4096] matrix has 256 row tiles for 148 SMs x 16 warps)
+    ws.slots = rows <= 64 && n % 4 == 0 ? MAX_K_SPLITS : 1;
+    if (ws.slots > 1) ws.eo = carve<float>(base, off, (size_t)rows * n * ws.slots);
+    if (rows > GEMM_MIN_ROWS_EXACT && dtype != CANDLE_GGML_Q8_0) {
+        off = align_up(off, 1024);
+        ws.gemm = base ? base + off : reinterpret_cast<void*>(1);
+        off += expert_gemm_scratch_bytes(rows, k);
+    }
+    ws.total = align_up(off, 256);
+    return ws;
+}
+}  // namespace
+
+int candle_moe_qmatmul_workspace_bytes(int32_t dtype, int64_t rows, int32_t n, int32_t k, size_t* out_bytes) {
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (rows < 0 || rows > (int64_t)1 << 24 || n <= 0 || k <= 0 || k % block_elems(dtype)) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = qmm_layout(dtype, rows, n, k, nullptr).total;
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int32_t dtype, int32_t n, int32_t k,
+                       const float* x, int64_t rows, float* out, void* workspace, size_t workspace_bytes) {
+    if (!dtype_supported(dtype)) return CANDLE_MOE_E_DTYPE;
+    if (rows < 0 || rows > (int64_t)1 << 24 || n <= 0 || k <= 0 || k % block_elems(dtype)) return CANDLE_MOE_E_SHAPE;
+    if (rows == 0) return CANDLE_MOE_OK;
+    if (!w || !x || !out || !workspace) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 15))
+        return CANDLE_MOE_E_ALIGN;
+    const QmmWorkspace ws = qmm_layout(dtype, rows, n, k, workspace);
+    if (workspace_bytes < ws.total) return CANDLE_MOE_E_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    ExpertPtrs pw{}, pp{};
+    pw.p[0] = static_cast<const uint8_t*>(w);
+    pp.p[0] = static_cast<const uint8_t*>(w_prepacked);
+    CM_TRY(rc(launch_quantize_act(st, x, rows, k, dtype, ws.xq, ws.xs, ws.xb)));
+    CM_TRY(rc(launch_single_group(st, ws.offsets, (uint32_t)rows)));
+    float* dst = ws.eo ? ws.eo : out;
+    const int64_t stride = rows * (int64_t)n;
+    int splits = 1;
+    bool done = false;
+    // the row count is exact here (not a bound as in a routed block): the tensor-core form pays off above 16 rows
+    const bool large = ws.gemm && gemm_enabled();
+    if (w_prepacked && rows <= 64 && !large) {
+        const cudaError_t ce = launch_expert_direct(st, false, pp, pp, dtype, 1, k, n, ws.offsets, nullptr, rows, ws.xq, ws.xs,
+                                                    ws.xb, dst, &splits, stride, ws.slots, 1);
+        if (ce == cudaSuccess)
+            done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+        else
+            splits = 1;
+    }
+    if (!done && large) {
+        const bool rp = dtype == CANDLE_GGML_Q6K && w_prepacked;
+        const cudaError_t ce = launch_expert_gemm(st, false, rp ? pp : pw, rp ? pp : pw, dtype, rp, 1, k, n, ws.offsets, nullptr,
+                                                  rows, rows, ws.xq, ws.xs, ws.xb, dst, ws.gemm, ws.slots, &splits, stride);
+        if (ce == cudaSuccess)
+            done = true;
+        else if (ce != cudaErrorNotSupported)
+            return (int)ce;
+        else
+            splits = 1;
+    }
+    if (!done)
+        CM_TRY(rc(launch_grouped_down(st, pw, dtype, 1, n, k, ws.offsets, rows, ws.xq, ws.xs, ws.xb, dst, stride, ws.slots,
+                                      &splits)));
+    if (ws.eo) return rc(launch_ep_scatter(st, ws.eo, splits, stride, nullptr, rows, n, out));
+    return CANDLE_MOE_OK;
+}
+
 }  // extern "C"

@@ -639,6 +639,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             while (have) {
                 const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
                 const CUtensorMap* m0 = P.wmaps + 2 * tc.e;
+                // the maps were written by a kernel earlier on the stream (every lane fences: any may be elected)
+                tensormap_fence_acquire(m0);
+                if (GATE_UP) tensormap_fence_acquire(m0 + 1);
+                if (have_n && tcn.e != tc.e) {
+                    tensormap_fence_acquire(P.wmaps + 2 * tcn.e);
+                    if (GATE_UP) tensormap_fence_acquire(P.wmaps + 2 * tcn.e + 1);
+                }
                 const int y0 = GATE_UP ? tc.mt * 64 : tc.mt * 128;
                 for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                     if (ab >= 1) mbar_wait(&empty_w, (ab - 1) & 1, abort_flag);
@@ -809,6 +816,21 @@ bool make_map_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
 
 int g_gemm_sms = -1;
 
+// Tensor maps of the weight matrices reach device memory as kernel PARAMETERS of a small copy kernel, never
+// from host memory on the stream: a copy node recorded while a stream is being captured into a CUDA graph reads
+// its host source again at every replay, long after the array it pointed to has gone.
+constexpr int MAPS_PER_CHUNK = 16;
+struct MapChunk {
+    CUtensorMap m[MAPS_PER_CHUNK];
+};
+__global__ void __launch_bounds__(128) write_maps_kernel(const __grid_constant__ MapChunk c, CUtensorMap* dst, int n) {
+    pdl_trigger();
+    pdl_wait();  // the previous user of this scratch has finished
+    const uint4* src = reinterpret_cast<const uint4*>(&c);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    for (int i = threadIdx.x; i < n * (int)(sizeof(CUtensorMap) / 16); i += blockDim.x) d[i] = src[i];
+}
+
 template <class F, bool GATE_UP, int TN>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
     const int smem_bytes = G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
@@ -870,15 +892,19 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     // written to the head of the scratch on the stream before the kernel
     CUtensorMap* wmaps_dev = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(d8t) + align_up((size_t)kb * p_pad * 4, 256));
     if (dtype == CANDLE_GGML_Q4K) {
-        CUtensorMap host_maps[2 * CANDLE_MOE_MAX_EXPERTS];
         const uint64_t n_rows = (uint64_t)N, rb = (uint64_t)kb * Q4K_BYTES;
-        for (int e2 = 0; e2 < E; ++e2) {
-            if (!make_map_bytes(&host_maps[2 * e2], wa.p[e2], n_rows, rb, Q4K_BYTES, 64)) return cudaErrorNotSupported;
-            if (!make_map_bytes(&host_maps[2 * e2 + 1], gate_up ? wb.p[e2] : wa.p[e2], n_rows, rb, Q4K_BYTES, 64))
-                return cudaErrorNotSupported;
+        for (int m0 = 0; m0 < 2 * E; m0 += MAPS_PER_CHUNK) {
+            MapChunk chunk;
+            const int n_maps = std::min(MAPS_PER_CHUNK, 2 * E - m0);
+            for (int i = 0; i < n_maps; ++i) {
+                const int e2 = (m0 + i) >> 1;
+                const uint8_t* wp = ((m0 + i) & 1) && gate_up ? wb.p[e2] : wa.p[e2];
+                if (!make_map_bytes(&chunk.m[i], wp, n_rows, rb, Q4K_BYTES, 64)) return cudaErrorNotSupported;
+            }
+            for (int i = n_maps; i < MAPS_PER_CHUNK; ++i) chunk.m[i] = chunk.m[0];
+            e = launch_k(write_maps_kernel, dim3(1), dim3(128), 0, st, chunk, wmaps_dev + m0, n_maps);
+            if (e != cudaSuccess) return e;
         }
-        e = cudaMemcpyAsync(wmaps_dev, host_maps, sizeof(CUtensorMap) * 2 * E, cudaMemcpyHostToDevice, st);
-        if (e != cudaSuccess) return e;
     }
 
     GemmParams G{};

@@ -145,6 +145,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 // the same box requested into L2 only (no shared-memory destination, no completion)
+// Orders this thread's later uses of a tensor map through the tensor-map proxy after writes to the map's 128
+// bytes that are already visible to it through the generic proxy (another kernel wrote the map to global memory).
+__device__ __forceinline__ void tensormap_fence_acquire(const void* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }

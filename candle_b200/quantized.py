@@ -8,7 +8,7 @@ GGUF blocks, row-major `[n][k / block]`, exactly the bytes `QCudaStorage` keeps
 from __future__ import annotations
 
 import enum
-from typing import Tuple
+from typing import Optional, Tuple
 
 import numpy as np
 import torch
@@ -124,12 +124,25 @@ class QMatMul:
 
     def __init__(self, qtensor: QTensor):
         self.inner = qtensor
+        self._ws: Optional[torch.Tensor] = None
+        self._ws_rows = 0
+        self._prepacked: Optional[torch.Tensor] = None
 
     @classmethod
     def from_qtensor(cls, qtensor: QTensor) -> "QMatMul":
         return cls(qtensor)
 
+    def prepack(self) -> "QMatMul":
+        """Make the decode-path copy of the matrix (one-time; Q4_K / Q6_K whose shape the repack takes)."""
+        n, k = self.inner.shape()
+        dt = self.inner.dtype()
+        if dt in (GgmlDType.Q4K, GgmlDType.Q6K) and n % 16 == 0 and k % 256 == 0 and (dt == GgmlDType.Q4K or (k // 256) % 2 == 0):
+            self._prepacked = self.inner.prepack()
+        return self
+
     def forward(self, xs: torch.Tensor) -> torch.Tensor:
+        """`QMatMul::forward` (mod.rs:533-537) through `candle_moe_qmatmul`."""
+        import ctypes as C
         lib = _lib.load()
         n, k = self.inner.shape()
         if xs.shape[-1] != k:
@@ -140,23 +153,25 @@ class QMatMul:
         x2 = xs.reshape(-1, k).contiguous()
         rows = x2.shape[0]
         dev, dt = x2.device, int(self.inner.dtype())
-        ab = 32 if dt == GgmlDType.Q8_0 else 256
-        qs = torch.empty((rows, k), dtype=torch.int8, device=dev)
-        sc = torch.empty((rows, k // ab), dtype=torch.float32, device=dev)
-        bs = torch.empty((rows, k // 16), dtype=torch.int16, device=dev)
-        offs = torch.tensor([0, rows], dtype=torch.int32, device=dev)
         out = torch.empty((rows, n), dtype=torch.float32, device=dev)
-        import ctypes as C
-        ptrs = (C.c_void_p * 1)(self.inner.device_ptr())
+        if rows == 0:
+            return out.reshape(*lead, n)
+        if self._ws is None or rows > self._ws_rows:
+            need = C.c_size_t(0)
+            cap = max(rows, 2 * self._ws_rows)
+            _lib.check("candle_moe_qmatmul_workspace_bytes", lib.candle_moe_qmatmul_workspace_bytes(dt, cap, n, k, C.byref(need)))
+            # rows <= 64 and rows > 64 lay the scratch out differently: hold the larger of the two
+            small = C.c_size_t(0)
+            _lib.check("candle_moe_qmatmul_workspace_bytes",
+                       lib.candle_moe_qmatmul_workspace_bytes(dt, min(cap, 64), n, k, C.byref(small)))
+            self._ws = torch.empty(max(need.value, small.value) + 256, dtype=torch.uint8, device=dev)
+            self._ws_rows = cap
+        ws_ptr = (self._ws.data_ptr() + 255) // 256 * 256
+        pp = None if self._prepacked is None else self._prepacked.data_ptr()
         with torch.cuda.device(dev):
-            st = _stream_ptr(dev)
-            _lib.check("candle_moe_quantize_act",
-                       lib.candle_moe_quantize_act(st, x2.data_ptr(), rows, k, dt, qs.data_ptr(), sc.data_ptr(),
-                                                   bs.data_ptr()))
-            # W is [n, k]: the "down" form computes out[p, :] = W . act[p]
-            _lib.check("candle_moe_grouped_down",
-                       lib.candle_moe_grouped_down(st, ptrs, dt, 1, n, k, offs.data_ptr(), rows, qs.data_ptr(),
-                                                   sc.data_ptr(), bs.data_ptr(), out.data_ptr()))
+            _lib.check("candle_moe_qmatmul",
+                       lib.candle_moe_qmatmul(_stream_ptr(dev), self.inner.device_ptr(), pp, dt, n, k, x2.data_ptr(), rows,
+                                              out.data_ptr(), ws_ptr, self._ws.numel() - 256))
         return out.reshape(*lead, n)
 
     __call__ = forward

@@ -234,6 +234,18 @@ CANDLE_MOE_API int candle_moe_ep_experts(void* stream, const candle_moe_weights_
                                          int64_t max_rows_per_expert, float* out_rows, void* workspace,
                                          size_t workspace_bytes);
 
+/* One quantized matrix over a batch of rows: out[rows, n] = x[rows, k] . W^T with W [n, k] in GGUF blocks
+ * -- `QMatMul::forward` (candle-core/src/quantized/mod.rs:533-537 -> `QTensor::cuda_fwd` :520-530 -> `QCudaStorage::fwd`, cuda.rs:484-505)
+ * for the dense projections of the model (attention wq/wk/wv/wo quantized_llama.rs:275-277,345, lm head :897).
+ * The rows are quantized as `k_quants::matmul` does (k_quants.rs:1873-1920), then the product runs on the same
+ * kernels as the experts' down product with one group: the decode kernels over `w_prepacked` (optional, from
+ * candle_moe_prepack; up to 64 rows), the tensor-core GEMM (more than 16 rows; Q6_K needs w_prepacked there) or
+ * the forms that read the GGUF layout.  Workspace: candle_moe_qmatmul_workspace_bytes bytes, 256-byte aligned. */
+CANDLE_MOE_API int candle_moe_qmatmul_workspace_bytes(int32_t dtype, int64_t rows, int32_t n, int32_t k, size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int32_t dtype, int32_t n,
+                                      int32_t k, const float* x, int64_t rows, float* out, void* workspace,
+                                      size_t workspace_bytes);
+
 /* One-time repack of a Q4_K / Q6_K matrix [n_rows, k] (n_rows a multiple of 8 -- 16 for w2 --, k a
  * multiple of 256) into the register-fragment order the decode kernels read with coalesced
  * 128-bit loads.  Q4_K grows by 2.8 % (its 12-byte packed 6-bit scales are widened to 16 bytes),

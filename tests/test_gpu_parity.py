@@ -206,6 +206,52 @@ def test_combine_order_and_shared_expert(orc, torch_cuda):
 
 # ------------------------------------------------------------------------------------------------
 # quantized products (QMatMul::forward)
+@pytest.mark.parametrize("name,m,k,n,prepack", [
+    ("Q4K", 1, 4096, 512, True),     # decode kernels over the repacked copy, K split over the device
+    ("Q6K", 3, 2048, 256, True),
+    ("Q4K", 9, 1024, 64, True),
+    ("Q4K", 40, 1024, 256, False),   # tensor-core form over the GGUF blocks
+    ("Q4K", 200, 2048, 384, True),
+    ("Q6K", 150, 1024, 256, True),   # tensor-core form over the repacked copy
+    ("Q6K", 150, 1024, 256, False),  # no repacked copy: the streaming form
+    ("Q8_0", 90, 1024, 128, False),
+])
+def test_qmatmul_forward_every_form(orc, torch_cuda, name, m, k, n, prepack):
+    """The dense projections (attention wq/wk/wv/wo, lm head) take the experts' kernels with one group."""
+    torch = torch_cuda
+    from candle_b200 import GgmlDType, QMatMul, QTensor
+    dt = getattr(orc, name)
+    rng = np.random.default_rng(m * 1000 + k + n)
+    w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    wq = orc.quantize(dt, w)
+    ref = orc.matmul(dt, x, wq, n)
+    mm = QMatMul.from_qtensor(QTensor.from_blocks(wq, GgmlDType(dt), (n, k)))
+    if prepack:
+        mm.prepack()
+        assert mm._prepacked is not None
+    got = mm.forward(torch.from_numpy(x).cuda().reshape(1, m, k)).cpu().numpy().reshape(m, n)
+    # the tensor-core form rounds its accumulation differently from the integer forms
+    assert H.rel_l2(got, ref) <= 3e-4 and H.max_rel(got, ref) <= H.MAX_REL_TOL
+    assert _device_status() == 0
+    # a smaller batch through the same object (the scratch is kept) and row independence
+    got1 = mm.forward(torch.from_numpy(x[:1]).cuda()).cpu().numpy()
+    assert H.rel_l2(got1, ref[:1]) <= 3e-4
+
+
+@pytest.mark.parametrize("T", [3, 70])
+def test_dense_mlp_matches_oracle(orc, torch_cuda, T):
+    """`MlpOrMoe::Mlp` (quantized_llama.rs:124-131, :145): w2(silu(w1 x) * w3 x) for every row."""
+    torch = torch_cuda
+    mw = orc.make_moe_weights(31, 512, 1024, 1, 1, orc.Q4K, orc.Q6K)
+    x = orc.make_activations(32, T, 512)
+    ref, _ = orc.mlp_forward(orc.Q4K, orc.Q6K, x, mw.w1[0], mw.w3[0], mw.w2[0], 1024)
+    blk = H.device_block(orc, mw)
+    y = blk.experts[0].forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    assert H.rel_l2(y, ref) <= H.REL_L2_TOL and H.max_rel(y, ref) <= H.MAX_REL_TOL
+
+
+
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("name,m,k,n", [("Q4K", 1, 256, 8), ("Q4K", 11, 512, 21), ("Q4K", 5, 4096, 96),
                                         ("Q6K", 1, 256, 8), ("Q6K", 11, 512, 21), ("Q6K", 3, 14336, 40),
@@ -586,3 +632,31 @@ def test_ffn_layer_norm_block_residual(orc, torch_cuda, T, prepack):
     ffn = y[same] - x[same]
     assert H.rel_l2(ffn, ref.y[same]) <= H.REL_L2_TOL and H.max_rel(ffn, ref.y[same]) <= H.MAX_REL_TOL
     assert H.rel_l2(y[same], want[same]) < 5e-4
+
+
+@pytest.mark.parametrize("T", [4, 300])
+def test_forward_replayed_from_a_cuda_graph(orc, torch_cuda, T):
+    """A decode loop captures the block once and replays it.  Nothing a call puts on the stream may read host
+    memory later (the tensor maps of the large-batch form travel as kernel parameters), so a replay over new
+    inputs gives what the eager call gives, bit for bit."""
+    torch = torch_cuda
+    mw = orc.make_moe_weights(41, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    blk = H.device_block(orc, mw).prepack()
+    blk.reserve(T)
+    xa = torch.from_numpy(orc.make_activations(42, T, 512)).cuda()
+    xb = torch.from_numpy(orc.make_activations(43, T, 512)).cuda()
+    want = [blk.forward(xa).clone(), blk.forward(xb).clone()]
+    x_static, y_static = torch.empty_like(xa), torch.empty_like(xa)
+    x_static.copy_(xa)
+    blk.forward(x_static, out=y_static)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        blk.forward(x_static, out=y_static)
+    junk = [np.random.default_rng(i).bytes(1 << 16) for i in range(8)]  # host memory churn between capture and replay
+    for x_new, y_want in ((xa, want[0]), (xb, want[1]), (xa, want[0])):
+        x_static.copy_(x_new)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y_static, y_want)
+    assert _device_status() == 0 and len(junk) == 8
