@@ -368,16 +368,25 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) f[nt][i] = 0.f;
-                // fill one ring slot with block bk of both half-tiles (16-byte cp.async per lane)
+                // fill one ring slot with block bk of both half-tiles (16-byte cp.async per lane).  The vector index
+                // of a lane in pass i is lane + 32 i, so which half-tile a pass reads is known at compile time except
+                // for the one pass that straddles the boundary: straight-line code, one predicate for the ragged end.
                 auto issue = [&](int bk) {
                     if (bk < nblk) {
-                        const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
-                        const uint8_t* sa = hta + (size_t)bk * F::HTB;
-                        const uint8_t* sb = htb + (size_t)bk * F::HTB;
-                        for (int v = lane; v < 2 * VEC_PER_HT; v += 32) {
-                            const bool second = v >= VEC_PER_HT;
-                            const int vv = second ? v - VEC_PER_HT : v;
-                            cp_async16(slot + 16 * v, (second ? sb : sa) + 16 * vv);
+                        const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES + 16 * lane;
+                        const uint8_t* sa = hta + (size_t)bk * F::HTB + 16 * lane;
+                        const uint8_t* sb = htb + (size_t)bk * F::HTB + 16 * lane - 16 * VEC_PER_HT;
+                        constexpr int PASSES = (2 * VEC_PER_HT + 31) / 32;
+#pragma unroll
+                        for (int i = 0; i < PASSES; ++i) {
+                            const uint8_t* src;
+                            if (32 * i + 31 < VEC_PER_HT)
+                                src = sa;
+                            else if (32 * i >= VEC_PER_HT)
+                                src = sb;
+                            else
+                                src = lane + 32 * i >= VEC_PER_HT ? sb : sa;
+                            if (32 * i + 31 < 2 * VEC_PER_HT || lane + 32 * i < 2 * VEC_PER_HT) cp_async16(slot + 512 * i, src + 512 * i);
                         }
                     }
                     cp_async_commit();  // one group per block, empty past the end: the count stays in step
