@@ -398,7 +398,7 @@ static int forward_impl(void* stream, const candle_moe_weights_t* w, const float
         return CANDLE_MOE_E_ALIGN;
     const Workspace ws = layout(w, T, workspace);
     if (workspace_bytes < ws.total) return CANDLE_MOE_E_WORKSPACE;
-    const int E = w->n_experts, k = w->top_k, d = w->d_model, ff = w->d_ff;
+    const int E = w->n_experts, k = w->top_k, d = w->d_model;
     ExpertPtrs p1, p3, p2;
     CM_TRY(fill_ptrs(w->w1, E, p1));
     CM_TRY(fill_ptrs(w->w3, E, p3));

@@ -55,19 +55,20 @@ struct DirQ4K {
         uint32_t dmA, dmB;   // f16 d | f16 dmin
         uint2 scA, scB, mA, mB;
     };
-    // hta / htb: shared-window addresses of the two half-tile blocks inside the warp's ring slot
-    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, uint32_t htb, int lane) {
+    // hta: shared-window address of the first half-tile block inside the warp's ring slot; the second follows it
+    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, int lane) {
         const int g = lane >> 2;
-        F.qa[0] = lds128(hta + lane * 16);
-        F.qa[1] = lds128(hta + 512 + lane * 16);
-        F.qb[0] = lds128(htb + lane * 16);
-        F.qb[1] = lds128(htb + 512 + lane * 16);
-        F.dmA = lds32(hta + 1024 + 4 * g);
-        F.dmB = lds32(htb + 1024 + 4 * g);
-        F.scA = lds64(hta + 1056 + 8 * g);
-        F.scB = lds64(htb + 1056 + 8 * g);
-        F.mA = lds64(hta + 1120 + 8 * g);
-        F.mB = lds64(htb + 1120 + 8 * g);
+        const uint32_t bq = hta + lane * 16, bd = hta + 4 * g, bs = hta + 8 * g;
+        F.qa[0] = lds128_o<0>(bq);
+        F.qa[1] = lds128_o<512>(bq);
+        F.qb[0] = lds128_o<HTB>(bq);
+        F.qb[1] = lds128_o<HTB + 512>(bq);
+        F.dmA = lds32_o<1024>(bd);
+        F.dmB = lds32_o<HTB + 1024>(bd);
+        F.scA = lds64_o<1056>(bs);
+        F.scB = lds64_o<HTB + 1056>(bs);
+        F.mA = lds64_o<1120>(bs);
+        F.mB = lds64_o<HTB + 1120>(bs);
     }
     template <int NT, int NTL>
     __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
@@ -81,9 +82,9 @@ struct DirQ4K {
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
         const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
-#pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-            const int jl = 2 * grp, jh = 2 * grp + 1;
+        static_for<4>([&](auto G) {
+            constexpr int grp = decltype(G)::value;
+            constexpr int jl = 2 * grp, jh = 2 * grp + 1;
             const uint4 wa = F.qa[grp >> 1], wb = F.qb[grp >> 1];
             // fragment order a0 (row g, k 0-15), a1 (row g+8, k 0-15), a2 (row g, k 16-31), a3 (row g+8, k 16-31)
             const uint32_t a0 = (grp & 1) ? wa.z : wa.x, a2 = (grp & 1) ? wa.w : wa.y;
@@ -96,7 +97,7 @@ struct DirQ4K {
 #pragma unroll
             for (int nt = 0; nt < NTL; ++nt) {
                 uint32_t b[4];
-                ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 64 * grp);
+                ldmatrix_x4_o<64 * grp>(b, b_addr + nt * 8 * A.act_stride);
                 int p[4], q[4];
                 mma_s8_k32_z(p, alo, b[0], b[1]);
                 mma_s8_k32_z(q, ahi, b[2], b[3]);
@@ -105,7 +106,7 @@ struct DirQ4K {
                 c[nt][2] += sBl * p[2] + sBh * q[2];
                 c[nt][3] += sBl * p[3] + sBh * q[3];
             }
-        }
+        });
         // min term: sum_j min_j * bsum_j as a [16 x 8] by [8 x 8] product (lanes t = 0, 1 carry the mins)
         const uint32_t am0 = t == 0 ? F.mA.x : (t == 1 ? F.mA.y : 0u);
         const uint32_t am1 = t == 0 ? F.mB.x : (t == 1 ? F.mB.y : 0u);
@@ -144,18 +145,19 @@ struct DirQ6K {
         uint4 scA, scB;        // 16 int8 scales
         uint32_t dA, dB;       // f16 d
     };
-    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, uint32_t htb, int lane) {
+    __device__ static __forceinline__ void load(Frag& F, uint32_t hta, int lane) {
         const int g = lane >> 2;
-        F.qlA[0] = lds128(hta + lane * 16);
-        F.qlA[1] = lds128(hta + 512 + lane * 16);
-        F.qhA = lds128(hta + 1024 + lane * 16);
-        F.qlB[0] = lds128(htb + lane * 16);
-        F.qlB[1] = lds128(htb + 512 + lane * 16);
-        F.qhB = lds128(htb + 1024 + lane * 16);
-        F.scA = lds128(hta + 1536 + 16 * g);
-        F.scB = lds128(htb + 1536 + 16 * g);
-        F.dA = lds16(hta + 1664 + 2 * g);
-        F.dB = lds16(htb + 1664 + 2 * g);
+        const uint32_t bq = hta + lane * 16, bs = hta + 16 * g, bd = hta + 2 * g;
+        F.qlA[0] = lds128_o<0>(bq);
+        F.qlA[1] = lds128_o<512>(bq);
+        F.qhA = lds128_o<1024>(bq);
+        F.qlB[0] = lds128_o<HTB>(bq);
+        F.qlB[1] = lds128_o<HTB + 512>(bq);
+        F.qhB = lds128_o<HTB + 1024>(bq);
+        F.scA = lds128_o<1536>(bs);
+        F.scB = lds128_o<HTB + 1536>(bs);
+        F.dA = lds16_o<1664>(bd);
+        F.dB = lds16_o<HTB + 1664>(bd);
     }
     __device__ static __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
@@ -170,8 +172,8 @@ struct DirQ6K {
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
         const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        static_for<2>([&](auto Hc) {
+            constexpr int h = decltype(Hc)::value;
             uint32_t hqA[2][4], hqB[2][4];  // [lr][quarter]: the 2-bit highs moved to bits 4..5
 #pragma unroll
             for (int lr = 0; lr < 2; ++lr) {
@@ -185,8 +187,8 @@ struct DirQ6K {
                 hqB[lr][2] = qb & 0x30303030u;
                 hqB[lr][3] = (qb >> 2) & 0x30303030u;
             }
-#pragma unroll
-            for (int y = 0; y < 2; ++y) {  // 64 elements = quarters 2y, 2y+1
+            static_for<2>([&](auto Yc) {  // 64 elements = quarters 2y, 2y+1
+                constexpr int y = decltype(Yc)::value;
                 uint32_t aA[4], aB[4];
                 int sA[4], sB[4];
 #pragma unroll
@@ -206,7 +208,7 @@ struct DirQ6K {
 #pragma unroll
                 for (int nt = 0; nt < NTL; ++nt) {
                     uint32_t b[4];
-                    ldmatrix_x4(b, b_addr + nt * 8 * A.act_stride + 128 * h + 64 * y);
+                    ldmatrix_x4_o<128 * h + 64 * y>(b, b_addr + nt * 8 * A.act_stride);
 #pragma unroll
                     for (int s4 = 0; s4 < 4; ++s4) {
                         int p[4];
@@ -217,8 +219,8 @@ struct DirQ6K {
                         c[nt][3] += sB[s4] * p[3];
                     }
                 }
-            }
-        }
+            });
+        });
         const uint32_t sa = scA[t], sb = scB[t];
 #pragma unroll
         for (int nt = 0; nt < NTL; ++nt) {
@@ -377,8 +379,8 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                         const uint8_t* sa = hta + (size_t)bk * F::HTB + 16 * lane;
                         const uint8_t* sb = htb + (size_t)bk * F::HTB + 16 * lane - 16 * VEC_PER_HT;
                         constexpr int PASSES = (2 * VEC_PER_HT + 31) / 32;
-#pragma unroll
-                        for (int i = 0; i < PASSES; ++i) {
+                        static_for<PASSES>([&](auto Ic) {
+                            constexpr int i = decltype(Ic)::value;
                             const uint8_t* src;
                             if (32 * i + 31 < VEC_PER_HT)
                                 src = sa;
@@ -386,8 +388,8 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                                 src = sb;
                             else
                                 src = lane + 32 * i >= VEC_PER_HT ? sb : sa;
-                            if (32 * i + 31 < 2 * VEC_PER_HT || lane + 32 * i < 2 * VEC_PER_HT) cp_async16(slot + 512 * i, src + 512 * i);
-                        }
+                            if (32 * i + 31 < 2 * VEC_PER_HT || lane + 32 * i < 2 * VEC_PER_HT) cp_async16_o<512 * i>(slot, src);
+                        });
                     }
                     cp_async_commit();  // one group per block, empty past the end: the count stays in step
                 };
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     issue(bk + DEPTH - 1);
                     typename F::Frag cur;
                     const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
-                    F::load(cur, slot, slot + F::HTB, lane);
+                    F::load(cur, slot, lane);
                     A.kblk_local = bk;
                     if (NT == 1 || ntiles == 1)
                         F::template compute<NT, 1>(cur, A, lane, f);

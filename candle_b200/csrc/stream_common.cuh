@@ -1,6 +1,8 @@
 // PTX wrappers used by the streaming expert kernels: mbarrier, bulk async copy (TMA without a
 // tensor map), ldmatrix and the int8 tensor-core MMAs.  Every wait is bounded.
 #pragma once
+#include <utility>
+#include <type_traits>
 
 #include <stdint.h>
 
@@ -112,6 +114,52 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
+}
+// A loop whose index is a compile-time constant in the body (usable as a template argument there):
+// static_for<N>([&](auto I) { constexpr int i = decltype(I)::value; ... });
+template <class Fn, int... Is>
+__device__ __forceinline__ void static_for_impl(Fn&& f, std::integer_sequence<int, Is...>) {
+    (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, class Fn>
+__device__ __forceinline__ void static_for(Fn&& f) {
+    static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
+
+// The same with a compile-time byte offset folded into the instruction (one base register serves many accesses)
+template <int OFF>
+__device__ __forceinline__ void ldmatrix_x4_o(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4 + %5];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr), "n"(OFF));
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_o(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1 + %2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16_o(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1 + %2];" : "=h"(v) : "r"(addr), "n"(OFF));
+    return (uint32_t)v;
+}
+template <int OFF>
+__device__ __forceinline__ uint2 lds64_o(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2 + %3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_o(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4 + %5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ void cp_async16_o(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %2], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
 }
 // 16-byte asynchronous global -> shared copy (per thread, bypassing L1) and its group fences
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
