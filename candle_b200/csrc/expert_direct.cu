@@ -24,6 +24,7 @@
 // Q4_K grows by 2.8 % (the 12-byte packed scales become 16 bytes); Q6_K keeps its size.
 #include "common.cuh"
 #include "stream_common.cuh"
+#include "tc5_common.cuh"
 
 namespace cmoe {
 
@@ -71,7 +72,7 @@ struct DirQ4K {
         F.mB = lds64_o<HTB + 1120>(bs);
     }
     template <int NT, int NTL>
-    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
+    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, uint64_t (&fp)[NT][2]) {
         const int g = lane >> 2, t = lane & 3;
         const float dA = half_bits_to_float((uint16_t)(F.dmA & 0xffff)), mnA = half_bits_to_float((uint16_t)(F.dmA >> 16));
         const float dB = half_bits_to_float((uint16_t)(F.dmB & 0xffff)), mnB = half_bits_to_float((uint16_t)(F.dmB >> 16));
@@ -119,12 +120,15 @@ struct DirQ4K {
             int ch[4], cl[4];
             mma_s8_k16_z(ch, am0, am1, bh);
             mma_s8_k16_z(cl, am0, am1, bl);
+            // two positions of one row at a time in packed f32x2 arithmetic: f += d8 * (d * c - dmin * m)
+            const uint64_t d8p = f32x2_pack(d8a, d8b);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float d8 = (i & 1) ? d8b : d8a;
-                const float dw = (i >> 1) ? dB : dA, mw = (i >> 1) ? mnB : mnA;
-                f[nt][i] = fmaf(d8 * dw, (float)c[nt][i], f[nt][i]);
-                f[nt][i] = fmaf(-(d8 * mw), (float)(128 * ch[i] + cl[i]), f[nt][i]);
+            for (int r = 0; r < 2; ++r) {
+                const float dw = r ? dB : dA, mw = r ? mnB : mnA;
+                const uint64_t fc = f32x2_pack((float)c[nt][2 * r], (float)c[nt][2 * r + 1]);
+                const uint64_t fm = f32x2_pack((float)(128 * ch[2 * r] + cl[2 * r]), (float)(128 * ch[2 * r + 1] + cl[2 * r + 1]));
+                const uint64_t tq = f32x2_fma(f32x2_pack(-mw, -mw), fm, f32x2_mul(f32x2_pack(dw, dw), fc));
+                fp[nt][r] = f32x2_fma(d8p, tq, fp[nt][r]);
             }
         }
     }
@@ -162,7 +166,7 @@ struct DirQ6K {
     __device__ static __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
     template <int NT, int NTL>
-    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, float (&f)[NT][4]) {
+    __device__ static __forceinline__ void compute(const Frag& F, const ActArgs& A, int lane, uint64_t (&fp)[NT][2]) {
         const int g = lane >> 2, t = lane & 3;
         const float dA = half_bits_to_float((uint16_t)F.dA), dB = half_bits_to_float((uint16_t)F.dB);
         const uint32_t scA[4] = {F.scA.x, F.scA.y, F.scA.z, F.scA.w}, scB[4] = {F.scB.x, F.scB.y, F.scB.z, F.scB.w};
@@ -231,11 +235,13 @@ struct DirQ6K {
             mma_s8u8_k16_z(cl, sa, sb, bl);
             const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
             const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
+            const uint64_t d8p = f32x2_pack(d8a, d8b);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int isum = c[nt][i] - 32 * (256 * ch[i] + cl[i]);
-                const float dd = ((i & 1) ? d8b : d8a) * ((i >> 1) ? dB : dA);
-                f[nt][i] = fmaf(dd, (float)isum, f[nt][i]);
+            for (int r = 0; r < 2; ++r) {
+                const float dw = r ? dB : dA;
+                const int i0 = c[nt][2 * r] - 32 * (256 * ch[2 * r] + cl[2 * r]);
+                const int i1 = c[nt][2 * r + 1] - 32 * (256 * ch[2 * r + 1] + cl[2 * r + 1]);
+                fp[nt][r] = f32x2_fma(f32x2_mul(d8p, f32x2_pack(dw, dw)), f32x2_pack((float)i0, (float)i1), fp[nt][r]);
             }
         }
     }
@@ -365,11 +371,9 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     hta = P.wa.p[e] + (size_t)(2 * tile) * ht_stride + (size_t)blk0 * F::HTB;
                     htb = hta + ht_stride;
                 }
-                float f[NT][4];
+                uint64_t fp[NT][2];  // per position tile: (row g | row g + 8) x two positions, packed f32 pairs
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) f[nt][i] = 0.f;
+                for (int nt = 0; nt < NT; ++nt) fp[nt][0] = fp[nt][1] = 0ull;
                 // fill one ring slot with block bk of both half-tiles (16-byte cp.async per lane).  The vector index
                 // of a lane in pass i is lane + 32 i, so which half-tile a pass reads is known at compile time except
                 // for the one pass that straddles the boundary: straight-line code, one predicate for the ragged end.
@@ -405,23 +409,26 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     F::load(cur, slot, lane);
                     A.kblk_local = bk;
                     if (NT == 1 || ntiles == 1)
-                        F::template compute<NT, 1>(cur, A, lane, f);
+                        F::template compute<NT, 1>(cur, A, lane, fp);
                     else
-                        F::template compute<NT, NT>(cur, A, lane, f);
+                        F::template compute<NT, NT>(cur, A, lane, fp);
                 }
                 const int g = lane >> 2, t = lane & 3;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
+                    float f[1][4];
+                    f32x2_unpack(fp[nt][0], f[0][0], f[0][1]);
+                    f32x2_unpack(fp[nt][1], f[0][2], f[0][3]);
 #pragma unroll
                     for (int cc = 0; cc < 2; ++cc) {
                         const uint32_t p = p_base + nt * 8 + 2 * t + cc;
                         if (p < p_end) {
                             if (GATE_UP) {
-                                P.out[(int64_t)p * P.N + tile * 8 + g] = silu_f(f[nt][cc]) * f[nt][2 + cc];
+                                P.out[(int64_t)p * P.N + tile * 8 + g] = silu_f(f[0][cc]) * f[0][2 + cc];
                             } else {
                                 float* o = P.out + (int64_t)sp * P.out_split_stride + (int64_t)p * P.N + tile * 16 + g;
-                                o[0] = f[nt][cc];
-                                o[8] = f[nt][2 + cc];
+                                o[0] = f[0][cc];
+                                o[8] = f[0][2 + cc];
                             }
                         }
                     }
