@@ -35,11 +35,14 @@ constexpr int Q6K_HTB = 1680;
 constexpr int DIRECT_WARPS = 16;
 constexpr int DIRECT_THREADS = 32 * DIRECT_WARPS;
 
-// Shared-memory side of a block product (32-bit shared-window addresses)
+// Shared-memory side of a block product: 32-bit shared-window addresses of this lane's share of the current
+// K-block, advanced by the kernel from block to block, so that every access is base + compile-time offset.
+//   act_blk  int8 rows [MT][act_stride]: row (lane & 7), 16-byte chunk (lane >> 3) of the block   (ldmatrix)
+//   sc_blk   f32 activation scales [block][MT]: the pair of positions 2t, 2t + 1
+//   bs_blk   block sums [block][hi | lo][MT][BS_PER_BLOCK] bytes: row g, the lane's four sub-blocks
 struct ActArgs {
-    uint32_t act, act_scale, bs_hi, bs_lo;
-    int act_stride, scale_stride, bs_stride;
-    int kblk_local;
+    uint32_t act_blk, sc_blk, bs_blk;
+    int act_stride8;  // bytes between position tiles (8 rows) of the int8 activations
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -82,7 +85,6 @@ struct DirQ4K {
         for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
-        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
         static_for<4>([&](auto G) {
             constexpr int grp = decltype(G)::value;
             constexpr int jl = 2 * grp, jh = 2 * grp + 1;
@@ -98,7 +100,7 @@ struct DirQ4K {
 #pragma unroll
             for (int nt = 0; nt < NTL; ++nt) {
                 uint32_t b[4];
-                ldmatrix_x4_o<64 * grp>(b, b_addr + nt * 8 * A.act_stride);
+                ldmatrix_x4_o<64 * grp>(b, A.act_blk + nt * A.act_stride8);
                 int p[4], q[4];
                 mma_s8_k32_z(p, alo, b[0], b[1]);
                 mma_s8_k32_z(q, ahi, b[2], b[3]);
@@ -111,17 +113,15 @@ struct DirQ4K {
         // min term: sum_j min_j * bsum_j as a [16 x 8] by [8 x 8] product (lanes t = 0, 1 carry the mins)
         const uint32_t am0 = t == 0 ? F.mA.x : (t == 1 ? F.mA.y : 0u);
         const uint32_t am1 = t == 0 ? F.mB.x : (t == 1 ? F.mB.y : 0u);
-#pragma unroll
-        for (int nt = 0; nt < NTL; ++nt) {
-            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 8 + 4 * (t & 1);
-            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
-            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
-            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
+        static_for<NTL>([&](auto Nc) {
+            constexpr int nt = decltype(Nc)::value;
+            const uint32_t bh = lds32_o<nt * 8 * BS_PER_BLOCK>(A.bs_blk), bl = lds32_o<(8 * NT + nt * 8) * BS_PER_BLOCK>(A.bs_blk);
+            const uint2 d8v = lds64_o<32 * nt>(A.sc_blk);
             int ch[4], cl[4];
             mma_s8_k16_z(ch, am0, am1, bh);
             mma_s8_k16_z(cl, am0, am1, bl);
             // two positions of one row at a time in packed f32x2 arithmetic: f += d8 * (d * c - dmin * m)
-            const uint64_t d8p = f32x2_pack(d8a, d8b);
+            const uint64_t d8p = f32x2_pack_bits(d8v.x, d8v.y);
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const float dw = r ? dB : dA, mw = r ? mnB : mnA;
@@ -130,7 +130,7 @@ struct DirQ4K {
                 const uint64_t tq = f32x2_fma(f32x2_pack(-mw, -mw), fm, f32x2_mul(f32x2_pack(dw, dw), fc));
                 fp[nt][r] = f32x2_fma(d8p, tq, fp[nt][r]);
             }
-        }
+        });
     }
 };
 
@@ -175,7 +175,6 @@ struct DirQ6K {
         for (int nt = 0; nt < NTL; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) c[nt][i] = 0;
-        const uint32_t b_addr = A.act + (lane & 7) * A.act_stride + A.kblk_local * 256 + 16 * (lane >> 3);
         static_for<2>([&](auto Hc) {
             constexpr int h = decltype(Hc)::value;
             uint32_t hqA[2][4], hqB[2][4];  // [lr][quarter]: the 2-bit highs moved to bits 4..5
@@ -212,7 +211,7 @@ struct DirQ6K {
 #pragma unroll
                 for (int nt = 0; nt < NTL; ++nt) {
                     uint32_t b[4];
-                    ldmatrix_x4_o<128 * h + 64 * y>(b, b_addr + nt * 8 * A.act_stride);
+                    ldmatrix_x4_o<128 * h + 64 * y>(b, A.act_blk + nt * A.act_stride8);
 #pragma unroll
                     for (int s4 = 0; s4 < 4; ++s4) {
                         int p[4];
@@ -226,16 +225,14 @@ struct DirQ6K {
             });
         });
         const uint32_t sa = scA[t], sb = scB[t];
-#pragma unroll
-        for (int nt = 0; nt < NTL; ++nt) {
-            const uint32_t boff = (nt * 8 + g) * A.bs_stride + A.kblk_local * 16 + 4 * t;
-            const uint32_t bh = lds32(A.bs_hi + boff), bl = lds32(A.bs_lo + boff);
+        static_for<NTL>([&](auto Nc) {
+            constexpr int nt = decltype(Nc)::value;
+            const uint32_t bh = lds32_o<nt * 8 * BS_PER_BLOCK>(A.bs_blk), bl = lds32_o<(8 * NT + nt * 8) * BS_PER_BLOCK>(A.bs_blk);
             int ch[4], cl[4];
             mma_s8_k16_z(ch, sa, sb, bh);
             mma_s8u8_k16_z(cl, sa, sb, bl);
-            const float d8a = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t) * A.scale_stride + A.kblk_local));
-            const float d8b = ldsf(A.act_scale + 4 * ((nt * 8 + 2 * t + 1) * A.scale_stride + A.kblk_local));
-            const uint64_t d8p = f32x2_pack(d8a, d8b);
+            const uint2 d8v = lds64_o<32 * nt>(A.sc_blk);
+            const uint64_t d8p = f32x2_pack_bits(d8v.x, d8v.y);
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const float dw = r ? dB : dA;
@@ -243,7 +240,7 @@ struct DirQ6K {
                 const int i1 = c[nt][2 * r + 1] - 32 * (256 * ch[2 * r + 1] + cl[2 * r + 1]);
                 fp[nt][r] = f32x2_fma(f32x2_mul(d8p, f32x2_pack(dw, dw)), f32x2_pack((float)i0, (float)i1), fp[nt][r]);
             }
-        }
+        });
     }
 };
 
@@ -258,8 +255,8 @@ struct DirectParams {
     int64_t out_split_stride;
     int E, K, N, kb, splits, MT;
     int blk_start[9];  // split s covers blocks [blk_start[s], blk_start[s + 1])
-    int act_stride, scale_stride, bs_stride;
-    uint32_t off_act, off_scale, off_bs_hi, off_bs_lo, off_ring;
+    int act_stride;
+    uint32_t off_act, off_scale, off_bs, off_ring;
 };
 
 // DEPTH = ring slots per warp (DEPTH - 1 blocks in flight while one is multiplied)
@@ -277,17 +274,15 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
     __syncthreads();
 
     uint8_t* act = smem + P.off_act;
-    float* act_scale = reinterpret_cast<float*>(smem + P.off_scale);
-    uint8_t* bs_hi = smem + P.off_bs_hi;
-    uint8_t* bs_lo = smem + P.off_bs_lo;
+    float* act_scale = reinterpret_cast<float*>(smem + P.off_scale);  // [block][MT]
+    uint8_t* bs = smem + P.off_bs;                                    // [block][hi | lo][MT][BS_PER_BLOCK]
+    constexpr int BSB = F::BS_PER_BLOCK;
     ActArgs A;
-    A.act = smem_u32(act);
-    A.act_scale = smem_u32(act_scale);
-    A.bs_hi = smem_u32(bs_hi);
-    A.bs_lo = smem_u32(bs_lo);
-    A.act_stride = P.act_stride;
-    A.scale_stride = P.scale_stride;
-    A.bs_stride = P.bs_stride;
+    A.act_stride8 = 8 * P.act_stride;
+    // this lane's share of K-block 0 (see ActArgs)
+    const uint32_t act_lane = smem_u32(act) + (lane & 7) * P.act_stride + 16 * (lane >> 3);
+    const uint32_t sc_lane = smem_u32(act_scale) + 8 * (lane & 3);
+    const uint32_t bs_lane = smem_u32(bs) + (lane >> 2) * BSB + (BSB == 8 ? 4 * (lane & 1) : 4 * (lane & 3));
     constexpr int SLOT_BYTES = 2 * F::HTB;       // both half-tile blocks of one K-block
     constexpr int VEC_PER_HT = F::HTB / 16;      // 16-byte vectors per half-tile block
     const uint32_t ring = smem_u32(smem + P.off_ring) + (uint32_t)warp * (DEPTH * SLOT_BYTES);
@@ -345,7 +340,7 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                 for (int idx = tid; idx < MT * nblk; idx += DIRECT_THREADS) {
                     const int j = idx / nblk, bb = idx - j * nblk;
                     const int row = s_rows[j];
-                    act_scale[j * P.scale_stride + bb] = row >= 0 ? P.ascale[(int64_t)row * P.kb + blk0 + bb] : 0.f;
+                    act_scale[bb * MT + j] = row >= 0 ? P.ascale[(int64_t)row * P.kb + blk0 + bb] : 0.f;
                 }
                 const int per_row = nblk * F::BS_PER_BLOCK;
                 for (int idx = tid; idx < MT * per_row; idx += DIRECT_THREADS) {
@@ -354,8 +349,9 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     const int v = row >= 0 ? F::bs_value(P.absum + (int64_t)row * (P.K / 16) + blk0 * 16, bb) : 0;
                     uint8_t h8, l8;
                     F::bs_split(v, h8, l8);
-                    bs_lo[j * P.bs_stride + bb] = l8;
-                    bs_hi[j * P.bs_stride + bb] = h8;
+                    const int blk = bb / BSB, i = bb - blk * BSB;
+                    bs[((2 * blk) * MT + j) * BSB + i] = h8;
+                    bs[((2 * blk + 1) * MT + j) * BSB + i] = l8;
                 }
             }
             __syncthreads();
@@ -407,7 +403,9 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     typename F::Frag cur;
                     const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
                     F::load(cur, slot, lane);
-                    A.kblk_local = bk;
+                    A.act_blk = act_lane + bk * 256;
+                    A.sc_blk = sc_lane + bk * (4 * MT);
+                    A.bs_blk = bs_lane + bk * (2 * MT * BSB);
                     if (NT == 1 || ntiles == 1)
                         F::template compute<NT, 1>(cur, A, lane, fp);
                     else
@@ -560,13 +558,9 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
             return o;
         };
         P.act_stride = ks_blocks * 256 + 16;
-        P.scale_stride = ks_blocks;
-        P.bs_stride = ks_blocks * bs_per_block + 16;
-        while ((P.bs_stride / 4) % 8 != 4) P.bs_stride += 4;
         P.off_act = take((uint32_t)MT * P.act_stride);
-        P.off_scale = take((uint32_t)MT * P.scale_stride * 4);
-        P.off_bs_hi = take((uint32_t)MT * P.bs_stride);
-        P.off_bs_lo = take((uint32_t)MT * P.bs_stride);
+        P.off_scale = take((uint32_t)MT * ks_blocks * 4);
+        P.off_bs = take((uint32_t)2 * MT * ks_blocks * bs_per_block);
         // per-warp rings of DEPTH K-blocks: 4 slots for Q4_K (2368 B each), 3 for Q6_K (3360 B each)
         const int depth = dtype == CANDLE_GGML_Q4K ? 4 : 3;
         const uint32_t slot_bytes = 2u * (dtype == CANDLE_GGML_Q4K ? Q4K_HTB : Q6K_HTB);
