@@ -30,6 +30,13 @@ namespace cmoe {
 
 namespace {
 
+// a * b + c in one instruction (the compiler may otherwise regroup sums of products)
+__device__ __forceinline__ int imad(int a, int b, int c) {
+    int d;
+    asm("mad.lo.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 constexpr int Q4K_HTB = 1184;
 constexpr int Q6K_HTB = 1680;
 constexpr int DIRECT_WARPS = 16;
@@ -104,10 +111,11 @@ struct DirQ4K {
                 int p[4], q[4];
                 mma_s8_k32_z(p, alo, b[0], b[1]);
                 mma_s8_k32_z(q, ahi, b[2], b[3]);
-                c[nt][0] += sAl * p[0] + sAh * q[0];
-                c[nt][1] += sAl * p[1] + sAh * q[1];
-                c[nt][2] += sBl * p[2] + sBh * q[2];
-                c[nt][3] += sBl * p[3] + sBh * q[3];
+                // two multiply-adds per accumulator (written as a chain: a sum of the two products first costs a third add)
+                c[nt][0] = imad(sAh, q[0], imad(sAl, p[0], c[nt][0]));
+                c[nt][1] = imad(sAh, q[1], imad(sAl, p[1], c[nt][1]));
+                c[nt][2] = imad(sBh, q[2], imad(sBl, p[2], c[nt][2]));
+                c[nt][3] = imad(sBh, q[3], imad(sBl, p[3], c[nt][3]));
             }
         });
         // min term: sum_j min_j * bsum_j as a [16 x 8] by [8 x 8] product (lanes t = 0, 1 carry the mins)
@@ -216,10 +224,10 @@ struct DirQ6K {
                     for (int s4 = 0; s4 < 4; ++s4) {
                         int p[4];
                         mma_s8_k16_z(p, aA[s4], aB[s4], b[s4]);
-                        c[nt][0] += sA[s4] * p[0];
-                        c[nt][1] += sA[s4] * p[1];
-                        c[nt][2] += sB[s4] * p[2];
-                        c[nt][3] += sB[s4] * p[3];
+                        c[nt][0] = imad(sA[s4], p[0], c[nt][0]);
+                        c[nt][1] = imad(sA[s4], p[1], c[nt][1]);
+                        c[nt][2] = imad(sB[s4], p[2], c[nt][2]);
+                        c[nt][3] = imad(sB[s4], p[3], c[nt][3]);
                     }
                 }
             });
