@@ -417,9 +417,11 @@ static int forward_impl(void* stream, const candle_moe_weights_t* w, const float
         g_probe->hit[0] = true;
     }
     CM_TRY(rc(launch_router_topk(st, x, w->router, w->router_bias, T, d, E, k, w->renorm, ws.topk_ids, ws.topk_w,
-                                 fuse_q ? ws.xq : nullptr, fuse_q ? ws.xs : nullptr, fuse_q ? ws.xb : nullptr)));
+                                 fuse_q ? ws.xq : nullptr, fuse_q ? ws.xs : nullptr, fuse_q ? ws.xb : nullptr,
+                                 T == 1 ? ws.counts : nullptr, ws.offsets, ws.perm_token, ws.pair_pos)));
     mark(st, 0);
-    CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
+    // one token: the router kernel has written the dispatch itself
+    if (T > 1) CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
     mark(st, 1);
     if (!fuse_q) CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
     mark(st, 2);

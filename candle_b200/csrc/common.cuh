@@ -148,7 +148,8 @@ cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
 // qs / scales / bsums non-null: also quantize every row of x the Q8K way (fused, one pass over x)
 cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
                                int d, int E, int k, int renorm, uint32_t* ids, float* w, int8_t* qs = nullptr,
-                               float* scales = nullptr, int16_t* bsums = nullptr);
+                               float* scales = nullptr, int16_t* bsums = nullptr, uint32_t* counts = nullptr,
+                               uint32_t* offsets = nullptr, uint32_t* perm_token = nullptr, uint32_t* pair_pos = nullptr);
 cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
                            uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos);
 // offsets[0..2) = {0, rows}: one group holding every row (used for the always-on shared expert)

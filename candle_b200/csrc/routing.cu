@@ -30,7 +30,9 @@ constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, const float* __restrict__ bias,
                    int d, int E, int k, int renorm, uint32_t* __restrict__ ids, float* __restrict__ wout,
-                   int8_t* __restrict__ qs, float* __restrict__ scales, int16_t* __restrict__ bsums) {
+                   int8_t* __restrict__ qs, float* __restrict__ scales, int16_t* __restrict__ bsums,
+                   uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm_token,
+                   uint32_t* __restrict__ pair_pos) {
     pdl_trigger();
     pdl_wait();
     __shared__ float s_logits[CANDLE_MOE_MAX_EXPERTS];
@@ -146,14 +148,42 @@ router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, co
             }
         }
     }
+    // A single token (the step of one-sequence decoding): its k experts are distinct, so the dispatch is their
+    // ascending order and needs no pass of its own.  Every lane holds the selection.
+    if (counts) {
+        for (int e = lane; e < E; e += 32) {
+            uint32_t hit = 0, below = 0;
+#pragma unroll
+            for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+                if (r < k) {
+                    hit += sel_e[r] == e;
+                    below += sel_e[r] < e;
+                }
+            }
+            counts[e] = hit;
+            offsets[e] = below;
+        }
+        if (lane == 0) offsets[E] = (uint32_t)k;
+#pragma unroll
+        for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
+            if (r < k && lane == r) {
+                uint32_t pos = 0;
+#pragma unroll
+                for (int r2 = 0; r2 < CANDLE_MOE_MAX_TOPK; ++r2) pos += (r2 < k && sel_e[r2] < sel_e[r]);
+                perm_token[pos] = 0u;
+                pair_pos[r] = pos;
+            }
+        }
+    }
 }
 
 cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* router, const float* bias, int64_t T,
                                int d, int E, int k, int renorm, uint32_t* ids, float* w, int8_t* qs, float* scales,
-                               int16_t* bsums) {
+                               int16_t* bsums, uint32_t* counts, uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos) {
     if (T == 0) return cudaSuccess;
+    if (counts && (T != 1 || !offsets || !perm_token || !pair_pos)) return cudaErrorInvalidValue;  // single-token dispatch only
     return launch_k(router_topk_kernel, dim3((unsigned)T), dim3(ROUTER_THREADS), 0, st, x, router, bias, d, E, k, renorm,
-                    ids, w, qs, scales, bsums);
+                    ids, w, qs, scales, bsums, counts, offsets, perm_token, pair_pos);
 }
 
 // ------------------------------------------------------------------------------------------------
