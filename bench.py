@@ -421,7 +421,7 @@ def run_ours(args, cfg):
                 "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]}
-        if T > 64 and cfg["dt13"] != 8:
+        if T > 128 and cfg["dt13"] != 8:
             # large batches run the tcgen05 grouped GEMM: the bound is the tensor pipe.  Algorithmic flops of the
             # dominant product (the second multiply of every Q6_K slab is not counted).
             sus, burst, kind = tensor_peaks()

@@ -13,9 +13,13 @@ namespace {
 
 // Above this bound on the rows of one expert the tensor-core GEMM takes the k-quant products (below, the decode
 // kernels); CANDLE_MOE_GEMM_MIN_ROWS overrides it (experiments).
+// A single-device forward only knows the bound T on the rows of an expert, and its experts usually hold about
+// k T / E rows, i.e. a few of the decode kernels' 16-row groups.  Measured on the Mixtral-shaped layer (decode
+// kernels / GEMM, microseconds): T = 65 349 / 503, 96 384 / 537, 128 473 / 554, 160 569 / 584.
+constexpr int64_t DECODE_MAX_ROWS = 128;
 inline int64_t gemm_min_rows() {
     const char* v = std::getenv("CANDLE_MOE_GEMM_MIN_ROWS");
-    return v && v[0] ? std::atoll(v) : 64;
+    return v && v[0] ? std::atoll(v) : DECODE_MAX_ROWS;
 }
 // When the caller knows the ACTUAL largest row count of an expert (expert parallelism: the host has the counts), the
 // GEMM already pays off above 16 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
@@ -25,7 +29,7 @@ constexpr int64_t GEMM_MIN_ROWS_EXACT = 16;
 constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
-inline int k_split_slots(int64_t T) { return T <= 64 ? MAX_K_SPLITS : 4; }
+inline int k_split_slots(int64_t T) { return T <= gemm_min_rows() ? MAX_K_SPLITS : 4; }
 
 struct Workspace {
     // routing
@@ -272,7 +276,7 @@ struct ExpertBufs {
 };
 
 // The routed experts over P rows grouped by expert (device offsets [E + 1]); no expert has more than max_rows
-// rows.  Picks, per product, the decode kernels over the repacked copies (max_rows <= 64), the tensor-core GEMM
+// rows.  Picks, per product, the decode kernels over the repacked copies (max_rows <= 128), the tensor-core GEMM
 // (more than that, scratch present), or the streaming / row forms.  Leaves *eo_splits partial outputs in b.eo.
 int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs& p1, const ExpertPtrs& p3,
                 const ExpertPtrs& p2, int64_t max_rows, int64_t P, const uint32_t* offsets, const uint32_t* row_of,
@@ -280,7 +284,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
                 bool marks, bool rows_exact = false) {
     const int E = w->n_experts, d = w->d_model, ff = w->d_ff;
     const bool large = b.gemm && max_rows > (rows_exact ? GEMM_MIN_ROWS_EXACT : gemm_min_rows()) && gemm_enabled();
-    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= 64 && !large;
+    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= std::max<int64_t>(gemm_min_rows(), 64) && !large;
     bool gate_done = false, down_done = false;
     *eo_splits = 1;
     ExpertPtrs q1, q3, q2;

@@ -78,7 +78,7 @@ typedef struct candle_moe_weights {
     const void* shared_w2;        /* device, [d_model, d_ff_shared] */
     const float* shared_gate;     /* device f32 [d_model] (shared_expert_gate) */
     /* Optional decode-path copies made by candle_moe_prepack (host arrays of device pointers, or
-     * NULL): when all three are given, batches of up to 64 rows read these instead of the GGUF
+     * NULL): when all three are given, batches of up to 128 rows read these instead of the GGUF
      * blocks.  The GGUF pointers above stay required (larger batches use them). */
     const void* const* w1_prepacked;
     const void* const* w3_prepacked;

@@ -151,8 +151,10 @@ def test_single_rank_equals_the_single_device_block(orc, torch_cuda, T, prepack)
     y_one = blk.forward(xd).cpu().numpy()
     ref = orc.moe_forward(mw, x)
     assert H.rel_l2(y_ep, ref.y) <= H.REL_L2_TOL and H.max_rel(y_ep, ref.y) <= H.MAX_REL_TOL
-    # same kernels over the same quantized rows: the expert-parallel path changes no arithmetic
-    assert H.rel_l2(y_ep, y_one) < 1e-6
+    # same quantized rows; where both paths pick the same kernels the expert-parallel path changes no arithmetic.
+    # At 96 and 110 rows the local phase knows the actual rows per expert (above 16: tensor-core form) while the
+    # single-device block only knows the bound T (up to 128: decode kernels), and the two forms round differently.
+    assert H.rel_l2(y_ep, y_one) < (3e-4 if T in (96, 110) else 1e-6)
     assert ep.last_rows == T * 2
 
 
