@@ -534,7 +534,7 @@ def run_ep(args, cfg, torch, dist, rank, world, local, dev):
         El = cfg["E"] // world
         per13, per2 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], d), mat_bytes(cfg["dt2"], d, cfg["ff"])
         ex_ms = phase_ms["experts"]
-        if rows_expert_max > 64:  # the tensor-core form; up to 64 rows per expert take the decode kernels
+        if rows_expert_max > 16:  # the tensor-core form; up to 16 actual rows per expert take the decode kernels
             sus, burst, kind = tensor_peaks()
             flops = 2.0 * rows_max * 3 * d * cfg["ff"]
             tf = flops / (ex_ms * 1e-3) / 1e12
