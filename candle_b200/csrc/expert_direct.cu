@@ -295,37 +295,41 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
     constexpr int VEC_PER_HT = F::HTB / 16;      // 16-byte vectors per half-tile block
     const uint32_t ring = smem_u32(smem + P.off_ring) + (uint32_t)warp * (DEPTH * SLOT_BYTES);
 
-    // cost-balanced contiguous share of the (token group, split, tile) sequence, cost = blocks streamed
+    // Cost-balanced contiguous share of the (token group, split, tile) sequence.  Cost = blocks streamed, weighted
+    // by what a block costs to multiply: a group of more than eight rows takes two position tiles per block, which
+    // is 11 : 8 in issued instructions against a group of up to eight.
     const int tiles = P.N / TILE_N;
-    int gtot = 0;
-    for (int i = 0; i < P.E; ++i) gtot += (int)((s_offs[i + 1] - s_offs[i] + MT - 1) / MT);
-    const long long gcost = (long long)tiles * P.kb;
-    const long long ctot = gcost * gtot;
+    auto group_weight = [](uint32_t rows) { return (NT > 1 && rows > 8) ? 11 : 8; };
+    long long ctot = 0;
+    for (int i = 0; i < P.E; ++i) {
+        const uint32_t cnt = s_offs[i + 1] - s_offs[i];
+        ctot += (long long)tiles * P.kb * ((long long)(cnt / MT) * group_weight(MT) + (cnt % MT ? group_weight(cnt % MT) : 0));
+    }
     const long long lo = ctot * blockIdx.x / gridDim.x, hi = ctot * (blockIdx.x + 1) / gridDim.x;
     if (lo >= hi) return;
     const size_t ht_stride = (size_t)P.kb * F::HTB;  // bytes of one half-tile over the whole K
 
-    int e = 0, acc_groups = 0;
-    for (int gidx = (int)(lo / gcost); gidx <= (int)((hi - 1) / gcost); ++gidx) {
-        // (expert, token group) of gidx
-        while (e < P.E) {
-            const int ng = (int)((s_offs[e + 1] - s_offs[e] + MT - 1) / MT);
-            if (gidx < acc_groups + ng) break;
-            acc_groups += ng;
-            ++e;
-        }
-        if (e >= P.E) break;
-        const int grp = gidx - acc_groups;
-        const uint32_t p_base = s_offs[e] + (uint32_t)grp * MT;
-        const uint32_t p_end = min(s_offs[e + 1], p_base + MT);
-        const int ntiles = (int)(p_end - p_base + 7) / 8;
+    long long acc = 0;  // cost of the groups before the current one
+    for (int e = 0; e < P.E && acc < hi; ++e) {
+      const uint32_t cnt = s_offs[e + 1] - s_offs[e];
+      for (uint32_t g0 = 0; g0 < cnt && acc < hi; g0 += MT) {
+        const uint32_t rows = min((uint32_t)MT, cnt - g0);
+        const int w = group_weight(rows);
+        const long long gcost = (long long)tiles * P.kb * w;
+        const long long g_lo = acc;
+        acc += gcost;
+        if (acc <= lo) continue;
+        const uint32_t p_base = s_offs[e] + g0;
+        const uint32_t p_end = p_base + rows;
+        const int ntiles = (int)(rows + 7) / 8;
         for (int sp = 0; sp < P.splits; ++sp) {
             const int blk0 = P.blk_start[sp], nblk = P.blk_start[sp + 1] - blk0;
-            const long long ph_lo = (long long)gidx * gcost + (long long)tiles * blk0;
-            const long long ph_hi = ph_lo + (long long)tiles * nblk;
+            const long long unit = (long long)nblk * w;  // cost of one tile over this split
+            const long long ph_lo = g_lo + (long long)tiles * blk0 * w;
+            const long long ph_hi = ph_lo + (long long)tiles * unit;
             const long long a = lo > ph_lo ? lo : ph_lo, b = hi < ph_hi ? hi : ph_hi;
             if (a >= b) continue;
-            const int tile_lo = (int)((a - ph_lo + nblk - 1) / nblk), tile_hi = (int)((b - ph_lo + nblk - 1) / nblk);
+            const int tile_lo = (int)((a - ph_lo + unit - 1) / unit), tile_hi = (int)((b - ph_lo + unit - 1) / unit);
             if (tile_lo >= tile_hi) continue;
 
             // ---- make the token group's int8 rows, scales and block sums resident ----
@@ -441,6 +445,7 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                 }
             }
         }
+      }
     }
 }
 
