@@ -264,12 +264,16 @@ struct DirectParams {
     int E, K, N, kb, splits, MT;
     int blk_start[9];  // split s covers blocks [blk_start[s], blk_start[s + 1])
     int act_stride;
-    uint32_t off_act, off_scale, off_bs, off_ring;
+    uint32_t off_act, off_scale, off_bs, off_ring, off_part;
 };
 
 // DEPTH = ring slots per warp (DEPTH - 1 blocks in flight while one is multiplied)
 template <class F, bool GATE_UP, int NT, int DEPTH>
-__global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const __grid_constant__ DirectParams P) {
+// The one-position-tile Q4_K kernels are held to 96 registers (a bound of 608 threads; they are launched with 512,
+// and Q6_K would spill): the
+// registers a CTA leaves free let the CTAs of the next kernel on the stream become resident and run their
+// prologue under programmatic dependent launch while this one drains.
+__global__ void __launch_bounds__(NT == 1 && F::HTB == Q4K_HTB ? 608 : DIRECT_THREADS, 1) expert_direct_kernel(const __grid_constant__ DirectParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     __shared__ int s_rows[16];
@@ -294,6 +298,7 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
     constexpr int SLOT_BYTES = 2 * F::HTB;       // both half-tile blocks of one K-block
     constexpr int VEC_PER_HT = F::HTB / 16;      // 16-byte vectors per half-tile block
     const uint32_t ring = smem_u32(smem + P.off_ring) + (uint32_t)warp * (DEPTH * SLOT_BYTES);
+    const uint32_t part_base = smem_u32(smem + P.off_part);  // 512 bytes per warp (one-position-tile kernels only)
 
     // Cost-balanced contiguous share of the (token group, split, tile) sequence.  Cost = blocks streamed, weighted
     // by what a block costs to multiply: a group of more than eight rows takes two position tiles per block, which
@@ -368,28 +373,100 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
             }
             __syncthreads();
 
-            // ---- every warp streams its own tiles over the whole K-range of this split ----
-            for (int tile = tile_lo + warp; tile < tile_hi; tile += DIRECT_WARPS) {
+            // ---- every warp streams its own tiles over the K-range of this split ----
+            // Whole rounds of 16 tiles go one tile per warp over all the blocks.  The tiles left over (fewer than 16)
+            // are shared so that no warp of the CTA idles through a last round, and the partial sums meet in shared
+            // memory, added in block order by the warp that holds a tile's first block:
+            //   one position tile (a scratch of 512 bytes per warp exists): the left-over tiles' blocks, taken as one
+            //     sequence, are cut into 16 equal ranges; a range touches at most two tiles;
+            //   two position tiles (no room for the scratch): teams of 2, 4, 8 or 16 warps split a tile's blocks and
+            //     hand their sums over through their own rings, which are free by then.
+            const int n_t = tile_hi - tile_lo, n_rounds = n_t / DIRECT_WARPS, rem = n_t - n_rounds * DIRECT_WARPS;
+            constexpr bool RANGES = NT == 1;
+            int team = 1;
+            if (!RANGES && rem > 0)
+                while (2 * team * rem <= DIRECT_WARPS) team *= 2;
+            const bool shared_round = rem > 0 && (RANGES || team > 1);  // uniform over the CTA
+            const int my_rem = warp / team, part = warp - my_rem * team;
+            const int rem_blocks = rem * nblk;  // RANGES: this warp's range [q0, q1) of the left-over block sequence
+            const int q0 = RANGES ? rem_blocks * warp / DIRECT_WARPS : 0, q1 = RANGES ? rem_blocks * (warp + 1) / DIRECT_WARPS : 0;
+            int n_items = n_rounds;
+            if (RANGES) {
+                if (q1 > q0) n_items += 1 + ((q1 - 1) / nblk > q0 / nblk);
+            } else if (my_rem < rem) {
+                n_items += 1;
+            }
+            const int g = lane >> 2, t = lane & 3;
+            uint64_t fp[NT][2];  // per position tile: (row g | row g + 8) x two positions, packed f32 pairs
+            auto store_tile = [&](int tile) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    float f[4];
+                    f32x2_unpack(fp[nt][0], f[0], f[1]);
+                    f32x2_unpack(fp[nt][1], f[2], f[3]);
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const uint32_t p = p_base + nt * 8 + 2 * t + cc;
+                        if (p < p_end) {
+                            if (GATE_UP) {
+                                P.out[(int64_t)p * P.N + tile * 8 + g] = silu_f(f[cc]) * f[2 + cc];
+                            } else {
+                                float* o = P.out + (int64_t)sp * P.out_split_stride + (int64_t)p * P.N + tile * 16 + g;
+                                o[0] = f[cc];
+                                o[8] = f[2 + cc];
+                            }
+                        }
+                    }
+                }
+            };
+            int own_tile = -1;    // left-over tile whose sum this warp completes after the barrier
+            bool hand_over;       // this item's sum goes to the scratch for another warp to add
+            for (int it = 0; it < n_items; ++it) {
+                int tile = tile_lo + warp + DIRECT_WARPS * it, b0 = 0, b1 = nblk;
+                hand_over = false;
+                if (it >= n_rounds) {
+                    if (RANGES) {
+                        const int q = it == n_rounds ? q0 : (q0 / nblk + 1) * nblk;  // second item: the next tile from its start
+                        const int tl = q / nblk;
+                        b0 = q - tl * nblk;
+                        b1 = min(nblk, b0 + (q1 - q));
+                        tile = tile_lo + n_rounds * DIRECT_WARPS + tl;
+                        if (b0 > 0)
+                            hand_over = true;
+                        else if (b1 < nblk)
+                            own_tile = tile;
+                    } else {
+                        tile = tile_lo + n_rounds * DIRECT_WARPS + my_rem;
+                        if (team > 1) {
+                            b0 = nblk * part / team;
+                            b1 = nblk * (part + 1) / team;
+                            if (part == 0)
+                                own_tile = tile;
+                            else
+                                hand_over = true;
+                        }
+                    }
+                }
+                const int nb = b1 - b0;
                 const uint8_t* hta;
                 const uint8_t* htb;
                 if (GATE_UP) {
-                    hta = P.wa.p[e] + (size_t)tile * ht_stride + (size_t)blk0 * F::HTB;
-                    htb = P.wb.p[e] + (size_t)tile * ht_stride + (size_t)blk0 * F::HTB;
+                    hta = P.wa.p[e] + (size_t)tile * ht_stride + (size_t)(blk0 + b0) * F::HTB;
+                    htb = P.wb.p[e] + (size_t)tile * ht_stride + (size_t)(blk0 + b0) * F::HTB;
                 } else {
-                    hta = P.wa.p[e] + (size_t)(2 * tile) * ht_stride + (size_t)blk0 * F::HTB;
+                    hta = P.wa.p[e] + (size_t)(2 * tile) * ht_stride + (size_t)(blk0 + b0) * F::HTB;
                     htb = hta + ht_stride;
                 }
-                uint64_t fp[NT][2];  // per position tile: (row g | row g + 8) x two positions, packed f32 pairs
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) fp[nt][0] = fp[nt][1] = 0ull;
-                // fill one ring slot with block bk of both half-tiles (16-byte cp.async per lane).  The vector index
+                // fill one ring slot with block j of both half-tiles (16-byte cp.async per lane).  The vector index
                 // of a lane in pass i is lane + 32 i, so which half-tile a pass reads is known at compile time except
                 // for the one pass that straddles the boundary: straight-line code, one predicate for the ragged end.
-                auto issue = [&](int bk) {
-                    if (bk < nblk) {
-                        const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES + 16 * lane;
-                        const uint8_t* sa = hta + (size_t)bk * F::HTB + 16 * lane;
-                        const uint8_t* sb = htb + (size_t)bk * F::HTB + 16 * lane - 16 * VEC_PER_HT;
+                auto issue = [&](int j) {
+                    if (j < nb) {
+                        const uint32_t slot = ring + (uint32_t)(j % DEPTH) * SLOT_BYTES + 16 * lane;
+                        const uint8_t* sa = hta + (size_t)j * F::HTB + 16 * lane;
+                        const uint8_t* sb = htb + (size_t)j * F::HTB + 16 * lane - 16 * VEC_PER_HT;
                         constexpr int PASSES = (2 * VEC_PER_HT + 31) / 32;
                         static_for<PASSES>([&](auto Ic) {
                             constexpr int i = decltype(Ic)::value;
@@ -408,13 +485,14 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                 __syncwarp();  // the previous tile's last slot reads are done in every lane
 #pragma unroll
                 for (int i = 0; i < DEPTH - 1; ++i) issue(i);
-                for (int bk = 0; bk < nblk; ++bk) {
-                    cp_async_wait<DEPTH - 2>();  // this lane's copies of block bk have landed
-                    __syncwarp();                // ... and everyone else's; slot (bk - 1) % DEPTH is free again
-                    issue(bk + DEPTH - 1);
+                for (int j = 0; j < nb; ++j) {
+                    cp_async_wait<DEPTH - 2>();  // this lane's copies of block j have landed
+                    __syncwarp();                // ... and everyone else's; slot (j - 1) % DEPTH is free again
+                    issue(j + DEPTH - 1);
                     typename F::Frag cur;
-                    const uint32_t slot = ring + (uint32_t)(bk % DEPTH) * SLOT_BYTES;
+                    const uint32_t slot = ring + (uint32_t)(j % DEPTH) * SLOT_BYTES;
                     F::load(cur, slot, lane);
+                    const int bk = b0 + j;
                     A.act_blk = act_lane + bk * 256;
                     A.sc_blk = sc_lane + bk * (4 * MT);
                     A.bs_blk = bs_lane + bk * (2 * MT * BSB);
@@ -423,25 +501,41 @@ __global__ void __launch_bounds__(DIRECT_THREADS, 1) expert_direct_kernel(const 
                     else
                         F::template compute<NT, NT>(cur, A, lane, fp);
                 }
-                const int g = lane >> 2, t = lane & 3;
+                if (hand_over) {
+                    // RANGES: a scratch of its own.  Teams: the warp's ring; this is its last item and nothing of its
+                    // copies is in flight any more (the groups still pending are empty ones).
+                    const uint32_t dst = RANGES ? part_base + (uint32_t)warp * 512u : ring;
+                    __syncwarp();
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    float f[1][4];
-                    f32x2_unpack(fp[nt][0], f[0][0], f[0][1]);
-                    f32x2_unpack(fp[nt][1], f[0][2], f[0][3]);
+                    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        const uint32_t p = p_base + nt * 8 + 2 * t + cc;
-                        if (p < p_end) {
-                            if (GATE_UP) {
-                                P.out[(int64_t)p * P.N + tile * 8 + g] = silu_f(f[0][cc]) * f[0][2 + cc];
-                            } else {
-                                float* o = P.out + (int64_t)sp * P.out_split_stride + (int64_t)p * P.N + tile * 16 + g;
-                                o[0] = f[0][cc];
-                                o[8] = f[0][2 + cc];
-                            }
+                        for (int r = 0; r < 2; ++r) sts64(dst + (uint32_t)(((nt * 2 + r) * 32 + lane) * 8), fp[nt][r]);
+                } else if (own_tile != tile) {
+                    store_tile(tile);
+                }
+            }
+            if (shared_round) {
+                __syncthreads();
+                if (own_tile >= 0) {
+                    const int tl = own_tile - (tile_lo + n_rounds * DIRECT_WARPS);
+                    for (int w2 = warp + 1; w2 < DIRECT_WARPS; ++w2) {
+                        uint32_t src;
+                        if (RANGES) {
+                            const int r0 = rem_blocks * w2 / DIRECT_WARPS, r1 = rem_blocks * (w2 + 1) / DIRECT_WARPS;
+                            if (r0 >= (tl + 1) * nblk) break;  // the next tile begins: nothing more belongs to this one
+                            if (r1 == r0) continue;
+                            src = part_base + (uint32_t)w2 * 512u;
+                        } else {
+                            if (w2 >= warp + team) break;
+                            src = ring + (uint32_t)(w2 - warp) * (DEPTH * SLOT_BYTES);
                         }
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int r = 0; r < 2; ++r)
+                                fp[nt][r] = f32x2_add(fp[nt][r], lds64u(src + (uint32_t)(((nt * 2 + r) * 32 + lane) * 8)));
                     }
+                    store_tile(own_tile);
                 }
             }
         }
@@ -578,6 +672,7 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
         const int depth = dtype == CANDLE_GGML_Q4K ? 4 : 3;
         const uint32_t slot_bytes = 2u * (dtype == CANDLE_GGML_Q4K ? Q4K_HTB : Q6K_HTB);
         P.off_ring = take((uint32_t)DIRECT_WARPS * depth * slot_bytes);
+        P.off_part = NT == 1 ? take((uint32_t)DIRECT_WARPS * 512u) : 0u;
         if ((int)off > g_dir_max_smem - 1024) continue;
         P.splits = splits;
         int bs = 0;

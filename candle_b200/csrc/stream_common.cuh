@@ -161,6 +161,12 @@ template <int OFF>
 __device__ __forceinline__ void cp_async16_o(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0 + %2], [%1 + %2], 16;" ::"r"(dst), "l"(src), "n"(OFF) : "memory");
 }
+__device__ __forceinline__ void sts64(uint32_t addr, uint64_t v) { asm volatile("st.shared.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+__device__ __forceinline__ uint64_t lds64u(uint32_t addr) {
+    uint64_t v;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+    return v;
+}
 // 16-byte asynchronous global -> shared copy (per thread, bypassing L1) and its group fences
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
