@@ -639,9 +639,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             while (have) {
                 const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
                 const CUtensorMap* m0 = P.wmaps + 2 * tc.e;
-                // the maps were written by a kernel earlier on the stream (every lane fences: any may be elected)
-                tensormap_fence_acquire(m0);
-                if (GATE_UP) tensormap_fence_acquire(m0 + 1);
+                // the maps were written by a kernel earlier on the stream: fence each once, before its first use by
+                // this warp -- the current expert's on the first tile, the next expert's one tile ahead, because the
+                // prefetches reach into it (every lane fences: any may be elected)
+                if (ab == 0) {
+                    tensormap_fence_acquire(m0);
+                    if (GATE_UP) tensormap_fence_acquire(m0 + 1);
+                }
                 if (have_n && tcn.e != tc.e) {
                     tensormap_fence_acquire(P.wmaps + 2 * tcn.e);
                     if (GATE_UP) tensormap_fence_acquire(P.wmaps + 2 * tcn.e + 1);
