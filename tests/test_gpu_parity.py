@@ -374,7 +374,11 @@ def test_streaming_form_equals_row_form(orc, torch_cuda, name, rows_per_expert, 
 @pytest.mark.parametrize("name,rows_per_expert,k,n,gate_up", [
     ("Q4K", [3, 0, 8, 1], 4096, 64, True), ("Q4K", [16, 5], 1024, 48, True), ("Q4K", [37, 2, 9], 2048, 32, True),
     ("Q4K", [7, 1, 0, 12], 3584, 64, False), ("Q6K", [5, 8, 0, 1], 6144, 64, False), ("Q6K", [16, 23], 2048, 32, False),
-    ("Q6K", [3, 4], 4096, 32, True), ("Q4K", [1], 6144, 128, True), ("Q6K", [7], 4096, 32, False), ("Q4K", [64], 512, 16, False)])
+    ("Q6K", [3, 4], 4096, 32, True), ("Q4K", [1], 6144, 128, True), ("Q6K", [7], 4096, 32, False), ("Q4K", [64], 512, 16, False),
+    # more than 16 tiles per CTA: whole rounds plus left-over tiles shared between the warps (block ranges with
+    # one position tile, teams with two)
+    ("Q4K", [3, 5, 1, 7], 512, 5120, True), ("Q4K", [3, 9, 1, 7], 512, 5120, True),
+    ("Q6K", [2, 8, 6], 512, 13312, False), ("Q6K", [12, 3, 16], 1024, 10240, False)])
 def test_prepacked_form_matches_oracle(orc, torch_cuda, name, rows_per_expert, k, n, gate_up):
     """Decode kernels over the prepacked (register-fragment order) copy of the weights: same integers
     as the oracle's vec_dot, f32 sums in a different order."""
