@@ -193,9 +193,12 @@ struct GemmQ4K {
     // the same pieces from the staged copy of the block (row_addr: shared-window address of the row's 144 bytes;
     // rows are 36 words apart, so the eight lanes of a 16-byte load phase cover all 32 banks once)
     __device__ static __forceinline__ void load_staged(Pre& pr, uint32_t row_addr, int h) {
-        pr.hdr = lds128(row_addr);
-#pragma unroll
-        for (int s = 0; s < 4; ++s) pr.q[s] = lds128(row_addr + 16 + 32 * s + 16 * h);
+        pr.hdr = lds128_o<0>(row_addr);
+        const uint32_t rb = row_addr + 16 * h;
+        pr.q[0] = lds128_o<16>(rb);
+        pr.q[1] = lds128_o<48>(rb);
+        pr.q[2] = lds128_o<80>(rb);
+        pr.q[3] = lds128_o<112>(rb);
     }
     // d (low half) and dmin (high half) of the block, fp16 bits
     __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.hdr.x; }
@@ -483,12 +486,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 uint32_t stg[2][16];
                 tmem_ld16(t_main, stg[0]);
                 tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < NS; ++c) {
+                static_for<NS>([&](auto Cc) {
+                    constexpr int c = decltype(Cc)::value;
                     if (c + 1 < NS) tmem_ld16(t_main + 16 * (c + 1), stg[(c + 1) & 1]);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 dv = lds128(d8_addr + 64 * c + 16 * q);
+                    static_for<4>([&](auto Qc) {
+                        constexpr int q = decltype(Qc)::value;
+                        const uint4 dv = lds128_o<64 * c + 16 * q>(d8_addr);  // base + constant: no address arithmetic
                         // the two scale products of a column pair in one packed multiply, then one fma per value
                         float s0, s1, s2, s3;
                         f32x2_unpack(f32x2_mul(dw2, f32x2_pack_bits(dv.x, dv.y)), s0, s1);
@@ -497,14 +500,14 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         acc[16 * c + 4 * q + 1] = fmaf(s1, __uint_as_float(stg[c & 1][4 * q + 1]), acc[16 * c + 4 * q + 1]);
                         acc[16 * c + 4 * q + 2] = fmaf(s2, __uint_as_float(stg[c & 1][4 * q + 2]), acc[16 * c + 4 * q + 2]);
                         acc[16 * c + 4 * q + 3] = fmaf(s3, __uint_as_float(stg[c & 1][4 * q + 3]), acc[16 * c + 4 * q + 3]);
-                    }
+                    });
                     if (c + 1 < NS) tmem_ld_wait();
                     if (c == (NS >= 2 ? NS - 2 : 0)) {  // every column of this thread has been read: the buffer may be overwritten
                         tc5_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&epi_done[buf]);
                     }
-                }
+                });
                 if (pre) {
                     if (lane < CH) s_d8[ew][buf ^ 1][lane] = d8_n0;
                     if (CH > 32) s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
