@@ -293,7 +293,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         CM_TRY(fill_ptrs(w->w3_prepacked, E, q3));
         CM_TRY(fill_ptrs(w->w2_prepacked, E, q2));
         const cudaError_t ce = launch_expert_direct(st, true, q1, q3, w->dtype_w13, E, d, ff, offsets, row_of, max_rows, xq,
-                                                    xs, xb, b.hidden, nullptr, 0, 1);
+                                                    xs, xb, b.hidden, nullptr, 0, 1, 0, P);
         if (ce == cudaSuccess)
             gate_done = true;
         else if (ce != cudaErrorNotSupported)
@@ -322,7 +322,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
     if (marks) mark(st, 4);
     if (use_prepacked) {
         const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, offsets, nullptr, max_rows, b.hq,
-                                                    b.hs, b.hb, b.eo, eo_splits, P * d, slots, (int)(P < E ? P : E));
+                                                    b.hs, b.hb, b.eo, eo_splits, P * d, slots, (int)(P < E ? P : E), P);
         if (ce == cudaSuccess)
             down_done = true;
         else if (ce != cudaErrorNotSupported)

@@ -183,7 +183,7 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of,
                                  int64_t max_rows_per_expert, const int8_t* aq, const float* ascale,
                                  const int16_t* absum, float* out, int* n_splits_out, int64_t split_stride,
-                                 int max_splits, int max_active_experts = 0);
+                                 int max_splits, int max_active_experts = 0, int64_t total_rows = 0);
 // large-batch grouped GEMM on tcgen05 / TMEM: Q4_K in GGUF layout (repacked = false), Q6_K in the repacked
 // layout (repacked = true); `scratch` of expert_gemm_scratch_bytes(P, K) bytes
 size_t expert_gemm_scratch_bytes(int64_t P, int K);
