@@ -757,16 +757,9 @@ int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int
     bool done = false;
     // the row count is exact here (not a bound as in a routed block): the tensor-core form pays off above 16 rows
     const bool large = ws.gemm && gemm_enabled();
-    if (w_prepacked && rows <= 64 && !large) {
-        const cudaError_t ce = launch_expert_direct(st, false, pp, pp, dtype, 1, k, n, ws.offsets, nullptr, rows, ws.xq, ws.xs,
-                                                    ws.xb, dst, &splits, stride, ws.slots, 1);
-        if (ce == cudaSuccess)
-            done = true;
-        else if (ce != cudaErrorNotSupported)
-            return (int)ce;
-        else
-            splits = 1;
-    }
+    // The decode kernels over the repacked copy are not used here: with a single group their tiles are too few and
+    // too short, and the streaming form over the GGUF blocks is faster (measured, [4096, 4096] Q4_K / [32000, 4096]
+    // Q6_K: 1 row 10.8 / 44.5 us against 17.2 / 46.2; 8 rows 13.5 / 48.6 against 17.7 / 60.1).
     if (!done && large) {
         const bool rp = dtype == CANDLE_GGML_Q6K && w_prepacked;
         const cudaError_t ce = launch_expert_gemm(st, false, rp ? pp : pw, rp ? pp : pw, dtype, rp, 1, k, n, ws.offsets, nullptr,

@@ -238,9 +238,9 @@ CANDLE_MOE_API int candle_moe_ep_experts(void* stream, const candle_moe_weights_
  * -- `QMatMul::forward` (candle-core/src/quantized/mod.rs:533-537 -> `QTensor::cuda_fwd` :520-530 -> `QCudaStorage::fwd`, cuda.rs:484-505)
  * for the dense projections of the model (attention wq/wk/wv/wo quantized_llama.rs:275-277,345, lm head :897).
  * The rows are quantized as `k_quants::matmul` does (k_quants.rs:1873-1920), then the product runs on the same
- * kernels as the experts' down product with one group: the decode kernels over `w_prepacked` (optional, from
- * candle_moe_prepack; up to 64 rows), the tensor-core GEMM (more than 16 rows; Q6_K needs w_prepacked there) or
- * the forms that read the GGUF layout.  Workspace: candle_moe_qmatmul_workspace_bytes bytes, 256-byte aligned. */
+ * kernels as the experts' down product with one group: the tensor-core GEMM above 16 rows (Q6_K reads
+ * `w_prepacked` there, the optional copy made by candle_moe_prepack) and the forms that read the GGUF layout
+ * otherwise (with one group they are faster than the decode kernels over the repacked copy).  Workspace: candle_moe_qmatmul_workspace_bytes bytes, 256-byte aligned. */
 CANDLE_MOE_API int candle_moe_qmatmul_workspace_bytes(int32_t dtype, int64_t rows, int32_t n, int32_t k, size_t* out_bytes);
 CANDLE_MOE_API int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int32_t dtype, int32_t n,
                                       int32_t k, const float* x, int64_t rows, float* out, void* workspace,
