@@ -1,16 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the quantized MoE feed-forward block (candle quantized_llama MlpOrMoe::MoE).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--workload c2|c1|c4|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--workload c2|c1|c4|c5|c3|proj]
     python bench.py --impl reference ...      # the CPU restatement of candle's path, same workload
 
-Workload (default): BASELINE config 2, a Mixtral-8x7B-shaped layer (d=4096, ff=14336, 8 experts,
-top-2, w1/w3 Q4_K, w2 Q6_K, f32 router) at T = 32 decode rows per GPU.  Weights are N(0, 0.02)
-quantized with the reference's quantizer arithmetic, activations N(0, 1); everything synthetic.
-One "step" is one forward of the block over the T rows.  With N > 1 every rank holds the layer and
-processes its own T rows (no data-path collective): weak scaling over token shards.
+Workload (default, "c2"): a Mixtral-8x7B-shaped layer (d=4096, ff=14336, 8 experts, top-2, w1/w3 Q4_K, w2 Q6_K,
+f32 router) at T = 32 decode rows per GPU.  Weights are N(0, 0.02) quantized with the reference's quantizer
+arithmetic, activations N(0, 1); everything synthetic.  One "step" is one forward of the block over the T rows.
+With N > 1 the experts are sharded over the ranks (expert parallelism, one process per GPU): every rank routes
+its own T rows, the packed quantized rows and the expert outputs cross NVLink in two NCCL all-to-alls issued
+inside the library (weak scaling: `value` = N T / step time).  "c1" is the CPU-runnable shape, "c4" the
+fine-grained Q8_0 layer with a shared expert, "c5" the Mixtral-8x22B-shaped layer with skewed routing, "c3" a
+32-layer decode step around the block, "proj" the dense projections.
 
-Output: ONE JSON line on rank 0 (see README / DESIGN.md for the keys).
+Timing: W warm-up steps, then batches of exactly K steps, each bracketed by a barrier + synchronize and a pair of
+CUDA events; batches repeat until a second of device time has been measured and the MEDIAN batch is reported
+(max over ranks).  GPU clocks are sampled with nvidia-smi while those batches run.
+
+Output: ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -146,6 +153,17 @@ def cpu_weights(cfg, seed=0):
     return mw
 
 
+def use_all_host_threads(orc):
+    """OpenMP threads = host cores, whatever OMP_NUM_THREADS says (torch.distributed.run sets it to 1)."""
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0)) or n
+    except (AttributeError, OSError):
+        pass
+    orc.set_threads(n)
+    return orc.max_threads()
+
+
 def time_oracle(mw, x, steps, warmup):
     from oracle import oracle as orc
     for _ in range(warmup):
@@ -164,6 +182,7 @@ def run_reference(args, cfg):
         return
     from oracle import oracle as orc
     orc.build()
+    cores = use_all_host_threads(orc)
     T = args.tokens
     # a step is bounded to a sample of the workload's rows so that K steps stay within minutes
     ops_per_row = 2.0 * cfg["k"] * 3 * cfg["d"] * cfg["ff"] + 2.0 * 3 * cfg["d"] * cfg["ff_shared"]
@@ -171,13 +190,12 @@ def run_reference(args, cfg):
     Ts = min(T, max_rows)
     mw = cpu_weights(cfg)
     x = np.random.default_rng([1, 7]).standard_normal((Ts, cfg["d"]), dtype=np.float32)
-    sec = time_oracle(mw, x, args.steps, min(args.warmup, 2))
+    sec = time_oracle(mw, x, args.steps, args.warmup)
     val = Ts / sec
-    cores = orc.max_threads()
     sample = f"{Ts} of {T} rows per step, all {cfg['E']} experts resident, {cores} OpenMP threads"
     line = {
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": sec * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot / f32 accumulate",
         "data": "synthetic", "config": config_dict(args, cfg),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
@@ -213,7 +231,7 @@ def weights_bytes(cfg):
 # --------------------------------------------------------------------------------------------
 # our arm
 # --------------------------------------------------------------------------------------------
-def build_ep_block(torch, cfg, device, rank, world, prepack=True):
+def build_ep_block(torch, cfg, device, rank, world, prepack=True, max_tokens=None):
     """Expert-parallel block: this rank's E/world experts (expert e is seeded by e, whatever the rank count) and
     the replicated router."""
     from candle_b200 import ExpertParallelMoe, GgmlDType, Mlp, QMatMul, QTensor
@@ -231,7 +249,8 @@ def build_ep_block(torch, cfg, device, rank, world, prepack=True):
     g = torch.Generator(device=device).manual_seed(999)
     router = torch.randn((E, d), generator=g, device=device, dtype=torch.float32) * 0.02
     bias = torch.log(1.0 / (torch.arange(E, dtype=torch.float32) + 1.0)) if cfg.get("zipf_bias") else None
-    return ExpertParallelMoe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], router_bias=bias, prepack=prepack)
+    return ExpertParallelMoe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], router_bias=bias, prepack=prepack,
+                             max_tokens=max_tokens)
 
 
 def build_block(torch, cfg, device, seed=0, prepack=True):
@@ -275,9 +294,12 @@ def oracle_view(torch, blk, cfg):
     return mw
 
 
-# DRAM traffic (dram__bytes_read + dram__bytes_write) per launch of the dominant kernel from one ncu
-# --set full capture of the default workload (profiles/expert_direct_c2_t32.md); other workloads: null.
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the dominant kernel, from one
+# `ncu --set full` capture of this same command line (the default workload); other workloads: null.
 NCU_TRAFFIC_BYTES = {("c2", 32, "gate_up"): 551.5e6, ("c2", 32, "down"): 396.8e6}
+
+MIN_TIMED_SECONDS = 1.0   # batches of K steps repeat until this much device time has been measured
+MAX_BATCHES = 400
 
 
 def time_stages(torch, blk, x, steps):
@@ -290,6 +312,66 @@ def time_stages(torch, blk, x, steps):
             acc = ms if acc is None else {k: acc[k] + v for k, v in ms.items()}
     _, _, counts, _ = blk.last_routing(x.shape[0])
     return {k: v / steps for k, v in acc.items()}, int((counts > 0).sum())
+
+
+def timed_batches(torch, step, steps, barrier, flush=None, min_seconds=MIN_TIMED_SECONDS, agree=None):
+    """Batches of exactly `steps` steps, each between a barrier + synchronize on both sides and timed with CUDA
+    events on the launching stream.  Returns (list of batch milliseconds, wall seconds of the whole region).
+    With `flush` every step is timed on its own so that the L2 flush stays outside the timed region.
+    `agree(n)`: makes every rank run the same number of batches (the steps may hold collectives)."""
+    out = []
+    t0 = time.perf_counter()
+    n_batches = None
+    while True:
+        barrier()
+        if flush is not None:
+            tot = 0.0
+            for _ in range(steps):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step()
+                e1.record()
+                torch.cuda.synchronize()
+                tot += e0.elapsed_time(e1)
+            out.append(tot)
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                step()
+            e1.record()
+            barrier()
+            out.append(e0.elapsed_time(e1))
+        if n_batches is None:
+            # after the first batch: how many batches make up the minimum region (at least 3), agreed between ranks
+            want = max(3, min(MAX_BATCHES, int(min_seconds * 1e3 / max(out[0], 1e-3)) + 1))
+            n_batches = agree(want) if agree else want
+        if len(out) >= n_batches:
+            break
+    barrier()
+    return out, time.perf_counter() - t0
+
+
+def parity_vs_oracle(orc, mw, x_rows, y_rows, ids_rows):
+    """GPU rows against the CPU oracle on the same rows: ids exact (near-ties apart), max-rel and rel-L2 of y."""
+    ref = orc.moe_forward(mw, x_rows)
+    same = (ref.topk_ids == ids_rows).all(axis=1) if ids_rows is not None else np.ones(len(x_rows), bool)
+    a, b = y_rows[same].astype(np.float64), ref.y[same].astype(np.float64)
+    return {"rows": int(len(x_rows)), "ids_exact": bool(same.all()), "ids_mismatched_rows": int((~same).sum()),
+            "rel_l2": float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)),
+            "max_rel": float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)),
+            "bounds": {"rel_l2": 1e-3, "max_rel": 2e-3}}
+
+
+def tensor_roofline(cfg, T_rows, ms, what, flops):
+    sus, burst, kind = tensor_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    note = f"{kind} cuBLAS bf16, sustained (burst {burst:.0f})"
+    if cfg["dt13"] == 8:
+        note += "; the Q8_0 products run on int8 tensor-core MMAs, quoted against the measured bf16 figure"
+    return {"bound": "tensor", "kernel": what, "achieved": tf, "peak": sus, "unit": "TFLOP/s", "frac": tf / sus,
+            "traffic": None, "peak_source": note, "algorithmic_flops_per_launch": flops, "kernel_ms": ms}
 
 
 def run_ours(args, cfg):
@@ -307,7 +389,7 @@ def run_ours(args, cfg):
     if world > 1:
         import datetime
         # a rank that falls out of step must end the run with an error, not hang it
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     import candle_b200  # noqa: F401  loads libcandle_moe_sm100.so or raises
 
     T, d = args.tokens, cfg["d"]
@@ -322,248 +404,250 @@ def run_ours(args, cfg):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
 
     def barrier():
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize(dev)
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    t_load0 = time.perf_counter()
-
-    # ---- device-resident timing: exactly K steps between events, barrier + sync on both sides ----
+    # ---- device-resident timing ----
     for _ in range(args.warmup):
         blk.forward(x, out=y)
     barrier()
-    if small:
-        # each step is timed on its own so the L2 flush stays outside the timed region
-        tot = 0.0
-        for _ in range(args.steps):
-            flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            blk.forward(x, out=y)
-            e1.record()
-            torch.cuda.synchronize(dev)
-            tot += e0.elapsed_time(e1)
-        ms_total = tot
-    else:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            blk.forward(x, out=y)
-        e1.record()
-        barrier()
-        ms_total = e0.elapsed_time(e1)
-    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, barrier, flush)
+    clocks = sampler.stop()
+    ms_total = statistics.median(batches)
 
     # ---- end to end through the public API with host buffers: H2D of x, forward, D2H of y ----
     hx = torch.randn((T, d), dtype=torch.float32).pin_memory()
     hy = torch.empty((T, d), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        blk.forward(x, out=y)
+        hy.copy_(y, non_blocking=True)
+
     for _ in range(min(args.warmup, 3)):
-        x.copy_(hx, non_blocking=True)
-        blk.forward(x, out=y)
-        hy.copy_(y, non_blocking=True)
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(args.steps):
-        x.copy_(hx, non_blocking=True)
-        blk.forward(x, out=y)
-        hy.copy_(y, non_blocking=True)
-        if small:
-            pass
-    e3.record()
-    barrier()
-    ms_e2e = e2.elapsed_time(e3)
+        e2e_step()
+    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, 0.3)
+    ms_e2e = statistics.median(e2e_batches)
 
-    # keep the GPU under the same load until the clock sampler has seen it (not part of any timing)
-    while time.perf_counter() - t_load0 < 1.5:
-        for _ in range(10):
-            blk.forward(x, out=y)
+    x.copy_(torch.randn((T, d), generator=torch.Generator().manual_seed(1), dtype=torch.float32))
+    stage_ms, active = time_stages(torch, blk, x, max(min(args.steps, 50), 10))
+    per_expert13 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], cfg["d"])
+    per_expert2 = mat_bytes(cfg["dt2"], cfg["d"], cfg["ff"])
+    # algorithmic bytes of the block: active experts' blocks + router + x read + y write
+    block_bytes = active * (per_expert13 + per_expert2) + cfg["E"] * d * 4 + 2 * T * d * 4
+    if cfg["ff_shared"]:
+        block_bytes += 2 * mat_bytes(cfg["dt13"], cfg["ff_shared"], d) + mat_bytes(cfg["dt2"], d, cfg["ff_shared"]) + 4 * d
+    block_ops = 2.0 * T * cfg["k"] * 3 * d * cfg["ff"] + 2.0 * T * d * cfg["E"] + 2.0 * T * 3 * d * cfg["ff_shared"]
+    peak, peak_kind = peaks()
+    top = max(("gate_up", "down"), key=lambda n: stage_ms[n])
+    top_bytes = active * (per_expert13 if top == "gate_up" else per_expert2)
+    ach = top_bytes / (stage_ms[top] * 1e-3) / 1e9
+    ms_step = ms_total / args.steps
+    blk_gbs = block_bytes / (ms_step * 1e-3) / 1e9
+
+    # CPU baseline on the same weights (device bytes copied to the host) and the parity of the timed workload
+    from oracle import oracle as orc
+    orc.build()
+    cores = use_all_host_threads(orc)
+    mw = oracle_view(torch, blk, cfg)
+    ops_per_row = 2.0 * cfg["k"] * 3 * d * cfg["ff"] + 2.0 * 3 * d * cfg["ff_shared"]
+    Ts = max(1, min(T, int(1.5e11 / ops_per_row)))
+    xh = x[:Ts].cpu().numpy()
+    n_cpu = 5 if Ts * ops_per_row < 5e10 else 2
+    sec = time_oracle(mw, xh, n_cpu, 1)
+    got = blk.forward(x).cpu().numpy()
+    ids = blk.last_routing(T)[0].numpy().astype(np.uint32)
+    parity = parity_vs_oracle(orc, mw, xh, got[:Ts], ids[:Ts])
+
+    roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s",
+            "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
+            "peak_source": f"{peak_kind} copy bandwidth",
+            "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]}
+    if T > 128:
+        # large batches run tensor-core grouped products: the bound is the tensor pipe.  Algorithmic flops of the
+        # dominant product (the second multiply of every Q6_K slab is not counted).
+        flops = 2.0 * T * cfg["k"] * d * cfg["ff"] * (2 if top == "gate_up" else 1)
+        roof = tensor_roofline(cfg, T, stage_ms[top], top, flops)
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
+        "roofline": roof,
+        "block_roofline": {"bound": "hbm", "algorithmic_bytes": block_bytes, "achieved": blk_gbs,
+                           "frac": blk_gbs / peak, "frac_of_nominal_8TBps": blk_gbs / 8000.0,
+                           "active_experts": active, "tensor_ops": block_ops,
+                           "achieved_tops": block_ops / (ms_step * 1e-3) / 1e12,
+                           "frac_of_tensor_peak": block_ops / (ms_step * 1e-3) / 1e12 / tensor_peaks()[0]},
+        "stage_ms": stage_ms,
+        "timing": {"batches": len(batches), "steps_per_batch": args.steps, "timed_region_s": region_s,
+                   "batch_ms_median": ms_total, "batch_ms_min": min(batches), "batch_ms_max": max(batches)},
+        "parity": parity,
+        "cpu_baseline": {"value": Ts / sec, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{Ts} of {T} rows, same weights and inputs as the GPU step, {n_cpu} timed passes"},
+        "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": ((6 if cfg["dt13"] != 8 else 7) + (5 if cfg["ff_shared"] else 0)) * args.steps,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def ep_oracle_weights(torch, cfg, device):
+    """All E experts of the expert-parallel workload rebuilt on one device (expert e is seeded by e alone, whatever
+    the rank count) and copied to the host for the oracle."""
+    from candle_b200 import GgmlDType, QTensor
+    from oracle import oracle as orc
+    d, ff, E = cfg["d"], cfg["ff"], cfg["E"]
+    w = {"w1": [], "w3": [], "w2": []}
+    for e in range(E):
+        g = torch.Generator(device=device).manual_seed(1000 + e)
+        for name, shape, dt in (("w1", (ff, d), cfg["dt13"]), ("w2", (d, ff), cfg["dt2"]), ("w3", (ff, d), cfg["dt13"])):
+            t = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02
+            w[name].append(QTensor.quantize(t, GgmlDType(dt)).data.cpu().numpy())
+            del t
+    g = torch.Generator(device=device).manual_seed(999)
+    router = (torch.randn((E, d), generator=g, device=device, dtype=torch.float32) * 0.02).cpu().numpy()
+    bias = np.log(1.0 / (np.arange(E) + 1.0)).astype(np.float32) if cfg.get("zipf_bias") else None
+    return orc.MoeWeights(d, ff, cfg["k"], cfg["dt13"], cfg["dt2"], router, w["w1"], w["w3"], w["w2"], renorm=cfg["renorm"],
+                          router_bias=bias)
+
+
+def ep_measure(args, cfg, torch, dist, rank, world, dev, T, steps, warmup, min_seconds, parity_rows, sampler=None):
+    """One expert-parallel workload: T rows per rank per step.  Returns the record (rank 0) or None."""
+    d = cfg["d"]
+    blk = build_ep_block(torch, cfg, dev, rank, world, prepack=not args.no_prepack, max_tokens=T)
+    gx = torch.Generator(device=dev).manual_seed(1 + rank)
+    x = torch.randn((T, d), generator=gx, device=dev, dtype=torch.float32)
+    y = torch.empty_like(x)
+
+    def barrier():
+        dist.barrier()
         torch.cuda.synchronize(dev)
-    clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
+    def agree(n):
+        t = torch.tensor([n if rank == 0 else 0], dtype=torch.int64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = float(t[0]), float(t[1])
+        return int(t)
 
-    if rank == 0:
-        x.copy_(torch.randn((T, d), generator=torch.Generator().manual_seed(1), dtype=torch.float32))
-        stage_ms, active = time_stages(torch, blk, x, max(min(args.steps, 50), 10))
-        per_expert13 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], cfg["d"])
-        per_expert2 = mat_bytes(cfg["dt2"], cfg["d"], cfg["ff"])
-        # algorithmic bytes of the block: active experts' blocks + router + x read + y write
-        block_bytes = active * (per_expert13 + per_expert2) + cfg["E"] * d * 4 + 2 * T * d * 4
-        block_ops = 2.0 * T * cfg["k"] * 3 * d * cfg["ff"] + 2.0 * T * d * cfg["E"]
-        peak, peak_kind = peaks()
-        top = max(("gate_up", "down"), key=lambda n: stage_ms[n])
-        top_bytes = active * (per_expert13 if top == "gate_up" else per_expert2)
-        ach = top_bytes / (stage_ms[top] * 1e-3) / 1e9
-        ms_step = ms_total / args.steps
-        blk_gbs = block_bytes / (ms_step * 1e-3) / 1e9
+    for _ in range(warmup):
+        blk.forward(x, out=y)
+    barrier()
+    if sampler is not None:
+        sampler.start()
+    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), steps, barrier, None, min_seconds, agree)
+    clocks = sampler.stop() if sampler is not None else None
 
-        # CPU baseline on the same weights (device bytes copied to the host) and a parity check
+    hx = torch.randn((T, d), dtype=torch.float32).pin_memory()
+    hy = torch.empty((T, d), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        blk.forward(x, out=y)
+        hy.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    e2e_batches, _ = timed_batches(torch, e2e_step, steps, barrier, None, min(0.3, min_seconds), agree)
+
+    # per-phase device times (events between the phases of a step), outside the timed regions above
+    x.copy_(torch.randn((T, d), generator=torch.Generator(device=dev).manual_seed(1 + rank), device=dev))
+    n_ph = len(blk.PHASES)
+    acc = [0.0] * n_ph
+    reps = max(min(steps, 20), 3)
+    for _ in range(reps):
+        _, ms = blk.forward(x, out=y, timed=True)
+        for i, n in enumerate(blk.PHASES):
+            acc[i] += ms[n] / reps
+    form = blk.form()
+    t = torch.tensor([statistics.median(batches), statistics.median(e2e_batches)] + acc +
+                     [float(blk.last_max_rows), float(blk.last_rows)], dtype=torch.float64, device=dev)
+    tmax = t.clone()
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    rows_all = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+    dist.all_gather(rows_all, torch.tensor([blk.last_rows], dtype=torch.int64, device=dev))
+    rows_per_rank = [int(v) for v in rows_all]
+
+    # the parity forward is a step like any other: every rank takes part, rank 0 compares its own rows
+    yy = blk.forward(x, out=y).cpu().numpy()
+    parity = None
+    if rank == 0 and parity_rows > 0:
         from oracle import oracle as orc
         orc.build()
-        mw = oracle_view(torch, blk, cfg)
-        ops_per_row = 2.0 * cfg["k"] * 3 * d * cfg["ff"] + 2.0 * 3 * d * cfg["ff_shared"]
-        Ts = max(1, min(T, int(1.5e11 / ops_per_row)))
-        xh = x[:Ts].cpu().numpy()
-        n_cpu = 5 if Ts * ops_per_row < 5e10 else 2
-        sec = time_oracle(mw, xh, n_cpu, 1)
-        ref = orc.moe_forward(mw, xh)
-        got = blk.forward(x[:Ts].clone()).cpu().numpy()
-        rel_l2 = float(np.linalg.norm(got.astype(np.float64) - ref.y) / max(np.linalg.norm(ref.y), 1e-30))
-
-        roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s",
-                "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
-                "peak_source": f"{peak_kind} copy bandwidth",
-                "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]}
-        if T > 128 and cfg["dt13"] != 8:
-            # large batches run the tcgen05 grouped GEMM: the bound is the tensor pipe.  Algorithmic flops of the
-            # dominant product (the second multiply of every Q6_K slab is not counted).
-            sus, burst, kind = tensor_peaks()
-            flops = 2.0 * T * cfg["k"] * d * cfg["ff"] * (2 if top == "gate_up" else 1)
-            tf = flops / (stage_ms[top] * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": top, "achieved": tf, "peak": sus, "unit": "TFLOP/s", "frac": tf / sus,
-                    "traffic": None, "peak_source": f"{kind} cuBLAS bf16, sustained (burst {burst:.0f})",
-                    "algorithmic_flops_per_launch": flops, "kernel_ms": stage_ms[top]}
-        line = {
-            "metric": "moe_layer_tokens_per_s", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
-            "roofline": roof,
-            "block_roofline": {"bound": "hbm", "algorithmic_bytes": block_bytes, "achieved": blk_gbs,
-                               "frac": blk_gbs / peak, "frac_of_nominal_8TBps": blk_gbs / 8000.0,
-                               "active_experts": active, "tensor_ops": block_ops,
-                               "achieved_tops": block_ops / (ms_step * 1e-3) / 1e12},
-            "stage_ms": stage_ms,
-            "cpu_baseline": {"value": Ts / sec, "unit": "tokens/s", "cores": orc.max_threads(), "kind": "port",
-                             "sample": f"{Ts} of {T} rows, same weights and inputs as the GPU step, {n_cpu} timed passes",
-                             "gpu_vs_oracle_rel_l2": rel_l2},
-            "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
-                    "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": ((6 if cfg["dt13"] != 8 else 7) + (5 if cfg["ff_shared"] else 0)) * args.steps,
-            "clocks": clocks,
-        }
-        print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        use_all_host_threads(orc)
+        mw = ep_oracle_weights(torch, cfg, dev)
+        n = min(parity_rows, T)
+        parity = parity_vs_oracle(orc, mw, x[:n].cpu().numpy(), yy[:n], None)
+        parity["note"] = "rank 0's rows; the oracle holds all experts, rebuilt from their seeds"
+        del mw
+    blk.close()
+    if rank != 0:
+        return None
+    ms_step = float(tmax[0]) / steps
+    ms_e2e = float(tmax[1]) / steps
+    phase_ms = {n: float(tmax[2 + i]) for i, n in enumerate(blk.PHASES)}
+    rows_expert_max, rows_max = int(tmax[-2]), int(tmax[-1])
+    El = cfg["E"] // world
+    per13, per2 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], d), mat_bytes(cfg["dt2"], d, cfg["ff"])
+    ex_ms = phase_ms["experts"]
+    if rows_expert_max > 64:  # tensor-core form
+        roof = tensor_roofline(cfg, rows_max, ex_ms, "local experts (gate_up + down) on the busiest rank",
+                               2.0 * rows_max * 3 * d * cfg["ff"])
+    else:
+        peak, peak_kind = peaks()
+        byts = El * (per13 + per2)
+        gbs = byts / (ex_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": "local experts (gate_up + down)", "achieved": gbs, "peak": peak,
+                "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": byts, "kernel_ms": ex_ms}
+    row_b = d + d // 8 + d // 64
+    mean_rows = sum(rows_per_rank) / world
+    return {
+        "value": T * world / (ms_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_step,
+        "tokens_per_step_per_gpu": T, "form": {1: "slots (no host synchronisation)", 2: "exact (counts checked on the host)"}[form],
+        "roofline": roof, "stage_ms": phase_ms,
+        "timing": {"batches": len(batches), "steps_per_batch": steps, "timed_region_s": region_s,
+                   "batch_ms_median": float(tmax[0])},
+        "exchange": {"rows_sent_per_rank": T * cfg["k"], "row_bytes_forward": row_b, "row_bytes_back": 4 * d,
+                     "rows_received_per_rank": rows_per_rank, "busiest_over_mean": max(rows_per_rank) / max(mean_rows, 1e-9),
+                     "rows_of_busiest_expert": rows_expert_max},
+        "parity": parity,
+        "e2e": {"value": T * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T * d * 4,
+                "d2h_bytes_per_step": T * d * 4, "ms_per_step": ms_e2e},
+        "clocks": clocks,
+    }
 
 
 def run_ep(args, cfg, torch, dist, rank, world, local, dev):
     """N > 1: expert parallelism.  Every rank holds E / N experts and routes its own T rows per step."""
     if cfg["E"] % world or cfg["dt13"] == 8 or cfg["ff_shared"]:
         raise SystemExit(f"workload {args.workload} has no expert-parallel form over {world} ranks")
-    T, d = args.tokens, cfg["d"]
-    blk = build_ep_block(torch, cfg, dev, rank, world, prepack=not args.no_prepack)
-    gx = torch.Generator(device=dev).manual_seed(1 + rank)
-    x = torch.randn((T, d), generator=gx, device=dev, dtype=torch.float32)
-
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    sampler = ClockSampler(local)
+    T = args.tokens
+    sampler = ClockSampler(local) if rank == 0 else None
+    rec = ep_measure(args, cfg, torch, dist, rank, world, dev, T, args.steps, args.warmup, MIN_TIMED_SECONDS,
+                     parity_rows=min(T, 64), sampler=sampler)
+    c5 = None
+    if args.workload == "c2" and not args.no_c5:
+        # the Mixtral-8x22B-shaped layer with skewed routing, 8192 rows per step split over the ranks
+        cfg5 = dict(WORKLOADS["c5"], zipf_bias=True)
+        torch.cuda.empty_cache()
+        c5 = ep_measure(args, cfg5, torch, dist, rank, world, dev, 8192 // world, 5, 3, 0.2, parity_rows=64)
     if rank == 0:
-        sampler.start()
-    t_load0 = time.perf_counter()
-    for _ in range(args.warmup):
-        y = blk.forward(x)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        y = blk.forward(x)
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-
-    hx = torch.randn((T, d), dtype=torch.float32).pin_memory()
-    hy = torch.empty((T, d), dtype=torch.float32).pin_memory()
-    for _ in range(3):
-        x.copy_(hx, non_blocking=True)
-        hy.copy_(blk.forward(x), non_blocking=True)
-    barrier()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(args.steps):
-        x.copy_(hx, non_blocking=True)
-        hy.copy_(blk.forward(x), non_blocking=True)
-    e3.record()
-    barrier()
-    ms_e2e = e2.elapsed_time(e3)
-
-    # per-phase device times (events between the phases of a step), outside the timed regions above
-    n_ph = len(blk.PHASES)
-    acc = [0.0] * n_ph
-    reps = max(min(args.steps, 20), 5)
-    for _ in range(reps):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph + 1)]
-        it = iter(evs[1:])
-        evs[0].record()
-        blk.forward(x, mark=lambda: next(it).record())
-        torch.cuda.synchronize(dev)
-        for i in range(n_ph):
-            acc[i] += evs[i].elapsed_time(evs[i + 1]) / reps
-    rows_here = blk.last_rows
-    # keep the GPUs under the same load until the clock sampler has seen it.  Every forward holds collectives,
-    # so all ranks must run the SAME number of extra steps: rank 0's estimate, agreed through an all-reduce.
-    left = max(0.0, 1.5 - (time.perf_counter() - t_load0))
-    n_extra = torch.tensor([int(left / max(ms_total / args.steps * 1e-3, 1e-5)) + 1 if rank == 0 else 0],
-                           dtype=torch.int64, device=dev)
-    dist.all_reduce(n_extra, op=dist.ReduceOp.MAX)
-    for _ in range(min(int(n_extra), 20000)):
-        blk.forward(x)
-    torch.cuda.synchronize(dev)
-    clocks = sampler.stop() if rank == 0 else None
-
-    t = torch.tensor([ms_total, ms_e2e] + acc + [float(blk.last_max_rows), float(rows_here)], dtype=torch.float64, device=dev)
-    tmax = t.clone()
-    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = float(tmax[0]), float(tmax[1])
-    phase_ms = {n: float(tmax[2 + i]) for i, n in enumerate(blk.PHASES)}
-    if rank == 0:
-        ms_step = ms_total / args.steps
-        rows_max, rows_expert_max = int(tmax[-1]), int(tmax[-2])
-        El = cfg["E"] // world
-        per13, per2 = 2 * mat_bytes(cfg["dt13"], cfg["ff"], d), mat_bytes(cfg["dt2"], d, cfg["ff"])
-        ex_ms = phase_ms["experts"]
-        if rows_expert_max > 16:  # the tensor-core form; up to 16 actual rows per expert take the decode kernels
-            sus, burst, kind = tensor_peaks()
-            flops = 2.0 * rows_max * 3 * d * cfg["ff"]
-            tf = flops / (ex_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": "local experts (gate_up + down) on the busiest rank", "achieved": tf,
-                    "peak": sus, "unit": "TFLOP/s", "frac": tf / sus, "traffic": None,
-                    "peak_source": f"{kind} cuBLAS bf16, sustained (burst {burst:.0f})",
-                    "algorithmic_flops_per_launch": flops, "kernel_ms": ex_ms}
-        else:
-            peak, peak_kind = peaks()
-            byts = El * (per13 + per2)
-            gbs = byts / (ex_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": "local experts (gate_up + down)", "achieved": gbs, "peak": peak,
-                    "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
-                    "algorithmic_bytes_per_launch": byts, "kernel_ms": ex_ms}
-        row_b = d + d // 8 + d // 64
         line = {
-            "metric": "moe_layer_tokens_per_s", "value": T * world / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "metric": "moe_layer_tokens_per_s", "value": rec["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 dot / f32 accumulate", "data": "synthetic", "config": config_dict(args, cfg),
-            "roofline": roof, "stage_ms": phase_ms,
-            "exchange": {"rows_sent_per_rank": T * cfg["k"], "row_bytes_forward": row_b, "row_bytes_back": 4 * d,
-                         "rows_on_busiest_rank": rows_max, "rows_of_busiest_expert": rows_expert_max},
-            "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
-                    "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": 12 * args.steps,
-            "clocks": clocks,
+            "roofline": rec["roofline"], "stage_ms": rec["stage_ms"], "timing": rec["timing"], "form": rec["form"],
+            "exchange": rec["exchange"], "parity": rec["parity"], "e2e": rec["e2e"],
+            "gpu_launches": 10 * args.steps, "clocks": rec["clocks"],
         }
+        if c5 is not None:
+            c5["workload"] = (f"c5: MoE FFN layer d=6144 ff=16384 E=8 top2 w1/w3 Q4_K w2 Q6_K, router bias log(1/(i+1)), "
+                              f"8192 rows per step = {8192 // world} per GPU over {world} GPUs")
+            line["c5"] = c5
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
@@ -642,6 +726,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["proj"])
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--no-c5", action="store_true",
+                    help="N > 1: skip the Mixtral-8x22B-shaped sub-record that accompanies the default workload")
     ap.add_argument("--no-prepack", action="store_true",
                     help="decode straight from the GGUF blocks instead of the one-time prepacked copies")
     args = ap.parse_args()

@@ -22,7 +22,12 @@ ERROR_NAMES = {
     -5: "CANDLE_MOE_E_ALIGN (pointer alignment)",
     -6: "CANDLE_MOE_E_NO_DEVICE",
     -7: "CANDLE_MOE_E_STATIC_SCRATCH (needs more than the built-in 16 MiB scratch)",
+    -8: "CANDLE_MOE_E_NCCL (libnccl missing or an NCCL call failed)",
+    -9: "CANDLE_MOE_E_EP_MISMATCH (the ranks' exchange metadata disagree; nothing was exchanged)",
 }
+
+# candle_moe_set_tuning keys
+TUNE_GEMM_ENABLED, TUNE_GEMM_MIN_ROWS, TUNE_STREAM_MAX_ROWS, TUNE_FORCE_ROWS, TUNE_MID_ENABLED = range(5)
 
 
 class CandleMoeError(RuntimeError):
@@ -49,11 +54,23 @@ class MoeWeightsC(C.Structure):
     ]
 
 
+class EpConfigC(C.Structure):
+    """candle_moe_ep_config_t"""
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32), ("n_experts_global", C.c_int32), ("top_k", C.c_int32),
+        ("renorm", C.c_int32), ("max_tokens", C.c_int32), ("force_form", C.c_int32),
+        ("inject_count_mismatch", C.c_int32), ("max_recv_rows", C.c_int64),
+        ("router", C.c_void_p), ("router_bias", C.c_void_p),
+    ]
+
+
 # every symbol include/candle_moe.h declares: name -> (restype, argtypes)
 _P, _I32, _I64, _SZ = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t
 _PP = C.POINTER(C.c_void_p)
 SYMBOLS = {
     "candle_moe_version": (C.c_char_p, []),
+    "candle_moe_set_tuning": (C.c_int, [C.c_int32, C.c_int64]),
+    "candle_moe_get_tuning": (C.c_int, [C.c_int32, C.POINTER(C.c_int64)]),
     "candle_moe_workspace_bytes": (C.c_int, [C.POINTER(MoeWeightsC), _I64, C.POINTER(_SZ)]),
     "candle_moe_router_topk": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _P, _P]),
     "candle_moe_permute": (C.c_int, [_P, _P, _I64, _I32, _I32, _P, _P, _P, _P]),
@@ -72,6 +89,19 @@ SYMBOLS = {
     "candle_moe_grouped_gate_up_prepacked": (C.c_int, [_P, _PP, _PP, _I32, _I32, _I32, _I32, _P, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_grouped_down_prepacked": (C.c_int, [_P, _PP, _I32, _I32, _I32, _I32, _P, _I64, _P, _P, _P, _P]),
     "candle_moe_device_status": (C.c_int, [C.POINTER(C.c_int32)]),
+    "candle_moe_device_status_reset": (C.c_int, []),
+    "candle_moe_selftest_bounded_wait": (C.c_int, [_P, _I32]),
+    "candle_moe_ep_unique_id": (C.c_int, [_P]),
+    "candle_moe_ep_comm_init": (C.c_int, [_P, _I32, _I32, C.POINTER(C.c_void_p)]),
+    "candle_moe_ep_comm_from_nccl": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
+    "candle_moe_ep_comm_destroy": (C.c_int, [_P]),
+    "candle_moe_ep_last_error": (C.c_char_p, []),
+    "candle_moe_ep_forward_workspace_bytes": (C.c_int, [C.POINTER(EpConfigC), C.POINTER(MoeWeightsC), C.POINTER(_SZ)]),
+    "candle_moe_ep_forward_form": (C.c_int, [C.POINTER(EpConfigC), C.POINTER(MoeWeightsC), C.POINTER(C.c_int32),
+                                             C.POINTER(C.c_int64)]),
+    "candle_moe_ep_forward": (C.c_int, [_P, _P, C.POINTER(EpConfigC), C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ]),
+    "candle_moe_ep_forward_timed": (C.c_int, [_P, _P, C.POINTER(EpConfigC), C.POINTER(MoeWeightsC), _P, _I64, _P, _P, _SZ,
+                                              _P, _P]),
     "candle_moe_ep_row_bytes": (C.c_int, [_I32, C.POINTER(C.c_size_t)]),
     "candle_moe_ep_pack": (C.c_int, [_P, _P, _I64, _I32, _P, _P, _P, _P]),
     "candle_moe_ep_workspace_bytes": (C.c_int, [C.POINTER(MoeWeightsC), _I64, C.POINTER(C.c_size_t)]),

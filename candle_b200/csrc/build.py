@@ -24,10 +24,11 @@ SOURCES = {
     "expert_direct.cu": [],
     "expert_gemm.cu": [],
     "expert_parallel.cu": [],
+    "ep_nccl.cu": [],
     "expert_q80.cu": [],
 }
-# extra nvcc flags for local experiments, e.g. CANDLE_MOE_NVCC_FLAGS="-DCMOE_STREAM_TIMING"
-EXTRA = os.environ.get("CANDLE_MOE_NVCC_FLAGS", "").split()
+
+
 COMMON = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
           "-Xcompiler", "-fvisibility=hidden"]
 
@@ -54,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src, extra in SOURCES.items():
         obj = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc(), *COMMON, *EXTRA, *extra, "-c", os.path.join(HERE, src), "-o", obj]
+        cmd = [nvcc(), *COMMON, *extra, "-c", os.path.join(HERE, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -68,7 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    cmd = [nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+    cmd = [nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart", "-ldl"]
     subprocess.run(cmd, check=True)
     return LIB
 

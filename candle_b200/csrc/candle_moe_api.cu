@@ -5,28 +5,23 @@
 #include <cstring>
 #include <mutex>
 
-#include "common.cuh"
+#include "api_internal.cuh"
 
 using namespace cmoe;
 
 namespace {
 
-// Above this bound on the rows of one expert the tensor-core GEMM takes the k-quant products (below, the decode
-// kernels); CANDLE_MOE_GEMM_MIN_ROWS overrides it (experiments).
+// Above this bound on the rows of one expert (default 128) the tensor-core GEMM takes the k-quant products (below,
+// the decode kernels); the tuning key GEMM_MIN_ROWS changes it.
 // A single-device forward only knows the bound T on the rows of an expert, and its experts usually hold about
 // k T / E rows, i.e. a few of the decode kernels' 16-row groups.  Measured on the Mixtral-shaped layer (decode
 // kernels / GEMM, microseconds): T = 65 349 / 503, 96 384 / 537, 128 473 / 554, 160 569 / 584.
-constexpr int64_t DECODE_MAX_ROWS = 128;
-inline int64_t gemm_min_rows() {
-    const char* v = std::getenv("CANDLE_MOE_GEMM_MIN_ROWS");
-    return v && v[0] ? std::atoll(v) : DECODE_MAX_ROWS;
-}
+inline int64_t gemm_min_rows() { return tuning_get(TUNE_GEMM_MIN_ROWS); }
 // When the caller knows the ACTUAL largest row count of an expert (expert parallelism: the host has the counts), the
 // GEMM already pays off above 16 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
 // with 32-wide position tiles).  (A single-device
 // forward only knows the bound T, and its experts usually hold a fraction of that.)
 constexpr int64_t GEMM_MIN_ROWS_EXACT = 16;
-constexpr int MAX_K_SPLITS = 8;  // partial outputs the down product may leave for the combine kernel
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
 inline int k_split_slots(int64_t T) { return T <= gemm_min_rows() ? MAX_K_SPLITS : 4; }
@@ -62,14 +57,6 @@ struct Workspace {
     void* gemm;  // operand scratch of the large-batch tensor-core GEMM (null for decode-sized T)
     size_t total;
 };
-
-template <class T>
-T* carve(uint8_t* base, size_t& off, size_t count) {
-    off = align_up(off, 256);
-    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
-    off += count * sizeof(T);
-    return p;
-}
 
 Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     uint8_t* base = static_cast<uint8_t*>(base_);
@@ -127,7 +114,8 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     return ws;
 }
 
-int check_weights(const candle_moe_weights_t* w) {
+}  // namespace
+int cmoe::check_weights(const candle_moe_weights_t* w) {
     if (!w) return CANDLE_MOE_E_NULL;
     if (w->d_model <= 0 || w->d_ff <= 0 || w->n_experts <= 0 || w->top_k <= 0) return CANDLE_MOE_E_SHAPE;
     if (w->n_experts > CANDLE_MOE_MAX_EXPERTS || w->top_k > CANDLE_MOE_MAX_TOPK || w->top_k > w->n_experts)
@@ -145,7 +133,7 @@ int check_weights(const candle_moe_weights_t* w) {
     return CANDLE_MOE_OK;
 }
 
-int fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
+int cmoe::fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
     if (!host) return CANDLE_MOE_E_NULL;
     std::memset(&out, 0, sizeof(out));
     for (int e = 0; e < E; ++e) {
@@ -156,13 +144,9 @@ int fill_ptrs(const void* const* host, int E, ExpertPtrs& out) {
     return CANDLE_MOE_OK;
 }
 
-inline int rc(cudaError_t e) { return e == cudaSuccess ? CANDLE_MOE_OK : (int)e; }
-
-// CANDLE_MOE_GEMM=0 keeps large batches on the streaming form (A/B checks)
-inline bool gemm_enabled() {
-    const char* v = std::getenv("CANDLE_MOE_GEMM");
-    return !(v && v[0] == '0');
-}
+namespace {
+// tuning key GEMM_ENABLED = 0 keeps large batches on the streaming form (A/B checks)
+inline bool gemm_enabled() { return tuning_get(TUNE_GEMM_ENABLED) != 0; }
 
 // Optional per-stage event marks for candle_moe_forward_timed (null in normal calls).
 constexpr int N_STAGES = 8;  // router, permute, quantize_x, gate_up, quantize_h, down, shared expert, combine
@@ -178,17 +162,19 @@ inline void mark(cudaStream_t st, int stage_done) {
     }
 }
 
-#define CM_TRY(expr)                    \
-    do {                                \
-        const int _r = (expr);          \
-        if (_r != CANDLE_MOE_OK) return _r; \
-    } while (0)
-
 }  // namespace
 
 extern "C" {
 
 const char* candle_moe_version(void) { return "candle_moe_sm100 0.1"; }
+
+int candle_moe_set_tuning(int32_t key, int64_t value) { return tuning_set(key, value) ? CANDLE_MOE_OK : CANDLE_MOE_E_SHAPE; }
+int candle_moe_get_tuning(int32_t key, int64_t* value) {
+    if (!value) return CANDLE_MOE_E_NULL;
+    if (key < 0 || key >= TUNE_N_KEYS) return CANDLE_MOE_E_SHAPE;
+    *value = tuning_get(key);
+    return CANDLE_MOE_OK;
+}
 
 int candle_moe_workspace_bytes(const candle_moe_weights_t* w, int64_t max_tokens, size_t* out_bytes) {
     if (!out_bytes) return CANDLE_MOE_E_NULL;
@@ -265,23 +251,17 @@ int candle_moe_grouped_down(void* stream, const void* const* w2, int32_t dtype, 
                                   hbsums, out, 0, 1, nullptr));
 }
 
-namespace {
-struct ExpertBufs {
-    float* hidden;  // [P, ff]
-    int8_t* hq;
-    float* hs;
-    int16_t* hb;
-    float* eo;      // [slots][P, d]
-    void* gemm;     // scratch of the large-batch GEMM (may be null)
-};
+}  // extern "C"
 
+namespace cmoe {
 // The routed experts over P rows grouped by expert (device offsets [E + 1]); no expert has more than max_rows
 // rows.  Picks, per product, the decode kernels over the repacked copies (max_rows <= 128), the tensor-core GEMM
 // (more than that, scratch present), or the streaming / row forms.  Leaves *eo_splits partial outputs in b.eo.
 int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs& p1, const ExpertPtrs& p3,
                 const ExpertPtrs& p2, int64_t max_rows, int64_t P, const uint32_t* offsets, const uint32_t* row_of,
                 const int8_t* xq, const float* xs, const int16_t* xb, const ExpertBufs& b, int slots, int* eo_splits,
-                bool marks, bool rows_exact = false) {
+                bool marks, bool rows_exact, const uint32_t* row_limit, int64_t total_rows_hint) {
+    if (total_rows_hint <= 0) total_rows_hint = P;
     const int E = w->n_experts, d = w->d_model, ff = w->d_ff;
     const bool large = b.gemm && max_rows > (rows_exact ? GEMM_MIN_ROWS_EXACT : gemm_min_rows()) && gemm_enabled();
     const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= std::max<int64_t>(gemm_min_rows(), 64) && !large;
@@ -293,7 +273,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         CM_TRY(fill_ptrs(w->w3_prepacked, E, q3));
         CM_TRY(fill_ptrs(w->w2_prepacked, E, q2));
         const cudaError_t ce = launch_expert_direct(st, true, q1, q3, w->dtype_w13, E, d, ff, offsets, row_of, max_rows, xq,
-                                                    xs, xb, b.hidden, nullptr, 0, 1, 0, P);
+                                                    xs, xb, b.hidden, nullptr, 0, 1, 0, total_rows_hint);
         if (ce == cudaSuccess)
             gate_done = true;
         else if (ce != cudaErrorNotSupported)
@@ -318,11 +298,11 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         CM_TRY(rc(launch_grouped_gate_up(st, p1, p3, w->dtype_w13, E, d, ff, offsets, row_of, max_rows, xq, xs, xb,
                                          b.hidden)));
     if (marks) mark(st, 3);
-    CM_TRY(rc(launch_quantize_act(st, b.hidden, P, ff, w->dtype_w2, b.hq, b.hs, b.hb)));
+    CM_TRY(rc(launch_quantize_act(st, b.hidden, P, ff, w->dtype_w2, b.hq, b.hs, b.hb, row_limit)));
     if (marks) mark(st, 4);
     if (use_prepacked) {
         const cudaError_t ce = launch_expert_direct(st, false, q2, q2, w->dtype_w2, E, ff, d, offsets, nullptr, max_rows, b.hq,
-                                                    b.hs, b.hb, b.eo, eo_splits, P * d, slots, (int)(P < E ? P : E), P);
+                                                    b.hs, b.hb, b.eo, eo_splits, P * d, slots, (int)(total_rows_hint < E ? total_rows_hint : E), total_rows_hint);
         if (ce == cudaSuccess)
             down_done = true;
         else if (ce != cudaErrorNotSupported)
@@ -348,18 +328,6 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
     return CANDLE_MOE_OK;
 }
 
-// Scratch of the expert-parallel local phase for up to P rows
-struct EpWorkspace {
-    uint32_t* plan;     // [2 * 1024]
-    uint32_t* offsets;  // [E + 1]
-    uint32_t* back;     // [P]
-    int8_t* xq;
-    float* xs;
-    int16_t* xb;
-    ExpertBufs eb;
-    int64_t eo_rows;    // rows x slots the eo region holds
-    size_t total;
-};
 EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
     uint8_t* base = static_cast<uint8_t*>(base_);
     EpWorkspace ws{};
@@ -375,9 +343,7 @@ EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
     ws.eb.hq = carve<int8_t>(base, off, (size_t)P * ff);
     ws.eb.hs = carve<float>(base, off, (size_t)P * ff / 256);
     ws.eb.hb = carve<int16_t>(base, off, (size_t)P * ff / 16);
-    // K-split slots: 8 while no expert has more than 64 rows (then P <= 64 E), 4 beyond
-    const size_t small_rows = std::min<size_t>((size_t)P, 64 * E);
-    ws.eo_rows = (int64_t)std::max<size_t>((size_t)P * 4, small_rows * MAX_K_SPLITS);
+    ws.eo_rows = P * ep_eo_slots(P, (int)E);
     ws.eb.eo = carve<float>(base, off, (size_t)ws.eo_rows * d);
     if (P > GEMM_MIN_ROWS_EXACT) {
         const size_t g = std::max(expert_gemm_scratch_bytes(P, (int)d), expert_gemm_scratch_bytes(P, (int)ff));
@@ -388,7 +354,9 @@ EpWorkspace ep_layout(const candle_moe_weights_t* w, int64_t P, void* base_) {
     ws.total = align_up(off, 256);
     return ws;
 }
-}  // namespace
+}  // namespace cmoe
+
+extern "C" {
 
 static int forward_impl(void* stream, const candle_moe_weights_t* w, const float* x, int64_t T, float* y, void* workspace,
                         size_t workspace_bytes, const float* residual) {
@@ -433,7 +401,7 @@ static int forward_impl(void* stream, const candle_moe_weights_t* w, const float
     int eo_splits = 1, so_splits = 1;
     const ExpertBufs eb{ws.hidden, ws.hq, ws.hs, ws.hb, ws.eo, ws.gemm};
     CM_TRY(run_experts(st, w, p1, p3, p2, T, Tk, ws.offsets, ws.perm_token, ws.xq, ws.xs, ws.xb, eb, k_split_slots(T),
-                       &eo_splits, true));
+                       &eo_splits, true, false, nullptr, 0));
     mark(st, 5);
 
     const float* shared_out = nullptr;
@@ -497,7 +465,10 @@ int candle_moe_forward_timed(void* stream, const candle_moe_weights_t* w, const 
     StageProbe probe{};
     for (int i = 0; i <= N_STAGES; ++i) {
         const cudaError_t e = cudaEventCreate(&probe.ev[i]);
-        if (e != cudaSuccess) return (int)e;
+        if (e != cudaSuccess) {
+            for (int j = 0; j < i; ++j) cudaEventDestroy(probe.ev[j]);
+            return (int)e;
+        }
     }
     g_probe = &probe;
     const int st = candle_moe_forward(stream, w, x, T, y, workspace, workspace_bytes);
@@ -586,7 +557,7 @@ int candle_moe_grouped_gate_up_prepacked(void* stream, const void* const* w1p, c
                                          const float* xscales, const int16_t* xbsums, float* hidden) {
     if (!expert_offsets || !xq || !xscales || !xbsums || !hidden) return CANDLE_MOE_E_NULL;
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
-    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || d % 256 || max_rows < 0 || max_rows > 64)
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || d % 256 || max_rows < 0 || max_rows > 128)
         return CANDLE_MOE_E_SHAPE;
     ExpertPtrs p1, p3;
     CM_TRY(fill_ptrs(w1p, E, p1));
@@ -601,7 +572,7 @@ int candle_moe_grouped_down_prepacked(void* stream, const void* const* w2p, int3
                                       const float* hscales, const int16_t* hbsums, float* out) {
     if (!expert_offsets || !hq || !hscales || !hbsums || !out) return CANDLE_MOE_E_NULL;
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
-    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || ff % 256 || max_rows < 0 || max_rows > 64)
+    if (E <= 0 || E > CANDLE_MOE_MAX_EXPERTS || d <= 0 || ff <= 0 || ff % 256 || max_rows < 0 || max_rows > 128)
         return CANDLE_MOE_E_SHAPE;
     ExpertPtrs p2;
     CM_TRY(fill_ptrs(w2p, E, p2));
@@ -616,6 +587,16 @@ int candle_moe_device_status(int32_t* flags) {
     const cudaError_t e = read_stream_status(&v);
     *flags = v;
     return rc(e);
+}
+
+int candle_moe_device_status_reset(void) {
+    const cudaError_t e = cudaDeviceSynchronize();
+    return e != cudaSuccess ? (int)e : rc(reset_stream_status());
+}
+
+int candle_moe_selftest_bounded_wait(void* stream, int32_t poll_limit) {
+    if (poll_limit < 1 || poll_limit > (1 << 20)) return CANDLE_MOE_E_SHAPE;
+    return rc(launch_selftest_wait((cudaStream_t)stream, poll_limit));
 }
 
 int candle_moe_quantize_weights(void* stream, int32_t dtype, const float* src, int64_t n_elems, void* dst) {
@@ -685,9 +666,9 @@ int candle_moe_ep_experts(void* stream, const candle_moe_weights_t* w, const voi
     CM_TRY(rc(launch_ep_regroup(st, recv_rows, recv_counts, n_src, E, n_rows, d, ws.plan, ws.xq, ws.xs, ws.xb, ws.offsets,
                                 ws.back)));
     int eo_splits = 1;
-    const int slots = max_rows_per_expert <= 64 ? MAX_K_SPLITS : 4;
+    const int slots = ep_eo_slots(n_rows, E);
     CM_TRY(run_experts(st, w, p1, p3, p2, max_rows_per_expert, n_rows, ws.offsets, nullptr, ws.xq, ws.xs, ws.xb, ws.eb, slots,
-                       &eo_splits, false, true));
+                       &eo_splits, false, true, nullptr, 0));
     return rc(launch_ep_scatter(st, ws.eb.eo, eo_splits, n_rows * d, ws.back, n_rows, d, out_rows));
 }
 

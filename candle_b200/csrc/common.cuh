@@ -129,6 +129,19 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 bool pdl_enabled();  // CANDLE_MOE_PDL=0 turns the launch attribute off
 
+// Kernel-selection switches (candle_moe_set_tuning / candle_moe_get_tuning).  Each starts from its
+// environment variable, read once when the library is first used; afterwards only the setter changes it.
+enum TuningKey {
+    TUNE_GEMM_ENABLED = CANDLE_MOE_TUNE_GEMM_ENABLED,
+    TUNE_GEMM_MIN_ROWS = CANDLE_MOE_TUNE_GEMM_MIN_ROWS,
+    TUNE_STREAM_MAX_ROWS = CANDLE_MOE_TUNE_STREAM_MAX_ROWS,
+    TUNE_FORCE_ROWS = CANDLE_MOE_TUNE_FORCE_ROWS,
+    TUNE_MID_ENABLED = CANDLE_MOE_TUNE_MID_ENABLED,
+    TUNE_N_KEYS
+};
+int64_t tuning_get(int key);
+bool tuning_set(int key, int64_t value);  // false: unknown key
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -154,8 +167,9 @@ cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int 
                            uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos);
 // offsets[0..2) = {0, rows}: one group holding every row (used for the always-on shared expert)
 cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows);
+// row_limit (Q8K only, may be null): device-side row count; rows at or beyond it are skipped
 cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, int kdim, int for_dtype, int8_t* qs,
-                                float* scales, int16_t* bsums);
+                                float* scales, int16_t* bsums, const uint32_t* row_limit = nullptr);
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
                                    int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden);
@@ -200,11 +214,14 @@ cudaError_t launch_ep_pack(cudaStream_t st, const uint32_t* row_of, int64_t n_ro
                            const int16_t* xb, void* send);
 cudaError_t launch_ep_regroup(cudaStream_t st, const void* recv, const uint32_t* counts, int n_src, int E, int64_t n_rows, int d,
                               uint32_t* plan, int8_t* xq, float* xs, int16_t* xb, uint32_t* offsets, uint32_t* back_index);
+// row_limit (device, may be null): rows at or beyond *row_limit are skipped (n_rows is then a capacity bound)
 cudaError_t launch_ep_scatter(cudaStream_t st, const float* eo, int n_splits, int64_t split_stride, const uint32_t* back_index,
-                              int64_t n_rows, int d, float* out);
+                              int64_t n_rows, int d, float* out, const uint32_t* row_limit = nullptr);
 // flags raised by kernels whose bounded waits expired (0 = none); synchronises the device
 cudaError_t read_stream_status(int* out);
 cudaError_t stream_status_ptr(int** out);  // device address of that health word
+cudaError_t reset_stream_status();
+cudaError_t launch_selftest_wait(cudaStream_t st, int limit);
 cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);
 cudaError_t launch_dequantize(cudaStream_t st, int dtype, const void* blocks, int64_t n, float* dst);
 

@@ -40,23 +40,6 @@
 
 namespace cmoe {
 
-#ifdef CMOE_GEMM_TRACE
-// Event timeline of CTA 0 (local experiments only): g_gemm_trace[stream][index] = clock at the event.
-__device__ unsigned g_gemm_trace[16][1024];
-extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_trace(unsigned* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned) * 16 * 1024);
-}
-#define TR(stream, idx) do { if (blockIdx.x == 0 && (idx) < 1024u) g_gemm_trace[stream][idx] = (unsigned)clock(); } while (0)
-#else
-#define TR(stream, idx) do { } while (0)
-#endif
-#ifdef CMOE_GEMM_TIMING
-__device__ long long g_gemm_timing[32];
-extern "C" __attribute__((visibility("default"))) int candle_moe_debug_gemm_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_gemm_timing, sizeof(long long) * 32);
-}
-#endif
-
 namespace {
 
 constexpr int G_TILE_M = 128, G_SLAB_K = 64;  // the position tile (N) is a template parameter: 128, or 32 for small batches
@@ -72,20 +55,7 @@ constexpr int G_REGS_EPI = 128, G_REGS_MISC = 32;  // budgets after the trade: 2
 constexpr int G_TMEM_COLS = 512;
 constexpr int G_TM_MAIN = 0;    // + 128 * buffer
 constexpr int G_TM_A = 256;     // weight operand ring: columns 256..511
-constexpr int Q6K_HTB_BYTES = 1680;
-
-
-// Cycle counters of CTA 0 (local experiments only, -DCMOE_GEMM_TIMING): where each role waits.
-#ifdef CMOE_GEMM_TIMING
-#define GT_BEGIN() long long gt_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long gt0_ = clock64()
-#define GT(i, stmt) do { const long long t_ = clock64(); stmt; gt_[i] += clock64() - t_; } while (0)
-#define GT_END(base, leader) do { if (blockIdx.x == 0 && (leader)) { for (int i_ = 0; i_ < 7; ++i_) g_gemm_timing[(base) + i_] = gt_[i_]; \
-    g_gemm_timing[(base) + 7] = clock64() - gt0_; } } while (0)
-#else
-#define GT_BEGIN() do { } while (0)
-#define GT(i, stmt) do { stmt; } while (0)
-#define GT_END(base, leader) do { } while (0)
-#endif  // repacked half-tile block: 8 rows x 256 elements (expert_direct.cu)
+constexpr int Q6K_HTB_BYTES = 1680;  // repacked half-tile block: 8 rows x 256 elements (expert_direct.cu)
 
 // ---------------------------------------------------------------------------------------------
 // Operand preparation: the int8 activation rows in grouped order as fp16 (B operand), the block scales
@@ -447,7 +417,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         long long tile = blockIdx.x;
         TileCoord tc, tcn;
         bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc);
-        GT_BEGIN();
         if (have) {
             const float* dp = P.d8t + (size_t)tc.kb0 * P.P_pad + tc.p0 + colhalf * CH;
             for (int i = lane; i < CH; i += 32) s_d8[ew][0][i] = dp[i];
@@ -472,12 +441,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     if (lane < CH) d8_n0 = dp[0];
                     if (CH > 32) d8_n1 = dp[32];
                 }
-                if (threadIdx.x == 32 * G_WARP_EPI0) TR(0, ab);
-                GT(0, mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag));
+                mbar_wait(&tmem_full[buf], (ab >> 1) & 1, abort_flag);
                 tc5_fence_after_sync();
                 const float dw = s_dw[ab & 7][r];  // left by the unpack warps when they produced this block
                 const uint64_t dw2 = f32x2_pack(dw, dw);
-                if (threadIdx.x == 32 * G_WARP_EPI0) TR(1, ab);
                 const uint32_t t_main = ta_lane + (uint32_t)(G_TM_MAIN + buf * TN);
                 const uint32_t d8_addr = smem_u32(&s_d8[ew][buf][0]);
                 // Four steps of 16 columns; the load of step i+1 is in flight while step i is scaled into
@@ -513,12 +480,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     if (CH > 32) s_d8[ew][buf ^ 1][lane + 32] = d8_n1;
                 }
                 __syncwarp();
-                if (threadIdx.x == 32 * G_WARP_EPI0) TR(2, ab);
             }
             // ---- store the tile ----
-#ifdef CMOE_GEMM_TIMING
-            const long long ts_ = clock64();
-#endif
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             const uint32_t pc0 = tc.p0 + colhalf * CH;
             float* out_k = P.out + (size_t)tc.ks * P.split_stride;
@@ -537,14 +500,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 for (int c = 0; c < CH; ++c)
                     if (pc0 + c < tc.p_end) out_k[(size_t)(pc0 + c) * P.N + n] = acc[c];
             }
-#ifdef CMOE_GEMM_TIMING
-            gt_[4] += clock64() - ts_;
-#endif
             tile += gridDim.x;
             tc = tcn;
             have = have_n;
         }
-        GT_END(16, threadIdx.x == 32 * G_WARP_EPI0);
     } else if (warp < G_WARP_DQ0 + G_DQ_WARPS) {
         // ===================== weight unpack -> fp16 operand in tensor memory =====================
         const int quarter = warp & 3, h = (warp - G_WARP_DQ0) >> 2;
@@ -557,7 +516,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         bool have = decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc);
         typename F::Row rowc{}, rown{};
         typename F::Pre cur, nxt;
-        GT_BEGIN();
         // staged row of tile row r: gate_up keeps the W1 rows first, then the W3 rows
         const uint32_t w_row = smem_u32(smem_w) + (GATE_UP ? (uint32_t)((r & 1) * (G_TILE_M / 2 * F::W_ROW_BYTES) + (r >> 1) * F::W_ROW_BYTES)
                                                            : (uint32_t)(r * F::W_ROW_BYTES));
@@ -576,7 +534,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 if (F::STAGE_W) {
                     // this block's raw bytes were copied to shared memory by the loader warp
-                    GT(1, mbar_wait(&full_w, ab & 1, abort_flag));
+                    mbar_wait(&full_w, ab & 1, abort_flag);
                     F::load_staged(cur, w_row, h);
                 } else if (blk + 1 < tc.kb1) {
                     F::load(nxt, rowc, blk + 1, h);
@@ -597,26 +555,23 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     // wait is never ambiguous -- while the TMEM slot is the pair index modulo the ring size: before
                     // writing it, wait for the MMAs of the block that used it last.
                     const uint32_t bidx = 2 * (ab & 1) + pr, slot = bidx % F::A_PAIRS;
-                    if (lane == 0 && warp == G_WARP_DQ0) TR(3, ita);
                     if (ab >= F::A_PAIRS / 2) {
                         const uint32_t abp = ab - F::A_PAIRS / 2;
-                        GT(0, mbar_wait_relaxed(&empty_a[2 * (abp & 1) + pr], (abp >> 1) & 1, abort_flag));
+                        mbar_wait_relaxed(&empty_a[2 * (abp & 1) + pr], (abp >> 1) & 1, abort_flag);
                     }
                     tc5_fence_after_sync();
-                    if (lane == 0 && warp == G_WARP_DQ0) TR(4, ita);
-                    GT(2, F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * slot * F::A_COLS), h));
-                    GT(2, F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * slot + 1) * F::A_COLS), h));
+                    F::emit(2 * pr, cur, ctx, ta_lane + (uint32_t)(2 * slot * F::A_COLS), h);
+                    F::emit(2 * pr + 1, cur, ctx, ta_lane + (uint32_t)((2 * slot + 1) * F::A_COLS), h);
                     if (F::HAS_MIN && pr == 1) {
                         // weight side of the min term, handed over with the second pair.  Its slot was last read by
                         // the min MMAs of block ab - 2, issued before the commit whose completion the wait above saw.
                         F::emit_min(cur, ctx, smem_min_a + (size_t)(ab & 1) * G_TILE_BYTES + min_row_off, h, r & 7);
                         fence_proxy_async_smem();
                     }
-                    GT(3, tmem_st_wait());
+                    tmem_st_wait();
                     tc5_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_a[bidx]);
-                    if (lane == 0 && warp == G_WARP_DQ0) TR(5, ita);
                 }
                 if (!F::STAGE_W) cur = nxt;
             }
@@ -625,7 +580,6 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             rowc = rown;
             have = have_n;
         }
-        GT_END(8, threadIdx.x == 32 * G_WARP_DQ0);
     } else if (warp == G_WARP_LOAD) {
         // ===================== weight loader: raw blocks of the tile rows -> shared memory =====================
         // One TMA box per matrix and block: [64 or 128 rows x 144 bytes] of the byte matrix [n_rows, row_bytes]
@@ -687,12 +641,11 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         // the whole warp walks the loop (uniform control flow and addresses), one elected lane issues
         uint32_t ab = 0;
         TileCoord tc;
-        GT_BEGIN();
         for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc); tile += gridDim.x) {
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
                 const int st = ab & 1;
-                if (ab >= 2) GT(0, mbar_wait_relaxed(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag));
+                if (ab >= 2) mbar_wait_relaxed(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag);
                 uint8_t* dst = smem + (size_t)st * G_STAGE_BYTES;
                 if (elect_one()) {
                     mbar_expect_tx(&full_b[st], G_STAGE_BYTES);
@@ -704,13 +657,11 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 __syncwarp();
             }
         }
-        GT_END(24, lane == 0);
     } else if (warp == G_WARP_MMA) {
         // ===================== MMA issue =====================
         // (Splitting the blocks by parity over two issuing warps was measured: no gain.)
         uint32_t ita = 0, ab = 0;
         TileCoord tc;
-        GT_BEGIN();
         const uint32_t a_base = tmem_base + (uint32_t)G_TM_A;
         const uint64_t b_desc0 = umma_desc_sw128(smem_u32(smem));
         const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a));
@@ -719,24 +670,19 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 const int buf = ab & 1;  // main accumulator and B stage of this block
                 // the drain of block ab - 2 has released this main accumulator
-                if (ab >= 2) GT(2, mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag));
-                if (lane == 0) TR(13, ab);
+                if (ab >= 2) mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag);
                 const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * TN);
                 const uint64_t db = b_desc0 + (uint64_t)(buf * (G_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
                     const uint32_t bidx = 2 * (ab & 1) + pr, slot = bidx % F::A_PAIRS;  // barrier, TMEM slot (see the unpack warps)
-                    if (lane == 0) TR(9, ita);
-                    if (!rdy_a) GT(0, mbar_wait(&full_a[bidx], (ab >> 1) & 1, abort_flag));
-                    if (lane == 0) TR(10, ita);
-                    if (pr == 0 && !rdy_b) GT(1, mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag));
-                    if (lane == 0) TR(11, ita);
+                    if (!rdy_a) mbar_wait(&full_a[bidx], (ab >> 1) & 1, abort_flag);
+                    if (pr == 0 && !rdy_b) mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag);
                     tc5_fence_after_sync();
                     // look at this warp's next barriers now: the answers arrive while the MMAs are issued
                     rdy_a = pr == 0 ? mbar_test(&full_a[bidx + 1], (ab >> 1) & 1)                    // second pair of this block
                                     : mbar_test(&full_a[2 * ((ab + 1) & 1)], ((ab + 1) >> 1) & 1);  // first pair of the next
                     if (pr == 1) rdy_b = mbar_test(&full_b[buf ^ 1], ((ab + 1) >> 1) & 1);
-                    if (lane == 0) TR(6, ita);
                     const uint32_t a_t = a_base + (uint32_t)(2 * slot * F::A_COLS);
                     if (elect_one()) {
 #pragma unroll
@@ -745,10 +691,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                             const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (B_TILE >> 4) + 2 * (k & 3));
                             umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
                             if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
-                            if (k == 0) TR(15, ita);
-                            if (k == 3) TR(7, ita);
                         }
-                        TR(8, ita);
                         if (pr == 1 && F::HAS_MIN) {
                             // the min term joins the same accumulator: three tf32 steps, last in the block
                             const uint64_t da = ma_desc0 + (uint64_t)(buf * (G_TILE_BYTES >> 4)), dm = db + (uint64_t)(4 * (B_TILE >> 4));
@@ -762,12 +705,9 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         }
                     }
                     __syncwarp();
-                    if (lane == 0) TR(12, ita);
                 }
-                if (lane == 0) TR(14, ab);
             }
         }
-        GT_END(0, lane == 0);
     }
     tc5_fence_before_sync();
     __syncthreads();

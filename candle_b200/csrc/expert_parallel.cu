@@ -11,7 +11,8 @@
 //   regroup  received rows (source-major, expert-minor) -> planar activation arrays in expert-major
 //            order (what the grouped expert kernels read), expert offsets, and the way back
 //   scatter  expert outputs (K-split partials summed here) -> rows in received order, ready to return
-// The collectives themselves (counts, rows, results) are issued by the host between these calls.
+// The collectives themselves (counts, rows, results) are issued between these steps: by candle_moe_ep_forward
+// (ep_nccl.cu), or by a host that drives the steps itself.
 #include "common.cuh"
 
 namespace cmoe {
@@ -101,11 +102,11 @@ ep_regroup_kernel(const uint8_t* __restrict__ recv, int64_t n_rows, int d, int r
 // out[back_index[p]] = sum over the K-split partials of expert output row p, in split order
 __global__ void __launch_bounds__(256)
 ep_scatter_kernel(const float* __restrict__ eo, int n_splits, int64_t split_stride, const uint32_t* __restrict__ back_index,
-                  int64_t n_rows, int d, float* __restrict__ out) {
+                  int64_t n_rows, int d, float* __restrict__ out, const uint32_t* __restrict__ row_limit) {
     pdl_trigger();
     pdl_wait();
     const int64_t p = blockIdx.x;
-    if (p >= n_rows) return;
+    if (p >= n_rows || (row_limit && p >= (int64_t)*row_limit)) return;
     const int64_t r = back_index ? (int64_t)back_index[p] : p;
     for (int i = threadIdx.x; i < d / 4; i += blockDim.x) {
         float4 a = reinterpret_cast<const float4*>(eo + p * d)[i];
@@ -142,10 +143,10 @@ cudaError_t launch_ep_regroup(cudaStream_t st, const void* recv, const uint32_t*
 }
 
 cudaError_t launch_ep_scatter(cudaStream_t st, const float* eo, int n_splits, int64_t split_stride, const uint32_t* back_index,
-                              int64_t n_rows, int d, float* out) {
+                              int64_t n_rows, int d, float* out, const uint32_t* row_limit) {
     if (n_rows == 0) return cudaSuccess;
     return launch_k(ep_scatter_kernel, dim3((unsigned)n_rows), dim3(256), 0, st, eo, n_splits, split_stride, back_index, n_rows,
-                    d, out);
+                    d, out, row_limit);
 }
 
 }  // namespace cmoe

@@ -11,26 +11,16 @@
 // count, unaligned Q6_K / Q8_0 rows) and is the path used for shapes the tiled kernels do not
 // take.  One warp owns one weight row (for gate_up: the same row of W1 and of W3) and walks the
 // expert's activation rows TOK at a time, so a weight row is fetched from HBM once per expert.
-#include <cstdlib>
-
 #include "common.cuh"
 
 namespace cmoe {
 
 // Rows per expert up to which the streaming form is used.  Beyond 16 rows per expert it walks the
 // expert's rows in groups of 16 and re-streams the weights for each group (mostly from L2), which
-// is still far faster than the row-per-warp form; CANDLE_MOE_STREAM_MAX_ROWS lowers the limit.
-constexpr int64_t STREAM_MAX_ROWS_DEFAULT = (int64_t)1 << 40;
-
-static int64_t stream_max_rows() {
-    const char* v = std::getenv("CANDLE_MOE_STREAM_MAX_ROWS");
-    return v ? std::atoll(v) : STREAM_MAX_ROWS_DEFAULT;
-}
-
-static bool force_rows() {
-    const char* v = std::getenv("CANDLE_MOE_FORCE_ROWS");
-    return v && v[0] == '1';
-}
+// is still far faster than the row-per-warp form; the tuning key STREAM_MAX_ROWS lowers the limit and
+// FORCE_ROWS sends everything to the row-per-warp form (A/B checks in the tests).
+static int64_t stream_max_rows() { return tuning_get(TUNE_STREAM_MAX_ROWS); }
+static bool force_rows() { return tuning_get(TUNE_FORCE_ROWS) != 0; }
 
 constexpr int ROWS_WARPS = 8;  // weight rows per CTA
 constexpr int TOK = 4;         // activation rows per pass

@@ -27,9 +27,6 @@
 
 namespace cmoe {
 
-#ifdef CMOE_STREAM_TIMING
-__device__ long long g_stream_timing[32];  // cycle counters of one probed CTA (local experiments only)
-#endif
 
 namespace {
 
@@ -381,13 +378,6 @@ struct Walker {
 };
 
 // CW = consumer warps = 256-element blocks per stage chunk.
-#ifdef CMOE_STREAM_TIMING
-#define TMARK(var) const long long var = clock64()
-#define TADD(slot, a, b) do { if (tprobe) tacc[slot] += (b) - (a); } while (0)
-#else
-#define TMARK(var)
-#define TADD(slot, a, b)
-#endif
 
 template <class F, bool GATE_UP, int NT, int CW>
 __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const __grid_constant__ StreamParams P) {
@@ -417,11 +407,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
     __syncthreads();
     volatile int* abort_flag = &s_abort;
 
-#ifdef CMOE_STREAM_TIMING
-    const bool tprobe = blockIdx.x == 40 && lane == 0 && (warp == 0 || warp == 3);
-    long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long t_begin = clock64();
-#endif
     Walker wk(P, s_offs, blockIdx.x, gridDim.x);
     const size_t row_bytes = (size_t)P.kb * F::BLOCK_BYTES;
     uint8_t* stage0 = smem + P.off_stage;
@@ -443,10 +428,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
                 const uint32_t ph = (it / P.stages) & 1;
-                TMARK(tp0);
                 if (it >= (uint32_t)P.stages) mbar_wait(&empty_bar[s], ph ^ 1, abort_flag);
-                TMARK(tp1);
-                TADD(0, tp0, tp1);
                 const int blocks = min(CW, P.kb - ch * CW);
                 const uint32_t bytes = (uint32_t)blocks * F::BLOCK_BYTES;
                 if (lane == 0) mbar_expect_tx(&full_bar[s], bytes * TILE_ROWS);
@@ -487,7 +469,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                 cur_e = w.e;
                 cur_grp = w.grp;
                 cur_split = w.split;
-                TMARK(tq0);
                 consumer_sync(N_CONS);
                 if (ctid < MT) {
                     const uint32_t pp = p_base + ctid;
@@ -521,8 +502,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                     }
                 }
                 consumer_sync(N_CONS);
-                TMARK(tq1);
-                TADD(1, tq0, tq1);
             }
 
             BlockArgs bargs;
@@ -542,10 +521,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
 
             for (int ch = P.chunk_start[w.split]; ch < P.chunk_start[w.split + 1]; ++ch, ++it) {
                 const int s = it % P.stages;
-                TMARK(tc0);
                 const bool ok = mbar_wait(&full_bar[s], (it / P.stages) & 1, abort_flag);
-                TMARK(tc1);
-                TADD(2, tc0, tc1);
                 const int blk = ch * CW + cw;
                 if (ok && blk < P.kb) {
                     bargs.kblk_local = blk - blk0;
@@ -557,10 +533,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);
-                TMARK(tc2);
-                TADD(3, tc1, tc2);
             }
-            TMARK(tr0);
 
             // ---- the CW K-slices of the tile meet in shared memory (two buffers, one barrier per
             // item: a buffer is rewritten only after every warp has passed the next item's barrier) ----
@@ -576,8 +549,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                     }
             }
             consumer_sync(N_CONS);
-            TMARK(tr1);
-            TADD(4, tr0, tr1);
             // four threads per output: each adds a quarter of the K-slices, two shuffles finish the sum
             for (int idx = ctid; idx < MT * TILE_N * 4; idx += N_CONS) {
                 const int o4 = idx >> 2, part = idx & 3;
@@ -603,20 +574,8 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1) expert_stream_kernel(const _
                         P.out[(int64_t)w.split * P.out_split_stride + o] = va;
                 }
             }
-            TMARK(tr2);
-            TADD(5, tr1, tr2);
-#ifdef CMOE_STREAM_TIMING
-            if (tprobe) tacc[6] += 1;
-#endif
         }
     }
-#ifdef CMOE_STREAM_TIMING
-    if (tprobe) {
-        const int base = warp == 0 ? 0 : 16;
-        for (int i = 0; i < 8; ++i) g_stream_timing[base + i] = tacc[i];
-        g_stream_timing[base + 8] = clock64() - t_begin;
-    }
-#endif
     __syncthreads();
     if (threadIdx.x == 0 && s_abort) atomicOr(P.status, 1);
 }
@@ -656,11 +615,6 @@ cudaError_t launch_nt(cudaStream_t st, bool gate_up, int NT, const StreamParams&
 }  // namespace
 
 __device__ int g_stream_status = 0;
-#ifdef CMOE_STREAM_TIMING
-extern "C" __attribute__((visibility("default"))) int candle_moe_debug_timing(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_stream_timing, sizeof(long long) * 32);
-}
-#endif
 
 // Plans and launches the streaming kernel; returns cudaErrorNotSupported when the shape is outside
 // what the streaming form takes (the caller then uses the row-per-warp form).
@@ -761,6 +715,36 @@ cudaError_t stream_status_ptr(int** out) {
 
 cudaError_t read_stream_status(int* out) {
     return cudaMemcpyFromSymbol(out, g_stream_status, sizeof(int));
+}
+
+cudaError_t reset_stream_status() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
+}
+
+namespace {
+// Waits on a barrier that nothing completes: the bounded wait gives up after `limit` polls and the kernel returns.
+__global__ void selftest_wait_kernel(int limit, int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    mbar_wait(&bar, 0, &s_abort, limit);
+    __syncthreads();
+    if (threadIdx.x == 0 && s_abort) atomicOr(status, 1);
+}
+}  // namespace
+
+cudaError_t launch_selftest_wait(cudaStream_t st, int limit) {
+    int* status = nullptr;
+    const cudaError_t e = stream_status_ptr(&status);
+    if (e != cudaSuccess) return e;
+    selftest_wait_kernel<<<1, 64, 0, st>>>(limit, status);
+    return cudaGetLastError();
 }
 
 }  // namespace cmoe

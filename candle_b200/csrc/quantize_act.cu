@@ -16,12 +16,15 @@ namespace cmoe {
 // BlockQ8K::from_float: one warp per 256-element block (quantize_q8k_block in common.cuh).
 __global__ void __launch_bounds__(256)
 quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __restrict__ qs,
-                    float* __restrict__ scales, int16_t* __restrict__ bsums) {
+                    float* __restrict__ scales, int16_t* __restrict__ bsums, const uint32_t* __restrict__ row_limit,
+                    int blocks_per_row) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (blk >= n_blocks) return;
+    // rows past the device-side count hold nothing (expert parallelism sizes its launches by a capacity bound)
+    if (row_limit && blk >= (int64_t)*row_limit * blocks_per_row) return;
     quantize_q8k_block(x + blk * QK_K, lane, qs + blk * QK_K, scales + blk, bsums + blk * 16);
 }
 
@@ -64,14 +67,14 @@ quantize_q8_0_kernel(const float* __restrict__ x, int64_t n_elems, int8_t* __res
 }
 
 cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, int kdim, int for_dtype, int8_t* qs,
-                                float* scales, int16_t* bsums) {
+                                float* scales, int16_t* bsums, const uint32_t* row_limit) {
     const int64_t n = rows * (int64_t)kdim;
     const int64_t n256 = (n + 255) / 256;
     if (n256 == 0) return cudaSuccess;
     const unsigned grid = (unsigned)((n256 + 7) / 8);
     if (for_dtype == CANDLE_GGML_Q8_0)
         return launch_k(quantize_q8_0_kernel, dim3(grid), dim3(256), 0, st, x, n, qs, scales);
-    return launch_k(quantize_q8k_kernel, dim3(grid), dim3(256), 0, st, x, n256, qs, scales, bsums);
+    return launch_k(quantize_q8k_kernel, dim3(grid), dim3(256), 0, st, x, n256, qs, scales, bsums, row_limit, kdim / 256);
 }
 
 }  // namespace cmoe

@@ -2,6 +2,7 @@
 // combine of the quantized MoE block.  All three are small, latency- or HBM-bound kernels.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace cmoe {
@@ -12,6 +13,33 @@ bool pdl_enabled() {
         return !(v && v[0] == '0');
     }();
     return on;
+}
+
+namespace {
+struct TuningTable {
+    std::atomic<int64_t> v[TUNE_N_KEYS];
+    TuningTable() {
+        const auto env = [](const char* name, int64_t dflt) {
+            const char* s = std::getenv(name);
+            return s && s[0] ? (int64_t)std::atoll(s) : dflt;
+        };
+        v[TUNE_GEMM_ENABLED] = env("CANDLE_MOE_GEMM", 1);
+        v[TUNE_GEMM_MIN_ROWS] = env("CANDLE_MOE_GEMM_MIN_ROWS", 128);
+        v[TUNE_STREAM_MAX_ROWS] = env("CANDLE_MOE_STREAM_MAX_ROWS", (int64_t)1 << 40);
+        v[TUNE_FORCE_ROWS] = env("CANDLE_MOE_FORCE_ROWS", 0);
+        v[TUNE_MID_ENABLED] = env("CANDLE_MOE_MID", 1);
+    }
+};
+TuningTable& tuning_table() {
+    static TuningTable t;
+    return t;
+}
+}  // namespace
+int64_t tuning_get(int key) { return key >= 0 && key < TUNE_N_KEYS ? tuning_table().v[key].load() : 0; }
+bool tuning_set(int key, int64_t value) {
+    if (key < 0 || key >= TUNE_N_KEYS) return false;
+    tuning_table().v[key].store(value);
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -105,38 +133,55 @@ router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, co
     }
     s = warp_sum(s);
 #pragma unroll
-    for (int j = 0; j < PER; ++j) p[j] = (lane + 32 * j) < E ? p[j] / s : -1.f;  // -1 = not a candidate
+    for (int j = 0; j < PER; ++j) p[j] = (lane + 32 * j) < E ? p[j] / s : 0.f;
 
+    // Selection in the order of Rust's f32::total_cmp (the reference sorts with it, quantized_llama.rs:166), so
+    // that it is total: a row holding a NaN or an infinity turns every probability into the same NaN, all keys
+    // tie, and the lowest expert ids win -- the reference's stable sort gives exactly that.  Every selected id
+    // is below E whatever the input holds.
+    int key[PER];
+    uint32_t open_mask = 0;  // bit j: expert lane + 32 j exists and has not been selected yet
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int b = (p[j] != p[j]) ? 0x7fffffff : __float_as_int(p[j]);  // all NaNs alike (they only occur together)
+        key[j] = b ^ (int)(((uint32_t)(b >> 31)) >> 1);
+        if (lane + 32 * j < E) open_mask |= 1u << j;
+    }
     float sel_p[CANDLE_MOE_MAX_TOPK];
     int sel_e[CANDLE_MOE_MAX_TOPK];
     float sum = 0.f;
 #pragma unroll
     for (int r = 0; r < CANDLE_MOE_MAX_TOPK; ++r) {
         if (r < k) {
-            float bv = -1.f;
-            int be = 0x7fffffff;
+            int bk = 0, be = -1;  // be < 0: no candidate in this lane
+            float bv = 0.f;
 #pragma unroll
             for (int j = 0; j < PER; ++j) {  // ascending expert id inside a lane: strict > keeps the lower id
-                if (p[j] > bv) {
+                if (((open_mask >> j) & 1u) && (be < 0 || key[j] > bk)) {
+                    bk = key[j];
                     bv = p[j];
                     be = lane + 32 * j;
                 }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int ok = __shfl_xor_sync(0xffffffffu, bk, o);
                 const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) {
-                    bv = ov;
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                if (oe >= 0 && (be < 0 || ok > bk || (ok == bk && oe < be))) {
+                    bk = ok;
                     be = oe;
+                    bv = ov;
                 }
             }
+            // k <= E, so a candidate always exists; the clamp only keeps a corrupted launch inside the tables
+            be = min(max(be, 0), E - 1);
             sel_p[r] = bv;
             sel_e[r] = be;
             sum += bv;  // rank order, like `sum_routing_weights += routing_weight`
 #pragma unroll
             for (int j = 0; j < PER; ++j)
-                if (lane + 32 * j == be) p[j] = -1.f;
+                if (lane + 32 * j == be) open_mask &= ~(1u << j);
         }
     }
     if (lane == 0) {

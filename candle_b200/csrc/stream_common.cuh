@@ -50,9 +50,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached, or
 // as soon as another thread of the CTA has raised the flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int limit = SPIN_LIMIT) {
     if (mbar_try_wait(bar, parity)) return true;  // the common case costs one instruction and a branch
-    for (int i = 0; i < SPIN_LIMIT; ++i) {
+    for (int i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (i > 128) __nanosleep(20);

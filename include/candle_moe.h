@@ -49,6 +49,8 @@ extern "C" {
 #define CANDLE_MOE_E_ALIGN (-5)       /* a pointer does not meet the documented alignment */
 #define CANDLE_MOE_E_NO_DEVICE (-6)   /* no CUDA device / not an sm_100 device */
 #define CANDLE_MOE_E_STATIC_SCRATCH (-7) /* the call needs more scratch than CANDLE_MOE_STATIC_SCRATCH_BYTES */
+#define CANDLE_MOE_E_NCCL (-8)        /* libnccl could not be loaded or an NCCL call failed (candle_moe_ep_last_error) */
+#define CANDLE_MOE_E_EP_MISMATCH (-9) /* the ranks' exchange metadata disagree; every rank returns this, nothing was exchanged */
 
 /* size of the built-in scratch area used by candle_moe_forward_static (per GPU, held until exit) */
 #define CANDLE_MOE_STATIC_SCRATCH_BYTES (16u << 20)
@@ -84,6 +86,21 @@ typedef struct candle_moe_weights {
     const void* const* w3_prepacked;
     const void* const* w2_prepacked;
 } candle_moe_weights_t;
+
+/* Kernel-selection switches, for A/B checks and for re-tuning the thresholds on other shapes.  Each value starts
+ * from an environment variable read once when the library is first used (CANDLE_MOE_GEMM, CANDLE_MOE_GEMM_MIN_ROWS,
+ * CANDLE_MOE_STREAM_MAX_ROWS, CANDLE_MOE_FORCE_ROWS, CANDLE_MOE_MID); later changes go through candle_moe_set_tuning
+ * only, so a workspace size query and the forward that follows see the same values unless the caller changes them
+ * in between.  The reference has the same kind of switch as a process-wide flag
+ * (candle-core/src/quantized/cuda.rs:21-25, `FORCE_DMMV` / `set_force_dmmv`).  Results stay within the documented bounds under every
+ * setting; only which kernel form runs changes. */
+#define CANDLE_MOE_TUNE_GEMM_ENABLED 0     /* 0: large batches stay on the streaming form (default 1) */
+#define CANDLE_MOE_TUNE_GEMM_MIN_ROWS 1    /* bound on the rows of an expert above which the tensor-core GEMM runs (128) */
+#define CANDLE_MOE_TUNE_STREAM_MAX_ROWS 2  /* rows per expert up to which the streaming form is used (no limit) */
+#define CANDLE_MOE_TUNE_FORCE_ROWS 3       /* 1: every grouped product through the row-per-warp form (0) */
+#define CANDLE_MOE_TUNE_MID_ENABLED 4      /* 0: no four-position-tile decode kernels for 17..64 rows per expert (1) */
+CANDLE_MOE_API int candle_moe_set_tuning(int32_t key, int64_t value);
+CANDLE_MOE_API int candle_moe_get_tuning(int32_t key, int64_t* value);
 
 /* Library identification: returns a static string "candle_moe_sm100 <version>". */
 CANDLE_MOE_API const char* candle_moe_version(void);
@@ -234,6 +251,67 @@ CANDLE_MOE_API int candle_moe_ep_experts(void* stream, const candle_moe_weights_
                                          int64_t max_rows_per_expert, float* out_rows, void* workspace,
                                          size_t workspace_bytes);
 
+/* ---- Expert parallelism as ONE call per step, the collectives inside the library -------------------------------
+ * The reference has no expert-parallel block; what it has is the plumbing of its multi-process example, which these
+ * entry points follow: rank 0 makes an NCCL id and hands it to the others out of band, every rank builds its
+ * communicator from (id, rank, world) (candle-examples/examples/llama_multiprocess/main.rs:148-173, `Id::new`,
+ * `Comm::from_rank`), and the collective hides behind the op it belongs to (model.rs:30-90).
+ *
+ *   candle_moe_ep_unique_id      ncclGetUniqueId: CANDLE_MOE_EP_UNIQUE_ID_BYTES bytes to distribute to every rank
+ *   candle_moe_ep_comm_init      ncclCommInitRank with the current device, plus a little pinned host memory
+ *   candle_moe_ep_comm_from_nccl the same handle around a communicator the host already has (a cudarc `Comm`'s
+ *                                ncclComm_t); the handle does not own it
+ *   candle_moe_ep_comm_destroy   frees the handle (and the communicator if the handle made it)
+ *
+ * candle_moe_ep_forward: MlpOrMoe::MoE::forward (quantized_llama.rs:143-210) with the experts sharded: rank r owns
+ * experts [r E/N, (r+1) E/N) (`local` describes them: n_experts = E/N, its router/top_k fields are ignored) and
+ * routes its own T rows of x [T, d] into y [T, d] with the full router of `cfg`.  Inside: router + Q8K quantization +
+ * dispatch, all-to-all of the packed quantized rows, the local experts, all-to-all of the f32 outputs back, combine;
+ * both exchanges are grouped ncclSend / ncclRecv on `stream`.  Results are those of candle_moe_forward.
+ * Every rank of the communicator must make the call in the same step with the same cfg (rank apart); T may differ
+ * per rank (0 included) up to cfg->max_tokens.  Two forms, picked from cfg alone (candle_moe_ep_forward_form says
+ * which): "slots" (form 1, small steps: fixed-capacity slots with the counts in-band, no host synchronisation and
+ * no data-dependent size, so the call is a fixed sequence of launches) and "exact" (form 2, large steps: counts
+ * exchanged and checked on the host first -- one stream synchronisation, plus one for the all-reduce that makes
+ * every rank agree on the verdict -- then rows of exactly the needed sizes; a table that fails the check makes
+ * EVERY rank return CANDLE_MOE_E_EP_MISMATCH before any row is exchanged or any expert kernel launched).
+ * In the slot form a bad slot header is found on the device: that source's rows are dropped and bit 2 (value 4) of
+ * candle_moe_device_status is raised.  One step at a time per communicator.  K-quant experts only. */
+#define CANDLE_MOE_EP_UNIQUE_ID_BYTES 128
+typedef struct candle_moe_ep_comm candle_moe_ep_comm_t;
+typedef struct candle_moe_ep_config {
+    int32_t rank, world;          /* must match the communicator */
+    int32_t n_experts_global;     /* E, a multiple of world */
+    int32_t top_k;                /* n_expert_used */
+    int32_t renorm;               /* as candle_moe_weights_t.renorm */
+    int32_t max_tokens;           /* bound on T of ANY rank in a step; the same on every rank (sizes the slots) */
+    int32_t force_form;           /* 0: choose by size; 1: slots; 2: exact */
+    int32_t inject_count_mismatch;/* tests only: 1 makes this rank report a bad count table (exact form) */
+    int64_t max_recv_rows;        /* exact form: cap on the rows one rank may receive per step (0 = worst case,
+                                     world * max_tokens * min(top_k, E / world)); sizes the workspace */
+    const float* router;          /* device f32 [E, d_model], replicated on every rank */
+    const float* router_bias;     /* device f32 [E] or NULL */
+} candle_moe_ep_config_t;
+CANDLE_MOE_API int candle_moe_ep_unique_id(void* id_out);
+CANDLE_MOE_API int candle_moe_ep_comm_init(const void* unique_id, int32_t rank, int32_t world, candle_moe_ep_comm_t** comm_out);
+CANDLE_MOE_API int candle_moe_ep_comm_from_nccl(void* nccl_comm, candle_moe_ep_comm_t** comm_out);
+CANDLE_MOE_API int candle_moe_ep_comm_destroy(candle_moe_ep_comm_t* comm);
+CANDLE_MOE_API const char* candle_moe_ep_last_error(void);  /* text of the calling thread's last CANDLE_MOE_E_NCCL / _EP_MISMATCH */
+CANDLE_MOE_API int candle_moe_ep_forward_workspace_bytes(const candle_moe_ep_config_t* cfg, const candle_moe_weights_t* local,
+                                                         size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_ep_forward_form(const candle_moe_ep_config_t* cfg, const candle_moe_weights_t* local, int32_t* form,
+                                              int64_t* capacity_rows);
+/* comm may be NULL when cfg->world == 1 (the exchanges are then device copies). */
+CANDLE_MOE_API int candle_moe_ep_forward(void* stream, candle_moe_ep_comm_t* comm, const candle_moe_ep_config_t* cfg,
+                                         const candle_moe_weights_t* local, const float* x, int64_t T, float* y,
+                                         void* workspace, size_t workspace_bytes);
+/* The same step with CUDA events between its phases (synchronises the stream): phase_ms[5] = {route + pack, exchange of
+ * rows, local experts, exchange of results, combine}; rows_info[2] = {rows this rank received, rows of its busiest
+ * expert}.  For measurement only. */
+CANDLE_MOE_API int candle_moe_ep_forward_timed(void* stream, candle_moe_ep_comm_t* comm, const candle_moe_ep_config_t* cfg,
+                                               const candle_moe_weights_t* local, const float* x, int64_t T, float* y,
+                                               void* workspace, size_t workspace_bytes, float* phase_ms, int64_t* rows_info);
+
 /* One quantized matrix over a batch of rows: out[rows, n] = x[rows, k] . W^T with W [n, k] in GGUF blocks
  * -- `QMatMul::forward` (candle-core/src/quantized/mod.rs:533-537 -> `QTensor::cuda_fwd` :520-530 -> `QCudaStorage::fwd`, cuda.rs:484-505)
  * for the dense projections of the model (attention wq/wk/wv/wo quantized_llama.rs:275-277,345, lm head :897).
@@ -258,7 +336,7 @@ CANDLE_MOE_API int candle_moe_prepack(void* stream, int32_t dtype, const void* s
                                       void* dst);
 
 /* The grouped expert products over prepacked weights (same contracts as candle_moe_grouped_gate_up /
- * candle_moe_grouped_down; at most 64 rows per expert; CANDLE_MOE_E_SHAPE when the shape is not taken). */
+ * candle_moe_grouped_down; at most 128 rows per expert; CANDLE_MOE_E_SHAPE when the shape is not taken). */
 CANDLE_MOE_API int candle_moe_grouped_gate_up_prepacked(void* stream, const void* const* w1p, const void* const* w3p,
                                                         int32_t dtype, int32_t E, int32_t d, int32_t ff,
                                                         const uint32_t* expert_offsets, const uint32_t* row_of,
@@ -270,10 +348,17 @@ CANDLE_MOE_API int candle_moe_grouped_down_prepacked(void* stream, const void* c
                                                      const int16_t* hbsums, float* out);
 
 /* Health word of the device-side kernels.  Every wait inside a kernel (on a copy in flight) has an
- * iteration limit; a kernel whose wait expired raises bit 0 here and finishes without hanging.
- * Synchronises the device and returns the accumulated flags in *flags (0 = healthy).
+ * iteration limit; a kernel whose wait expired raises a bit here and finishes without hanging: bit 0 (1) the
+ * streaming kernels, bit 1 (2) the tensor-core GEMM; bit 2 (4) is raised by the expert-parallel slot form when a
+ * received slot header fails its checks.  candle_moe_device_status synchronises the device and returns the
+ * accumulated flags in *flags (0 = healthy); candle_moe_device_status_reset clears them.
+ * candle_moe_selftest_bounded_wait enqueues a one-CTA kernel that waits, with the library's own wait primitive and
+ * the given poll limit, on a barrier that nothing ever completes: the wait runs out, the kernel raises bit 0 and
+ * returns -- the way to see the give-up path work without a stuck copy.
  * No counterpart in the reference (its kernels do not wait on asynchronous copies). */
 CANDLE_MOE_API int candle_moe_device_status(int32_t* flags);
+CANDLE_MOE_API int candle_moe_device_status_reset(void);
+CANDLE_MOE_API int candle_moe_selftest_bounded_wait(void* stream, int32_t poll_limit);
 
 /* Weight quantization on the device, bit-exact with QTensor::quantize -> GgmlType::from_float for
  * Q8_0 / Q4K / Q6K (k_quants.rs:605-634, 1287-1345, 1675-1744); replaces the CPU round trip of

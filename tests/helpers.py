@@ -76,3 +76,37 @@ def q8_0_planar(orc, blocks: np.ndarray, rows: int, k: int):
     d = b[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(rows, k // 32)
     qs = b[:, 2:34].copy().view(np.int8).reshape(rows, k)
     return qs, d
+
+
+def random_device_block(orc, torch, cfg, seed=0, device="cuda"):
+    """A block of the given shape with N(0, 0.02) weights generated and quantized ON THE DEVICE, and the oracle-side
+    `MoeWeights` holding the same bytes.  cfg: d, ff, E, k, dt13, dt2, renorm, ff_shared, zipf (router bias
+    log(1/(i+1)))."""
+    from candle_b200 import GgmlDType, Mlp, MlpOrMoe, QMatMul, QTensor
+    d, ff, E = cfg["d"], cfg["ff"], cfg["E"]
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def q(shape, dt):
+        w = torch.randn(shape, generator=g, device=device, dtype=torch.float32) * 0.02
+        return QMatMul(QTensor.quantize(w, GgmlDType(dt)))
+
+    host = lambda qm: qm.inner.data.cpu().numpy()
+    experts = [Mlp(q((ff, d), cfg["dt13"]), q((d, ff), cfg["dt2"]), q((ff, d), cfg["dt13"])) for _ in range(E)]
+    router = torch.randn((E, d), generator=g, device=device, dtype=torch.float32) * 0.02
+    bias = np.log(1.0 / (np.arange(E) + 1.0)).astype(np.float32) if cfg.get("zipf") else None
+    kw = {}
+    if cfg.get("ff_shared"):
+        fs = cfg["ff_shared"]
+        kw["shared_expert"] = Mlp(q((fs, d), cfg["dt13"]), q((d, fs), cfg["dt2"]), q((fs, d), cfg["dt13"]))
+        kw["shared_expert_gate"] = torch.randn(d, generator=g, device=device, dtype=torch.float32) * 0.02
+    blk = MlpOrMoe.moe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"],
+                       router_bias=None if bias is None else torch.from_numpy(bias), **kw)
+    mw = orc.MoeWeights(d, ff, cfg["k"], cfg["dt13"], cfg["dt2"], router.cpu().numpy(),
+                        [host(m.feed_forward_w1) for m in experts], [host(m.feed_forward_w3) for m in experts],
+                        [host(m.feed_forward_w2) for m in experts], renorm=cfg["renorm"], router_bias=bias)
+    if cfg.get("ff_shared"):
+        s = kw["shared_expert"]
+        mw.d_ff_shared, mw.dtype_shared13, mw.dtype_shared2 = cfg["ff_shared"], cfg["dt13"], cfg["dt2"]
+        mw.sw1, mw.sw3, mw.sw2 = host(s.feed_forward_w1), host(s.feed_forward_w3), host(s.feed_forward_w2)
+        mw.shared_gate = kw["shared_expert_gate"].cpu().numpy()
+    return blk, mw

@@ -95,3 +95,47 @@ def test_host_mirror_rejects_cpu_tensors(lib):
     with pytest.raises(ValueError):
         QTensor(torch.zeros(144, dtype=torch.uint8), GgmlDType.Q4K, (1, 256))
     assert GgmlDType.Q4K.type_size() == 144 and GgmlDType.Q6K.type_size() == 210 and GgmlDType.Q8_0.type_size() == 34
+
+
+def test_tuning_switches_round_trip(lib):
+    L = lib.load()
+    v = C.c_int64(-1)
+    assert L.candle_moe_get_tuning(lib.TUNE_GEMM_MIN_ROWS, C.byref(v)) == 0
+    old = v.value
+    assert L.candle_moe_set_tuning(lib.TUNE_GEMM_MIN_ROWS, 77) == 0
+    assert L.candle_moe_get_tuning(lib.TUNE_GEMM_MIN_ROWS, C.byref(v)) == 0 and v.value == 77
+    assert L.candle_moe_set_tuning(lib.TUNE_GEMM_MIN_ROWS, old) == 0
+    assert L.candle_moe_set_tuning(99, 1) == -2 and L.candle_moe_get_tuning(99, C.byref(v)) == -2
+
+
+def _ep_cfg(lib, **kw):
+    cfg = lib.EpConfigC()
+    cfg.rank, cfg.world, cfg.n_experts_global, cfg.top_k, cfg.renorm, cfg.max_tokens = 0, 2, 8, 2, 1, 32
+    one = C.c_float(0)
+    cfg.router = C.cast(C.pointer(one), C.c_void_p)
+    for k, v in kw.items():
+        setattr(cfg, k, v)
+    return cfg, one
+
+
+def test_expert_parallel_geometry_is_host_only(lib):
+    """Form and workspace of candle_moe_ep_forward follow from the configuration alone (no device, no NCCL)."""
+    L = lib.load()
+    local = _weights(lib, n_experts=4)
+    form, cap, need = C.c_int32(0), C.c_int64(0), C.c_size_t(0)
+    cfg, keep = _ep_cfg(lib)
+    assert L.candle_moe_ep_forward_form(C.byref(cfg), C.byref(local), C.byref(form), C.byref(cap)) == 0
+    assert (form.value, cap.value) == (1, 64)  # decode-sized step: slots of max_tokens * min(k, local experts) rows
+    assert L.candle_moe_ep_forward_workspace_bytes(C.byref(cfg), C.byref(local), C.byref(need)) == 0 and need.value > 0
+    from candle_b200.expert_parallel import choose_form
+    for world, tokens, d in ((2, 32, 4096), (8, 32, 4096), (2, 4096, 6144), (4, 2048, 6144), (8, 1024, 4096)):
+        cfg, keep = _ep_cfg(lib, world=world, max_tokens=tokens)
+        local = _weights(lib, n_experts=8 // world, top_k=min(2, 8 // world), d_model=d, d_ff=16384)
+        assert L.candle_moe_ep_forward_form(C.byref(cfg), C.byref(local), C.byref(form), C.byref(cap)) == 0
+        assert form.value == choose_form(world, tokens, 2, 8 // world, d)[0]
+    # ranks must divide the experts; Q8_0 experts have no expert-parallel form; a missing communicator is refused
+    cfg, keep = _ep_cfg(lib, world=3)
+    assert L.candle_moe_ep_forward_form(C.byref(cfg), C.byref(_weights(lib, n_experts=4)), C.byref(form), None) == -2
+    cfg, keep = _ep_cfg(lib)
+    assert L.candle_moe_ep_forward_form(C.byref(cfg), C.byref(_weights(lib, n_experts=4, dtype_w13=8, d_model=4096)),
+                                        C.byref(form), None) == -3

@@ -343,7 +343,7 @@ def test_streaming_form_equals_row_form(orc, torch_cuda, name, rows_per_expert, 
     pb = (C.c_void_p * E)(*[w.data_ptr() for w in wbd])
     outs = {}
     for mode in ("0", "1"):
-        monkeypatch.setenv("CANDLE_MOE_FORCE_ROWS", mode)
+        assert L.candle_moe_set_tuning(_lib.TUNE_FORCE_ROWS, int(mode)) == 0
         out = torch.full((P, n), float("nan"), dtype=torch.float32, device="cuda")
         if gate_up:
             rc = L.candle_moe_grouped_gate_up(st, pa, pb, dt, E, k, n, offs.data_ptr(), perm.data_ptr(), max(rows_per_expert),
@@ -354,6 +354,7 @@ def test_streaming_form_equals_row_form(orc, torch_cuda, name, rows_per_expert, 
         assert rc == 0
         torch.cuda.synchronize()
         outs[mode] = out.cpu().numpy()
+    assert L.candle_moe_set_tuning(_lib.TUNE_FORCE_ROWS, 0) == 0
     flags = C.c_int32(-1)
     assert L.candle_moe_device_status(C.byref(flags)) == 0 and flags.value == 0
     # oracle
@@ -472,7 +473,7 @@ def test_block_small_ragged_q4k_q6k(orc, torch_cuda, T, prepack):
 
 
 def test_block_config1_shape(orc, torch_cuda):
-    """BASELINE config 1: d=1024, ff=3584, 8 experts, top-2, all Q4_K, 256 tokens, seeds 0 / 1."""
+    """d=1024, ff=3584, 8 experts, top-2, all Q4_K, 256 tokens, seeds 0 / 1 (the CPU-runnable shape)."""
     mw = orc.make_moe_weights(0, 1024, 3584, 8, 2, orc.Q4K, orc.Q4K)
     x = orc.make_activations(1, 256, 1024)
     blk, y, ref = _check_block(orc, torch_cuda, mw, x, "config 1")
@@ -490,15 +491,15 @@ def test_block_all_tokens_on_two_experts_and_empty_experts(orc, torch_cuda):
 
 
 def test_block_q8_0_top4_no_renorm_shared_expert(orc, torch_cuda):
-    """BASELINE config 4 at reduced token count: d=2048, 60 routed experts of ff=1408, top-4 without
-    renormalisation, shared expert ff=5632 gated by sigmoid(x.g), all Q8_0."""
+    """The fine-grained shape at a reduced token count: d=2048, 60 routed experts of ff=1408, top-4 without
+    renormalisation, shared expert ff=5632 gated by sigmoid(x.g), all Q8_0 (qwen2_moe.rs:261-323)."""
     mw = orc.make_moe_weights(7, 2048, 1408, 60, 4, orc.Q8_0, orc.Q8_0, renorm=False, ff_shared=5632)
     x = orc.make_activations(8, 96, 2048)
     _check_block(orc, torch_cuda, mw, x, "config 4 (T=96)")
 
 
 def test_block_mixtral_layer_decode_sizes(orc, torch_cuda):
-    """BASELINE config 2 (d=4096, ff=14336, 8 experts, top-2, w1/w3 Q4_K, w2 Q6_K) at T = 1, 8, 32.
+    """The Mixtral-8x7B layer (d=4096, ff=14336, 8 experts, top-2, w1/w3 Q4_K, w2 Q6_K) at T = 1, 8, 32.
     Weights are quantized on the device (bit-exact with the reference quantizer, see above) and the
     same bytes are handed to the oracle."""
     torch = torch_cuda
@@ -582,9 +583,11 @@ def test_block_large_batch_tensor_core_form(orc, torch_cuda, name13, name2, monk
     x = orc.make_activations(31, 300, 512)
     blk, y, ref = _check_block(orc, torch, mw, x, f"tensor-core form {name13}/{name2}", prepack=True)
     assert _device_status() == 0
-    monkeypatch.setenv("CANDLE_MOE_GEMM", "0")
-    y_stream = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
-    monkeypatch.delenv("CANDLE_MOE_GEMM")
+    assert _lib.load().candle_moe_set_tuning(_lib.TUNE_GEMM_ENABLED, 0) == 0
+    try:
+        y_stream = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
+    finally:
+        assert _lib.load().candle_moe_set_tuning(_lib.TUNE_GEMM_ENABLED, 1) == 0
     assert H.rel_l2(y, y_stream) < 2e-4
     y_again = blk.forward(torch.from_numpy(x).cuda()).cpu().numpy()
     assert np.array_equal(y, y_again)
