@@ -718,13 +718,174 @@ def run_projections(args):
                                  "prepacked": not args.no_prepack}, "projections": rows}))
 
 
+def run_c3(args):
+    """`--workload c3`: one decode step of a 32-layer Mixtral-8x7B-shaped model at batch 32 with a 4096-token context
+    (candle_b200/llama_decode.py: quantized products and the FFN half of every layer through this library, attention
+    and the other glue as stock PyTorch ops).  tokens/s = batch / step time."""
+    import torch
+    import torch.distributed as dist
+    from candle_b200.llama_decode import DecodeConfig, DecodeStep
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    import candle_b200  # noqa: F401
+    cfg = DecodeConfig()
+    if args.layers:
+        cfg.n_layer = args.layers
+    B = args.tokens or 32
+    ctx = min(args.context, cfg.max_seq)
+    index_pos = ctx - 1
+    ep = None
+    if world > 1:
+        from candle_b200 import ExpertParallelMoe
+        ep = {"world": world, "rank": rank,
+              "make": lambda lw: ExpertParallelMoe(cfg.n_expert_used, lw.router, lw.experts, prepack=not args.no_prepack,
+                                                   max_tokens=B)}
+    model = DecodeStep(cfg, B, dev, n_distinct=4, seed=0, prepack=not args.no_prepack, expert_parallel=ep)
+    tokens = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator(device=dev).manual_seed(5 + rank), device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def agree(n):
+        if world == 1:
+            return n
+        t = torch.tensor([n if rank == 0 else 0], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return int(t)
+
+    logits = model.forward(tokens, index_pos)  # also allocates every scratch buffer
+    for _ in range(max(args.warmup, 3) - 1):
+        logits = model.forward(tokens, index_pos)
+    barrier()
+    # the step replays from one CUDA graph where that is possible (single GPU): the host then adds nothing
+    graph = None
+    step = lambda: model.forward(tokens, index_pos)
+    if world == 1 and not args.eager:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g_logits = model.forward(tokens, index_pos)
+            graph.replay()
+            torch.cuda.synchronize()
+            step = graph.replay
+        except Exception as exc:  # noqa: BLE001
+            print(f"# graph capture failed ({type(exc).__name__}: {exc}); timing eager steps", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    batches, region_s = timed_batches(torch, step, args.steps, barrier, None, MIN_TIMED_SECONDS, agree)
+    clocks = sampler.stop() if sampler else None
+    ms_step = statistics.median(batches) / args.steps
+
+    # shares: the same layers' attention halves alone and FFN halves alone (eager, events around each loop)
+    x = torch.randn((B, cfg.d_model), device=dev)
+    def loop_ms(fn, reps=3):
+        best = []
+        for _ in range(reps):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for li in range(cfg.n_layer):
+                fn(li)
+            e1.record()
+            barrier()
+            best.append(e0.elapsed_time(e1))
+        return min(best)
+    ms_attn = loop_ms(lambda li: model.attention(li, x, index_pos))
+    ms_ffn = loop_ms(lambda li: model.ffn(li, x))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(5):
+        model.output.forward(x)
+    e1.record()
+    barrier()
+    ms_head = e0.elapsed_time(e1) / 5
+
+    # end to end: token ids from pinned host memory, logits back to pinned host memory
+    h_tok = tokens.cpu().pin_memory()
+    h_logits = torch.empty((B, cfg.vocab), dtype=torch.float32).pin_memory()
+    src = g_logits if graph is not None else None
+
+    def e2e_step():
+        tokens.copy_(h_tok, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+            h_logits.copy_(src, non_blocking=True)
+        else:
+            h_logits.copy_(model.forward(tokens, index_pos), non_blocking=True)
+
+    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, 0.3, agree)
+    ms_e2e = statistics.median(e2e_batches) / args.steps
+    t = torch.tensor([ms_step, ms_e2e, ms_attn, ms_ffn], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, ms_e2e, ms_attn, ms_ffn = (float(v) for v in t)
+    if rank == 0:
+        byts = model.bytes_per_step(index_pos)
+        if world > 1:
+            byts["moe_weights"] //= world
+        total = sum(byts.values())
+        peak, peak_kind = peaks()
+        line = {
+            "metric": "decode_tokens_per_s", "value": B * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot / f32 accumulate (quantized products), f32 (attention)",
+            "data": "synthetic",
+            "config": {"workload": f"c3: {cfg.n_layer}-layer Mixtral-8x7B-shaped decode step, batch {B} per GPU, context {ctx}, "
+                                   f"d={cfg.d_model} heads {cfg.n_head}/{cfg.n_kv_head} x {cfg.head_dim}, {cfg.n_expert} experts "
+                                   f"top-{cfg.n_expert_used} ff={cfg.d_ff}, vocab {cfg.vocab}",
+                       "weights": "4 distinct random layers rotate over the layers (attention Q4_K, w1/w3 Q4_K, w2 Q6_K, lm head Q6_K)",
+                       "library_parts": "wq/wk/wv/wo, lm head (candle_moe_qmatmul); ffn_norm + MoE block + residual (candle_moe_ffn_layer"
+                                        + (", experts sharded: candle_moe_ep_forward)" if world > 1 else ")"),
+                       "pytorch_parts": "embedding, attention_norm / final norm, interleaved RoPE, f32 KV cache append, "
+                                        "attention (q k^T, softmax, v as batched f32 matmuls)",
+                       "l2_policy": "a step reads tens of GB: nothing survives in the 126 MB L2 between steps",
+                       "timed": "CUDA graph replay" if graph is not None else "eager launches",
+                       "parallelism": "single GPU" if world == 1 else f"ep{world}: experts sharded, attention replicated, "
+                                      f"every rank decodes its own {B} sequences"},
+            "roofline": {"bound": "hbm", "kernel": "whole decode step", "achieved": total / (ms_step * 1e-3) / 1e9, "peak": peak,
+                         "unit": "GB/s", "frac": total / (ms_step * 1e-3) / 1e9 / peak, "traffic": None,
+                         "peak_source": f"{peak_kind} copy bandwidth", "algorithmic_bytes_per_launch": total,
+                         "bytes": byts, "ms_at_peak": total / (peak * 1e9) * 1e3},
+            "shares": {"attention_half_ms": ms_attn, "ffn_half_ms": ms_ffn, "lm_head_ms": ms_head,
+                       "ffn_share_of_step": ms_ffn / ms_step,
+                       "note": "halves timed alone over all layers with eager launches; the step itself may replay from a graph"},
+            "timing": {"batches": len(batches), "steps_per_batch": args.steps, "timed_region_s": region_s},
+            "cpu_baseline": None,
+            "e2e": {"value": B * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 8,
+                    "d2h_bytes_per_step": B * cfg.vocab * 4, "ms_per_step": ms_e2e},
+            "gpu_launches": cfg.n_layer * (4 * 3 + 6) * args.steps,
+            "finite": bool(torch.isfinite(logits).all()),
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["proj"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["proj", "c3"])
+    ap.add_argument("--layers", type=int, default=0, help="c3: number of layers (default 32)")
+    ap.add_argument("--context", type=int, default=4096, help="c3: tokens in the context, the new one included")
+    ap.add_argument("--eager", action="store_true", help="c3: time eager launches instead of a CUDA graph replay")
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-c5", action="store_true",
                     help="N > 1: skip the Mixtral-8x22B-shaped sub-record that accompanies the default workload")
@@ -733,6 +894,13 @@ def main():
     args = ap.parse_args()
     if args.workload == "proj":
         return run_projections(args)
+    if args.workload == "c3":
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the CPU restatement covers the MoE block, not attention: "
+                                                                      "no CPU arm for the whole decode step"}))
+            return
+        return run_c3(args)
     cfg = dict(WORKLOADS[args.workload])
     if args.workload == "c5":
         cfg["zipf_bias"] = True

@@ -1,0 +1,91 @@
+"""The decode-step harness (candle_b200/llama_decode.py) against a CPU restatement of the same step built from the
+oracle's pieces: `QMatMul::forward` as the oracle's quantized matmul, RmsNorm, the whole MoE block, and numpy for the
+attention glue, following `ModelWeights::forward` (candle-transformers/src/models/quantized_llama.rs:869-898) and
+`forward_attn` (:264-345) for one new token per sequence.  Reduced sizes (2 layers, 8 heads of 64, context 24)."""
+import math
+
+import numpy as np
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _host(qm):
+    return qm.inner.data.cpu().numpy()
+
+
+def _cpu_step(orc, model, tokens, index_pos, k_cache, v_cache):
+    cfg = model.cfg
+    B, hd, nh, nkv = model.batch, cfg.head_dim, cfg.n_head, cfg.n_kv_head
+    x = model.tok_embeddings.cpu().numpy()[tokens]
+    cos, sin = model.cos.cpu().numpy()[index_pos], model.sin.cpu().numpy()[index_pos]
+
+    def rope(t):  # [B, H, hd]
+        out = np.empty_like(t)
+        out[..., 0::2] = t[..., 0::2] * cos - t[..., 1::2] * sin
+        out[..., 1::2] = t[..., 0::2] * sin + t[..., 1::2] * cos
+        return out
+
+    for li in range(cfg.n_layer):
+        lw = model.sets[model.layer_set[li]]
+        h = orc.rms_norm(x, lw.attention_norm.cpu().numpy(), cfg.rms_eps)
+        q = orc.matmul(cfg.dt_attn, h, _host(lw.attention_wq), nh * hd).reshape(B, nh, hd)
+        k = orc.matmul(cfg.dt_attn, h, _host(lw.attention_wk), nkv * hd).reshape(B, nkv, hd)
+        v = orc.matmul(cfg.dt_attn, h, _host(lw.attention_wv), nkv * hd).reshape(B, nkv, hd)
+        q, k = rope(q), rope(k)
+        kc, vc = k_cache[li], v_cache[li]
+        kc[:, :, index_pos], vc[:, :, index_pos] = k, v
+        n = index_pos + 1
+        g = nh // nkv
+        y = np.empty((B, nh, hd), np.float32)
+        for b in range(B):
+            for hq in range(nh):
+                kk, vv = kc[b, hq // g, :n], vc[b, hq // g, :n]
+                att = (kk @ q[b, hq]) / np.float32(math.sqrt(hd))
+                att = np.exp(att - att.max())
+                att = att / att.sum()
+                y[b, hq] = att @ vv
+        x = orc.matmul(cfg.dt_attn, y.reshape(B, nh * hd), _host(lw.attention_wo), cfg.d_model) + x
+        mw = orc.MoeWeights(cfg.d_model, cfg.d_ff, cfg.n_expert_used, cfg.dt_w13, cfg.dt_w2, lw.router.cpu().numpy(),
+                            [_host(m.feed_forward_w1) for m in lw.experts], [_host(m.feed_forward_w3) for m in lw.experts],
+                            [_host(m.feed_forward_w2) for m in lw.experts])
+        hn = orc.rms_norm(x, lw.ffn_norm.cpu().numpy(), cfg.rms_eps)
+        x = orc.moe_forward(mw, hn).y + x
+    x = orc.rms_norm(x, model.norm.cpu().numpy(), cfg.rms_eps)
+    return orc.matmul(cfg.dt_output, x, _host(model.output), cfg.vocab)
+
+
+@pytest.mark.parametrize("prepack", [True, False])
+def test_decode_step_matches_the_cpu_restatement(orc, torch_cuda, prepack):
+    torch = torch_cuda
+    from candle_b200.llama_decode import DecodeConfig, DecodeStep
+    cfg = DecodeConfig(vocab=512, d_model=512, n_head=8, n_kv_head=2, head_dim=64, n_layer=2, n_expert=8, n_expert_used=2,
+                       d_ff=1024, max_seq=32)
+    B, index_pos = 5, 23
+    model = DecodeStep(cfg, B, torch.device("cuda"), n_distinct=2, seed=3, prepack=prepack)
+    tokens = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator(device="cuda").manual_seed(1), device="cuda")
+    k0 = [t.cpu().numpy().copy() for t in model.k_cache]
+    v0 = [t.cpu().numpy().copy() for t in model.v_cache]
+    logits = model.forward(tokens, index_pos).cpu().numpy()
+    ref = _cpu_step(orc, model, tokens.cpu().numpy(), index_pos, k0, v0)
+    assert np.isfinite(logits).all()
+    # two layers of re-quantized activations: each quantized product sees inputs that differ in their last bits from
+    # the CPU's, which flips a few int8 steps per row; the per-block bound (1e-3) applies to each block, the stack of
+    # two layers and the lm head stays within three times that
+    assert H.rel_l2(logits, ref) <= 3e-3 and H.max_rel(logits, ref) <= 6e-3, (H.rel_l2(logits, ref), H.max_rel(logits, ref))
+    # the cache holds the new position, and nothing else changed
+    for li in range(cfg.n_layer):
+        kc = model.k_cache[li].cpu().numpy()
+        assert np.array_equal(kc[:, :, :index_pos], k0[li][:, :, :index_pos])
+        assert H.rel_l2(kc[:, :, index_pos], k0[li][:, :, index_pos]) <= 1e-3
+    # determinism, and replay from a CUDA graph gives the same logits
+    again = model.forward(tokens, index_pos).cpu().numpy()
+    assert np.array_equal(again, logits)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.forward(tokens, index_pos)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), logits)

@@ -37,6 +37,8 @@ def test_forward_static_matches_forward_twice(orc):
         got = y.cpu().numpy()
         assert np.isfinite(got).all()
         assert H.max_rel(got, want) <= H.MAX_REL_TOL and H.rel_l2(got, want) <= H.REL_L2_TOL
+        ref = orc.moe_forward(mw, x.cpu().numpy())  # and against the CPU oracle directly
+        assert H.max_rel(got, ref.y) <= H.MAX_REL_TOL and H.rel_l2(got, ref.y) <= H.REL_L2_TOL
 
 
 def test_forward_static_refuses_oversized_calls(orc):
