@@ -391,10 +391,15 @@ def run_ours(args, cfg):
         # a rank that falls out of step must end the run with an error, not hang it
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     import candle_b200  # noqa: F401  loads libcandle_moe_sm100.so or raises
+    if args.gemm_min_rows:
+        from candle_b200 import _lib
+        _lib.check("candle_moe_set_tuning", _lib.load().candle_moe_set_tuning(_lib.TUNE_GEMM_MIN_ROWS, args.gemm_min_rows))
 
     T, d = args.tokens, cfg["d"]
     if world > 1:
         return run_ep(args, cfg, torch, dist, rank, world, local, dev)
+    if args.ep_local:
+        return run_ep_local(args, cfg, torch, dev)
     blk = build_block(torch, cfg, dev, seed=0, prepack=not args.no_prepack)
     blk.reserve(T)
     gx = torch.Generator(device=dev).manual_seed(1 + rank)
@@ -618,6 +623,32 @@ def ep_measure(args, cfg, torch, dist, rank, world, dev, T, steps, warmup, min_s
                 "d2h_bytes_per_step": T * d * 4, "ms_per_step": ms_e2e},
         "clocks": clocks,
     }
+
+
+def run_ep_local(args, cfg, torch, dev):
+    """`--ep-local`: the expert-parallel step on ONE GPU (world size 1: both exchanges are device copies), so that
+    its pack / plan / regroup / scatter kernels can be timed and profiled without a second GPU.  `--ep-form` picks the
+    slot form (1) or the exact form (2)."""
+    T, d = args.tokens, cfg["d"]
+    blk = build_ep_block(torch, cfg, dev, 0, 1, prepack=not args.no_prepack, max_tokens=T)
+    blk.force_form = args.ep_form
+    x = torch.randn((T, d), generator=torch.Generator(device=dev).manual_seed(1), device=dev, dtype=torch.float32)
+    y = torch.empty_like(x)
+    for _ in range(args.warmup):
+        blk.forward(x, out=y)
+    torch.cuda.synchronize()
+    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, torch.cuda.synchronize, None, 0.3)
+    acc = {n: 0.0 for n in blk.PHASES}
+    for _ in range(5):
+        _, ms = blk.forward(x, out=y, timed=True)
+        for n in acc:
+            acc[n] += ms[n] / 5
+    ms_step = statistics.median(batches) / args.steps
+    print(json.dumps({"metric": "moe_layer_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                      "data": "synthetic", "config": dict(config_dict(args, cfg), parallelism="expert-parallel step on one GPU "
+                                                          "(exchanges are device copies)", form=blk.form()),
+                      "stage_ms": acc, "rows_received": blk.last_rows}))
 
 
 def run_ep(args, cfg, torch, dist, rank, world, local, dev):
@@ -887,6 +918,10 @@ def main():
     ap.add_argument("--context", type=int, default=4096, help="c3: tokens in the context, the new one included")
     ap.add_argument("--eager", action="store_true", help="c3: time eager launches instead of a CUDA graph replay")
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--gemm-min-rows", type=int, default=0,
+                    help="bound on an expert's rows above which the tensor-core GEMM runs (default: the library's)")
+    ap.add_argument("--ep-local", action="store_true", help="N = 1: run the expert-parallel step on one GPU (profiling aid)")
+    ap.add_argument("--ep-form", type=int, default=0, choices=[0, 1, 2], help="--ep-local: 1 = slot form, 2 = exact form")
     ap.add_argument("--no-c5", action="store_true",
                     help="N > 1: skip the Mixtral-8x22B-shaped sub-record that accompanies the default workload")
     ap.add_argument("--no-prepack", action="store_true",

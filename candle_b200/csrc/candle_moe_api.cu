@@ -279,6 +279,9 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         else if (ce != cudaErrorNotSupported)
             return (int)ce;
     }
+    // Position-tile width of the GEMM: from the actual largest row count when it is known, else from five quarters
+    // of the average (an expert beyond the tile width simply takes a second tile)
+    const int64_t tile_rows = rows_exact ? max_rows : std::min<int64_t>(max_rows, (5 * total_rows_hint + 4 * E - 1) / (4 * E));
     if (!gate_done && large) {
         // Q6_K is read from the repacked copies (its GGUF blocks are only 2-byte aligned)
         const bool rp = w->dtype_w13 == CANDLE_GGML_Q6K && w->w1_prepacked && w->w3_prepacked;
@@ -287,7 +290,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
             CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
             CM_TRY(fill_ptrs(w->w3_prepacked, E, g3));
         }
-        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, offsets, row_of, P, max_rows, xq,
+        const cudaError_t ce = launch_expert_gemm(st, true, g1, g3, w->dtype_w13, rp, E, d, ff, offsets, row_of, P, tile_rows, xq,
                                                   xs, xb, b.hidden, b.gemm);
         if (ce == cudaSuccess)
             gate_done = true;
@@ -314,7 +317,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
         const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
         ExpertPtrs g2 = p2;
         if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
-        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, max_rows,
+        const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, tile_rows,
                                                   b.hq, b.hs, b.hb, b.eo, b.gemm, slots, eo_splits, P * d);
         if (ce == cudaSuccess) {
             down_done = true;

@@ -44,6 +44,7 @@ namespace {
 
 constexpr int G_TILE_M = 128, G_SLAB_K = 64;  // the position tile (N) is a template parameter: 128, or 32 for small batches
 constexpr int G_PAD_ROWS = 128;                // zero rows after the last position, so that no box leaves the buffers
+constexpr int G_W_STAGES_MAX = 4;  // raw weight blocks in flight per CTA (narrow position tiles leave room for a deep ring)
 constexpr int G_B_STAGES = 2;   // in shared memory, one 256-wide block each (four slabs + the min-term box for Q4_K)
 constexpr int G_TILE_BYTES = G_TILE_M * G_SLAB_K * 2;  // one [128 x 64] fp16 (or [128 x 32] tf32) operand tile, 16 KB
 constexpr int G_EPI_WARPS = 8, G_DQ_WARPS = 8;
@@ -318,6 +319,12 @@ struct GemmQ6K {
     __device__ static __forceinline__ float scale_of(uint32_t hdr) { return half_bits_to_float((uint16_t)hdr); }
 };
 
+// raw weight blocks staged per CTA (see the kernel): what fits beside the activation stages
+template <class F, int TN>
+__host__ __device__ constexpr int w_stages() {
+    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? 3 : 1));
+}
+
 struct TileCoord {
     int e, nt, mt;
     int ks, kb0, kb1;  // K split: this work item covers the 256-blocks [kb0, kb1) and writes partial output ks
@@ -359,7 +366,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                    const __grid_constant__ CUtensorMap map_bs) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_a[4], empty_a[4], full_b[G_B_STAGES], empty_b[G_B_STAGES];  // A: per pair of slabs
-    __shared__ uint64_t tmem_full[2], epi_done[2], full_w, empty_w;
+    __shared__ uint64_t tmem_full[2], epi_done[2], full_w[G_W_STAGES_MAX], empty_w[G_W_STAGES_MAX];
     __shared__ uint32_t s_offs[CANDLE_MOE_MAX_EXPERTS + 1];
     constexpr int CH = TN / 2;            // columns (positions) per epilogue warp: two warps share a TMEM lane quarter
     constexpr int B_TILE = TN * G_SLAB_K * 2;  // one [TN x 64] fp16 activation slab
@@ -375,7 +382,12 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * B_TILE;
     uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
-    uint8_t* smem_w = smem_min_a + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES;  // staged raw blocks of the tile rows (one block deep)
+    // staged raw blocks of the tile rows: a ring of WS blocks.  With 128-wide position tiles the activation stages
+    // leave room for one block only (the L2 prefetch ahead of it has to do); narrower tiles take a deeper ring, so
+    // that the copy of block b + WS - 1 is in flight while block b is unpacked.
+    constexpr int WS = w_stages<F, TN>();
+    constexpr int W_STAGE_BYTES = G_TILE_M * F::W_ROW_BYTES;
+    uint8_t* smem_w = smem_min_a + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES;
     for (int i = threadIdx.x; i <= P.E; i += G_THREADS) s_offs[i] = P.offsets[i];
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -391,8 +403,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             mbar_init(&tmem_full[b], 1);
             mbar_init(&epi_done[b], G_EPI_WARPS);
         }
-        mbar_init(&full_w, 1);
-        mbar_init(&empty_w, G_DQ_WARPS);
+        for (int s = 0; s < G_W_STAGES_MAX; ++s) {
+            mbar_init(&full_w[s], 1);
+            mbar_init(&empty_w[s], G_DQ_WARPS);
+        }
         fence_barrier_init();
     }
     if (warp == G_WARP_TMA) tmem_alloc(&s_tmem_base, G_TMEM_COLS);
@@ -534,8 +548,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 if (F::STAGE_W) {
                     // this block's raw bytes were copied to shared memory by the loader warp
-                    mbar_wait(&full_w, ab & 1, abort_flag);
-                    F::load_staged(cur, w_row, h);
+                    mbar_wait(&full_w[ab % WS], (ab / WS) & 1, abort_flag);
+                    F::load_staged(cur, w_row + (ab % WS) * W_STAGE_BYTES, h);
                 } else if (blk + 1 < tc.kb1) {
                     F::load(nxt, rowc, blk + 1, h);
                 } else if (have_n) {
@@ -546,7 +560,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 if (h == 0) s_dw[ab & 7][r] = F::scale_of(F::hdr_of(cur));  // read by the epilogue when it drains this block
                 if (F::STAGE_W) {  // the staged copy is in registers: the loader may refill it
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_w);
+                    if (lane == 0) mbar_arrive(&empty_w[ab % WS]);
                 }
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
@@ -609,15 +623,17 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 }
                 const int y0 = GATE_UP ? tc.mt * 64 : tc.mt * 128;
                 for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
-                    if (ab >= 1) mbar_wait(&empty_w, (ab - 1) & 1, abort_flag);
+                    const uint32_t ws = ab % WS;
+                    if (ab >= (uint32_t)WS) mbar_wait(&empty_w[ws], ((ab / WS) - 1) & 1, abort_flag);
                     if (elect_one()) {
-                        mbar_expect_tx(&full_w, G_TILE_M * F::W_ROW_BYTES);
+                        uint8_t* dst = smem_w + ws * W_STAGE_BYTES;
+                        mbar_expect_tx(&full_w[ws], G_TILE_M * F::W_ROW_BYTES);
                         if (GATE_UP) {
-                            tma_load_2d(smem_w, m0, blk * F::W_ROW_BYTES, y0, &full_w);
-                            tma_load_2d(smem_w + HALF, m0 + 1, blk * F::W_ROW_BYTES, y0, &full_w);
+                            tma_load_2d(dst, m0, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
+                            tma_load_2d(dst + HALF, m0 + 1, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
                         } else {
-                            tma_load_2d(smem_w, m0, blk * F::W_ROW_BYTES, y0, &full_w);
-                            tma_load_2d(smem_w + HALF, m0, blk * F::W_ROW_BYTES, y0 + 64, &full_w);
+                            tma_load_2d(dst, m0, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
+                            tma_load_2d(dst + HALF, m0, blk * F::W_ROW_BYTES, y0 + 64, &full_w[ws]);
                         }
                         // two blocks ahead, possibly in the next tile
                         const bool same = blk + 2 < tc.kb1;
@@ -781,7 +797,7 @@ __global__ void __launch_bounds__(128) write_maps_kernel(const __grid_constant__
 template <class F, bool GATE_UP, int TN>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
     const int smem_bytes = G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
-                           (F::STAGE_W ? G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
+                           (F::STAGE_W ? w_stages<F, TN>() * G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP, TN>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e != cudaSuccess) return e;
@@ -805,7 +821,7 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
                                void* scratch, int max_splits, int* n_splits_out, int64_t split_stride) {
     if (n_splits_out) *n_splits_out = 1;
     if (!scratch) return cudaErrorNotSupported;
-    const int tn = max_rows <= 32 ? 32 : 128;  // position tile: no expert has more than max_rows rows
+    const int tn = max_rows <= 32 ? 32 : (max_rows <= 64 ? 64 : 128);  // position tile, from the bound / hint on an expert's rows
     if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked))) return cudaErrorNotSupported;
     if (K % 256 != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
     if (!encode_tiled_fn()) return cudaErrorNotSupported;
@@ -885,10 +901,14 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     if (dtype == CANDLE_GGML_Q4K) {
         if (tn == 32)
             return gate_up ? launch_gemm_kernel<GemmQ4K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 32>(st, G, map_b, map_bs);
+        if (tn == 64)
+            return gate_up ? launch_gemm_kernel<GemmQ4K, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 64>(st, G, map_b, map_bs);
         return gate_up ? launch_gemm_kernel<GemmQ4K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 128>(st, G, map_b, map_bs);
     }
     if (tn == 32)
         return gate_up ? launch_gemm_kernel<GemmQ6K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 32>(st, G, map_b, map_bs);
+    if (tn == 64)
+        return gate_up ? launch_gemm_kernel<GemmQ6K, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 64>(st, G, map_b, map_bs);
     return gate_up ? launch_gemm_kernel<GemmQ6K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 128>(st, G, map_b, map_bs);
 }
 

@@ -16,7 +16,8 @@ def _host(qm):
     return qm.inner.data.cpu().numpy()
 
 
-def _cpu_step(orc, model, tokens, index_pos, k_cache, v_cache):
+def _cpu_step(orc, model, tokens, index_pos, k_cache, v_cache, stages=None):
+    """Logits of the step; `stages`, if a list, receives (layer, "attention" | "ffn", input, output) per half layer."""
     cfg = model.cfg
     B, hd, nh, nkv = model.batch, cfg.head_dim, cfg.n_head, cfg.n_kv_head
     x = model.tok_embeddings.cpu().numpy()[tokens]
@@ -47,12 +48,18 @@ def _cpu_step(orc, model, tokens, index_pos, k_cache, v_cache):
                 att = np.exp(att - att.max())
                 att = att / att.sum()
                 y[b, hq] = att @ vv
+        x_in = x
         x = orc.matmul(cfg.dt_attn, y.reshape(B, nh * hd), _host(lw.attention_wo), cfg.d_model) + x
+        if stages is not None:
+            stages.append((li, "attention", x_in, x))
         mw = orc.MoeWeights(cfg.d_model, cfg.d_ff, cfg.n_expert_used, cfg.dt_w13, cfg.dt_w2, lw.router.cpu().numpy(),
                             [_host(m.feed_forward_w1) for m in lw.experts], [_host(m.feed_forward_w3) for m in lw.experts],
                             [_host(m.feed_forward_w2) for m in lw.experts])
         hn = orc.rms_norm(x, lw.ffn_norm.cpu().numpy(), cfg.rms_eps)
+        x_in = x
         x = orc.moe_forward(mw, hn).y + x
+        if stages is not None:
+            stages.append((li, "ffn", x_in, x))
     x = orc.rms_norm(x, model.norm.cpu().numpy(), cfg.rms_eps)
     return orc.matmul(cfg.dt_output, x, _host(model.output), cfg.vocab)
 
@@ -69,12 +76,19 @@ def test_decode_step_matches_the_cpu_restatement(orc, torch_cuda, prepack):
     k0 = [t.cpu().numpy().copy() for t in model.k_cache]
     v0 = [t.cpu().numpy().copy() for t in model.v_cache]
     logits = model.forward(tokens, index_pos).cpu().numpy()
-    ref = _cpu_step(orc, model, tokens.cpu().numpy(), index_pos, k0, v0)
+    stages = []
+    ref = _cpu_step(orc, model, tokens.cpu().numpy(), index_pos, k0, v0, stages)
     assert np.isfinite(logits).all()
-    # two layers of re-quantized activations: each quantized product sees inputs that differ in their last bits from
-    # the CPU's, which flips a few int8 steps per row; the per-block bound (1e-3) applies to each block, the stack of
-    # two layers and the lm head stays within three times that
-    assert H.rel_l2(logits, ref) <= 3e-3 and H.max_rel(logits, ref) <= 6e-3, (H.rel_l2(logits, ref), H.max_rel(logits, ref))
+    # every half layer on the CPU's own input: the per-block bounds hold for each (the attention half adds a softmax
+    # over f32 scores and two more quantized products)
+    for li, what, x_in, x_out in stages:
+        xd = torch.from_numpy(x_in).cuda()
+        got = (model.attention(li, xd, index_pos) if what == "attention" else model.ffn(li, xd)).cpu().numpy()
+        mr, l2 = H.max_rel(got, x_out), H.rel_l2(got, x_out)
+        assert mr <= H.MAX_REL_TOL and l2 <= H.REL_L2_TOL, f"layer {li} {what}: max-rel {mr:.3e} rel-L2 {l2:.3e}"
+    # the whole step: differences of the order of one int8 step in a re-quantized activation row (1 / 128 of the
+    # row's largest value) are amplified by the following layers at these small widths (d = 512: two blocks per row)
+    assert H.rel_l2(logits, ref) <= 2e-2, (H.rel_l2(logits, ref), H.max_rel(logits, ref))
     # the cache holds the new position, and nothing else changed
     for li in range(cfg.n_layer):
         kc = model.k_cache[li].cpu().numpy()
