@@ -34,6 +34,7 @@ struct Workspace {
     uint32_t* offsets;
     uint32_t* perm_token;
     uint32_t* pair_pos;
+    uint32_t* perm_scratch;  // per-chunk tables of the many-CTA dispatch
     // quantized input rows (one per token; experts gather through perm_token)
     int8_t* xq;
     float* xs;
@@ -69,6 +70,7 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     ws.offsets = carve<uint32_t>(base, off, E + 1);
     ws.perm_token = carve<uint32_t>(base, off, Tk);
     ws.pair_pos = carve<uint32_t>(base, off, Tk);
+    ws.perm_scratch = carve<uint32_t>(base, off, permute_scratch_words((int64_t)Tk, (int)E));
     ws.xq = carve<int8_t>(base, off, (size_t)T * d);
     ws.xs = carve<float>(base, off, (size_t)T * d / act_block(w->dtype_w13));
     ws.xb = carve<int16_t>(base, off, (size_t)T * d / 16);
@@ -396,7 +398,7 @@ static int forward_impl(void* stream, const candle_moe_weights_t* w, const float
                                  T == 1 ? ws.counts : nullptr, ws.offsets, ws.perm_token, ws.pair_pos)));
     mark(st, 0);
     // one token: the router kernel has written the dispatch itself
-    if (T > 1) CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos)));
+    if (T > 1) CM_TRY(rc(launch_permute(st, ws.topk_ids, T, k, E, ws.counts, ws.offsets, ws.perm_token, ws.pair_pos, ws.perm_scratch)));
     mark(st, 1);
     if (!fuse_q) CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_w13, ws.xq, ws.xs, ws.xb)));
     mark(st, 2);

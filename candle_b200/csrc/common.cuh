@@ -163,8 +163,10 @@ cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* rou
                                int d, int E, int k, int renorm, uint32_t* ids, float* w, int8_t* qs = nullptr,
                                float* scales = nullptr, int16_t* bsums = nullptr, uint32_t* counts = nullptr,
                                uint32_t* offsets = nullptr, uint32_t* perm_token = nullptr, uint32_t* pair_pos = nullptr);
+// scratch (may be null): permute_scratch_words(T * k, E) words; with it, large batches are sorted by many CTAs
+size_t permute_scratch_words(int64_t n_pairs, int E);
 cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
-                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos);
+                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos, uint32_t* scratch = nullptr);
 // offsets[0..2) = {0, rows}: one group holding every row (used for the always-on shared expert)
 cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows);
 // row_limit (Q8K only, may be null): device-side row count; rows at or beyond it are skipped

@@ -184,7 +184,7 @@ int geometry(const candle_moe_ep_config_t* c, const candle_moe_weights_t* w, EpG
 }
 
 struct EpFwdWorkspace {
-    uint32_t *ids, *counts, *offsets, *perm, *pair_pos, *slot_pos;
+    uint32_t *ids, *counts, *offsets, *perm, *pair_pos, *slot_pos, *perm_scratch;
     float* tw;
     int8_t* xq;
     float* xs;
@@ -209,6 +209,7 @@ EpFwdWorkspace fwd_layout(const EpGeometry& g, const candle_moe_weights_t* w, vo
     ws.perm = carve<uint32_t>(base, off, Tk);
     ws.pair_pos = carve<uint32_t>(base, off, Tk);
     ws.slot_pos = carve<uint32_t>(base, off, Tk);
+    ws.perm_scratch = carve<uint32_t>(base, off, permute_scratch_words((int64_t)Tk, g.E));
     ws.xq = carve<int8_t>(base, off, (size_t)g.Tm * d);
     ws.xs = carve<float>(base, off, (size_t)g.Tm * d / 256);
     ws.xb = carve<int16_t>(base, off, (size_t)g.Tm * d / 16);
@@ -478,7 +479,7 @@ int ep_forward_impl(cudaStream_t st, candle_moe_ep_comm* cm, const candle_moe_ep
         CU_TRY(launch_router_topk(st, x, cfg->router, cfg->router_bias, T, d, E, k, cfg->renorm, ws.ids, ws.tw, ws.xq, ws.xs, ws.xb));
     }
     // with no rows the dispatch still has to say so: counts and offsets of zero
-    CU_TRY(launch_permute(st, ws.ids, T, k, E, ws.counts, ws.offsets, ws.perm, ws.pair_pos));
+    CU_TRY(launch_permute(st, ws.ids, T, k, E, ws.counts, ws.offsets, ws.perm, ws.pair_pos, ws.perm_scratch));
 
     int eo_splits = 1;
     if (g.slots) {

@@ -52,9 +52,10 @@ bool tuning_set(int key, int64_t value) {
 // quantize the same row of x the Q8K way for the expert products (one pass over x instead of two
 // kernels).  Arithmetic is plain f32 FMA (no TF32): the reference's router product is full f32.
 // ------------------------------------------------------------------------------------------------
-constexpr int ROUTER_THREADS = 1024;
-constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
-
+// Few tokens: 1024 threads per token (the whole product in one round of loads).  Many tokens: 256 threads per token,
+// so that eight CTAs share an SM and their load rounds overlap.  The two sizes add the partial sums in different
+// orders (last-bit differences of the logits, as between any two f32 dot-product orders).
+template <int ROUTER_THREADS>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, const float* __restrict__ bias,
                    int d, int E, int k, int renorm, uint32_t* __restrict__ ids, float* __restrict__ wout,
@@ -63,6 +64,7 @@ router_topk_kernel(const float* __restrict__ x, const float* __restrict__ wg, co
                    uint32_t* __restrict__ pair_pos) {
     pdl_trigger();
     pdl_wait();
+    constexpr int ROUTER_WARPS = ROUTER_THREADS / 32;
     __shared__ float s_logits[CANDLE_MOE_MAX_EXPERTS];
     __shared__ float s_part[ROUTER_WARPS][8];
     const int64_t t = blockIdx.x;
@@ -227,8 +229,11 @@ cudaError_t launch_router_topk(cudaStream_t st, const float* x, const float* rou
                                int16_t* bsums, uint32_t* counts, uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos) {
     if (T == 0) return cudaSuccess;
     if (counts && (T != 1 || !offsets || !perm_token || !pair_pos)) return cudaErrorInvalidValue;  // single-token dispatch only
-    return launch_k(router_topk_kernel, dim3((unsigned)T), dim3(ROUTER_THREADS), 0, st, x, router, bias, d, E, k, renorm,
-                    ids, w, qs, scales, bsums, counts, offsets, perm_token, pair_pos);
+    if (T > 64)
+        return launch_k(router_topk_kernel<256>, dim3((unsigned)T), dim3(256), 0, st, x, router, bias, d, E, k, renorm, ids, w, qs,
+                        scales, bsums, counts, offsets, perm_token, pair_pos);
+    return launch_k(router_topk_kernel<1024>, dim3((unsigned)T), dim3(1024), 0, st, x, router, bias, d, E, k, renorm, ids, w, qs,
+                    scales, bsums, counts, offsets, perm_token, pair_pos);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -284,10 +289,106 @@ permute_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int k, int E, 
     }
 }
 
+// The same counting sort over many CTAs, for large batches: the pair list is cut into chunks of PERMUTE_CHUNK pairs.
+//   count  every CTA counts its chunk's pairs per expert                       -> table[chunk][expert]
+//   scan   one CTA: expert offsets, and table[chunk][expert] becomes the first position of that chunk's pairs of
+//          that expert (earlier chunks first: the order inside an expert stays the pair order)
+//   place  every CTA walks its chunk again, 32 pairs at a time per expert with a ballot, as the one-CTA kernel does
+constexpr int PERMUTE_CHUNK = 512;
+
+__global__ void __launch_bounds__(256)
+permute_count_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int E, uint32_t* __restrict__ table) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ uint32_t s_hist[CANDLE_MOE_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+    __syncthreads();
+    const int64_t i0 = (int64_t)blockIdx.x * PERMUTE_CHUNK;
+    for (int j = threadIdx.x; j < PERMUTE_CHUNK; j += blockDim.x) {
+        const int64_t i = i0 + j;
+        if (i < n_pairs) {
+            const uint32_t e = ids[i];
+            if (e < (uint32_t)E) atomicAdd(&s_hist[e], 1u);  // a count: the order of the additions does not matter
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) table[(size_t)blockIdx.x * E + e] = s_hist[e];
+}
+
+__global__ void __launch_bounds__(128)
+permute_scan_kernel(uint32_t* __restrict__ table, int n_chunks, int E, uint32_t* __restrict__ counts,
+                    uint32_t* __restrict__ offsets) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ uint32_t s_count[CANDLE_MOE_MAX_EXPERTS], s_off[CANDLE_MOE_MAX_EXPERTS + 1];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        uint32_t c = 0;
+        for (int b = 0; b < n_chunks; ++b) c += table[(size_t)b * E + e];
+        s_count[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (int e = 0; e < E; ++e) {
+            s_off[e] = run;
+            run += s_count[e];
+        }
+        s_off[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        counts[e] = s_count[e];
+        uint32_t run = s_off[e];
+        for (int b = 0; b < n_chunks; ++b) {
+            const uint32_t c = table[(size_t)b * E + e];
+            table[(size_t)b * E + e] = run;
+            run += c;
+        }
+    }
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = s_off[e];
+}
+
+__global__ void __launch_bounds__(PERMUTE_THREADS)
+permute_place_kernel(const uint32_t* __restrict__ ids, int64_t n_pairs, int k, int E, const uint32_t* __restrict__ table,
+                     uint32_t* __restrict__ perm_token, uint32_t* __restrict__ pair_pos) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = PERMUTE_THREADS / 32;
+    const int64_t c0 = (int64_t)blockIdx.x * PERMUTE_CHUNK;
+    const int64_t c1 = c0 + PERMUTE_CHUNK < n_pairs ? c0 + PERMUTE_CHUNK : n_pairs;
+    for (int e = warp; e < E; e += n_warps) {
+        uint32_t base = table[(size_t)blockIdx.x * E + e];
+        for (int64_t i0 = c0; i0 < c1; i0 += 32) {
+            const int64_t i = i0 + lane;
+            const bool hit = i < c1 && ids[i] == (uint32_t)e;
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const uint32_t pos = base + __popc(m & ((1u << lane) - 1u));
+                perm_token[pos] = (uint32_t)(i / k);
+                pair_pos[i] = pos;
+            }
+            base += __popc(m);
+        }
+    }
+}
+
+size_t permute_scratch_words(int64_t n_pairs, int E) {
+    return (size_t)((n_pairs + PERMUTE_CHUNK - 1) / PERMUTE_CHUNK) * (size_t)E;
+}
+
 cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int k, int E, uint32_t* counts,
-                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos) {
-    return launch_k(permute_kernel, dim3(1), dim3(PERMUTE_THREADS), 0, st, ids, T * k, k, E, counts, offsets, perm_token,
-                    pair_pos);
+                           uint32_t* offsets, uint32_t* perm_token, uint32_t* pair_pos, uint32_t* scratch) {
+    const int64_t n_pairs = T * k;
+    if (!scratch || n_pairs <= 4 * PERMUTE_CHUNK)
+        return launch_k(permute_kernel, dim3(1), dim3(PERMUTE_THREADS), 0, st, ids, n_pairs, k, E, counts, offsets, perm_token,
+                        pair_pos);
+    const int n_chunks = (int)((n_pairs + PERMUTE_CHUNK - 1) / PERMUTE_CHUNK);
+    cudaError_t e = launch_k(permute_count_kernel, dim3(n_chunks), dim3(256), 0, st, ids, n_pairs, E, scratch);
+    if (e != cudaSuccess) return e;
+    e = launch_k(permute_scan_kernel, dim3(1), dim3(128), 0, st, scratch, n_chunks, E, counts, offsets);
+    if (e != cudaSuccess) return e;
+    return launch_k(permute_place_kernel, dim3(n_chunks), dim3(PERMUTE_THREADS), 0, st, ids, n_pairs, k, E,
+                    (const uint32_t*)scratch, perm_token, pair_pos);
 }
 
 __global__ void single_group_kernel(uint32_t* offsets, uint32_t rows) {
