@@ -272,7 +272,7 @@ def build_block(torch, cfg, device, seed=0, prepack=True):
     if cfg.get("zipf_bias"):
         kw["router_bias"] = torch.log(1.0 / (torch.arange(E, dtype=torch.float32) + 1.0))
     blk = MlpOrMoe.moe(cfg["k"], router, experts, norm_topk_prob=cfg["renorm"], **kw)
-    if prepack and cfg["dt13"] in (12, 14) and cfg["dt2"] in (12, 14):
+    if prepack:
         blk.prepack()
     return blk
 
@@ -345,7 +345,7 @@ def timed_batches(torch, step, steps, barrier, flush=None, min_seconds=MIN_TIMED
             out.append(e0.elapsed_time(e1))
         if n_batches is None:
             # after the first batch: how many batches make up the minimum region (at least 3), agreed between ranks
-            want = max(3, min(MAX_BATCHES, int(min_seconds * 1e3 / max(out[0], 1e-3)) + 1))
+            want = 1 if min_seconds <= 0 else max(3, min(MAX_BATCHES, int(min_seconds * 1e3 / max(out[0], 1e-3)) + 1))
             n_batches = agree(want) if agree else want
         if len(out) >= n_batches:
             break
@@ -417,7 +417,7 @@ def run_ours(args, cfg):
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
-    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, barrier, flush)
+    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, barrier, flush, args.min_seconds)
     clocks = sampler.stop()
     ms_total = statistics.median(batches)
 
@@ -432,7 +432,7 @@ def run_ours(args, cfg):
 
     for _ in range(min(args.warmup, 3)):
         e2e_step()
-    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, 0.3)
+    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, min(0.3, args.min_seconds))
     ms_e2e = statistics.median(e2e_batches)
 
     x.copy_(torch.randn((T, d), generator=torch.Generator().manual_seed(1), dtype=torch.float32))
@@ -637,7 +637,7 @@ def run_ep_local(args, cfg, torch, dev):
     for _ in range(args.warmup):
         blk.forward(x, out=y)
     torch.cuda.synchronize()
-    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, torch.cuda.synchronize, None, 0.3)
+    batches, region_s = timed_batches(torch, lambda: blk.forward(x, out=y), args.steps, torch.cuda.synchronize, None, min(0.3, args.min_seconds))
     acc = {n: 0.0 for n in blk.PHASES}
     for _ in range(5):
         _, ms = blk.forward(x, out=y, timed=True)
@@ -657,7 +657,7 @@ def run_ep(args, cfg, torch, dist, rank, world, local, dev):
         raise SystemExit(f"workload {args.workload} has no expert-parallel form over {world} ranks")
     T = args.tokens
     sampler = ClockSampler(local) if rank == 0 else None
-    rec = ep_measure(args, cfg, torch, dist, rank, world, dev, T, args.steps, args.warmup, MIN_TIMED_SECONDS,
+    rec = ep_measure(args, cfg, torch, dist, rank, world, dev, T, args.steps, args.warmup, args.min_seconds,
                      parity_rows=min(T, 64), sampler=sampler)
     c5 = None
     if args.workload == "c2" and not args.no_c5:
@@ -778,7 +778,8 @@ def run_c3(args):
         ep = {"world": world, "rank": rank,
               "make": lambda lw: ExpertParallelMoe(cfg.n_expert_used, lw.router, lw.experts, prepack=not args.no_prepack,
                                                    max_tokens=B)}
-    model = DecodeStep(cfg, B, dev, n_distinct=4, seed=0, prepack=not args.no_prepack, expert_parallel=ep)
+    model = DecodeStep(cfg, B, dev, n_distinct=4, seed=0, prepack=not args.no_prepack, expert_parallel=ep,
+                       attention=args.attention)
     tokens = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator(device=dev).manual_seed(5 + rank), device=dev)
 
     def barrier():
@@ -815,7 +816,7 @@ def run_c3(args):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    batches, region_s = timed_batches(torch, step, args.steps, barrier, None, MIN_TIMED_SECONDS, agree)
+    batches, region_s = timed_batches(torch, step, args.steps, barrier, None, args.min_seconds, agree)
     clocks = sampler.stop() if sampler else None
     ms_step = statistics.median(batches) / args.steps
 
@@ -857,7 +858,7 @@ def run_c3(args):
         else:
             h_logits.copy_(model.forward(tokens, index_pos), non_blocking=True)
 
-    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, 0.3, agree)
+    e2e_batches, _ = timed_batches(torch, e2e_step, args.steps, barrier, None, min(0.3, args.min_seconds), agree)
     ms_e2e = statistics.median(e2e_batches) / args.steps
     t = torch.tensor([ms_step, ms_e2e, ms_attn, ms_ffn], dtype=torch.float64, device=dev)
     if world > 1:
@@ -879,9 +880,10 @@ def run_c3(args):
                                    f"top-{cfg.n_expert_used} ff={cfg.d_ff}, vocab {cfg.vocab}",
                        "weights": "4 distinct random layers rotate over the layers (attention Q4_K, w1/w3 Q4_K, w2 Q6_K, lm head Q6_K)",
                        "library_parts": "wq/wk/wv/wo, lm head (candle_moe_qmatmul); ffn_norm + MoE block + residual (candle_moe_ffn_layer"
-                                        + (", experts sharded: candle_moe_ep_forward)" if world > 1 else ")"),
-                       "pytorch_parts": "embedding, attention_norm / final norm, interleaved RoPE, f32 KV cache append, "
-                                        "attention (q k^T, softmax, v as batched f32 matmuls)",
+                                        + (", experts sharded: candle_moe_ep_forward)" if world > 1 else ")")
+                                        + ("; attention over the f32 KV cache (candle_moe_decode_attention)" if args.attention == "library" else ""),
+                       "pytorch_parts": "embedding, attention_norm / final norm, interleaved RoPE, f32 KV cache append"
+                                        + ("" if args.attention == "library" else ", attention (q k^T, softmax, v as batched f32 matmuls)"),
                        "l2_policy": "a step reads tens of GB: nothing survives in the 126 MB L2 between steps",
                        "timed": "CUDA graph replay" if graph is not None else "eager launches",
                        "parallelism": "single GPU" if world == 1 else f"ep{world}: experts sharded, attention replicated, "
@@ -917,7 +919,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="c3: number of layers (default 32)")
     ap.add_argument("--context", type=int, default=4096, help="c3: tokens in the context, the new one included")
     ap.add_argument("--eager", action="store_true", help="c3: time eager launches instead of a CUDA graph replay")
+    ap.add_argument("--attention", default="library", choices=["library", "pytorch"],
+                    help="c3: attention over the KV cache by this library's kernel or by PyTorch's batched matmuls")
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                    help="device time the timed batches must add up to (0: a single batch, for profiler runs)")
     ap.add_argument("--gemm-min-rows", type=int, default=0,
                     help="bound on an expert's rows above which the tensor-core GEMM runs (default: the library's)")
     ap.add_argument("--ep-local", action="store_true", help="N = 1: run the expert-parallel step on one GPU (profiling aid)")

@@ -25,6 +25,7 @@ SOURCES = {
     "expert_gemm.cu": [],
     "expert_parallel.cu": [],
     "ep_nccl.cu": [],
+    "decode_attention.cu": [],
     "expert_q80.cu": [],
 }
 

@@ -1,6 +1,7 @@
 // extern "C" entry points of libcandle_moe_sm100.so (declared in include/candle_moe.h): argument
 // validation on the host, workspace carving, and the launch sequence of the whole block.
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -100,11 +101,14 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
     if (T > gemm_min_rows()) {
         // large batches: fp16 activation operand of the tcgen05 GEMM (Q4_K matrices), reused by gate_up and down
         size_t g = 0;
-        const auto takes = [](int dt, const void* const* packed) {
-            return dt == CANDLE_GGML_Q4K || (dt == CANDLE_GGML_Q6K && packed != nullptr);
+        const auto takes = [](int dt, const void* packed) {
+            return dt == CANDLE_GGML_Q4K || ((dt == CANDLE_GGML_Q6K || dt == CANDLE_GGML_Q8_0) && packed != nullptr);
         };
         if (takes(w->dtype_w13, w->w1_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d));
         if (takes(w->dtype_w2, w->w2_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)ff));
+        if (w->d_ff_shared > 0 && w->dtype_shared13 == CANDLE_GGML_Q8_0 && w->shared_w1_prepacked && w->shared_w3_prepacked &&
+            w->shared_w2_prepacked)
+            g = std::max(g, std::max(expert_gemm_scratch_bytes(T, (int)d), expert_gemm_scratch_bytes(T, w->d_ff_shared)));
         if (g) {
             off = align_up(off, 1024);
             ws.gemm = base ? base + off : nullptr;
@@ -266,7 +270,8 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
     if (total_rows_hint <= 0) total_rows_hint = P;
     const int E = w->n_experts, d = w->d_model, ff = w->d_ff;
     const bool large = b.gemm && max_rows > (rows_exact ? GEMM_MIN_ROWS_EXACT : gemm_min_rows()) && gemm_enabled();
-    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && max_rows <= std::max<int64_t>(gemm_min_rows(), 64) && !large;
+    const bool use_prepacked = w->w1_prepacked && w->w3_prepacked && w->w2_prepacked && w->dtype_w13 != CANDLE_GGML_Q8_0 &&
+                               w->dtype_w2 != CANDLE_GGML_Q8_0 && max_rows <= std::max<int64_t>(gemm_min_rows(), 64) && !large;
     bool gate_done = false, down_done = false;
     *eo_splits = 1;
     ExpertPtrs q1, q3, q2;
@@ -285,8 +290,8 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
     // of the average (an expert beyond the tile width simply takes a second tile)
     const int64_t tile_rows = rows_exact ? max_rows : std::min<int64_t>(max_rows, (5 * total_rows_hint + 4 * E - 1) / (4 * E));
     if (!gate_done && large) {
-        // Q6_K is read from the repacked copies (its GGUF blocks are only 2-byte aligned)
-        const bool rp = w->dtype_w13 == CANDLE_GGML_Q6K && w->w1_prepacked && w->w3_prepacked;
+        // Q6_K and Q8_0 are read from the repacked copies (their GGUF blocks are only 2-byte aligned)
+        const bool rp = (w->dtype_w13 == CANDLE_GGML_Q6K || w->dtype_w13 == CANDLE_GGML_Q8_0) && w->w1_prepacked && w->w3_prepacked;
         ExpertPtrs g1 = p1, g3 = p3;
         if (rp) {
             CM_TRY(fill_ptrs(w->w1_prepacked, E, g1));
@@ -316,7 +321,7 @@ int run_experts(cudaStream_t st, const candle_moe_weights_t* w, const ExpertPtrs
             *eo_splits = 1;
     }
     if (!down_done && large) {
-        const bool rp = w->dtype_w2 == CANDLE_GGML_Q6K && w->w2_prepacked;
+        const bool rp = (w->dtype_w2 == CANDLE_GGML_Q6K || w->dtype_w2 == CANDLE_GGML_Q8_0) && w->w2_prepacked;
         ExpertPtrs g2 = p2;
         if (rp) CM_TRY(fill_ptrs(w->w2_prepacked, E, g2));
         const cudaError_t ce = launch_expert_gemm(st, false, g2, g2, w->dtype_w2, rp, E, ff, d, offsets, nullptr, P, tile_rows,
@@ -419,11 +424,43 @@ static int forward_impl(void* stream, const candle_moe_weights_t* w, const float
         s2.p[0] = static_cast<const uint8_t*>(w->shared_w2);
         if (ws.sxq != ws.xq)
             CM_TRY(rc(launch_quantize_act(st, x, T, d, w->dtype_shared13, ws.sxq, ws.sxs, ws.sxb)));
-        CM_TRY(rc(launch_grouped_gate_up(st, s1, s3, w->dtype_shared13, 1, d, fs, ws.sh_offsets, nullptr, T, ws.sxq,
-                                         ws.sxs, ws.sxb, ws.shidden)));
+        // large batches over repacked Q8_0 copies: the tensor-core GEMM with one group holding every row
+        const bool sh_gemm = ws.gemm && T > gemm_min_rows() && gemm_enabled() && w->dtype_shared13 == CANDLE_GGML_Q8_0 &&
+                             w->dtype_shared2 == CANDLE_GGML_Q8_0 && w->shared_w1_prepacked && w->shared_w3_prepacked &&
+                             w->shared_w2_prepacked;
+        bool sh_done = false;
+        if (sh_gemm) {
+            ExpertPtrs r1{}, r3{};
+            r1.p[0] = static_cast<const uint8_t*>(w->shared_w1_prepacked);
+            r3.p[0] = static_cast<const uint8_t*>(w->shared_w3_prepacked);
+            const cudaError_t ce = launch_expert_gemm(st, true, r1, r3, CANDLE_GGML_Q8_0, true, 1, d, fs, ws.sh_offsets, nullptr, T, T,
+                                                      ws.sxq, ws.sxs, ws.sxb, ws.shidden, ws.gemm);
+            if (ce == cudaSuccess)
+                sh_done = true;
+            else if (ce != cudaErrorNotSupported)
+                return (int)ce;
+        }
+        if (!sh_done)
+            CM_TRY(rc(launch_grouped_gate_up(st, s1, s3, w->dtype_shared13, 1, d, fs, ws.sh_offsets, nullptr, T, ws.sxq,
+                                             ws.sxs, ws.sxb, ws.shidden)));
         CM_TRY(rc(launch_quantize_act(st, ws.shidden, T, fs, w->dtype_shared2, ws.shq, ws.shs, ws.shb)));
-        CM_TRY(rc(launch_grouped_down(st, s2, w->dtype_shared2, 1, d, fs, ws.sh_offsets, T, ws.shq, ws.shs, ws.shb,
-                                      ws.so, T * (int64_t)d, k_split_slots(T), &so_splits)));
+        sh_done = false;
+        if (sh_gemm) {
+            ExpertPtrs r2{};
+            r2.p[0] = static_cast<const uint8_t*>(w->shared_w2_prepacked);
+            const cudaError_t ce = launch_expert_gemm(st, false, r2, r2, CANDLE_GGML_Q8_0, true, 1, fs, d, ws.sh_offsets, nullptr, T, T,
+                                                      ws.shq, ws.shs, ws.shb, ws.so, ws.gemm, k_split_slots(T), &so_splits,
+                                                      T * (int64_t)d);
+            if (ce == cudaSuccess)
+                sh_done = true;
+            else if (ce != cudaErrorNotSupported)
+                return (int)ce;
+            else
+                so_splits = 1;
+        }
+        if (!sh_done)
+            CM_TRY(rc(launch_grouped_down(st, s2, w->dtype_shared2, 1, d, fs, ws.sh_offsets, T, ws.shq, ws.shs, ws.shb,
+                                          ws.so, T * (int64_t)d, k_split_slots(T), &so_splits)));
         shared_out = ws.so;
     }
     mark(st, 6);
@@ -541,6 +578,11 @@ int candle_moe_workspace_views(const candle_moe_weights_t* w, int64_t T, void* w
 
 int candle_moe_prepacked_bytes(int32_t dtype, int64_t n_rows, int32_t k, size_t* out_bytes) {
     if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (dtype == CANDLE_GGML_Q8_0) {
+        if (n_rows < 0 || k <= 0 || k % 32) return CANDLE_MOE_E_SHAPE;
+        *out_bytes = prepacked_q80_bytes(n_rows, k);
+        return CANDLE_MOE_OK;
+    }
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
     if (n_rows < 0 || k <= 0) return CANDLE_MOE_E_SHAPE;
     *out_bytes = prepacked_bytes(dtype, n_rows, k);
@@ -549,6 +591,11 @@ int candle_moe_prepacked_bytes(int32_t dtype, int64_t n_rows, int32_t k, size_t*
 
 int candle_moe_prepack(void* stream, int32_t dtype, const void* src_blocks, int64_t n_rows, int32_t k, void* dst) {
     if (!src_blocks || !dst) return CANDLE_MOE_E_NULL;
+    if (dtype == CANDLE_GGML_Q8_0) {
+        if (n_rows < 0 || k <= 0 || k % 32) return CANDLE_MOE_E_SHAPE;
+        if ((reinterpret_cast<uintptr_t>(src_blocks) & 1) || (reinterpret_cast<uintptr_t>(dst) & 15)) return CANDLE_MOE_E_ALIGN;
+        return rc(launch_prepack_q80((cudaStream_t)stream, src_blocks, n_rows, k, dst));
+    }
     if (dtype != CANDLE_GGML_Q4K && dtype != CANDLE_GGML_Q6K) return CANDLE_MOE_E_DTYPE;
     if (n_rows < 0 || k <= 0 || k % 256 || n_rows % 8) return CANDLE_MOE_E_SHAPE;
     if ((reinterpret_cast<uintptr_t>(src_blocks) | reinterpret_cast<uintptr_t>(dst)) & 15) return CANDLE_MOE_E_ALIGN;
@@ -602,6 +649,30 @@ int candle_moe_device_status_reset(void) {
 int candle_moe_selftest_bounded_wait(void* stream, int32_t poll_limit) {
     if (poll_limit < 1 || poll_limit > (1 << 20)) return CANDLE_MOE_E_SHAPE;
     return rc(launch_selftest_wait((cudaStream_t)stream, poll_limit));
+}
+
+int candle_moe_decode_attention_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim, int32_t n_ctx, size_t* out_bytes) {
+    if (!out_bytes) return CANDLE_MOE_E_NULL;
+    if (batch < 0 || n_head <= 0 || head_dim <= 0 || n_ctx < 0) return CANDLE_MOE_E_SHAPE;
+    *out_bytes = decode_attention_workspace_bytes(batch, n_head, head_dim, n_ctx);
+    return CANDLE_MOE_OK;
+}
+
+int candle_moe_decode_attention(void* stream, const float* q, const float* k_cache, const float* v_cache, int32_t batch,
+                                int32_t n_head, int32_t n_kv_head, int32_t head_dim, int64_t max_seq, int32_t n_ctx, float* out,
+                                void* workspace, size_t workspace_bytes) {
+    if (batch < 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head || head_dim <= 0 || n_ctx < 0 || n_ctx > max_seq)
+        return CANDLE_MOE_E_SHAPE;
+    if (batch == 0 || n_ctx == 0) return CANDLE_MOE_OK;
+    if (!q || !k_cache || !v_cache || !out || !workspace) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+         reinterpret_cast<uintptr_t>(workspace)) & 15)
+        return CANDLE_MOE_E_ALIGN;
+    if (workspace_bytes < decode_attention_workspace_bytes(batch, n_head, head_dim, n_ctx)) return CANDLE_MOE_E_WORKSPACE;
+    const float scale = 1.0f / sqrtf((float)head_dim);
+    const cudaError_t e = launch_decode_attention((cudaStream_t)stream, q, k_cache, v_cache, batch, n_head, n_kv_head, head_dim,
+                                                  max_seq, n_ctx, scale, out, static_cast<float*>(workspace));
+    return e == cudaErrorNotSupported ? CANDLE_MOE_E_SHAPE : rc(e);
 }
 
 int candle_moe_quantize_weights(void* stream, int32_t dtype, const float* src, int64_t n_elems, void* dst) {

@@ -203,6 +203,9 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
 // large-batch grouped GEMM on tcgen05 / TMEM: Q4_K in GGUF layout (repacked = false), Q6_K in the repacked
 // layout (repacked = true); `scratch` of expert_gemm_scratch_bytes(P, K) bytes
 size_t expert_gemm_scratch_bytes(int64_t P, int K);
+// Q8_0 rows repacked for the GEMM: [n][ceil(k / 256)][256 int8 | 8 f16 scales]
+size_t prepacked_q80_bytes(int64_t n_rows, int k);
+cudaError_t launch_prepack_q80(cudaStream_t st, const void* raw, int64_t n_rows, int k, void* dst);
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
@@ -224,6 +227,10 @@ cudaError_t read_stream_status(int* out);
 cudaError_t stream_status_ptr(int** out);  // device address of that health word
 cudaError_t reset_stream_status();
 cudaError_t launch_selftest_wait(cudaStream_t st, int limit);
+// attention of one new token per sequence over an f32 KV cache (decode_attention.cu); cudaErrorNotSupported for shapes not taken
+size_t decode_attention_workspace_bytes(int B, int n_head, int head_dim, int n_ctx);
+cudaError_t launch_decode_attention(cudaStream_t st, const float* q, const float* kc, const float* vc, int B, int n_head, int n_kv,
+                                    int head_dim, int64_t max_seq, int n_ctx, float scale, float* y, float* workspace);
 cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);
 cudaError_t launch_dequantize(cudaStream_t st, int dtype, const void* blocks, int64_t n, float* dst);
 

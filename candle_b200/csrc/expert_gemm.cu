@@ -114,6 +114,60 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
     if (lane == 0) d8t[(int64_t)blk * P_pad + p] = d8;
 }
 
+// Q8_0 activations (int8 values, one f32 scale per 32, candle_moe_quantize_act) as the fp16 operand d * q, rows in
+// grouped order, columns padded with zeros to K_pad (a multiple of 256); the per-block scale table is all ones.
+__global__ void __launch_bounds__(256)
+prep_gemm_b_q80_kernel(const int8_t* __restrict__ aq, const float* __restrict__ ascale, const uint32_t* __restrict__ row_of, int P,
+                       int P_pad, int K, int K_pad, __half* __restrict__ bf16, float* __restrict__ d8t) {
+    pdl_trigger();
+    pdl_wait();
+    const int kb = K_pad >> 8;
+    const int lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (p, block of 256)
+    if (unit >= (int64_t)P_pad * kb) return;
+    const int p = (int)(unit / kb), blk = (int)(unit - (int64_t)p * kb);
+    uint4 o = make_uint4(0, 0, 0, 0);
+    const int k0 = blk * 256 + lane * 8;
+    if (p < P && k0 < K) {  // K is a multiple of 32: a lane's eight values lie inside one 32-block
+        const int64_t row = row_of ? (int64_t)row_of[p] : (int64_t)p;
+        const uint2 v = *reinterpret_cast<const uint2*>(aq + row * K + k0);
+        const int8_t* b = reinterpret_cast<const int8_t*>(&v);
+        const __half d = __float2half_rn(ascale[row * (K / 32) + (k0 >> 5)]);  // exact: the scale is an f16 value
+        __half2 h[4];
+        h[0] = __halves2half2(__hmul(__int2half_rn(b[0]), d), __hmul(__int2half_rn(b[2]), d));
+        h[1] = __halves2half2(__hmul(__int2half_rn(b[1]), d), __hmul(__int2half_rn(b[3]), d));
+        h[2] = __halves2half2(__hmul(__int2half_rn(b[4]), d), __hmul(__int2half_rn(b[6]), d));
+        h[3] = __halves2half2(__hmul(__int2half_rn(b[5]), d), __hmul(__int2half_rn(b[7]), d));
+        o = *reinterpret_cast<uint4*>(h);
+    }
+    *reinterpret_cast<uint4*>(bf16 + (int64_t)p * K_pad + blk * 256 + lane * 8) = o;
+    if (lane == 0) d8t[(int64_t)blk * P_pad + p] = 1.0f;
+}
+
+// Q8_0 GGUF rows [n][K / 32 blocks of 34 bytes] -> [n][K_pad / 256][272]: 256 int8 then 8 f16 scales, zeros past K.
+// One warp per (row, 256-block); a lane moves eight values with 2-byte loads (the 34-byte blocks are 2-byte aligned).
+__global__ void __launch_bounds__(256)
+prepack_q80_kernel(const uint8_t* __restrict__ raw, int64_t n_rows, int K, int K_pad, uint8_t* __restrict__ dst) {
+    const int kb = K_pad >> 8, lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= n_rows * kb) return;
+    const int64_t row = unit / kb;
+    const int blk = (int)(unit - row * kb);
+    uint8_t* out = dst + unit * 272;
+    const int k0 = blk * 256 + lane * 8;  // this lane's eight values
+    uint16_t v[4] = {0, 0, 0, 0};
+    if (k0 < K) {
+        const uint8_t* b = raw + (row * (K / 32) + (k0 >> 5)) * Q8_0_BYTES;
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + (k0 & 31));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = q[i];
+        if ((lane & 3) == 0) reinterpret_cast<uint16_t*>(out + 256)[lane >> 2] = *reinterpret_cast<const uint16_t*>(b);
+    } else if ((lane & 3) == 0) {
+        reinterpret_cast<uint16_t*>(out + 256)[lane >> 2] = 0;
+    }
+    reinterpret_cast<uint2*>(out)[lane] = make_uint2((uint32_t)v[0] | ((uint32_t)v[1] << 16), (uint32_t)v[2] | ((uint32_t)v[3] << 16));
+}
+
 struct GemmParams {
     ExpertPtrs wa, wb;            // gate_up: W1 / W3, down: W2 (wb unused); GGUF blocks (Q4_K) or repacked (Q6_K)
     const uint32_t* offsets;      // [E + 1]
@@ -148,6 +202,8 @@ struct GemmQ4K {
     static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;  // 8 slabs of 32 columns: two blocks in flight
     static constexpr bool STAGE_W = true;                         // raw blocks of the tile pass through shared memory
     static constexpr int W_ROW_BYTES = Q4K_BYTES;
+    static constexpr int W_MAP_ELEM = 1;     // the tensor map of the raw blocks counts bytes
+    static constexpr int W_STAGES_WIDE = 1;  // staged blocks that fit beside 128-wide activation stages
     struct Row {
         const uint8_t* p;
     };
@@ -250,6 +306,8 @@ struct GemmQ6K {
     static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;  // 4 slabs of 64 columns (two operand parts each)
     static constexpr bool STAGE_W = false;
     static constexpr int W_ROW_BYTES = 0;
+    static constexpr int W_MAP_ELEM = 1;
+    static constexpr int W_STAGES_WIDE = 1;
     struct Row {
         const uint8_t* p;  // half-tile block 0 of the row's group of 8
         int g;
@@ -319,10 +377,79 @@ struct GemmQ6K {
     __device__ static __forceinline__ float scale_of(uint32_t hdr) { return half_bits_to_float((uint16_t)hdr); }
 };
 
+// ------------------------------------------------------------------------------------------------
+// Q8_0, repacked layout (prepack_q80_kernel): per row and 256 elements a 272-byte record [256 int8 | 8 f16
+// scales], rows padded with zero records to a multiple of 256 elements.  The reference multiplies per 32-element
+// block (sum of int8 products) * d_w * d_a in f32 (k_quants.rs:636-668); here both scales are folded into the fp16
+// operands -- weight d_w * q, activation d_a * q, each rounded once to fp16 (2^-12 relative) -- and the products
+// are accumulated in f32 by the tensor core over the whole row, so no per-block scaling is left for the epilogue.
+// The rounding of the operands is the one deviation from the reference's arithmetic on this path: it shows as a
+// relative L2 error of a few 1e-4 on a product, inside the block's bound (1e-3), and is measured by the tests.
+// Used for the down product only (see launch_expert_gemm for why gate_up cannot afford that rounding).
+// Thread (row, h) owns bytes 16h..16h+15 and 32+16h..32+16h+15 of each 64-element slab, like the Q4_K thread.
+// ------------------------------------------------------------------------------------------------
+struct GemmQ80 {
+    static constexpr bool HAS_MIN = false;
+    static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;
+    static constexpr bool STAGE_W = true;
+    static constexpr int W_ROW_BYTES = 272;
+    static constexpr int W_MAP_ELEM = 4;     // the tensor map counts 4-byte elements (a box row of 272 bytes exceeds 256 bytes)
+    static constexpr int W_STAGES_WIDE = 2;  // staged blocks beside 128-wide activation stages
+    struct Row {
+        const uint8_t* p;
+    };
+    __device__ static __forceinline__ Row row(const uint8_t* w, int n, int kb) { return Row{w + (size_t)n * kb * W_ROW_BYTES}; }
+    struct Pre {
+        uint4 sc;       // 8 f16 scales
+        uint4 q[4][2];  // per slab: bytes 16h.. and 32 + 16h..
+    };
+    __device__ static __forceinline__ void load(Pre&, const Row&, int, int) {}
+    __device__ static __forceinline__ void load_staged(Pre& pr, uint32_t row_addr, int h) {
+        pr.sc = lds128_o<256>(row_addr);
+        const uint32_t rb = row_addr + 16 * h;
+        pr.q[0][0] = lds128_o<0>(rb);
+        pr.q[0][1] = lds128_o<32>(rb);
+        pr.q[1][0] = lds128_o<64>(rb);
+        pr.q[1][1] = lds128_o<96>(rb);
+        pr.q[2][0] = lds128_o<128>(rb);
+        pr.q[2][1] = lds128_o<160>(rb);
+        pr.q[3][0] = lds128_o<192>(rb);
+        pr.q[3][1] = lds128_o<224>(rb);
+    }
+    __device__ static __forceinline__ uint32_t hdr_of(const Pre&) { return 0u; }
+    struct Ctx {};
+    __device__ static __forceinline__ void begin(const Pre&, Ctx&) {}
+    __device__ static __forceinline__ float scale_of(uint32_t) { return 1.0f; }  // the scales are inside the operands
+    // 16 int8 -> 8 columns of fp16 pairs (k0, k2), (k1, k3) per word, times d: the byte plus 128 is dropped into the
+    // mantissa of 1024 (0x6400 | b + 128 = 1152 + b), 1152 comes off exactly, one multiply rounds
+    __device__ static __forceinline__ void cvt16(const uint4& v, __half2 d, uint32_t (&o)[8]) {
+        const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+        const __half2 k1152 = __float2half2_rn(1152.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t e, f;
+            asm("prmt.b32 %0, %1, %2, 0x4240;" : "=r"(e) : "r"(w[i]), "r"(0x64646464u));  // bytes 0 and 2
+            asm("prmt.b32 %0, %1, %2, 0x4341;" : "=r"(f) : "r"(w[i]), "r"(0x64646464u));  // bytes 1 and 3
+            o[2 * i] = bits_h2(__hmul2(__hsub2(h2_bits(e), k1152), d));
+            o[2 * i + 1] = bits_h2(__hmul2(__hsub2(h2_bits(f), k1152), d));
+        }
+    }
+    __device__ static __forceinline__ void emit(int s, const Pre& pr, const Ctx&, uint32_t ta, int h) {
+        const uint32_t dw = s == 0 ? pr.sc.x : (s == 1 ? pr.sc.y : (s == 2 ? pr.sc.z : pr.sc.w));  // scales of blocks 2s, 2s + 1
+        const __half2 d2 = h2_bits(dw);
+        uint32_t lo[8], hi[8];
+        cvt16(pr.q[s][0], __low2half2(d2), lo);
+        cvt16(pr.q[s][1], __high2half2(d2), hi);
+        tmem_st8(ta + 8 * h, lo);
+        tmem_st8(ta + 16 + 8 * h, hi);
+    }
+    __device__ static __forceinline__ void emit_min(const Pre&, const Ctx&, uint8_t*, int, int) {}
+};
+
 // raw weight blocks staged per CTA (see the kernel): what fits beside the activation stages
 template <class F, int TN>
 __host__ __device__ constexpr int w_stages() {
-    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? 3 : 1));
+    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? 3 : F::W_STAGES_WIDE));
 }
 
 struct TileCoord {
@@ -629,18 +756,18 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                         uint8_t* dst = smem_w + ws * W_STAGE_BYTES;
                         mbar_expect_tx(&full_w[ws], G_TILE_M * F::W_ROW_BYTES);
                         if (GATE_UP) {
-                            tma_load_2d(dst, m0, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
-                            tma_load_2d(dst + HALF, m0 + 1, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
+                            tma_load_2d(dst, m0, blk * (F::W_ROW_BYTES / F::W_MAP_ELEM), y0, &full_w[ws]);
+                            tma_load_2d(dst + HALF, m0 + 1, blk * (F::W_ROW_BYTES / F::W_MAP_ELEM), y0, &full_w[ws]);
                         } else {
-                            tma_load_2d(dst, m0, blk * F::W_ROW_BYTES, y0, &full_w[ws]);
-                            tma_load_2d(dst + HALF, m0, blk * F::W_ROW_BYTES, y0 + 64, &full_w[ws]);
+                            tma_load_2d(dst, m0, blk * (F::W_ROW_BYTES / F::W_MAP_ELEM), y0, &full_w[ws]);
+                            tma_load_2d(dst + HALF, m0, blk * (F::W_ROW_BYTES / F::W_MAP_ELEM), y0 + 64, &full_w[ws]);
                         }
                         // two blocks ahead, possibly in the next tile
                         const bool same = blk + 2 < tc.kb1;
                         if (same || have_n) {
                             const CUtensorMap* mp = same ? m0 : P.wmaps + 2 * tcn.e;
                             const int yp = same ? y0 : (GATE_UP ? tcn.mt * 64 : tcn.mt * 128);
-                            const int xp = (same ? blk + 2 : tcn.kb0 + blk + 2 - tc.kb1) * F::W_ROW_BYTES;
+                            const int xp = (same ? blk + 2 : tcn.kb0 + blk + 2 - tc.kb1) * (F::W_ROW_BYTES / F::W_MAP_ELEM);
                             tma_prefetch_2d(mp, xp, yp);
                             tma_prefetch_2d(GATE_UP ? mp + 1 : mp, xp, GATE_UP ? yp : yp + 64);
                         }
@@ -765,14 +892,15 @@ bool make_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int
 }
 
 // byte matrix [rows, row_bytes] -> boxes of [box_rows x box_bytes], no swizzle
-bool make_map_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, uint32_t box_rows) {
+bool make_map_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_bytes, uint32_t box_rows,
+                    int elem = 1) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t dims[2] = {row_bytes / elem, rows};  // elem = 4: counted in 32-bit words (a box dimension holds at most 256 elements)
     const cuuint64_t strides[1] = {row_bytes};
-    const cuuint32_t box[2] = {box_bytes, box_rows};
+    const cuuint32_t box[2] = {box_bytes / elem, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+    return fn(map, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -806,15 +934,27 @@ cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUten
 
 }  // namespace
 
+size_t prepacked_q80_bytes(int64_t n_rows, int k) { return (size_t)n_rows * (size_t)((k + 255) / 256) * GemmQ80::W_ROW_BYTES; }
+cudaError_t launch_prepack_q80(cudaStream_t st, const void* raw, int64_t n_rows, int k, void* dst) {
+    const int k_pad = (k + 255) / 256 * 256;
+    const int64_t units = n_rows * (k_pad / 256);
+    if (units == 0) return cudaSuccess;
+    prepack_q80_kernel<<<(unsigned)((units + 7) / 8), 256, 0, st>>>(static_cast<const uint8_t*>(raw), n_rows, k, k_pad,
+                                                                 static_cast<uint8_t*>(dst));
+    return cudaGetLastError();
+}
+
 // Scratch the GEMM needs for P grouped rows of length K (fp16 operand, block-sum operand, scales).
 size_t expert_gemm_scratch_bytes(int64_t P, int K) {
+    K = (K + 255) / 256 * 256;  // Q8_0 rows are padded to whole 256-element blocks
     const size_t p_pad = (size_t)P + G_PAD_ROWS, kb = (size_t)K / 256;
     return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256) +
            sizeof(CUtensorMap) * 2 * CANDLE_MOE_MAX_EXPERTS;
 }
 
-// Takes Q4_K weights in GGUF layout (repacked = false) and Q6_K weights in the repacked layout of the
-// decode kernels (repacked = true); cudaErrorNotSupported for every other shape / dtype / layout.
+// Takes Q4_K weights in GGUF layout (repacked = false), Q6_K weights in the repacked layout of the decode kernels
+// and Q8_0 weights in the layout of prepack_q80_kernel (repacked = true); cudaErrorNotSupported for every other
+// shape / dtype / layout.
 cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& wa, const ExpertPtrs& wb, int dtype,
                                bool repacked, int E, int K, int N, const uint32_t* offsets, const uint32_t* row_of, int64_t P,
                                int64_t max_rows, const int8_t* aq, const float* ascale, const int16_t* absum, float* out,
@@ -822,8 +962,17 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     if (n_splits_out) *n_splits_out = 1;
     if (!scratch) return cudaErrorNotSupported;
     const int tn = max_rows <= 32 ? 32 : (max_rows <= 64 ? 64 : 128);  // position tile, from the bound / hint on an expert's rows
-    if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked))) return cudaErrorNotSupported;
-    if (K % 256 != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
+    const bool q80 = dtype == CANDLE_GGML_Q8_0 && repacked;
+    if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked) || q80)) return cudaErrorNotSupported;
+    // Q8_0 takes this kernel for the DOWN product only.  Its operands carry the block scales rounded to fp16 (a few
+    // 1e-4 relative on a product), which a final product tolerates; the gate_up product does not: its f32 hidden rows
+    // are re-quantized to int8 before W2, and a relative difference of 1e-4 from the reference's hidden values already
+    // moves a few per cent of those int8 values by one step (1 / 127 of the block's largest value) -- measured, that
+    // amplification puts the block at 3e-3 .. 5e-3 relative L2, outside its bound.  gate_up stays on the exact int8 kernels.
+    if (q80 && gate_up) return cudaErrorNotSupported;
+    const int K_in = K;
+    if (q80) K = (K + 255) / 256 * 256;  // the repacked rows and the fp16 operand are padded with zeros
+    if (K_in % (q80 ? 32 : 256) != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
     if (!encode_tiled_fn()) return cudaErrorNotSupported;
     if (g_gemm_sms < 0) {
         int dev = 0;
@@ -841,8 +990,10 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     const bool has_min = dtype == CANDLE_GGML_Q4K;
 
     const int64_t units = p_pad * kb;
-    cudaError_t e = launch_k(prep_gemm_b_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, absum,
-                             row_of, (int)P, (int)p_pad, K, bf16, has_min ? bmin : (float*)nullptr, d8t);
+    cudaError_t e = q80 ? launch_k(prep_gemm_b_q80_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, row_of,
+                                   (int)P, (int)p_pad, K_in, K, bf16, d8t)
+                        : launch_k(prep_gemm_b_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, absum,
+                                   row_of, (int)P, (int)p_pad, K, bf16, has_min ? bmin : (float*)nullptr, d8t);
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_b, map_bs;
@@ -854,15 +1005,16 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
     // byte-matrix tensor maps of the raw weight blocks (Q4_K): [n_rows, kb * 144] with boxes of 64 rows x one block,
     // written to the head of the scratch on the stream before the kernel
     CUtensorMap* wmaps_dev = reinterpret_cast<CUtensorMap*>(reinterpret_cast<uint8_t*>(d8t) + align_up((size_t)kb * p_pad * 4, 256));
-    if (dtype == CANDLE_GGML_Q4K) {
-        const uint64_t n_rows = (uint64_t)N, rb = (uint64_t)kb * Q4K_BYTES;
+    if (dtype == CANDLE_GGML_Q4K || q80) {
+        const int rec = q80 ? GemmQ80::W_ROW_BYTES : Q4K_BYTES, elem = q80 ? GemmQ80::W_MAP_ELEM : 1;
+        const uint64_t n_rows = (uint64_t)N, rb = (uint64_t)kb * rec;
         for (int m0 = 0; m0 < 2 * E; m0 += MAPS_PER_CHUNK) {
             MapChunk chunk;
             const int n_maps = std::min(MAPS_PER_CHUNK, 2 * E - m0);
             for (int i = 0; i < n_maps; ++i) {
                 const int e2 = (m0 + i) >> 1;
                 const uint8_t* wp = ((m0 + i) & 1) && gate_up ? wb.p[e2] : wa.p[e2];
-                if (!make_map_bytes(&chunk.m[i], wp, n_rows, rb, Q4K_BYTES, 64)) return cudaErrorNotSupported;
+                if (!make_map_bytes(&chunk.m[i], wp, n_rows, rb, rec, 64, elem)) return cudaErrorNotSupported;
             }
             for (int i = n_maps; i < MAPS_PER_CHUNK; ++i) chunk.m[i] = chunk.m[0];
             e = launch_k(write_maps_kernel, dim3(1), dim3(128), 0, st, chunk, wmaps_dev + m0, n_maps);
@@ -904,6 +1056,13 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
         if (tn == 64)
             return gate_up ? launch_gemm_kernel<GemmQ4K, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 64>(st, G, map_b, map_bs);
         return gate_up ? launch_gemm_kernel<GemmQ4K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 128>(st, G, map_b, map_bs);
+    }
+    if (q80) {
+        if (tn == 32)
+            return gate_up ? launch_gemm_kernel<GemmQ80, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 32>(st, G, map_b, map_bs);
+        if (tn == 64)
+            return gate_up ? launch_gemm_kernel<GemmQ80, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 64>(st, G, map_b, map_bs);
+        return gate_up ? launch_gemm_kernel<GemmQ80, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 128>(st, G, map_b, map_bs);
     }
     if (tn == 32)
         return gate_up ? launch_gemm_kernel<GemmQ6K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 32>(st, G, map_b, map_bs);

@@ -5,14 +5,15 @@ This is a HARNESS around the block, so that its share of a whole decode step can
 runtime.  What runs where:
 
 * this library (C ABI): every quantized product -- wq / wk / wv / wo and the lm head through `QMatMul.forward`
-  (`candle_moe_qmatmul`), the FFN half of each layer (`ffn_norm` -> MoE block -> `+ residual`) as one call
+  (`candle_moe_qmatmul`), the attention over the cache (`candle_moe_decode_attention`, or PyTorch's batched matmuls
+  with `attention="pytorch"`), the FFN half of each layer (`ffn_norm` -> MoE block -> `+ residual`) as one call
   (`candle_moe_ffn_layer`), or, with the experts sharded over ranks, `ExpertParallelMoe.forward` between a PyTorch
   RmsNorm and residual add;
 * stock PyTorch ops, with the reference's arithmetic: token embedding lookup, `attention_norm` / final norm (RmsNorm,
   candle-nn/src/ops.rs:504-514), interleaved rotary embedding (`rope_i`, candle-nn/src/rotary_emb.rs:53-66, tables of
-  quantized_llama.rs:410-427), the f32 KV cache append (candle-nn/src/kv_cache.rs:143-164) and the attention itself
-  as the reference's `standard_attention` (quantized_llama.rs:303-317: q k^T / sqrt(head_dim), softmax, times v, grouped
-  heads instead of a materialised `repeat_kv`).
+  quantized_llama.rs:410-427), the f32 KV cache append (candle-nn/src/kv_cache.rs:143-164) and, with
+  `attention="pytorch"`, the attention itself as the reference's `standard_attention` (quantized_llama.rs:303-317:
+  q k^T / sqrt(head_dim), softmax, times v, grouped heads instead of a materialised `repeat_kv`).
 
 One layer's quantized bytes may be shared by several layers (`n_distinct` sets of weights rotate over the layers):
 a random-init 32-layer model does not need 32 different random layers to be timed, only enough distinct bytes that
@@ -111,9 +112,12 @@ class DecodeStep:
     """One new token for each of `batch` sequences whose first `index_pos` positions are in the KV cache."""
 
     def __init__(self, cfg: DecodeConfig, batch: int, device, *, n_distinct: int = 4, seed: int = 0, prepack: bool = True,
-                 expert_parallel=None, kv_fill: float = 0.5):
-        """`expert_parallel`: None, or a callable (layer_weights) -> ExpertParallelMoe for the sharded form."""
+                 expert_parallel=None, kv_fill: float = 0.5, attention: str = "library"):
+        """`expert_parallel`: None, or {"world", "rank", "make": layer_weights -> ExpertParallelMoe} for the sharded form.
+        `attention`: "library" (candle_moe_decode_attention) or "pytorch" (batched f32 matmuls and softmax)."""
         self.cfg, self.batch, self.device = cfg, batch, device
+        self.attention_impl = attention
+        self._att_ws = None
         g = torch.Generator(device=device).manual_seed(seed)
         self.tok_embeddings = torch.randn((cfg.vocab, cfg.d_model), generator=g, device=device, dtype=torch.float32) * 0.02
         self.norm = 1.0 + 0.1 * torch.randn(cfg.d_model, generator=g, device=device)
@@ -153,12 +157,35 @@ class DecodeStep:
         kc[:, :, index_pos:index_pos + 1] = k
         vc[:, :, index_pos:index_pos + 1] = v
         n = index_pos + 1
-        g = cfg.n_head // cfg.n_kv_head
-        qg = q.reshape(B, cfg.n_kv_head, g, cfg.head_dim)              # the g query heads that share a kv head
-        att = torch.matmul(qg, kc[:, :, :n].transpose(-1, -2)) / math.sqrt(cfg.head_dim)
-        att = torch.softmax(att, dim=-1)
-        y = torch.matmul(att, vc[:, :, :n]).reshape(B, cfg.n_head * cfg.head_dim)
+        if self.attention_impl == "library":
+            y = self._library_attention(q, kc, vc, n)
+        else:
+            g = cfg.n_head // cfg.n_kv_head
+            qg = q.reshape(B, cfg.n_kv_head, g, cfg.head_dim)              # the g query heads that share a kv head
+            att = torch.matmul(qg, kc[:, :, :n].transpose(-1, -2)) / math.sqrt(cfg.head_dim)
+            att = torch.softmax(att, dim=-1)
+            y = torch.matmul(att, vc[:, :, :n]).reshape(B, cfg.n_head * cfg.head_dim)
         return lw.attention_wo.forward(y) + x
+
+    def _library_attention(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, n: int) -> torch.Tensor:
+        import ctypes as C
+        from . import _lib
+        from .quantized import _stream_ptr
+        cfg, B = self.cfg, self.batch
+        L = _lib.load()
+        if self._att_ws is None:
+            need = C.c_size_t(0)
+            _lib.check("candle_moe_decode_attention_workspace_bytes",
+                       L.candle_moe_decode_attention_workspace_bytes(B, cfg.n_head, cfg.head_dim, cfg.max_seq, C.byref(need)))
+            self._att_ws = torch.empty(need.value + 16, dtype=torch.uint8, device=self.device)
+        qc = q.reshape(B, cfg.n_head, cfg.head_dim).contiguous()
+        y = torch.empty((B, cfg.n_head * cfg.head_dim), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            st = L.candle_moe_decode_attention(_stream_ptr(self.device), qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, cfg.n_head,
+                                               cfg.n_kv_head, cfg.head_dim, cfg.max_seq, n, y.data_ptr(), self._att_ws.data_ptr(),
+                                               self._att_ws.numel())
+        _lib.check("candle_moe_decode_attention", st)
+        return y
 
     def ffn(self, li: int, x: torch.Tensor) -> torch.Tensor:
         """`ffn_norm` -> `mlp_or_moe` -> `+ residual` (quantized_llama.rs:886-891)."""

@@ -104,13 +104,19 @@ class MlpOrMoe:
         return cls(n_expert_used, feed_forward_gate_inp, experts, **kw)
 
     def prepack(self) -> "MlpOrMoe":
-        """Make the optional decode-path copies of every expert matrix (one-time, doubles the weight
-        memory of this block).  Batches of up to 64 rows then read the prepacked copies."""
+        """Make the optional repacked copies of every expert matrix (one-time, doubles the weight memory of this
+        block): k-quants for the decode kernels (batches of up to 128 rows) and Q6_K in the large-batch GEMM, Q8_0 for
+        the large-batch GEMM."""
         E = len(self.experts)
         self._p1 = self._arr(*[m.feed_forward_w1.inner.prepack().data_ptr() for m in self.experts])
         self._p3 = self._arr(*[m.feed_forward_w3.inner.prepack().data_ptr() for m in self.experts])
         self._p2 = self._arr(*[m.feed_forward_w2.inner.prepack().data_ptr() for m in self.experts])
         self._cw.w1_prepacked, self._cw.w3_prepacked, self._cw.w2_prepacked = self._p1, self._p3, self._p2
+        if self.shared_expert is not None and self.shared_expert.feed_forward_w1.inner.dtype() == GgmlDType.Q8_0:
+            s = self.shared_expert
+            self._cw.shared_w1_prepacked = s.feed_forward_w1.inner.prepack().data_ptr()
+            self._cw.shared_w3_prepacked = s.feed_forward_w3.inner.prepack().data_ptr()
+            self._cw.shared_w2_prepacked = s.feed_forward_w2.inner.prepack().data_ptr()
         return self
 
     @property

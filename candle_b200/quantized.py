@@ -138,6 +138,8 @@ class QMatMul:
         dt = self.inner.dtype()
         if dt in (GgmlDType.Q4K, GgmlDType.Q6K) and n % 16 == 0 and k % 256 == 0 and (dt == GgmlDType.Q4K or (k // 256) % 2 == 0):
             self._prepacked = self.inner.prepack()
+        elif dt == GgmlDType.Q8_0:
+            self._prepacked = self.inner.prepack()
         return self
 
     def forward(self, xs: torch.Tensor) -> torch.Tensor:

@@ -85,6 +85,10 @@ typedef struct candle_moe_weights {
     const void* const* w1_prepacked;
     const void* const* w3_prepacked;
     const void* const* w2_prepacked;
+    /* The same for the shared expert (device pointers or NULL; Q8_0 only: large batches then take the tensor-core GEMM). */
+    const void* shared_w1_prepacked;
+    const void* shared_w3_prepacked;
+    const void* shared_w2_prepacked;
 } candle_moe_weights_t;
 
 /* Kernel-selection switches, for A/B checks and for re-tuning the thresholds on other shapes.  Each value starts
@@ -324,10 +328,28 @@ CANDLE_MOE_API int candle_moe_qmatmul(void* stream, const void* w, const void* w
                                       int32_t k, const float* x, int64_t rows, float* out, void* workspace,
                                       size_t workspace_bytes);
 
+/* Attention of ONE new token per sequence over an f32 KV cache: `standard_attention` of quantized_llama.rs:303-317 at
+ * seq_len = 1 (q k^T / sqrt(head_dim), softmax_last_dim, times v) with `repeat_kv` folded into the indexing (query head
+ * h reads kv head h / (n_head / n_kv_head)).  Outside the MoE block; it exists so that a whole decode step around the
+ * block can be timed without the cache being read through generic batched matmuls.
+ *   q [batch, n_head, head_dim] (after the rotary embedding), k_cache / v_cache [batch, n_kv_head, max_seq, head_dim]
+ *   of which the first n_ctx positions are valid (the new token's k / v already appended), out [batch, n_head * head_dim].
+ * head_dim 128 with 1, 4 or 8 query heads per kv head, or head_dim 64 with 1 or 4 (CANDLE_MOE_E_SHAPE otherwise).
+ * The context is cut into chunks whose partial softmax sums are merged afterwards: f32 summation order differs from
+ * a one-pass softmax, nothing else. */
+CANDLE_MOE_API int candle_moe_decode_attention_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim, int32_t n_ctx,
+                                                               size_t* out_bytes);
+CANDLE_MOE_API int candle_moe_decode_attention(void* stream, const float* q, const float* k_cache, const float* v_cache,
+                                               int32_t batch, int32_t n_head, int32_t n_kv_head, int32_t head_dim, int64_t max_seq,
+                                               int32_t n_ctx, float* out, void* workspace, size_t workspace_bytes);
+
 /* One-time repack of a Q4_K / Q6_K matrix [n_rows, k] (n_rows a multiple of 8 -- 16 for w2 --, k a
  * multiple of 256) into the register-fragment order the decode kernels read with coalesced
  * 128-bit loads.  Q4_K grows by 2.8 % (its 12-byte packed 6-bit scales are widened to 16 bytes),
- * Q6_K keeps its size.  No counterpart in the reference, whose kernels read the GGUF layout
+ * Q6_K keeps its size.  A Q8_0 matrix (k a multiple of 32) is repacked for the large-batch tensor-core GEMM instead:
+ * per row and 256 elements a 16-byte aligned record of 256 int8 values and 8 f16 scales (the 34-byte GGUF blocks are
+ * only 2-byte aligned), rows padded with zero records to a multiple of 256 elements (+6 %, more for short rows).
+ * No counterpart in the reference, whose kernels read the GGUF layout
  * directly (candle-kernels/src/quantized.cu:2626-2698); optional here as well.
  *   candle_moe_prepacked_bytes: size of the destination buffer (0 bytes = shape or dtype not supported)
  *   candle_moe_prepack: src raw blocks -> dst, both device memory, 16-byte aligned */

@@ -64,14 +64,15 @@ def _cpu_step(orc, model, tokens, index_pos, k_cache, v_cache, stages=None):
     return orc.matmul(cfg.dt_output, x, _host(model.output), cfg.vocab)
 
 
+@pytest.mark.parametrize("attention", ["library", "pytorch"])
 @pytest.mark.parametrize("prepack", [True, False])
-def test_decode_step_matches_the_cpu_restatement(orc, torch_cuda, prepack):
+def test_decode_step_matches_the_cpu_restatement(orc, torch_cuda, prepack, attention):
     torch = torch_cuda
     from candle_b200.llama_decode import DecodeConfig, DecodeStep
     cfg = DecodeConfig(vocab=512, d_model=512, n_head=8, n_kv_head=2, head_dim=64, n_layer=2, n_expert=8, n_expert_used=2,
                        d_ff=1024, max_seq=32)
     B, index_pos = 5, 23
-    model = DecodeStep(cfg, B, torch.device("cuda"), n_distinct=2, seed=3, prepack=prepack)
+    model = DecodeStep(cfg, B, torch.device("cuda"), n_distinct=2, seed=3, prepack=prepack, attention=attention)
     tokens = torch.randint(0, cfg.vocab, (B,), generator=torch.Generator(device="cuda").manual_seed(1), device="cuda")
     k0 = [t.cpu().numpy().copy() for t in model.k_cache]
     v0 = [t.cpu().numpy().copy() for t in model.v_cache]
@@ -103,3 +104,36 @@ def test_decode_step_matches_the_cpu_restatement(orc, torch_cuda, prepack):
     graph.replay()
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), logits)
+
+
+@pytest.mark.parametrize("B,n_head,n_kv,hd,max_seq,n_ctx", [(3, 32, 8, 128, 1100, 1037), (2, 8, 8, 128, 64, 1), (5, 8, 2, 64, 600, 513),
+                                                              (1, 16, 2, 128, 512, 512)])
+def test_decode_attention_matches_a_plain_softmax(torch_cuda, B, n_head, n_kv, hd, max_seq, n_ctx):
+    """The chunked kernel against the one-pass f32 formula of `standard_attention` (quantized_llama.rs:303-317)."""
+    import ctypes as C
+    torch = torch_cuda
+    from candle_b200 import _lib
+    L = _lib.load()
+    g = torch.Generator(device="cuda").manual_seed(n_ctx)
+    q = torch.randn((B, n_head, hd), generator=g, device="cuda")
+    kc = torch.randn((B, n_kv, max_seq, hd), generator=g, device="cuda")
+    vc = torch.randn((B, n_kv, max_seq, hd), generator=g, device="cuda")
+    kc[:, :, n_ctx:] = float("nan")  # positions past the context must never be read
+    vc[:, :, n_ctx:] = float("nan")
+    need = C.c_size_t(0)
+    assert L.candle_moe_decode_attention_workspace_bytes(B, n_head, hd, n_ctx, C.byref(need)) == 0
+    ws = torch.empty(need.value + 16, dtype=torch.uint8, device="cuda")
+    y = torch.full((B, n_head * hd), float("nan"), device="cuda")
+    st = L.candle_moe_decode_attention(torch.cuda.current_stream().cuda_stream, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, n_head,
+                                       n_kv, hd, max_seq, n_ctx, y.data_ptr(), ws.data_ptr(), ws.numel())
+    assert st == 0
+    grp = n_head // n_kv
+    qd = q.double().reshape(B, n_kv, grp, hd)
+    att = torch.softmax(qd @ kc[:, :, :n_ctx].double().transpose(-1, -2) / math.sqrt(hd), dim=-1)
+    ref = (att @ vc[:, :, :n_ctx].double()).reshape(B, n_head * hd)
+    got = y.double()
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max() / ref.abs().max()) < 2e-6
+    # shapes outside the supported set are refused, not mis-computed
+    assert L.candle_moe_decode_attention(None, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, 6, 2, 128, max_seq, n_ctx,
+                                         y.data_ptr(), ws.data_ptr(), ws.numel()) in (-2, -4)

@@ -98,10 +98,13 @@ def test_mixtral_8x7b_mid_sized_batches(orc, torch_cuda, T):
     _full_size_case(orc, torch_cuda, "mixtral_8x7b", T, True, seed=4)
 
 
-def test_fine_grained_q8_0_4096_rows(orc, torch_cuda):
+@pytest.mark.parametrize("prepack", [True, False])
+def test_fine_grained_q8_0_4096_rows(orc, torch_cuda, prepack):
     """d=2048, 60 routed experts of ff=1408, top-4 without renormalisation, shared expert ff=5632 gated by
-    sigmoid(x.g), all Q8_0, 4096 rows (qwen2_moe.rs:261-323)."""
-    _full_size_case(orc, torch_cuda, "fine_grained_q8_0", 4096, False, seed=5)
+    sigmoid(x.g), all Q8_0, 4096 rows (qwen2_moe.rs:261-323).  With the repacked copies the products take the
+    tensor-core GEMM (scales folded into fp16 operands: the one path whose float side is not the reference's
+    per-block f32 scaling, held to the same bounds); without them the int8 tile kernel."""
+    _full_size_case(orc, torch_cuda, "fine_grained_q8_0", 4096, prepack, seed=5)
 
 
 def test_mixtral_8x22b_skewed_routing_1024_rows(orc, torch_cuda):
