@@ -18,11 +18,12 @@ namespace {
 // k T / E rows, i.e. a few of the decode kernels' 16-row groups.  Measured on the Mixtral-shaped layer (decode
 // kernels / GEMM, microseconds): T = 65 349 / 503, 96 384 / 537, 128 473 / 554, 160 569 / 584.
 inline int64_t gemm_min_rows() { return tuning_get(TUNE_GEMM_MIN_ROWS); }
-// When the caller knows the ACTUAL largest row count of an expert (expert parallelism: the host has the counts), the
-// GEMM already pays off above 16 rows: the decode kernels walk the weights once per 16 rows (up to 32 rows it runs
-// with 32-wide position tiles).  (A single-device
-// forward only knows the bound T, and its experts usually hold a fraction of that.)
-constexpr int64_t GEMM_MIN_ROWS_EXACT = 16;
+// When the caller knows the ACTUAL (or, in the slot form of expert parallelism, the expected) largest row count of an
+// expert, the GEMM takes over above 48 rows: up to there the decode kernels walk the weights at most three times (once
+// per 16 rows), which is cheaper than the GEMM's fixed cost per block of a tile when a rank holds only a few experts
+// (measured on 4 GPUs, 2 experts of ~33 rows per rank: GEMM 248 us for the local phase; the decode kernels take about
+// 64 us per expert at that size on one GPU).  (A single-device forward only knows the bound T.)
+constexpr int64_t GEMM_MIN_ROWS_EXACT = 48;
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
 inline int k_split_slots(int64_t T) { return T <= gemm_min_rows() ? MAX_K_SPLITS : 4; }
