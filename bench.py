@@ -881,9 +881,11 @@ def run_c3(args):
                        "weights": "4 distinct random layers rotate over the layers (attention Q4_K, w1/w3 Q4_K, w2 Q6_K, lm head Q6_K)",
                        "library_parts": "wq/wk/wv/wo, lm head (candle_moe_qmatmul); ffn_norm + MoE block + residual (candle_moe_ffn_layer"
                                         + (", experts sharded: candle_moe_ep_forward)" if world > 1 else ")")
-                                        + ("; attention over the f32 KV cache (candle_moe_decode_attention)" if args.attention == "library" else ""),
-                       "pytorch_parts": "embedding, attention_norm / final norm, interleaved RoPE, f32 KV cache append"
-                                        + ("" if args.attention == "library" else ", attention (q k^T, softmax, v as batched f32 matmuls)"),
+                                        + ("; attention_norm, rotary embedding + cache append, attention over the f32 KV cache (candle_moe_rmsnorm, "
+                                           "candle_moe_rope_kv_append, candle_moe_decode_attention)" if args.attention == "library" else ""),
+                       "pytorch_parts": "embedding, final norm, residual add of the attention half"
+                                        + ("" if args.attention == "library" else ", attention_norm, interleaved RoPE, f32 KV cache append, "
+                                           "attention (q k^T, softmax, v as batched f32 matmuls)"),
                        "l2_policy": "a step reads tens of GB: nothing survives in the 126 MB L2 between steps",
                        "timed": "CUDA graph replay" if graph is not None else "eager launches",
                        "parallelism": "single GPU" if world == 1 else f"ep{world}: experts sharded, attention replicated, "
@@ -899,7 +901,7 @@ def run_c3(args):
             "cpu_baseline": None,
             "e2e": {"value": B * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * 8,
                     "d2h_bytes_per_step": B * cfg.vocab * 4, "ms_per_step": ms_e2e},
-            "gpu_launches": cfg.n_layer * (4 * 3 + 6) * args.steps,
+            "gpu_launches": cfg.n_layer * (1 + 6 + 1 + 2 + 6 + 7) * args.steps,
             "finite": bool(torch.isfinite(logits).all()),
             "clocks": clocks,
         }

@@ -109,6 +109,8 @@ SYMBOLS = {
     "candle_moe_ep_experts": (C.c_int, [_P, C.POINTER(MoeWeightsC), _P, _P, _I32, _I64, _I64, _P, _P, C.c_size_t]),
     "candle_moe_qmatmul_workspace_bytes": (C.c_int, [_I32, _I64, _I32, _I32, C.POINTER(_SZ)]),
     "candle_moe_qmatmul": (C.c_int, [_P, _P, _P, _I32, _I32, _I32, _P, _I64, _P, _P, _SZ]),
+    "candle_moe_rmsnorm": (C.c_int, [_P, _P, _P, C.c_float, _I64, _I32, _P]),
+    "candle_moe_rope_kv_append": (C.c_int, [_P, _P, _I64, _P, _P, _I32, _I32, _I32, _I32, _I64, _I32, _P, _P, _P]),
     "candle_moe_decode_attention_workspace_bytes": (C.c_int, [_I32, _I32, _I32, _I32, C.POINTER(_SZ)]),
     "candle_moe_decode_attention": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _I32, _I64, _I32, _P, _P, _SZ]),
     "candle_moe_quantize_weights": (C.c_int, [_P, _I32, _P, _I64, _P]),

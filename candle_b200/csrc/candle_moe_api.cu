@@ -652,6 +652,26 @@ int candle_moe_selftest_bounded_wait(void* stream, int32_t poll_limit) {
     return rc(launch_selftest_wait((cudaStream_t)stream, poll_limit));
 }
 
+int candle_moe_rmsnorm(void* stream, const float* x, const float* weight, float eps, int64_t rows, int32_t d, float* y) {
+    if (rows < 0 || d <= 0 || d % 4) return CANDLE_MOE_E_SHAPE;
+    if (rows == 0) return CANDLE_MOE_OK;
+    if (!x || !weight || !y) return CANDLE_MOE_E_NULL;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15) return CANDLE_MOE_E_ALIGN;
+    return rc(launch_rmsnorm((cudaStream_t)stream, x, weight, eps, rows, d, y));
+}
+
+int candle_moe_rope_kv_append(void* stream, const float* qkv, int64_t row_stride, const float* cos, const float* sin, int32_t batch,
+                              int32_t n_head, int32_t n_kv_head, int32_t head_dim, int64_t max_seq, int32_t index_pos, float* q_out,
+                              float* k_cache, float* v_cache) {
+    if (batch < 0 || n_head <= 0 || n_kv_head <= 0 || head_dim <= 0 || head_dim % 2 || index_pos < 0 || index_pos >= max_seq ||
+        row_stride < (int64_t)(n_head + 2 * n_kv_head) * head_dim)
+        return CANDLE_MOE_E_SHAPE;
+    if (batch == 0) return CANDLE_MOE_OK;
+    if (!qkv || !cos || !sin || !q_out || !k_cache || !v_cache) return CANDLE_MOE_E_NULL;
+    return rc(launch_rope_kv_append((cudaStream_t)stream, qkv, row_stride, cos, sin, batch, n_head, n_kv_head, head_dim, max_seq,
+                                    index_pos, q_out, k_cache, v_cache));
+}
+
 int candle_moe_decode_attention_workspace_bytes(int32_t batch, int32_t n_head, int32_t head_dim, int32_t n_ctx, size_t* out_bytes) {
     if (!out_bytes) return CANDLE_MOE_E_NULL;
     if (batch < 0 || n_head <= 0 || head_dim <= 0 || n_ctx < 0) return CANDLE_MOE_E_SHAPE;
@@ -763,6 +783,12 @@ struct QmmWorkspace {
     void* gemm;
     size_t total;
 };
+// One group holds every row, so the row count is exact.  The tensor-core GEMM takes the product above 48 rows, and
+// from 17 rows on when the matrix has enough 128-row tiles to fill the SMs by itself (measured at 32 rows:
+// [32000, 4096] Q6_K 76 us through the GEMM against 108 us through the streaming form, [4096, 4096] Q4_K 25 against 23).
+inline bool qmm_takes_gemm(int dtype, int64_t rows, int n) {
+    return dtype != CANDLE_GGML_Q8_0 && (rows > GEMM_MIN_ROWS_EXACT || (rows > 16 && n >= 12800));
+}
 QmmWorkspace qmm_layout(int dtype, int64_t rows, int n, int k, void* base_) {
     uint8_t* base = static_cast<uint8_t*>(base_);
     QmmWorkspace ws{};
@@ -774,7 +800,7 @@ QmmWorkspace qmm_layout(int dtype, int64_t rows, int n, int k, void* base_) {
     // decode-sized batches split K to fill the device (a [4096, 4096] matrix has 256 row tiles for 148 SMs x 16 warps)
     ws.slots = rows <= 64 && n % 4 == 0 ? MAX_K_SPLITS : 1;
     if (ws.slots > 1) ws.eo = carve<float>(base, off, (size_t)rows * n * ws.slots);
-    if (rows > GEMM_MIN_ROWS_EXACT && dtype != CANDLE_GGML_Q8_0) {
+    if (qmm_takes_gemm(dtype, rows, n)) {
         off = align_up(off, 1024);
         ws.gemm = base ? base + off : reinterpret_cast<void*>(1);
         off += expert_gemm_scratch_bytes(rows, k);
@@ -813,7 +839,6 @@ int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int
     const int64_t stride = rows * (int64_t)n;
     int splits = 1;
     bool done = false;
-    // the row count is exact here (not a bound as in a routed block): the tensor-core form pays off above 16 rows
     const bool large = ws.gemm && gemm_enabled();
     // The decode kernels over the repacked copy are not used here: with a single group their tiles are too few and
     // too short, and the streaming form over the GGUF blocks is faster (measured, [4096, 4096] Q4_K / [32000, 4096]

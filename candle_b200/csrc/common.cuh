@@ -231,6 +231,8 @@ cudaError_t launch_selftest_wait(cudaStream_t st, int limit);
 size_t decode_attention_workspace_bytes(int B, int n_head, int head_dim, int n_ctx);
 cudaError_t launch_decode_attention(cudaStream_t st, const float* q, const float* kc, const float* vc, int B, int n_head, int n_kv,
                                     int head_dim, int64_t max_seq, int n_ctx, float scale, float* y, float* workspace);
+cudaError_t launch_rope_kv_append(cudaStream_t st, const float* qkv, int64_t row_stride, const float* cos, const float* sin, int B,
+                                  int n_head, int n_kv, int D, int64_t max_seq, int pos, float* q_out, float* kc, float* vc);
 cudaError_t launch_quantize_weights(cudaStream_t st, int dtype, const float* src, int64_t n, void* dst);
 cudaError_t launch_dequantize(cudaStream_t st, int dtype, const void* blocks, int64_t n, float* dst);
 

@@ -233,6 +233,51 @@ cudaError_t launch_att(cudaStream_t st, const float* q, const float* kc, const f
 
 }  // namespace
 
+namespace {
+// Interleaved rotary embedding of the new token's q and k (`rope_i`, candle-nn/src/rotary_emb.rs:53-66: pairs
+// (x[2i], x[2i+1]) rotated by the angle of (position, i), product then difference / sum like the CPU loop) and the
+// append of k and v to the f32 cache at that position (candle-nn/src/kv_cache.rs:143-164), in one pass.
+// qkv [B, row_stride] holds q (n_head * D), k (n_kv * D), v (n_kv * D) side by side; cos / sin [D / 2] of the position.
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(const float* __restrict__ qkv, int64_t row_stride, const float* __restrict__ cos, const float* __restrict__ sin,
+                      int n_head, int n_kv, int D, int64_t max_seq, int pos, float* __restrict__ q_out, float* __restrict__ kc,
+                      float* __restrict__ vc) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int half = D / 2, n_q = n_head * half, n_k = n_kv * half;
+    const float* row = qkv + (int64_t)b * row_stride;
+    for (int i = threadIdx.x; i < n_q + 2 * n_k; i += blockDim.x) {
+        if (i < n_q + n_k) {
+            const bool is_q = i < n_q;
+            const int j = is_q ? i : i - n_q;
+            const int h = j / half, ip = j - h * half;
+            const float* src = row + (is_q ? 0 : n_head * D) + h * D + 2 * ip;
+            const float x0 = src[0], x1 = src[1], c = cos[ip], s = sin[ip];
+            const float o0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)), o1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+            float* dst = is_q ? q_out + ((int64_t)b * n_head + h) * D + 2 * ip
+                              : kc + (((int64_t)b * n_kv + h) * max_seq + pos) * D + 2 * ip;
+            dst[0] = o0;
+            dst[1] = o1;
+        } else {
+            const int j = i - n_q - n_k;
+            const int h = j / half, ip = j - h * half;
+            const float* src = row + (n_head + n_kv) * D + h * D + 2 * ip;
+            float* dst = vc + (((int64_t)b * n_kv + h) * max_seq + pos) * D + 2 * ip;
+            dst[0] = src[0];
+            dst[1] = src[1];
+        }
+    }
+}
+}  // namespace
+
+cudaError_t launch_rope_kv_append(cudaStream_t st, const float* qkv, int64_t row_stride, const float* cos, const float* sin, int B,
+                                  int n_head, int n_kv, int D, int64_t max_seq, int pos, float* q_out, float* kc, float* vc) {
+    if (B == 0) return cudaSuccess;
+    return launch_k(rope_kv_append_kernel, dim3(B), dim3(256), 0, st, qkv, row_stride, cos, sin, n_head, n_kv, D, max_seq, pos, q_out,
+                    kc, vc);
+}
+
 size_t decode_attention_workspace_bytes(int B, int n_head, int head_dim, int n_ctx) {
     const size_t n_chunks = (size_t)(n_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
     return (size_t)B * n_head * n_chunks * (head_dim + 2) * sizeof(float);

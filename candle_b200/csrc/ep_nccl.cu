@@ -484,9 +484,11 @@ int ep_forward_impl(cudaStream_t st, candle_moe_ep_comm* cm, const candle_moe_ep
     int eo_splits = 1;
     if (g.slots) {
         const unsigned grid = (unsigned)((Tk + 7) / 8) + 1;
+        // tests: this rank's slot headers carry a wrong check word, so every receiver drops its rows and says so
+        const uint32_t fp_send = cfg->inject_count_mismatch == 1 ? g.fp ^ 0x5a5a5a5au : g.fp;
         CU_TRY(launch_k(ep_pack_slots_kernel, dim3(grid), dim3(256), 0, st, (const uint32_t*)ws.offsets, (const uint32_t*)ws.perm,
                         (const uint32_t*)ws.pair_pos, (int)Tk, (int)T, d, E, El, N, g.C, (const int8_t*)ws.xq, (const float*)ws.xs,
-                        (const int16_t*)ws.xb, ws.send, g.slot_bytes, (int)g.hdr_bytes, (int)g.row_bytes, g.fp, ws.slot_pos));
+                        (const int16_t*)ws.xb, ws.send, g.slot_bytes, (int)g.hdr_bytes, (int)g.row_bytes, fp_send, ws.slot_pos));
         ep_mark(st, 1);
         CM_TRY(exchange_fixed(a, cm, st, ws.send, ws.recv, g.slot_bytes));
         ep_mark(st, 2);

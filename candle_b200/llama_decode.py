@@ -4,16 +4,18 @@ quantized_llama (quantized_llama.rs:869-898) for one new token per sequence.
 This is a HARNESS around the block, so that its share of a whole decode step can be measured; it is not a model
 runtime.  What runs where:
 
-* this library (C ABI): every quantized product -- wq / wk / wv / wo and the lm head through `QMatMul.forward`
-  (`candle_moe_qmatmul`), the attention over the cache (`candle_moe_decode_attention`, or PyTorch's batched matmuls
-  with `attention="pytorch"`), the FFN half of each layer (`ffn_norm` -> MoE block -> `+ residual`) as one call
+* this library (C ABI): every quantized product -- wq / wk / wv (as one product over their concatenated rows) / wo and
+  the lm head through `QMatMul.forward` (`candle_moe_qmatmul`) --, and with `attention="library"` the rest of the
+  attention half: `attention_norm` (`candle_moe_rmsnorm`), rotary embedding + cache append
+  (`candle_moe_rope_kv_append`), the attention over the cache (`candle_moe_decode_attention`); the FFN half of each layer (`ffn_norm` -> MoE block -> `+ residual`) as one call
   (`candle_moe_ffn_layer`), or, with the experts sharded over ranks, `ExpertParallelMoe.forward` between a PyTorch
   RmsNorm and residual add;
-* stock PyTorch ops, with the reference's arithmetic: token embedding lookup, `attention_norm` / final norm (RmsNorm,
-  candle-nn/src/ops.rs:504-514), interleaved rotary embedding (`rope_i`, candle-nn/src/rotary_emb.rs:53-66, tables of
-  quantized_llama.rs:410-427), the f32 KV cache append (candle-nn/src/kv_cache.rs:143-164) and, with
-  `attention="pytorch"`, the attention itself as the reference's `standard_attention` (quantized_llama.rs:303-317:
-  q k^T / sqrt(head_dim), softmax, times v, grouped heads instead of a materialised `repeat_kv`).
+* stock PyTorch ops, with the reference's arithmetic: token embedding lookup, the final norm, the residual add of the
+  attention half, and, with `attention="pytorch"`, the whole glue of the attention half: RmsNorm
+  (candle-nn/src/ops.rs:504-514), interleaved rotary embedding (`rope_i`, candle-nn/src/rotary_emb.rs:53-66, tables of
+  quantized_llama.rs:410-427), the f32 KV cache append (candle-nn/src/kv_cache.rs:143-164) and the attention itself as
+  the reference's `standard_attention` (quantized_llama.rs:303-317: q k^T / sqrt(head_dim), softmax, times v, grouped
+  heads instead of a materialised `repeat_kv`).
 
 One layer's quantized bytes may be shared by several layers (`n_distinct` sets of weights rotate over the layers):
 a random-init 32-layer model does not need 32 different random layers to be timed, only enough distinct bytes that
@@ -91,6 +93,12 @@ class LayerWeights:
         self.attention_wk = q((cfg.n_kv_head * hd, d), cfg.dt_attn)
         self.attention_wv = q((cfg.n_kv_head * hd, d), cfg.dt_attn)
         self.attention_wo = q((d, cfg.n_head * hd), cfg.dt_attn)
+        # the three projections as ONE product over the concatenated rows wq | wk | wv (a row's result does not depend on
+        # which other rows the matrix holds, so this is the same arithmetic in one launch sequence instead of three)
+        qkv = torch.cat([self.attention_wq.inner.data, self.attention_wk.inner.data, self.attention_wv.inner.data])
+        self.attention_wqkv = QMatMul(QTensor(qkv, GgmlDType(cfg.dt_attn), ((cfg.n_head + 2 * cfg.n_kv_head) * hd, d)))
+        if prepack:
+            self.attention_wqkv.prepack()
         self.attention_norm = 1.0 + 0.1 * torch.randn(d, generator=gen, device=device)
         self.ffn_norm = 1.0 + 0.1 * torch.randn(d, generator=gen, device=device)
         self.router = torch.randn((cfg.n_expert, d), generator=gen, device=device, dtype=torch.float32) * 0.02
@@ -114,7 +122,8 @@ class DecodeStep:
     def __init__(self, cfg: DecodeConfig, batch: int, device, *, n_distinct: int = 4, seed: int = 0, prepack: bool = True,
                  expert_parallel=None, kv_fill: float = 0.5, attention: str = "library"):
         """`expert_parallel`: None, or {"world", "rank", "make": layer_weights -> ExpertParallelMoe} for the sharded form.
-        `attention`: "library" (candle_moe_decode_attention) or "pytorch" (batched f32 matmuls and softmax)."""
+        `attention`: "library" (the attention half through this library: candle_moe_rmsnorm, one product over wq | wk | wv,
+        candle_moe_rope_kv_append, candle_moe_decode_attention) or "pytorch" (three products, PyTorch ops for the rest)."""
         self.cfg, self.batch, self.device = cfg, batch, device
         self.attention_impl = attention
         self._att_ws = None
@@ -147,24 +156,39 @@ class DecodeStep:
         """`attention_norm` + `forward_attn` + residual (quantized_llama.rs:880-883, 264-345) for seq_len = 1."""
         cfg, B = self.cfg, self.batch
         lw = self.sets[self.layer_set[li]]
+        kc, vc = self.k_cache[li], self.v_cache[li]
+        n = index_pos + 1
+        if self.attention_impl == "library":
+            import ctypes as C
+            from . import _lib
+            from .quantized import _stream_ptr
+            L, st = _lib.load(), _stream_ptr(self.device)
+            x = x.contiguous()
+            h = torch.empty_like(x)
+            with torch.cuda.device(self.device):
+                _lib.check("candle_moe_rmsnorm", L.candle_moe_rmsnorm(st, x.data_ptr(), lw.attention_norm.data_ptr(), cfg.rms_eps, B,
+                                                                      cfg.d_model, h.data_ptr()))
+                qkv = lw.attention_wqkv.forward(h)
+                q = torch.empty((B, cfg.n_head, cfg.head_dim), dtype=torch.float32, device=self.device)
+                _lib.check("candle_moe_rope_kv_append",
+                           L.candle_moe_rope_kv_append(st, qkv.data_ptr(), qkv.shape[1], self.cos[index_pos].data_ptr(),
+                                                       self.sin[index_pos].data_ptr(), B, cfg.n_head, cfg.n_kv_head, cfg.head_dim,
+                                                       cfg.max_seq, index_pos, q.data_ptr(), kc.data_ptr(), vc.data_ptr()))
+            y = self._library_attention(q, kc, vc, n)
+            return lw.attention_wo.forward(y) + x
         h = rms_norm(x, lw.attention_norm, cfg.rms_eps)
         q = lw.attention_wq.forward(h).view(B, 1, cfg.n_head, cfg.head_dim).transpose(1, 2)
         k = lw.attention_wk.forward(h).view(B, 1, cfg.n_kv_head, cfg.head_dim).transpose(1, 2)
         v = lw.attention_wv.forward(h).view(B, 1, cfg.n_kv_head, cfg.head_dim).transpose(1, 2)
         cos, sin = self.cos[index_pos:index_pos + 1], self.sin[index_pos:index_pos + 1]
         q, k = rope_interleaved(q, cos, sin), rope_interleaved(k, cos, sin)
-        kc, vc = self.k_cache[li], self.v_cache[li]
         kc[:, :, index_pos:index_pos + 1] = k
         vc[:, :, index_pos:index_pos + 1] = v
-        n = index_pos + 1
-        if self.attention_impl == "library":
-            y = self._library_attention(q, kc, vc, n)
-        else:
-            g = cfg.n_head // cfg.n_kv_head
-            qg = q.reshape(B, cfg.n_kv_head, g, cfg.head_dim)              # the g query heads that share a kv head
-            att = torch.matmul(qg, kc[:, :, :n].transpose(-1, -2)) / math.sqrt(cfg.head_dim)
-            att = torch.softmax(att, dim=-1)
-            y = torch.matmul(att, vc[:, :, :n]).reshape(B, cfg.n_head * cfg.head_dim)
+        g = cfg.n_head // cfg.n_kv_head
+        qg = q.reshape(B, cfg.n_kv_head, g, cfg.head_dim)              # the g query heads that share a kv head
+        att = torch.matmul(qg, kc[:, :, :n].transpose(-1, -2)) / math.sqrt(cfg.head_dim)
+        att = torch.softmax(att, dim=-1)
+        y = torch.matmul(att, vc[:, :, :n]).reshape(B, cfg.n_head * cfg.head_dim)
         return lw.attention_wo.forward(y) + x
 
     def _library_attention(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, n: int) -> torch.Tensor:

@@ -290,7 +290,8 @@ typedef struct candle_moe_ep_config {
     int32_t renorm;               /* as candle_moe_weights_t.renorm */
     int32_t max_tokens;           /* bound on T of ANY rank in a step; the same on every rank (sizes the slots) */
     int32_t force_form;           /* 0: choose by size; 1: slots; 2: exact */
-    int32_t inject_count_mismatch;/* tests only: 1 makes this rank report a bad count table (exact form) */
+    int32_t inject_count_mismatch;/* tests only: 1 makes this rank announce bad metadata (exact form: a count table that fails
+                                     the check; slot form: slot headers with a wrong check word) */
     int64_t max_recv_rows;        /* exact form: cap on the rows one rank may receive per step (0 = worst case,
                                      world * max_tokens * min(top_k, E / world)); sizes the workspace */
     const float* router;          /* device f32 [E, d_model], replicated on every rank */
@@ -327,6 +328,20 @@ CANDLE_MOE_API int candle_moe_qmatmul_workspace_bytes(int32_t dtype, int64_t row
 CANDLE_MOE_API int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int32_t dtype, int32_t n,
                                       int32_t k, const float* x, int64_t rows, float* out, void* workspace,
                                       size_t workspace_bytes);
+
+/* The other pieces of a decode step's attention half, for the decode-step harness (none is part of the MoE block):
+ *   candle_moe_rmsnorm: y = x / sqrt(mean(x^2) + eps) * weight per row, f32 (`candle_nn::ops::rms_norm`,
+ *     candle-nn/src/ops.rs:504-514; `attention_norm` / final `norm`, quantized_llama.rs:880, 893); d a multiple of 4.
+ *   candle_moe_rope_kv_append: the interleaved rotary embedding of the new token's q and k (`rope_i`,
+ *     candle-nn/src/rotary_emb.rs:53-66, called from quantized_llama.rs:255-263) and the append of k and v to the
+ *     f32 cache at index_pos (`KvCache::append`, candle-nn/src/kv_cache.rs:143-164, 204-226), in one pass.
+ *     qkv [batch, row_stride] holds a row's q (n_head * head_dim), k and v (n_kv_head * head_dim each) side by side --
+ *     the output of one product over the concatenated wq | wk | wv rows --, cos / sin [head_dim / 2] are the table rows
+ *     of the position (quantized_llama.rs:410-427); q_out [batch, n_head, head_dim]; caches as below. */
+CANDLE_MOE_API int candle_moe_rmsnorm(void* stream, const float* x, const float* weight, float eps, int64_t rows, int32_t d, float* y);
+CANDLE_MOE_API int candle_moe_rope_kv_append(void* stream, const float* qkv, int64_t row_stride, const float* cos, const float* sin,
+                                             int32_t batch, int32_t n_head, int32_t n_kv_head, int32_t head_dim, int64_t max_seq,
+                                             int32_t index_pos, float* q_out, float* k_cache, float* v_cache);
 
 /* Attention of ONE new token per sequence over an f32 KV cache: `standard_attention` of quantized_llama.rs:303-317 at
  * seq_len = 1 (q k^T / sqrt(head_dim), softmax_last_dim, times v) with `repeat_kv` folded into the indexing (query head

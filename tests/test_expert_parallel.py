@@ -9,9 +9,12 @@ inside the process group's timeout.  Every rank's result must equal the oracle's
 rank's tokens bit for bit.
 
 GPU part: the C ABI path (`candle_moe_ep_forward`, NCCL inside the library).  One GPU: world size 1 (both forms,
-the exchanges are device copies), the local phase of a rank that holds one expert, a corrupted slot header.
+the exchanges are device copies), replay from a CUDA graph, the local phase of a rank that holds one expert, a slot
+header that fails its check (dropped on the device, reported through the health word), a bounded wait that runs out.
 Two or more GPUs (skipped when the box has one): child processes, one per GPU, compare every rank's output with
-the oracle, exercise the rejected count table and a rank that leaves between steps.
+the oracle, exercise the rejected count table and the replay of the slot form from a CUDA graph.  A rank that leaves
+between steps is a CPU (gloo) test only: the library's raw NCCL communicator has no watchdog, so the GPUs of the
+remaining ranks would wait without limit.
 """
 import ctypes as C
 import os
@@ -299,6 +302,54 @@ def test_single_rank_steps_of_different_sizes_and_no_rows(orc, torch_cuda):
 
 
 @pytest.mark.gpu
+def test_slot_form_replays_from_a_cuda_graph(orc, torch_cuda):
+    """No host synchronisation and no data-dependent size in the slot form: a captured step replays over new inputs."""
+    torch = torch_cuda
+    mw = orc.make_moe_weights(24, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    blk, ep = _device_block_and_ep(orc, torch, mw, True, force_form=1, max_tokens=40)
+    x = torch.from_numpy(orc.make_activations(5, 40, 512)).cuda()
+    ep.forward(x)
+    torch.cuda.synchronize()
+    y = torch.zeros_like(x)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ep.forward(x, out=y)
+    for seed in (6, 7):
+        xn = orc.make_activations(seed, 40, 512)
+        x.copy_(torch.from_numpy(xn))
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = orc.moe_forward(mw, xn)
+        assert H.rel_l2(y.cpu().numpy(), ref.y) <= H.REL_L2_TOL and H.max_rel(y.cpu().numpy(), ref.y) <= H.MAX_REL_TOL
+        assert torch.equal(y, ep.forward(x))
+
+
+@pytest.mark.gpu
+def test_slot_header_that_fails_its_check_is_dropped_and_reported(orc, torch_cuda):
+    """The receiving side checks every slot header on the device; a bad one counts as an empty slot (nothing is indexed
+    with numbers that cannot be trusted) and raises bit 2 of the health word.  The next, honest step is right again."""
+    torch = torch_cuda
+    from candle_b200 import _lib
+    L = _lib.load()
+    mw = orc.make_moe_weights(25, 512, 1024, 8, 2, orc.Q4K, orc.Q6K)
+    blk, ep = _device_block_and_ep(orc, torch, mw, True, force_form=1, max_tokens=16)
+    xn = orc.make_activations(8, 16, 512)
+    x = torch.from_numpy(xn).cuda()
+    assert L.candle_moe_device_status_reset() == 0
+    ep.inject_count_mismatch = True
+    ep.forward(x)
+    v = C.c_int32(-1)
+    assert L.candle_moe_device_status(C.byref(v)) == 0 and v.value == 4
+    assert ep.forward(x, timed=True) is not None and ep.last_rows == 0   # the rows of the bad slot were not processed
+    assert L.candle_moe_device_status_reset() == 0
+    ep.inject_count_mismatch = False
+    y = ep.forward(x).cpu().numpy()
+    ref = orc.moe_forward(mw, xn)
+    assert H.rel_l2(y, ref.y) <= H.REL_L2_TOL
+    assert L.candle_moe_device_status(C.byref(v)) == 0 and v.value == 0
+
+
+@pytest.mark.gpu
 def test_rank_holding_fewer_experts_than_top_k(orc, torch_cuda):
     """8 experts over 8 ranks with top-2: every rank holds ONE expert.  The local phase of one such rank runs on a
     single GPU through the step-by-step entry points; the rows come from eight made-up sources."""
@@ -388,6 +439,33 @@ def _gpu_rank(rank, world, port, mode, fail):
             ref = orc.moe_forward(mw, x.cpu().numpy())
             assert H.rel_l2(y, ref.y) <= H.REL_L2_TOL
             ep.close()
+        elif mode == "graph":
+            # the slot form is a fixed sequence of launches and NCCL calls: it replays from a CUDA graph
+            ep = ExpertParallelMoe(2, blk.feed_forward_gate_inp, mine, prepack=True, force_form=1, max_tokens=32,
+                                   router_bias=torch.from_numpy(mw.router_bias))
+            x = torch.from_numpy(orc.make_activations(700 + rank, 32 - rank, 512)).cuda()
+            y_eager = ep.forward(x).clone()          # also makes the communicator, the workspace and NCCL's connections
+            ep.forward(x)
+            torch.cuda.synchronize()
+            y_graph = torch.zeros_like(x)
+            ok, graph = 1, torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    ep.forward(x, out=y_graph)
+            except Exception as exc:  # noqa: BLE001
+                ok, why = 0, f"{type(exc).__name__}: {exc}"
+            # every rank must have captured before any rank replays (a replay holds collectives)
+            flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            assert int(flag) == 1, "capture failed on a rank" + (": " + why if not ok else "")
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(y_graph, y_eager)
+            ref = orc.moe_forward(mw, x.cpu().numpy())
+            assert H.rel_l2(y_graph.cpu().numpy(), ref.y) <= H.REL_L2_TOL
+            del graph
+            ep.close()
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
@@ -402,7 +480,7 @@ def _gpu_world():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["parity", "bad_table"])
+@pytest.mark.parametrize("mode", ["parity", "bad_table", "graph"])
 def test_multi_gpu_ranks_match_the_oracle(orc, torch_cuda, mode):
     world = _gpu_world()
     if world == 0:
