@@ -105,11 +105,12 @@ Workspace layout(const candle_moe_weights_t* w, int64_t T, void* base_) {
         const auto takes = [](int dt, const void* packed) {
             return dt == CANDLE_GGML_Q4K || ((dt == CANDLE_GGML_Q6K || dt == CANDLE_GGML_Q8_0) && packed != nullptr);
         };
-        if (takes(w->dtype_w13, w->w1_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d));
+        if (takes(w->dtype_w13, w->w1_prepacked))
+            g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)d, w->dtype_w13 == CANDLE_GGML_Q8_0 ? 2 : 1));
         if (takes(w->dtype_w2, w->w2_prepacked)) g = std::max(g, expert_gemm_scratch_bytes((int64_t)Tk, (int)ff));
         if (w->d_ff_shared > 0 && w->dtype_shared13 == CANDLE_GGML_Q8_0 && w->shared_w1_prepacked && w->shared_w3_prepacked &&
             w->shared_w2_prepacked)
-            g = std::max(g, std::max(expert_gemm_scratch_bytes(T, (int)d), expert_gemm_scratch_bytes(T, w->d_ff_shared)));
+            g = std::max(g, std::max(expert_gemm_scratch_bytes(T, (int)d, 2), expert_gemm_scratch_bytes(T, w->d_ff_shared)));
         if (g) {
             off = align_up(off, 1024);
             ws.gemm = base ? base + off : nullptr;

@@ -202,7 +202,7 @@ cudaError_t launch_expert_direct(cudaStream_t st, bool gate_up, const ExpertPtrs
                                  int max_splits, int max_active_experts = 0, int64_t total_rows = 0);
 // large-batch grouped GEMM on tcgen05 / TMEM: Q4_K in GGUF layout (repacked = false), Q6_K in the repacked
 // layout (repacked = true); `scratch` of expert_gemm_scratch_bytes(P, K) bytes
-size_t expert_gemm_scratch_bytes(int64_t P, int K);
+size_t expert_gemm_scratch_bytes(int64_t P, int K, int parts = 1);  // parts = 2: the exact Q8_0 gate_up operand
 // Q8_0 rows repacked for the GEMM: [n][ceil(k / 256)][256 int8 | 8 f16 scales]
 size_t prepacked_q80_bytes(int64_t n_rows, int k);
 cudaError_t launch_prepack_q80(cudaStream_t st, const void* raw, int64_t n_rows, int k, void* dst);

@@ -116,9 +116,11 @@ prep_gemm_b_kernel(const int8_t* __restrict__ aq, const float* __restrict__ asca
 
 // Q8_0 activations (int8 values, one f32 scale per 32, candle_moe_quantize_act) as the fp16 operand d * q, rows in
 // grouped order, columns padded with zeros to K_pad (a multiple of 256); the per-block scale table is all ones.
+// exact = 1: 64 d q as the fp16 pair (rounded product, exact residual), a row laid out [256 of part 0 | 256 of part 1]
+// per block, and 1 / 64 in the scale table.
 __global__ void __launch_bounds__(256)
 prep_gemm_b_q80_kernel(const int8_t* __restrict__ aq, const float* __restrict__ ascale, const uint32_t* __restrict__ row_of, int P,
-                       int P_pad, int K, int K_pad, __half* __restrict__ bf16, float* __restrict__ d8t) {
+                       int P_pad, int K, int K_pad, int exact, __half* __restrict__ bf16, float* __restrict__ d8t) {
     pdl_trigger();
     pdl_wait();
     const int kb = K_pad >> 8;
@@ -126,22 +128,33 @@ prep_gemm_b_q80_kernel(const int8_t* __restrict__ aq, const float* __restrict__ 
     const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (p, block of 256)
     if (unit >= (int64_t)P_pad * kb) return;
     const int p = (int)(unit / kb), blk = (int)(unit - (int64_t)p * kb);
-    uint4 o = make_uint4(0, 0, 0, 0);
+    uint4 o = make_uint4(0, 0, 0, 0), o1 = make_uint4(0, 0, 0, 0);
     const int k0 = blk * 256 + lane * 8;
     if (p < P && k0 < K) {  // K is a multiple of 32: a lane's eight values lie inside one 32-block
         const int64_t row = row_of ? (int64_t)row_of[p] : (int64_t)p;
         const uint2 v = *reinterpret_cast<const uint2*>(aq + row * K + k0);
         const int8_t* b = reinterpret_cast<const int8_t*>(&v);
-        const __half d = __float2half_rn(ascale[row * (K / 32) + (k0 >> 5)]);  // exact: the scale is an f16 value
-        __half2 h[4];
-        h[0] = __halves2half2(__hmul(__int2half_rn(b[0]), d), __hmul(__int2half_rn(b[2]), d));
-        h[1] = __halves2half2(__hmul(__int2half_rn(b[1]), d), __hmul(__int2half_rn(b[3]), d));
-        h[2] = __halves2half2(__hmul(__int2half_rn(b[4]), d), __hmul(__int2half_rn(b[6]), d));
-        h[3] = __halves2half2(__hmul(__int2half_rn(b[5]), d), __hmul(__int2half_rn(b[7]), d));
+        const float df = ascale[row * (K / 32) + (k0 >> 5)];  // an f16 value widened to f32
+        __half r0[8], r1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float t = __fmul_rn(__fmul_rn((float)b[i], df), exact ? 64.0f : 1.0f);  // exact in f32: 8 x 11 bits
+            r0[i] = __float2half_rn(t);
+            r1[i] = __float2half_rn(__fsub_rn(t, __half2float(r0[i])));
+        }
+        __half2 h[4] = {__halves2half2(r0[0], r0[2]), __halves2half2(r0[1], r0[3]), __halves2half2(r0[4], r0[6]), __halves2half2(r0[5], r0[7])};
+        __half2 g[4] = {__halves2half2(r1[0], r1[2]), __halves2half2(r1[1], r1[3]), __halves2half2(r1[4], r1[6]), __halves2half2(r1[5], r1[7])};
         o = *reinterpret_cast<uint4*>(h);
+        o1 = *reinterpret_cast<uint4*>(g);
     }
-    *reinterpret_cast<uint4*>(bf16 + (int64_t)p * K_pad + blk * 256 + lane * 8) = o;
-    if (lane == 0) d8t[(int64_t)blk * P_pad + p] = 1.0f;
+    if (exact) {
+        __half* dst = bf16 + (int64_t)p * (2 * K_pad) + blk * 512 + lane * 8;
+        *reinterpret_cast<uint4*>(dst) = o;
+        *reinterpret_cast<uint4*>(dst + 256) = o1;
+    } else {
+        *reinterpret_cast<uint4*>(bf16 + (int64_t)p * K_pad + blk * 256 + lane * 8) = o;
+    }
+    if (lane == 0) d8t[(int64_t)blk * P_pad + p] = exact ? 1.0f / 64.0f : 1.0f;
 }
 
 // Q8_0 GGUF rows [n][K / 32 blocks of 34 bytes] -> [n][K_pad / 256][272]: 256 int8 then 8 f16 scales, zeros past K.
@@ -179,6 +192,7 @@ struct GemmParams {
     int m_tiles;                  // tiles along the weight rows (N / 64 for gate_up, N / 128 for down)
     int ksplit;                   // K splits (down only): partial outputs out + ks * split_stride, summed by the caller
     long long split_stride;
+    uint32_t zero;                // 0 at run time, unknown to the compiler (see the release of a weight stage in the kernel)
 };
 
 __device__ __forceinline__ __half2 h2_bits(uint32_t v) { return *reinterpret_cast<const __half2*>(&v); }
@@ -200,6 +214,7 @@ __device__ __forceinline__ uint32_t w4(const uint4& v, int i) { return i == 0 ? 
 struct GemmQ4K {
     static constexpr bool HAS_MIN = true;
     static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;  // 8 slabs of 32 columns: two blocks in flight
+    static constexpr int B_PARTS = 1;
     static constexpr bool STAGE_W = true;                         // raw blocks of the tile pass through shared memory
     static constexpr int W_ROW_BYTES = Q4K_BYTES;
     static constexpr int W_MAP_ELEM = 1;     // the tensor map of the raw blocks counts bytes
@@ -226,6 +241,10 @@ struct GemmQ4K {
         pr.q[1] = lds128_o<48>(rb);
         pr.q[2] = lds128_o<80>(rb);
         pr.q[3] = lds128_o<112>(rb);
+    }
+    // one word of every vector load_staged fetched: a value that exists only when all of them have arrived
+    __device__ static __forceinline__ uint32_t staged_words(const Pre& pr) {
+        return pr.hdr.x | pr.q[0].x | pr.q[1].x | pr.q[2].x | pr.q[3].x;
     }
     // d (low half) and dmin (high half) of the block, fp16 bits
     __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.hdr.x; }
@@ -304,6 +323,7 @@ struct GemmQ4K {
 struct GemmQ6K {
     static constexpr bool HAS_MIN = false;
     static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;  // 4 slabs of 64 columns (two operand parts each)
+    static constexpr int B_PARTS = 1;
     static constexpr bool STAGE_W = false;
     static constexpr int W_ROW_BYTES = 0;
     static constexpr int W_MAP_ELEM = 1;
@@ -321,6 +341,7 @@ struct GemmQ6K {
     };
     __device__ static __forceinline__ uint32_t hdr_of(const Pre& pr) { return pr.d; }
     __device__ static __forceinline__ void load_staged(Pre&, uint32_t, int) {}
+    __device__ static __forceinline__ uint32_t staged_words(const Pre&) { return 0u; }
     __device__ static __forceinline__ void load(Pre& pr, const Row& r, int blk, int h) {
         const uint8_t* b = r.p + (size_t)blk * Q6K_HTB_BYTES + 64 * r.g + 32 * h;
 #pragma unroll
@@ -391,6 +412,7 @@ struct GemmQ6K {
 struct GemmQ80 {
     static constexpr bool HAS_MIN = false;
     static constexpr int A_COLS = 32, A_PARTS = 1, A_PAIRS = 4;
+    static constexpr int B_PARTS = 1;
     static constexpr bool STAGE_W = true;
     static constexpr int W_ROW_BYTES = 272;
     static constexpr int W_MAP_ELEM = 4;     // the tensor map counts 4-byte elements (a box row of 272 bytes exceeds 256 bytes)
@@ -415,6 +437,9 @@ struct GemmQ80 {
         pr.q[2][1] = lds128_o<160>(rb);
         pr.q[3][0] = lds128_o<192>(rb);
         pr.q[3][1] = lds128_o<224>(rb);
+    }
+    __device__ static __forceinline__ uint32_t staged_words(const Pre& pr) {
+        return pr.sc.x | pr.q[0][0].x | pr.q[0][1].x | pr.q[1][0].x | pr.q[1][1].x | pr.q[2][0].x | pr.q[2][1].x | pr.q[3][0].x | pr.q[3][1].x;
     }
     __device__ static __forceinline__ uint32_t hdr_of(const Pre&) { return 0u; }
     struct Ctx {};
@@ -446,10 +471,53 @@ struct GemmQ80 {
     __device__ static __forceinline__ void emit_min(const Pre&, const Ctx&, uint8_t*, int, int) {}
 };
 
+// ------------------------------------------------------------------------------------------------
+// Q8_0 with EXACT operands, for the gate_up product (whose f32 result is re-quantized to int8 and therefore has to
+// match the reference to f32 rounding, not to fp16 rounding).  d * q has up to 19 significant bits: it is carried as
+// two fp16 numbers, the rounded product and its exact residual (one more fused multiply-add), on both sides:
+//   weights      4096 d_w q  = A0 + A1      (the power of two keeps the residuals out of the fp16 subnormals;
+//   activations    64 d_a q  = B0 + B1       both come off again in the epilogue's scale)
+// and the tensor core accumulates A0 B0 + A1 B0 + A0 B1 in f32 (A1 B1 is below 2^-22 of a term).  Three MMAs per
+// K step and twice the activation stage, so the position tile is at most 64 wide.
+// ------------------------------------------------------------------------------------------------
+struct GemmQ80X : GemmQ80 {
+    static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;
+    static constexpr int B_PARTS = 2;
+    static constexpr int W_STAGES_WIDE = 1;
+    __device__ static __forceinline__ float scale_of(uint32_t) { return 1.0f / 4096.0f; }
+    __device__ static __forceinline__ void cvt16x(const uint4& v, __half2 d, uint32_t (&p0)[8], uint32_t (&p1)[8]) {
+        const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+        const __half2 k1152 = __float2half2_rn(1152.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t e, f;
+            asm("prmt.b32 %0, %1, %2, 0x4240;" : "=r"(e) : "r"(w[i]), "r"(0x64646464u));
+            asm("prmt.b32 %0, %1, %2, 0x4341;" : "=r"(f) : "r"(w[i]), "r"(0x64646464u));
+            const __half2 xe = __hsub2(h2_bits(e), k1152), xf = __hsub2(h2_bits(f), k1152);
+            const __half2 re = __hmul2(xe, d), rf = __hmul2(xf, d);
+            p0[2 * i] = bits_h2(re);
+            p0[2 * i + 1] = bits_h2(rf);
+            p1[2 * i] = bits_h2(__hfma2(xe, d, __hneg2(re)));  // exact: the residual of a 19-bit product has at most 8 bits
+            p1[2 * i + 1] = bits_h2(__hfma2(xf, d, __hneg2(rf)));
+        }
+    }
+    __device__ static __forceinline__ void emit(int s, const Pre& pr, const Ctx&, uint32_t ta, int h) {
+        const uint32_t dw = s == 0 ? pr.sc.x : (s == 1 ? pr.sc.y : (s == 2 ? pr.sc.z : pr.sc.w));
+        const __half2 d2 = __hmul2(h2_bits(dw), __float2half2_rn(4096.f));  // exact (a power of two)
+        uint32_t a0[8], a1[8];
+        cvt16x(pr.q[s][0], __low2half2(d2), a0, a1);
+        tmem_st8(ta + 8 * h, a0);
+        tmem_st8(ta + 32 + 8 * h, a1);
+        cvt16x(pr.q[s][1], __high2half2(d2), a0, a1);
+        tmem_st8(ta + 16 + 8 * h, a0);
+        tmem_st8(ta + 48 + 8 * h, a1);
+    }
+};
+
 // raw weight blocks staged per CTA (see the kernel): what fits beside the activation stages
 template <class F, int TN>
 __host__ __device__ constexpr int w_stages() {
-    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? 3 : F::W_STAGES_WIDE));
+    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? (F::B_PARTS == 2 ? 2 : 3) : F::W_STAGES_WIDE));
 }
 
 struct TileCoord {
@@ -507,7 +575,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * B_TILE;
+    constexpr int G_STAGE_BYTES = (4 * F::B_PARTS + (F::HAS_MIN ? 1 : 0)) * B_TILE;
     uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
     // staged raw blocks of the tile rows: a ring of WS blocks.  With 128-wide position tiles the activation stages
     // leave room for one block only (the L2 prefetch ahead of it has to do); narrower tiles take a deeper ring, so
@@ -685,9 +753,19 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 typename F::Ctx ctx;
                 F::begin(cur, ctx);
                 if (h == 0) s_dw[ab & 7][r] = F::scale_of(F::hdr_of(cur));  // read by the epilogue when it drains this block
-                if (F::STAGE_W) {  // the staged copy is in registers: the loader may refill it
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_w[ab % WS]);
+                // Handing the stage back to the loader.  The staged words must have ARRIVED in registers first: the
+                // loads are plain shared-memory loads, their results are not needed until the emits below, and an
+                // arrive that merely follows them in program order was observed to overtake them -- the refill then
+                // landed under loads still waiting behind the (long) wait for a free operand slot, and the first
+                // rows of a tile came out with the next block's weights, rarely and only when the MMAs are the
+                // bottleneck.  With a ring of two or more stages the stage is released after the emits (nothing
+                // reads it later than that, whatever the order of the instructions).  With a single stage that
+                // would serialise copy and unpack, so the release stays early and the barrier's ADDRESS is made to
+                // depend on one word of every load of every lane (OR-reduced over the warp, masked with a kernel
+                // parameter that is zero at run time): the arrive cannot be issued before those words exist.
+                if (F::STAGE_W && WS == 1) {
+                    const uint32_t dep = __reduce_or_sync(0xffffffffu, F::staged_words(cur)) & P.zero;
+                    if (lane == 0) mbar_arrive(&empty_w[dep]);
                 }
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
@@ -713,6 +791,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     tc5_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full_a[bidx]);
+                }
+                if (F::STAGE_W && WS > 1) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_w[ab % WS]);
                 }
                 if (!F::STAGE_W) cur = nxt;
             }
@@ -793,8 +875,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 if (elect_one()) {
                     mbar_expect_tx(&full_b[st], G_STAGE_BYTES);
 #pragma unroll
-                    for (int s4 = 0; s4 < 4; ++s4)
-                        tma_load_2d(dst + s4 * B_TILE, &map_b, blk * 256 + s4 * 64, (int)tc.p0, &full_b[st]);
+                    for (int s4 = 0; s4 < 4 * F::B_PARTS; ++s4)  // with two operand parts a row holds [256 of part 0 | 256 of part 1] per block
+                        tma_load_2d(dst + s4 * B_TILE, &map_b, blk * 256 * F::B_PARTS + s4 * 64, (int)tc.p0, &full_b[st]);
                     if (F::HAS_MIN) tma_load_2d(dst + 4 * B_TILE, &map_bs, blk * 32, (int)tc.p0, &full_b[st]);
                 }
                 __syncwarp();
@@ -834,6 +916,7 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                             const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (B_TILE >> 4) + 2 * (k & 3));
                             umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
                             if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
+                            if (F::B_PARTS == 2) umma_f16_ts(d_main, a_k, b_k + (uint64_t)(4 * (B_TILE >> 4)), IDESC, true);
                         }
                         if (pr == 1 && F::HAS_MIN) {
                             // the min term joins the same accumulator: three tf32 steps, last in the block
@@ -924,7 +1007,7 @@ __global__ void __launch_bounds__(128) write_maps_kernel(const __grid_constant__
 
 template <class F, bool GATE_UP, int TN>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
+    const int smem_bytes = G_B_STAGES * (4 * F::B_PARTS + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
                            (F::STAGE_W ? w_stages<F, TN>() * G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP, TN>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -945,10 +1028,10 @@ cudaError_t launch_prepack_q80(cudaStream_t st, const void* raw, int64_t n_rows,
 }
 
 // Scratch the GEMM needs for P grouped rows of length K (fp16 operand, block-sum operand, scales).
-size_t expert_gemm_scratch_bytes(int64_t P, int K) {
+size_t expert_gemm_scratch_bytes(int64_t P, int K, int parts) {
     K = (K + 255) / 256 * 256;  // Q8_0 rows are padded to whole 256-element blocks
     const size_t p_pad = (size_t)P + G_PAD_ROWS, kb = (size_t)K / 256;
-    return align_up(p_pad * K * 2, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256) +
+    return align_up(p_pad * K * 2 * parts, 256) + align_up(p_pad * kb * 64 * 2, 256) + align_up(kb * p_pad * 4, 256) +
            sizeof(CUtensorMap) * 2 * CANDLE_MOE_MAX_EXPERTS;
 }
 
@@ -961,15 +1044,16 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
                                void* scratch, int max_splits, int* n_splits_out, int64_t split_stride) {
     if (n_splits_out) *n_splits_out = 1;
     if (!scratch) return cudaErrorNotSupported;
-    const int tn = max_rows <= 32 ? 32 : (max_rows <= 64 ? 64 : 128);  // position tile, from the bound / hint on an expert's rows
+    int tn = max_rows <= 32 ? 32 : (max_rows <= 64 ? 64 : 128);  // position tile, from the bound / hint on an expert's rows
     const bool q80 = dtype == CANDLE_GGML_Q8_0 && repacked;
     if (!((dtype == CANDLE_GGML_Q4K && !repacked) || (dtype == CANDLE_GGML_Q6K && repacked) || q80)) return cudaErrorNotSupported;
-    // Q8_0 takes this kernel for the DOWN product only.  Its operands carry the block scales rounded to fp16 (a few
-    // 1e-4 relative on a product), which a final product tolerates; the gate_up product does not: its f32 hidden rows
-    // are re-quantized to int8 before W2, and a relative difference of 1e-4 from the reference's hidden values already
-    // moves a few per cent of those int8 values by one step (1 / 127 of the block's largest value) -- measured, that
-    // amplification puts the block at 3e-3 .. 5e-3 relative L2, outside its bound.  gate_up stays on the exact int8 kernels.
-    if (q80 && gate_up) return cudaErrorNotSupported;
+    // Q8_0: the DOWN product runs with operands that carry the block scales rounded to fp16 (a few 1e-4 relative on a
+    // product), which a final product tolerates.  The gate_up product does not: its f32 hidden rows are re-quantized to
+    // int8 before W2, and a relative difference of 1e-4 from the reference's hidden values already moves a few per cent
+    // of those int8 values by one step (1 / 127 of the block's largest value) -- measured, that amplification puts the
+    // block at 3e-3 .. 5e-3 relative L2, outside its bound.  gate_up therefore takes the exact two-part operands.
+    const bool q80x = q80 && gate_up;
+    const int parts = q80x ? 2 : 1;
     const int K_in = K;
     if (q80) K = (K + 255) / 256 * 256;  // the repacked rows and the fp16 operand are padded with zeros
     if (K_in % (q80 ? 32 : 256) != 0 || N % (gate_up ? 64 : 128) != 0 || P <= 0 || P > (1 << 30)) return cudaErrorNotSupported;
@@ -981,23 +1065,24 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
         e = cudaDeviceGetAttribute(&g_gemm_sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return e;
     }
+    if (q80x && tn > 64) tn = 64;  // twice the activation stage: 128-wide tiles do not fit
     const int kb = K / 256;
     const int64_t p_pad = P + G_PAD_ROWS;
     uint8_t* base = static_cast<uint8_t*>(scratch);
     __half* bf16 = reinterpret_cast<__half*>(base);
-    float* bmin = reinterpret_cast<float*>(base + align_up((size_t)p_pad * K * 2, 256));
+    float* bmin = reinterpret_cast<float*>(base + align_up((size_t)p_pad * K * 2 * parts, 256));
     float* d8t = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bmin) + align_up((size_t)p_pad * kb * 32 * 4, 256));
     const bool has_min = dtype == CANDLE_GGML_Q4K;
 
     const int64_t units = p_pad * kb;
     cudaError_t e = q80 ? launch_k(prep_gemm_b_q80_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, row_of,
-                                   (int)P, (int)p_pad, K_in, K, bf16, d8t)
+                                   (int)P, (int)p_pad, K_in, K, q80x ? 1 : 0, bf16, d8t)
                         : launch_k(prep_gemm_b_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, st, aq, ascale, absum,
                                    row_of, (int)P, (int)p_pad, K, bf16, has_min ? bmin : (float*)nullptr, d8t);
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_b, map_bs;
-    if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K, G_SLAB_K, tn))
+    if (!make_map_2d(&map_b, bf16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p_pad, (uint64_t)K * parts, G_SLAB_K, tn))
         return cudaErrorNotSupported;
     if (!make_map_2d(&map_bs, bmin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)p_pad, (uint64_t)kb * 32, 32, tn))
         return cudaErrorNotSupported;
@@ -1047,6 +1132,7 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
         *n_splits_out = ksplit;
     }
     G.ksplit = ksplit;
+    G.zero = 0;
     G.split_stride = split_stride;
     e = stream_status_ptr(&G.status);
     if (e != cudaSuccess) return e;
@@ -1057,12 +1143,11 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
             return gate_up ? launch_gemm_kernel<GemmQ4K, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 64>(st, G, map_b, map_bs);
         return gate_up ? launch_gemm_kernel<GemmQ4K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 128>(st, G, map_b, map_bs);
     }
+    if (q80x) return tn == 32 ? launch_gemm_kernel<GemmQ80X, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80X, true, 64>(st, G, map_b, map_bs);
     if (q80) {
-        if (tn == 32)
-            return gate_up ? launch_gemm_kernel<GemmQ80, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 32>(st, G, map_b, map_bs);
-        if (tn == 64)
-            return gate_up ? launch_gemm_kernel<GemmQ80, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 64>(st, G, map_b, map_bs);
-        return gate_up ? launch_gemm_kernel<GemmQ80, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80, false, 128>(st, G, map_b, map_bs);
+        if (tn == 32) return launch_gemm_kernel<GemmQ80, false, 32>(st, G, map_b, map_bs);
+        if (tn == 64) return launch_gemm_kernel<GemmQ80, false, 64>(st, G, map_b, map_bs);
+        return launch_gemm_kernel<GemmQ80, false, 128>(st, G, map_b, map_bs);
     }
     if (tn == 32)
         return gate_up ? launch_gemm_kernel<GemmQ6K, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ6K, false, 32>(st, G, map_b, map_bs);

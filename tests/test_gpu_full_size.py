@@ -102,8 +102,9 @@ def test_mixtral_8x7b_mid_sized_batches(orc, torch_cuda, T):
 def test_fine_grained_q8_0_4096_rows(orc, torch_cuda, prepack):
     """d=2048, 60 routed experts of ff=1408, top-4 without renormalisation, shared expert ff=5632 gated by
     sigmoid(x.g), all Q8_0, 4096 rows (qwen2_moe.rs:261-323).  With the repacked copies the products take the
-    tensor-core GEMM (scales folded into fp16 operands: the one path whose float side is not the reference's
-    per-block f32 scaling, held to the same bounds); without them the int8 tile kernel."""
+    tensor-core GEMM (gate_up with exact two-part fp16 operands, down with the scales folded into fp16 operands: the
+    one path whose float side is not the reference's per-block f32 scaling, held to the same bounds); without them
+    the int8 tile kernel."""
     _full_size_case(orc, torch_cuda, "fine_grained_q8_0", 4096, prepack, seed=5)
 
 
@@ -111,6 +112,25 @@ def test_mixtral_8x22b_skewed_routing_1024_rows(orc, torch_cuda):
     """d=6144, ff=16384, 8 experts, top-2, router bias log(1/(i+1)): Zipf-like load, expert 0 busiest."""
     counts = _full_size_case(orc, torch_cuda, "mixtral_8x22b_skewed", 1024, True, seed=6)
     assert counts[0] == counts.max() and counts.max() > 2 * counts.min()
+
+
+@pytest.mark.parametrize("dt13,dt2,ff", [(8, 8, 1408), (12, 14, 1536), (14, 14, 1536), (12, 12, 1536)])
+@pytest.mark.parametrize("T", [1024, 150])
+def test_repeated_forwards_are_bit_identical(orc, torch_cuda, dt13, dt2, ff, T):
+    """The same rows through the same block eight times: every kernel adds in a fixed order, so the outputs are equal
+    bit for bit.  (A difference here is a race: a stage of a copy ring handed back before its reader is done.)
+    T = 1024 fills several position tiles per expert and several tiles per CTA; T = 150 takes the narrow tiles."""
+    torch = torch_cuda
+    cfg = dict(d=2048, ff=ff, E=4, k=2, dt13=dt13, dt2=dt2, renorm=True, ff_shared=0, zipf=False)
+    blk, _ = H.random_device_block(orc, torch, cfg, seed=11)
+    blk.prepack()
+    g = torch.Generator(device="cuda").manual_seed(12)
+    x = torch.randn((T, cfg["d"]), generator=g, device="cuda", dtype=torch.float32)
+    ys = []
+    for _ in range(8):
+        ys.append(blk.forward(x).clone())
+        torch.cuda.synchronize()
+    assert all(torch.equal(ys[0], y) for y in ys[1:]), [int((ys[0] != y).sum()) for y in ys[1:]]
 
 
 # ------------------------------------------------------------------------------------------------
