@@ -18,12 +18,16 @@ namespace {
 // k T / E rows, i.e. a few of the decode kernels' 16-row groups.  Measured on the Mixtral-shaped layer (decode
 // kernels / GEMM, microseconds): T = 65 349 / 503, 96 384 / 537, 128 473 / 554, 160 569 / 584.
 inline int64_t gemm_min_rows() { return tuning_get(TUNE_GEMM_MIN_ROWS); }
-// When the caller knows the ACTUAL (or, in the slot form of expert parallelism, the expected) largest row count of an
-// expert, the GEMM takes over above 48 rows: up to there the decode kernels walk the weights at most three times (once
-// per 16 rows), which is cheaper than the GEMM's fixed cost per block of a tile when a rank holds only a few experts
-// (measured on 4 GPUs, 2 experts of ~33 rows per rank: GEMM 248 us for the local phase; the decode kernels take about
-// 64 us per expert at that size on one GPU).  (A single-device forward only knows the bound T.)
-constexpr int64_t GEMM_MIN_ROWS_EXACT = 48;
+// When the caller knows the ACTUAL largest row count of an expert (or, in the slot form of expert parallelism, a
+// bound five quarters of the expected one, so that the tile width leaves a margin), the GEMM takes over above 32 rows.
+// Measured on one GPU with the experts of one rank of the Mixtral-shaped layer (decode kernels / GEMM, microseconds
+// per step): one expert, 32 rows 92 / 98, 48 rows 122 / 98, 64 rows 134 / 103, 96 rows 190 / 129, 128 rows 229 / 129;
+// two experts, 32 rows each 163 / 159, 40 rows 193 / 165, 64 rows 246 / 200; four experts, 32 rows 272 / 262, 40 rows
+// 323 / 263.  (An earlier measurement of 248 us for two experts of ~33 rows had position tiles of 32, so that every
+// expert with a row more than expected took a second, almost empty tile.)  A single-device forward only knows the
+// bound T.
+constexpr int64_t GEMM_MIN_ROWS_EXACT = 32;
+constexpr int64_t QMM_GEMM_MIN_ROWS = 48;  // the dense product: one matrix, rows known exactly
 // Decode-sized batches may split K finely (more parallel items, smaller resident activations);
 // larger batches get four slots, enough for the streaming form's activation rows to fit.
 inline int k_split_slots(int64_t T) { return T <= gemm_min_rows() ? MAX_K_SPLITS : 4; }
@@ -788,7 +792,7 @@ struct QmmWorkspace {
 // from 17 rows on when the matrix has enough 128-row tiles to fill the SMs by itself (measured at 32 rows:
 // [32000, 4096] Q6_K 76 us through the GEMM against 108 us through the streaming form, [4096, 4096] Q4_K 25 against 23).
 inline bool qmm_takes_gemm(int dtype, int64_t rows, int n) {
-    return dtype != CANDLE_GGML_Q8_0 && (rows > GEMM_MIN_ROWS_EXACT || (rows > 16 && n >= 12800));
+    return dtype != CANDLE_GGML_Q8_0 && (rows > QMM_GEMM_MIN_ROWS || (rows > 16 && n >= 12800));
 }
 QmmWorkspace qmm_layout(int dtype, int64_t rows, int n, int k, void* base_) {
     uint8_t* base = static_cast<uint8_t*>(base_);

@@ -497,10 +497,13 @@ int ep_forward_impl(cudaStream_t st, candle_moe_ep_comm* cm, const candle_moe_ep
         CU_TRY(launch_k(ep_regroup_slots_kernel, dim3((unsigned)((g.P_cap + 7) / 8)), dim3(256), 0, st, (const uint8_t*)ws.recv,
                         g.slot_bytes, (int)g.hdr_bytes, (int)g.row_bytes, N, El, g.C, d, (const uint32_t*)ws.plan,
                         (const uint32_t*)ws.recv_counts, lw.xq, lw.xs, lw.xb, lw.back));
-        // kernels are chosen for the EXPECTED rows of an expert under even routing; any count is handled
+        // kernels and tile widths are chosen for five quarters of the EXPECTED rows of an expert under even routing
+        // (an expert with a few rows more than the average must not spill into a second, almost empty tile); any
+        // count is handled
         const int64_t expect = std::max<int64_t>(1, ((int64_t)N * g.Tm * k + E - 1) / E);
+        const int64_t bound = (5 * expect + 3) / 4;
         const int slots_k = ep_eo_slots(g.P_cap, El);
-        CM_TRY(run_experts(st, w, p1, p3, p2, expect, g.P_cap, lw.offsets, nullptr, lw.xq, lw.xs, lw.xb, lw.eb, slots_k, &eo_splits,
+        CM_TRY(run_experts(st, w, p1, p3, p2, bound, g.P_cap, lw.offsets, nullptr, lw.xq, lw.xs, lw.xb, lw.eb, slots_k, &eo_splits,
                            false, true, lw.offsets + El, expect * El));
         CU_TRY(launch_ep_scatter(st, lw.eb.eo, eo_splits, g.P_cap * d, lw.back, g.P_cap, d, ws.ret_send, lw.offsets + El));
         ep_mark(st, 3);

@@ -115,15 +115,19 @@ def test_mixtral_8x22b_skewed_routing_1024_rows(orc, torch_cuda):
 
 
 @pytest.mark.parametrize("dt13,dt2,ff", [(8, 8, 1408), (12, 14, 1536), (14, 14, 1536), (12, 12, 1536)])
-@pytest.mark.parametrize("T", [1024, 150])
-def test_repeated_forwards_are_bit_identical(orc, torch_cuda, dt13, dt2, ff, T):
+@pytest.mark.parametrize("T,prepack", [(1024, True), (150, True), (32, True), (32, False), (300, False)])
+def test_repeated_forwards_are_bit_identical(orc, torch_cuda, dt13, dt2, ff, T, prepack):
     """The same rows through the same block eight times: every kernel adds in a fixed order, so the outputs are equal
     bit for bit.  (A difference here is a race: a stage of a copy ring handed back before its reader is done.)
-    T = 1024 fills several position tiles per expert and several tiles per CTA; T = 150 takes the narrow tiles."""
+    T = 1024 fills several position tiles per expert and several tiles per CTA; T = 150 takes the narrow tiles; T = 32
+    the decode kernels (with the repacked copies) or the streaming kernels (without); T = 300 without the copies the
+    forms that read the GGUF blocks."""
     torch = torch_cuda
-    cfg = dict(d=2048, ff=ff, E=4, k=2, dt13=dt13, dt2=dt2, renorm=True, ff_shared=0, zipf=False)
+    # the all-Q8_0 block also carries a shared expert (its products take the same tensor-core forms)
+    cfg = dict(d=2048, ff=ff, E=4, k=2, dt13=dt13, dt2=dt2, renorm=True, ff_shared=2816 if dt13 == 8 else 0, zipf=False)
     blk, _ = H.random_device_block(orc, torch, cfg, seed=11)
-    blk.prepack()
+    if prepack:
+        blk.prepack()
     g = torch.Generator(device="cuda").manual_seed(12)
     x = torch.randn((T, cfg["d"]), generator=g, device="cuda", dtype=torch.float32)
     ys = []
