@@ -107,16 +107,32 @@ class MlpOrMoe:
         """Make the optional repacked copies of every expert matrix (one-time, doubles the weight memory of this
         block): k-quants for the decode kernels (batches of up to 128 rows) and Q6_K in the large-batch GEMM, Q8_0 for
         the large-batch GEMM."""
+        def copies(mats):
+            # every matrix of the family or none: a shape the repack does not take (CANDLE_MOE_E_SHAPE, e.g. Q6_K rows
+            # with an odd number of 256-blocks) leaves the family on its GGUF blocks
+            try:
+                return [m.inner.prepack() for m in mats]
+            except _lib.CandleMoeError as e:
+                if e.status != -2:  # CANDLE_MOE_E_SHAPE
+                    raise
+                return None
+
+        w13 = copies([m.feed_forward_w1 for m in self.experts] + [m.feed_forward_w3 for m in self.experts])
+        w2 = copies([m.feed_forward_w2 for m in self.experts])
         E = len(self.experts)
-        self._p1 = self._arr(*[m.feed_forward_w1.inner.prepack().data_ptr() for m in self.experts])
-        self._p3 = self._arr(*[m.feed_forward_w3.inner.prepack().data_ptr() for m in self.experts])
-        self._p2 = self._arr(*[m.feed_forward_w2.inner.prepack().data_ptr() for m in self.experts])
-        self._cw.w1_prepacked, self._cw.w3_prepacked, self._cw.w2_prepacked = self._p1, self._p3, self._p2
+        if w13 is not None:
+            self._p1 = self._arr(*[t.data_ptr() for t in w13[:E]])
+            self._p3 = self._arr(*[t.data_ptr() for t in w13[E:]])
+            self._cw.w1_prepacked, self._cw.w3_prepacked = self._p1, self._p3
+        if w2 is not None:
+            self._p2 = self._arr(*[t.data_ptr() for t in w2])
+            self._cw.w2_prepacked = self._p2
         if self.shared_expert is not None and self.shared_expert.feed_forward_w1.inner.dtype() == GgmlDType.Q8_0:
             s = self.shared_expert
-            self._cw.shared_w1_prepacked = s.feed_forward_w1.inner.prepack().data_ptr()
-            self._cw.shared_w3_prepacked = s.feed_forward_w3.inner.prepack().data_ptr()
-            self._cw.shared_w2_prepacked = s.feed_forward_w2.inner.prepack().data_ptr()
+            sh = copies([s.feed_forward_w1, s.feed_forward_w3, s.feed_forward_w2])
+            if sh is not None:
+                self._cw.shared_w1_prepacked, self._cw.shared_w3_prepacked, self._cw.shared_w2_prepacked = (
+                    t.data_ptr() for t in sh)
         return self
 
     @property
