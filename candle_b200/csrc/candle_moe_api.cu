@@ -838,8 +838,8 @@ int candle_moe_qmatmul(void* stream, const void* w, const void* w_prepacked, int
     ExpertPtrs pw{}, pp{};
     pw.p[0] = static_cast<const uint8_t*>(w);
     pp.p[0] = static_cast<const uint8_t*>(w_prepacked);
-    CM_TRY(rc(launch_quantize_act(st, x, rows, k, dtype, ws.xq, ws.xs, ws.xb)));
-    CM_TRY(rc(launch_single_group(st, ws.offsets, (uint32_t)rows)));
+    // the quantizer also writes the offsets of the one group that holds every row
+    CM_TRY(rc(launch_quantize_act(st, x, rows, k, dtype, ws.xq, ws.xs, ws.xb, nullptr, ws.offsets)));
     float* dst = ws.eo ? ws.eo : out;
     const int64_t stride = rows * (int64_t)n;
     int splits = 1;

@@ -171,7 +171,8 @@ cudaError_t launch_permute(cudaStream_t st, const uint32_t* ids, int64_t T, int 
 cudaError_t launch_single_group(cudaStream_t st, uint32_t* offsets, uint32_t rows);
 // row_limit (Q8K only, may be null): device-side row count; rows at or beyond it are skipped
 cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, int kdim, int for_dtype, int8_t* qs,
-                                float* scales, int16_t* bsums, const uint32_t* row_limit = nullptr);
+                                float* scales, int16_t* bsums, const uint32_t* row_limit = nullptr,
+                                uint32_t* single_group = nullptr);
 cudaError_t launch_grouped_gate_up(cudaStream_t st, const ExpertPtrs& w1, const ExpertPtrs& w3, int dtype, int E,
                                    int d, int ff, const uint32_t* offsets, const uint32_t* row_of, int64_t max_rows,
                                    const int8_t* xq, const float* xs, const int16_t* xb, float* hidden);

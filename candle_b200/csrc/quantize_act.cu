@@ -17,9 +17,10 @@ namespace cmoe {
 __global__ void __launch_bounds__(256)
 quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __restrict__ qs,
                     float* __restrict__ scales, int16_t* __restrict__ bsums, const uint32_t* __restrict__ row_limit,
-                    int blocks_per_row) {
+                    int blocks_per_row, uint32_t* __restrict__ single_group, uint32_t group_rows) {
     pdl_trigger();
     pdl_wait();
+    if (single_group && blockIdx.x == 0 && threadIdx.x < 2) single_group[threadIdx.x] = threadIdx.x ? group_rows : 0u;
     const int lane = threadIdx.x & 31;
     const int64_t blk = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (blk >= n_blocks) return;
@@ -33,9 +34,10 @@ quantize_q8k_kernel(const float* __restrict__ x, int64_t n_blocks, int8_t* __res
 // scale is d rounded to f16.
 __global__ void __launch_bounds__(256)
 quantize_q8_0_kernel(const float* __restrict__ x, int64_t n_elems, int8_t* __restrict__ qs,
-                     float* __restrict__ scales) {
+                     float* __restrict__ scales, uint32_t* __restrict__ single_group, uint32_t group_rows) {
     pdl_trigger();
     pdl_wait();
+    if (single_group && blockIdx.x == 0 && threadIdx.x < 2) single_group[threadIdx.x] = threadIdx.x ? group_rows : 0u;
     const int lane = threadIdx.x & 31;
     const int64_t grp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // 256 elements
     if (grp * 256 >= n_elems) return;
@@ -66,15 +68,18 @@ quantize_q8_0_kernel(const float* __restrict__ x, int64_t n_elems, int8_t* __res
     if ((lane & 3) == 0) scales[grp * 8 + (lane >> 2)] = __half2float(__float2half_rn(d));
 }
 
+// single_group (may be null): two words that receive {0, rows} -- the offsets of one group holding every row, which
+// the dense product needs and would otherwise write with a launch of its own
 cudaError_t launch_quantize_act(cudaStream_t st, const float* x, int64_t rows, int kdim, int for_dtype, int8_t* qs,
-                                float* scales, int16_t* bsums, const uint32_t* row_limit) {
+                                float* scales, int16_t* bsums, const uint32_t* row_limit, uint32_t* single_group) {
     const int64_t n = rows * (int64_t)kdim;
     const int64_t n256 = (n + 255) / 256;
     if (n256 == 0) return cudaSuccess;
     const unsigned grid = (unsigned)((n256 + 7) / 8);
     if (for_dtype == CANDLE_GGML_Q8_0)
-        return launch_k(quantize_q8_0_kernel, dim3(grid), dim3(256), 0, st, x, n, qs, scales);
-    return launch_k(quantize_q8k_kernel, dim3(grid), dim3(256), 0, st, x, n256, qs, scales, bsums, row_limit, kdim / 256);
+        return launch_k(quantize_q8_0_kernel, dim3(grid), dim3(256), 0, st, x, n, qs, scales, single_group, (uint32_t)rows);
+    return launch_k(quantize_q8k_kernel, dim3(grid), dim3(256), 0, st, x, n256, qs, scales, bsums, row_limit, kdim / 256,
+                    single_group, (uint32_t)rows);
 }
 
 }  // namespace cmoe
