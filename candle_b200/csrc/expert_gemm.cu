@@ -633,9 +633,10 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         }
         while (have) {
             const bool have_n = decode_tile<TN>(tile + gridDim.x, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tcn);
-            float acc[CH];
+            // the accumulators are kept as pairs of columns: one packed fused multiply-add per pair and block
+            uint64_t acc2[CH / 2];
 #pragma unroll
-            for (int i = 0; i < CH; ++i) acc[i] = 0.f;
+            for (int i = 0; i < CH / 2; ++i) acc2[i] = 0ull;
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 const int buf = ab & 1;
                 // scales of the next block (maybe of the next tile): in flight while this block is drained
@@ -668,14 +669,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                     static_for<4>([&](auto Qc) {
                         constexpr int q = decltype(Qc)::value;
                         const uint4 dv = lds128_o<64 * c + 16 * q>(d8_addr);  // base + constant: no address arithmetic
-                        // the two scale products of a column pair in one packed multiply, then one fma per value
-                        float s0, s1, s2, s3;
-                        f32x2_unpack(f32x2_mul(dw2, f32x2_pack_bits(dv.x, dv.y)), s0, s1);
-                        f32x2_unpack(f32x2_mul(dw2, f32x2_pack_bits(dv.z, dv.w)), s2, s3);
-                        acc[16 * c + 4 * q] = fmaf(s0, __uint_as_float(stg[c & 1][4 * q]), acc[16 * c + 4 * q]);
-                        acc[16 * c + 4 * q + 1] = fmaf(s1, __uint_as_float(stg[c & 1][4 * q + 1]), acc[16 * c + 4 * q + 1]);
-                        acc[16 * c + 4 * q + 2] = fmaf(s2, __uint_as_float(stg[c & 1][4 * q + 2]), acc[16 * c + 4 * q + 2]);
-                        acc[16 * c + 4 * q + 3] = fmaf(s3, __uint_as_float(stg[c & 1][4 * q + 3]), acc[16 * c + 4 * q + 3]);
+                        // per column pair: the two scale products in one packed multiply, the two accumulations in one
+                        // packed fused multiply-add (each half is the IEEE fma of the scalar form)
+                        acc2[8 * c + 2 * q] = f32x2_fma(f32x2_mul(dw2, f32x2_pack_bits(dv.x, dv.y)),
+                                                        f32x2_pack_bits(stg[c & 1][4 * q], stg[c & 1][4 * q + 1]), acc2[8 * c + 2 * q]);
+                        acc2[8 * c + 2 * q + 1] = f32x2_fma(f32x2_mul(dw2, f32x2_pack_bits(dv.z, dv.w)),
+                                                            f32x2_pack_bits(stg[c & 1][4 * q + 2], stg[c & 1][4 * q + 3]),
+                                                            acc2[8 * c + 2 * q + 1]);
                     });
                     if (c + 1 < NS) tmem_ld_wait();
                     if (c == (NS >= 2 ? NS - 2 : 0)) {  // every column of this thread has been read: the buffer may be overwritten
@@ -690,6 +690,9 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 }
                 __syncwarp();
             }
+            float acc[CH];
+#pragma unroll
+            for (int i = 0; i < CH / 2; ++i) f32x2_unpack(acc2[i], acc[2 * i], acc[2 * i + 1]);
             // ---- store the tile ----
             const int n = GATE_UP ? tc.mt * 64 + (r >> 1) : tc.mt * 128 + r;
             const uint32_t pc0 = tc.p0 + colhalf * CH;
