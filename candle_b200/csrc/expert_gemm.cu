@@ -478,12 +478,13 @@ struct GemmQ80 {
 //   weights      4096 d_w q  = A0 + A1      (the power of two keeps the residuals out of the fp16 subnormals;
 //   activations    64 d_a q  = B0 + B1       both come off again in the epilogue's scale)
 // and the tensor core accumulates A0 B0 + A1 B0 + A0 B1 in f32 (A1 B1 is below 2^-22 of a term).  Three MMAs per
-// K step and twice the activation stage, so the position tile is at most 64 wide.
+// K step; the activation operand is twice as large, so its two shared-memory stages hold half a block each (see the
+// kernel).
 // ------------------------------------------------------------------------------------------------
 struct GemmQ80X : GemmQ80 {
     static constexpr int A_COLS = 64, A_PARTS = 2, A_PAIRS = 2;
     static constexpr int B_PARTS = 2;
-    static constexpr int W_STAGES_WIDE = 1;
+    static constexpr int W_STAGES_WIDE = 2;
     __device__ static __forceinline__ float scale_of(uint32_t) { return 1.0f / 4096.0f; }
     __device__ static __forceinline__ void cvt16x(const uint4& v, __half2 d, uint32_t (&p0)[8], uint32_t (&p1)[8]) {
         const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
@@ -517,7 +518,7 @@ struct GemmQ80X : GemmQ80 {
 // raw weight blocks staged per CTA (see the kernel): what fits beside the activation stages
 template <class F, int TN>
 __host__ __device__ constexpr int w_stages() {
-    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? (F::B_PARTS == 2 ? 2 : 3) : F::W_STAGES_WIDE));
+    return !F::STAGE_W ? 1 : (TN <= 32 ? 4 : (TN <= 64 ? (F::B_PARTS == 2 ? 4 : 3) : F::W_STAGES_WIDE));
 }
 
 struct TileCoord {
@@ -575,7 +576,13 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
     pdl_trigger();
     pdl_wait();
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int G_STAGE_BYTES = (4 * F::B_PARTS + (F::HAS_MIN ? 1 : 0)) * B_TILE;
+    // One activation stage holds a whole 256-wide block (four slabs, + the min-term box for Q4_K).  With two operand
+    // parts (exact Q8_0) a whole block would be twice that, so there the two stages are the two HALVES of a block
+    // -- stage pr = the slabs of pair pr: [part 0: slab 2 pr, 2 pr + 1 | part 1: slab 2 pr, 2 pr + 1] -- each
+    // refilled for the next block as soon as its own pair's MMAs are done; the same shared memory then takes
+    // 128-wide position tiles.
+    constexpr bool B_HALF = F::B_PARTS == 2;
+    constexpr int G_STAGE_BYTES = (4 + (F::HAS_MIN ? 1 : 0)) * B_TILE;
     uint8_t* smem_min_a = smem + G_B_STAGES * G_STAGE_BYTES;  // Q4_K: 2 slots of the min operand (weights side)
     // staged raw blocks of the tile rows: a ring of WS blocks.  With 128-wide position tiles the activation stages
     // leave room for one block only (the L2 prefetch ahead of it has to do); narrower tiles take a deeper ring, so
@@ -871,6 +878,23 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         TileCoord tc;
         for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc); tile += gridDim.x) {
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
+                if constexpr (B_HALF) {
+                    // stage pr of every block: free once the MMAs of pair pr of the block before are done
+#pragma unroll
+                    for (int pr = 0; pr < 2; ++pr) {
+                        if (ab >= 1) mbar_wait_relaxed(&empty_b[pr], (ab - 1) & 1, abort_flag);
+                        uint8_t* dst = smem + (size_t)pr * G_STAGE_BYTES;
+                        if (elect_one()) {
+                            mbar_expect_tx(&full_b[pr], G_STAGE_BYTES);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)  // a row holds [256 of part 0 | 256 of part 1] per block
+                                tma_load_2d(dst + j * B_TILE, &map_b, blk * 512 + (j >> 1) * 256 + (2 * pr + (j & 1)) * 64, (int)tc.p0,
+                                            &full_b[pr]);
+                        }
+                        __syncwarp();
+                    }
+                    continue;
+                }
                 // one stage = the whole 256-wide block: four slabs (+ the activation side of the min term), one barrier
                 const int st = ab & 1;
                 if (ab >= 2) mbar_wait_relaxed(&empty_b[st], ((ab >> 1) & 1) ^ 1, abort_flag);
@@ -878,8 +902,8 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
                 if (elect_one()) {
                     mbar_expect_tx(&full_b[st], G_STAGE_BYTES);
 #pragma unroll
-                    for (int s4 = 0; s4 < 4 * F::B_PARTS; ++s4)  // with two operand parts a row holds [256 of part 0 | 256 of part 1] per block
-                        tma_load_2d(dst + s4 * B_TILE, &map_b, blk * 256 * F::B_PARTS + s4 * 64, (int)tc.p0, &full_b[st]);
+                    for (int s4 = 0; s4 < 4; ++s4)
+                        tma_load_2d(dst + s4 * B_TILE, &map_b, blk * 256 + s4 * 64, (int)tc.p0, &full_b[st]);
                     if (F::HAS_MIN) tma_load_2d(dst + 4 * B_TILE, &map_bs, blk * 32, (int)tc.p0, &full_b[st]);
                 }
                 __syncwarp();
@@ -895,41 +919,53 @@ expert_gemm_kernel(const __grid_constant__ GemmParams P, const __grid_constant__
         const uint64_t ma_desc0 = umma_desc_sw128(smem_u32(smem_min_a));
         bool rdy_a = false, rdy_b = false;
         for (long long tile = blockIdx.x; decode_tile<TN>(tile, s_offs, P.E, P.m_tiles, P.ksplit, P.kb, tc); tile += gridDim.x) {
+            // The last position tile of an expert is rarely full: its MMAs run N = the rows it holds, rounded up to 16
+            // (an MMA's time goes with N; the columns beyond are neither computed nor stored).
+            const uint32_t n_eff = min((uint32_t)TN, (tc.p_end - tc.p0 + 15u) & ~15u);
+            const uint32_t idesc = (IDESC & ~(0x3Fu << 17)) | ((n_eff >> 3) << 17);
+            const uint32_t idesc_tf32 = (IDESC_TF32 & ~(0x3Fu << 17)) | ((n_eff >> 3) << 17);
             for (int blk = tc.kb0; blk < tc.kb1; ++blk, ++ab) {
                 const int buf = ab & 1;  // main accumulator and B stage of this block
                 // the drain of block ab - 2 has released this main accumulator
                 if (ab >= 2) mbar_wait(&epi_done[buf], ((ab >> 1) & 1) ^ 1, abort_flag);
                 const uint32_t d_main = tmem_base + (uint32_t)(G_TM_MAIN + buf * TN);
-                const uint64_t db = b_desc0 + (uint64_t)(buf * (G_STAGE_BYTES >> 4));
+                const uint64_t db = b_desc0 + (uint64_t)((B_HALF ? 0 : buf) * (G_STAGE_BYTES >> 4));
 #pragma unroll
                 for (int pr = 0; pr < 2; ++pr, ita += 2) {
                     const uint32_t bidx = 2 * (ab & 1) + pr, slot = bidx % F::A_PAIRS;  // barrier, TMEM slot (see the unpack warps)
                     if (!rdy_a) mbar_wait(&full_a[bidx], (ab >> 1) & 1, abort_flag);
-                    if (pr == 0 && !rdy_b) mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag);
+                    if constexpr (B_HALF) {
+                        mbar_wait(&full_b[pr], ab & 1, abort_flag);
+                    } else {
+                        if (pr == 0 && !rdy_b) mbar_wait(&full_b[buf], (ab >> 1) & 1, abort_flag);
+                    }
                     tc5_fence_after_sync();
                     // look at this warp's next barriers now: the answers arrive while the MMAs are issued
                     rdy_a = pr == 0 ? mbar_test(&full_a[bidx + 1], (ab >> 1) & 1)                    // second pair of this block
                                     : mbar_test(&full_a[2 * ((ab + 1) & 1)], ((ab + 1) >> 1) & 1);  // first pair of the next
-                    if (pr == 1) rdy_b = mbar_test(&full_b[buf ^ 1], ((ab + 1) >> 1) & 1);
+                    if (!B_HALF && pr == 1) rdy_b = mbar_test(&full_b[buf ^ 1], ((ab + 1) >> 1) & 1);
                     const uint32_t a_t = a_base + (uint32_t)(2 * slot * F::A_COLS);
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {  // two slabs of four K steps
                             const uint32_t a_k = a_t + (uint32_t)((k >> 2) * F::A_COLS + 8 * (k & 3));
-                            const uint64_t b_k = db + (uint64_t)((2 * pr + (k >> 2)) * (B_TILE >> 4) + 2 * (k & 3));
-                            umma_f16_ts(d_main, a_k, b_k, IDESC, (pr | k) != 0);
-                            if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, IDESC, true);
-                            if (F::B_PARTS == 2) umma_f16_ts(d_main, a_k, b_k + (uint64_t)(4 * (B_TILE >> 4)), IDESC, true);
+                            // slab of this K step inside its stage: whole-block stages hold slabs 0..3, half-block
+                            // stages [part 0: two slabs | part 1: two slabs] of pair pr
+                            const uint64_t b_k = db + (uint64_t)((B_HALF ? pr * 4 + (k >> 2) : 2 * pr + (k >> 2)) * (B_TILE >> 4) + 2 * (k & 3));
+                            umma_f16_ts(d_main, a_k, b_k, idesc, (pr | k) != 0);
+                            if (F::A_PARTS == 2) umma_f16_ts(d_main, a_k + 32, b_k, idesc, true);
+                            if (F::B_PARTS == 2) umma_f16_ts(d_main, a_k, b_k + (uint64_t)(2 * (B_TILE >> 4)), idesc, true);
                         }
                         if (pr == 1 && F::HAS_MIN) {
                             // the min term joins the same accumulator: three tf32 steps, last in the block
                             const uint64_t da = ma_desc0 + (uint64_t)(buf * (G_TILE_BYTES >> 4)), dm = db + (uint64_t)(4 * (B_TILE >> 4));
 #pragma unroll
-                            for (int k = 0; k < 3; ++k) umma_tf32(d_main, da + 2 * k, dm + 2 * k, IDESC_TF32, true);
+                            for (int k = 0; k < 3; ++k) umma_tf32(d_main, da + 2 * k, dm + 2 * k, idesc_tf32, true);
                         }
                         umma_commit(&empty_a[bidx]);  // the stages may be refilled once these MMAs have read them
+                        if (B_HALF) umma_commit(&empty_b[pr]);
                         if (pr == 1) {
-                            umma_commit(&empty_b[buf]);
+                            if (!B_HALF) umma_commit(&empty_b[buf]);
                             umma_commit(&tmem_full[buf]);
                         }
                     }
@@ -1010,7 +1046,7 @@ __global__ void __launch_bounds__(128) write_maps_kernel(const __grid_constant__
 
 template <class F, bool GATE_UP, int TN>
 cudaError_t launch_gemm_kernel(cudaStream_t st, const GemmParams& G, const CUtensorMap& map_b, const CUtensorMap& map_bs) {
-    const int smem_bytes = G_B_STAGES * (4 * F::B_PARTS + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
+    const int smem_bytes = G_B_STAGES * (4 + (F::HAS_MIN ? 1 : 0)) * (TN * G_SLAB_K * 2) + (F::HAS_MIN ? 2 : 0) * G_TILE_BYTES +
                            (F::STAGE_W ? w_stages<F, TN>() * G_TILE_M * F::W_ROW_BYTES : 0) + 1024 /* alignment slack */;
     auto kfn = expert_gemm_kernel<F, GATE_UP, TN>;
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -1068,7 +1104,6 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
         e = cudaDeviceGetAttribute(&g_gemm_sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return e;
     }
-    if (q80x && tn > 64) tn = 64;  // twice the activation stage: 128-wide tiles do not fit
     const int kb = K / 256;
     const int64_t p_pad = P + G_PAD_ROWS;
     uint8_t* base = static_cast<uint8_t*>(scratch);
@@ -1146,7 +1181,11 @@ cudaError_t launch_expert_gemm(cudaStream_t st, bool gate_up, const ExpertPtrs& 
             return gate_up ? launch_gemm_kernel<GemmQ4K, true, 64>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 64>(st, G, map_b, map_bs);
         return gate_up ? launch_gemm_kernel<GemmQ4K, true, 128>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ4K, false, 128>(st, G, map_b, map_bs);
     }
-    if (q80x) return tn == 32 ? launch_gemm_kernel<GemmQ80X, true, 32>(st, G, map_b, map_bs) : launch_gemm_kernel<GemmQ80X, true, 64>(st, G, map_b, map_bs);
+    if (q80x) {
+        if (tn == 32) return launch_gemm_kernel<GemmQ80X, true, 32>(st, G, map_b, map_bs);
+        if (tn == 64) return launch_gemm_kernel<GemmQ80X, true, 64>(st, G, map_b, map_bs);
+        return launch_gemm_kernel<GemmQ80X, true, 128>(st, G, map_b, map_bs);
+    }
     if (q80) {
         if (tn == 32) return launch_gemm_kernel<GemmQ80, false, 32>(st, G, map_b, map_bs);
         if (tn == 64) return launch_gemm_kernel<GemmQ80, false, 64>(st, G, map_b, map_bs);
