@@ -472,7 +472,10 @@ def run_ours(args, cfg):
             "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, T, top)),
             "peak_source": f"{peak_kind} copy bandwidth",
             "algorithmic_bytes_per_launch": top_bytes, "kernel_ms": stage_ms[top]}
-    if T > 128:
+    from candle_b200 import _lib as _cm
+    gmin = C.c_int64(96)
+    _cm.load().candle_moe_get_tuning(_cm.TUNE_GEMM_MIN_ROWS, C.byref(gmin))
+    if T > gmin.value:
         # large batches run tensor-core grouped products: the bound is the tensor pipe.  Algorithmic flops of the
         # dominant product (the second multiply of every Q6_K slab is not counted).
         flops = 2.0 * T * cfg["k"] * d * cfg["ff"] * (2 if top == "gate_up" else 1)

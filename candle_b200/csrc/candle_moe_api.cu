@@ -12,11 +12,11 @@ using namespace cmoe;
 
 namespace {
 
-// Above this bound on the rows of one expert (default 128) the tensor-core GEMM takes the k-quant products (below,
+// Above this bound on the rows of one expert (default 96) the tensor-core GEMM takes the k-quant products (below,
 // the decode kernels); the tuning key GEMM_MIN_ROWS changes it.
 // A single-device forward only knows the bound T on the rows of an expert, and its experts usually hold about
 // k T / E rows, i.e. a few of the decode kernels' 16-row groups.  Measured on the Mixtral-shaped layer (decode
-// kernels / GEMM, microseconds): T = 65 349 / 503, 96 384 / 537, 128 473 / 554, 160 569 / 584.
+// kernels / GEMM, microseconds per step): T = 64 308 / 419, 80 376 / 421, 96 425 / 423, 112 504 / 449, 128 507 / 450.
 inline int64_t gemm_min_rows() { return tuning_get(TUNE_GEMM_MIN_ROWS); }
 // When the caller knows the ACTUAL largest row count of an expert (or, in the slot form of expert parallelism, a
 // bound five quarters of the expected one, so that the tile width leaves a margin), the GEMM takes over above 32 rows.

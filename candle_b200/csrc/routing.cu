@@ -24,7 +24,7 @@ struct TuningTable {
             return s && s[0] ? (int64_t)std::atoll(s) : dflt;
         };
         v[TUNE_GEMM_ENABLED] = env("CANDLE_MOE_GEMM", 1);
-        v[TUNE_GEMM_MIN_ROWS] = env("CANDLE_MOE_GEMM_MIN_ROWS", 128);
+        v[TUNE_GEMM_MIN_ROWS] = env("CANDLE_MOE_GEMM_MIN_ROWS", 96);
         v[TUNE_STREAM_MAX_ROWS] = env("CANDLE_MOE_STREAM_MAX_ROWS", (int64_t)1 << 40);
         v[TUNE_FORCE_ROWS] = env("CANDLE_MOE_FORCE_ROWS", 0);
         v[TUNE_MID_ENABLED] = env("CANDLE_MOE_MID", 1);

@@ -105,7 +105,7 @@ class MlpOrMoe:
 
     def prepack(self) -> "MlpOrMoe":
         """Make the optional repacked copies of every expert matrix (one-time, doubles the weight memory of this
-        block): k-quants for the decode kernels (batches of up to 128 rows) and Q6_K in the large-batch GEMM, Q8_0 for
+        block): k-quants for the decode kernels (batches of up to 96 rows) and Q6_K in the large-batch GEMM, Q8_0 for
         the large-batch GEMM."""
         def copies(mats):
             # every matrix of the family or none: a shape the repack does not take (CANDLE_MOE_E_SHAPE, e.g. Q6_K rows

@@ -99,7 +99,7 @@ typedef struct candle_moe_weights {
  * (candle-core/src/quantized/cuda.rs:21-25, `FORCE_DMMV` / `set_force_dmmv`).  Results stay within the documented bounds under every
  * setting; only which kernel form runs changes. */
 #define CANDLE_MOE_TUNE_GEMM_ENABLED 0     /* 0: large batches stay on the streaming form (default 1) */
-#define CANDLE_MOE_TUNE_GEMM_MIN_ROWS 1    /* bound on the rows of an expert above which the tensor-core GEMM runs (128) */
+#define CANDLE_MOE_TUNE_GEMM_MIN_ROWS 1    /* bound on the rows of an expert above which the tensor-core GEMM runs (96) */
 #define CANDLE_MOE_TUNE_STREAM_MAX_ROWS 2  /* rows per expert up to which the streaming form is used (no limit) */
 #define CANDLE_MOE_TUNE_FORCE_ROWS 3       /* 1: every grouped product through the row-per-warp form (0) */
 #define CANDLE_MOE_TUNE_MID_ENABLED 4      /* 0: no four-position-tile decode kernels for 17..64 rows per expert (1) */

@@ -595,7 +595,7 @@ def test_block_large_batch_tensor_core_form(orc, torch_cuda, name13, name2, monk
 
 @pytest.mark.parametrize("T", [300, 1000])
 def test_block_q8_0_large_batch_tensor_core_form(orc, torch_cuda, T):
-    """Q8_0 experts and shared expert over the repacked copies: more than 128 rows take the tcgen05 GEMM with both
+    """Q8_0 experts and shared expert over the repacked copies: more than 96 rows take the tcgen05 GEMM with both
     block scales folded into the fp16 operands.  ff = 320 is not a multiple of 256: the repacked rows are padded.
     Against the oracle (bounds of the block) and against the int8 tile / row kernels of the same block."""
     torch = torch_cuda
