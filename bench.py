@@ -364,6 +364,26 @@ def parity_vs_oracle(orc, mw, x_rows, y_rows, ids_rows):
             "bounds": {"rel_l2": 1e-3, "max_rel": 2e-3}}
 
 
+def block_launches(cfg, T, prepacked, gemm_min_rows):
+    """Kernels one forward of the block launches (the library's own, counted from its launch sequence)."""
+    q8 = cfg["dt13"] == 8
+    pairs = T * cfg["k"]
+    n = 1 + (0 if T == 1 else (3 if pairs > 2048 else 1)) + (1 if q8 else 0)  # router (+ x quantization fused unless Q8_0), dispatch
+    maps = lambda E: (2 * E + 15) // 16                                        # tensor-map copies, 16 maps per launch
+    gemm = T > gemm_min_rows
+    def product(dt, E, takes_gemm):
+        if gemm and takes_gemm:
+            return 1 + (maps(E) if dt in (12, 8) else 0) + 1                    # operand preparation, maps, GEMM
+        return 1
+    k13 = cfg["dt13"] == 12 or (prepacked and cfg["dt13"] in (14, 8))
+    k2 = cfg["dt2"] == 12 or (prepacked and cfg["dt2"] in (14, 8))
+    n += product(cfg["dt13"], cfg["E"], k13) + 1 + product(cfg["dt2"], cfg["E"], k2) + 1  # gate_up, quantize h, down, combine
+    if cfg["ff_shared"]:
+        sh = prepacked and q8
+        n += 1 + (0 if q8 else 1) + product(cfg["dt13"], 1, sh) + 1 + product(cfg["dt2"], 1, sh)  # offsets, (x), gate_up, quantize, down
+    return n
+
+
 def tensor_roofline(cfg, T_rows, ms, what, flops, prepacked=True):
     sus, burst, kind = tensor_peaks()
     tf = flops / (ms * 1e-3) / 1e12
@@ -500,7 +520,7 @@ def run_ours(args, cfg):
         "e2e": {"value": T * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": T * d * 4, "d2h_bytes_per_step": T * d * 4,
                 "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": ((6 if cfg["dt13"] != 8 else 7) + (5 if cfg["ff_shared"] else 0)) * args.steps,
+        "gpu_launches": block_launches(cfg, T, not args.no_prepack, gmin.value) * args.steps,
         "clocks": clocks,
     }
     print(json.dumps(line))
